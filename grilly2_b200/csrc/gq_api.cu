@@ -1,0 +1,657 @@
+// The C ABI of include/gq.h: context, buffers, transfers, statistics,
+// capture/replay, and the operator entry points, which validate their
+// operands and hand device pointers to the kernel launchers.
+//
+// Conventions follow the reference's Vulkan shim
+// (crates/grilly-sys/shim/gc_shim.cpp:343-354 `guarded`, :36 thread-local
+// error, :52-339 context bookkeeping): every entry point runs inside
+// guarded(), which turns any exception into GQ_ERR plus a message.
+#include <chrono>
+#include <cstdarg>
+#include <cstdlib>
+#include <cstring>
+
+#include "gq_internal.h"
+
+namespace gq {
+
+static thread_local std::string g_last_error;
+
+void fail(const char* fmt, ...) {
+    char buf[1024];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    throw Failure(buf);
+}
+
+template <class F>
+static int32_t guarded(F&& f) {
+    try {
+        f();
+        return GQ_OK;
+    } catch (const std::exception& e) {
+        g_last_error = e.what();
+    } catch (...) {
+        g_last_error = "unknown error";
+    }
+    return GQ_ERR;
+}
+
+static gq_ctx* need(gq_ctx* ctx) {
+    if (!ctx) fail("null context");
+    return ctx;
+}
+
+struct Locked {
+    gq_ctx* ctx;
+    std::lock_guard<std::mutex> lock;
+    explicit Locked(gq_ctx* c) : ctx(need(c)), lock(c->mutex) { GQ_CUDA(cudaSetDevice(c->device)); }
+};
+
+static Buffer& lookup(gq_ctx* ctx, gq_buf h, const char* what) {
+    auto it = ctx->buffers.find(h);
+    if (h == 0 || it == ctx->buffers.end() || it->second.released) fail("%s: invalid buffer handle %llu", what, (unsigned long long)h);
+    return it->second;
+}
+
+void* view(gq_ctx* ctx, gq_buf h, uint64_t off, uint64_t count, uint64_t elem, const char* what) {
+    Buffer& b = lookup(ctx, h, what);
+    // overflow-safe: off and count are element counts
+    if (off > b.bytes / elem || count > b.bytes / elem - off)
+        fail("%s: needs %llu elements of %llu bytes at element offset %llu, but the buffer holds %llu bytes", what,
+             (unsigned long long)count, (unsigned long long)elem, (unsigned long long)off, (unsigned long long)b.bytes);
+    return static_cast<char*>(b.ptr) + off * elem;
+}
+
+static uint64_t bucket_of(uint64_t bytes) {
+    // pooled blocks come in power-of-two sizes from 512 B, as the reference's
+    // pool does (gc_shim.h:37-41): a decode step's activations recycle.
+    uint64_t cap = 512;
+    while (cap < bytes) cap <<= 1;
+    return cap;
+}
+
+static void drop_ref(gq_ctx* ctx, gq_buf h) {
+    auto it = ctx->buffers.find(h);
+    if (it == ctx->buffers.end()) return;
+    Buffer& b = it->second;
+    if (--b.refs > 0) return;
+    if (b.owned && b.ptr) {
+        if (b.mem == GQ_MEM_DEVICE_PERSISTENT) {
+            cudaFree(b.ptr);  // waits for the device: nothing recorded can still be using it
+            ctx->stats.persistent_buffers--;
+            ctx->stats.persistent_bytes -= b.bytes;
+        } else {
+            // stream order makes reuse safe: the next user runs on the same stream
+            ctx->pool.emplace(b.capacity, b.ptr);
+        }
+    }
+    ctx->buffers.erase(it);
+}
+
+void after_launch(gq_ctx* ctx, const char* kernel, std::initializer_list<gq_buf> used) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) fail("launching %s: %s", kernel, cudaGetErrorString(e));
+    ctx->stats.launches++;
+    if (ctx->capturing) {
+        ctx->capture_nodes++;
+        for (gq_buf h : used) {
+            if (h == 0) continue;
+            auto it = ctx->buffers.find(h);
+            if (it == ctx->buffers.end()) continue;
+            it->second.refs++;
+            ctx->capture_retained.push_back(h);
+        }
+    } else if (ctx->launch_blocking) {
+        e = cudaStreamSynchronize(ctx->stream);
+        if (e != cudaSuccess) fail("%s failed on the device: %s", kernel, cudaGetErrorString(e));
+    }
+}
+
+void* ensure_scratch(gq_ctx* ctx, uint64_t bytes) {
+    if (ctx->scratch_bytes >= bytes) return ctx->scratch;
+    if (ctx->capturing) fail("the context's scratch would have to grow to %llu bytes inside a capture: run the step once eagerly first", (unsigned long long)bytes);
+    if (ctx->scratch) {
+        GQ_CUDA(cudaStreamSynchronize(ctx->stream));
+        cudaFree(ctx->scratch);
+        ctx->scratch = nullptr;
+        ctx->scratch_bytes = 0;
+    }
+    uint64_t cap = bucket_of(bytes);
+    GQ_CUDA(cudaMalloc(&ctx->scratch, cap));
+    ctx->scratch_bytes = cap;
+    ctx->stats.buffer_allocations++;
+    return ctx->scratch;
+}
+
+static void host_wait(gq_ctx* ctx) {
+    auto t0 = std::chrono::steady_clock::now();
+    cudaError_t e = cudaStreamSynchronize(ctx->stream);
+    uint64_t ns = (uint64_t)std::chrono::duration_cast<std::chrono::nanoseconds>(std::chrono::steady_clock::now() - t0).count();
+    ctx->stats.syncs++;
+    ctx->stats.wait_ns_total += ns;
+    ctx->stats.wait_ns_last = ns;
+    if (e != cudaSuccess) fail("the device reported an error while the host waited: %s", cudaGetErrorString(e));
+}
+
+static const char* const kCaptureRead =
+    "a capture read data back to the host. A replay re-issues the recorded work without running the host code "
+    "again, so nothing the host decides from a value can be reproduced: keep the value on the device, or leave "
+    "that step out of the capture.";
+static const char* const kCaptureWrite =
+    "a capture wrote host data into a buffer. A replay re-issues the recorded work, so it would write those same "
+    "bytes every time: put the value in a buffer and update it between replays instead, which is what a captured "
+    "step's inputs are for.";
+
+}  // namespace gq
+
+using namespace gq;
+
+extern "C" {
+
+const char* gq_last_error(void) { return g_last_error.c_str(); }
+
+int32_t gq_create(int32_t device, gq_ctx** out) {
+    return guarded([&] {
+        if (!out) fail("gq_create: null out pointer");
+        *out = nullptr;
+        int count = 0;
+        cudaError_t e = cudaGetDeviceCount(&count);
+        if (e != cudaSuccess || count == 0)
+            fail("gq_create: no CUDA device is visible (%s). This backend has no CPU path.", e == cudaSuccess ? "device count 0" : cudaGetErrorString(e));
+        if (device < 0 || device >= count) fail("gq_create: device %d out of range (0..%d)", device, count - 1);
+        GQ_CUDA(cudaSetDevice(device));
+        auto ctx = new gq_ctx();
+        try {
+            ctx->device = device;
+            GQ_CUDA(cudaGetDeviceProperties(&ctx->prop, device));
+            if (ctx->prop.major != 10)
+                fail("gq_create: device %d (%s) is compute capability %d.%d; the kernels are built for sm_100a (B200) only", device,
+                     ctx->prop.name, ctx->prop.major, ctx->prop.minor);
+            GQ_CUDA(cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking));
+            const char* lb = getenv("GQ_LAUNCH_BLOCKING");
+            ctx->launch_blocking = lb && lb[0] == '1';
+        } catch (...) {
+            delete ctx;
+            throw;
+        }
+        *out = ctx;
+    });
+}
+
+void gq_destroy(gq_ctx* ctx) {
+    if (!ctx) return;
+    guarded([&] {
+        {
+            std::lock_guard<std::mutex> lock(ctx->mutex);
+            cudaSetDevice(ctx->device);
+            cudaStreamSynchronize(ctx->stream);
+            for (auto& kv : ctx->buffers)
+                if (kv.second.owned && kv.second.ptr) cudaFree(kv.second.ptr);
+            for (auto& kv : ctx->pool) cudaFree(kv.second);
+            if (ctx->scratch) cudaFree(ctx->scratch);
+            cudaStreamDestroy(ctx->stream);
+        }
+        delete ctx;
+    });
+}
+
+int32_t gq_caps_get(gq_ctx* ctx, gq_caps* out) {
+    return guarded([&] {
+        Locked l(ctx);
+        if (!out) fail("gq_caps_get: null out pointer");
+        memset(out, 0, sizeof *out);
+        snprintf(out->device_name, sizeof out->device_name, "%s", ctx->prop.name);
+        out->cc_major = ctx->prop.major;
+        out->cc_minor = ctx->prop.minor;
+        out->sm_count = ctx->prop.multiProcessorCount;
+        out->max_shared_per_block = (uint32_t)ctx->prop.sharedMemPerBlockOptin;
+        out->total_memory = ctx->prop.totalGlobalMem;
+        out->l2_bytes = ctx->prop.l2CacheSize;
+    });
+}
+
+int32_t gq_buffer_create(gq_ctx* ctx, uint64_t bytes, uint32_t mem, gq_buf* out) {
+    return guarded([&] {
+        Locked l(ctx);
+        if (!out) fail("gq_buffer_create: null out pointer");
+        *out = 0;
+        if (mem != GQ_MEM_DEVICE && mem != GQ_MEM_DEVICE_PERSISTENT) fail("gq_buffer_create: unknown memory class %u", mem);
+        Buffer b;
+        b.bytes = bytes;
+        b.mem = mem;
+        if (mem == GQ_MEM_DEVICE_PERSISTENT) {
+            b.capacity = bytes;
+            if (bytes) GQ_CUDA(cudaMalloc(&b.ptr, bytes));
+            ctx->stats.buffer_allocations++;
+            ctx->stats.persistent_buffers++;
+            ctx->stats.persistent_bytes += bytes;
+            if (ctx->stats.persistent_bytes > ctx->stats.persistent_peak) ctx->stats.persistent_peak = ctx->stats.persistent_bytes;
+        } else {
+            b.capacity = bucket_of(bytes);
+            auto it = ctx->pool.find(b.capacity);
+            if (it != ctx->pool.end()) {
+                b.ptr = it->second;
+                ctx->pool.erase(it);
+                ctx->stats.pool_reuses++;
+            } else {
+                GQ_CUDA(cudaMalloc(&b.ptr, b.capacity));
+                ctx->stats.buffer_allocations++;
+            }
+        }
+        gq_buf h = ctx->next_handle++;
+        ctx->buffers.emplace(h, b);
+        ctx->stats.buffers_outstanding++;
+        *out = h;
+    });
+}
+
+int32_t gq_buffer_wrap(gq_ctx* ctx, void* device_ptr, uint64_t bytes, gq_buf* out) {
+    return guarded([&] {
+        Locked l(ctx);
+        if (!out) fail("gq_buffer_wrap: null out pointer");
+        *out = 0;
+        if (!device_ptr && bytes) fail("gq_buffer_wrap: null device pointer");
+        if (bytes) {
+            cudaPointerAttributes attr{};
+            cudaError_t e = cudaPointerGetAttributes(&attr, device_ptr);
+            if (e != cudaSuccess || (attr.type != cudaMemoryTypeDevice && attr.type != cudaMemoryTypeManaged)) {
+                cudaGetLastError();
+                fail("gq_buffer_wrap: %p is not device memory", device_ptr);
+            }
+        }
+        Buffer b;
+        b.ptr = device_ptr;
+        b.bytes = bytes;
+        b.owned = false;
+        gq_buf h = ctx->next_handle++;
+        ctx->buffers.emplace(h, b);
+        ctx->stats.buffers_outstanding++;
+        *out = h;
+    });
+}
+
+int32_t gq_buffer_release(gq_ctx* ctx, gq_buf buf) {
+    return guarded([&] {
+        Locked l(ctx);
+        Buffer& b = lookup(ctx, buf, "gq_buffer_release");
+        b.released = true;  // the handle dies now; the memory when no graph names it
+        ctx->stats.buffers_outstanding--;
+        drop_ref(ctx, buf);
+    });
+}
+
+int32_t gq_buffer_size(gq_ctx* ctx, gq_buf buf, uint64_t* out) {
+    return guarded([&] {
+        Locked l(ctx);
+        if (!out) fail("gq_buffer_size: null out pointer");
+        *out = lookup(ctx, buf, "gq_buffer_size").bytes;
+    });
+}
+
+int32_t gq_buffer_ptr(gq_ctx* ctx, gq_buf buf, void** out) {
+    return guarded([&] {
+        Locked l(ctx);
+        if (!out) fail("gq_buffer_ptr: null out pointer");
+        *out = lookup(ctx, buf, "gq_buffer_ptr").ptr;
+    });
+}
+
+int32_t gq_stream(gq_ctx* ctx, void** out) {
+    return guarded([&] {
+        Locked l(ctx);
+        if (!out) fail("gq_stream: null out pointer");
+        *out = (void*)ctx->stream;
+    });
+}
+
+int32_t gq_upload(gq_ctx* ctx, gq_buf dst, uint64_t offset, const void* src, uint64_t bytes) {
+    return guarded([&] {
+        Locked l(ctx);
+        if (ctx->capturing) fail("%s", kCaptureWrite);
+        void* d = view(ctx, dst, offset, bytes, 1, "gq_upload");
+        if (!bytes) return;
+        if (!src) fail("gq_upload: null source");
+        GQ_CUDA(cudaMemcpyAsync(d, src, bytes, cudaMemcpyHostToDevice, ctx->stream));
+        GQ_CUDA(cudaStreamSynchronize(ctx->stream));
+        ctx->stats.uploads++;
+    });
+}
+
+int32_t gq_download(gq_ctx* ctx, gq_buf src, uint64_t offset, void* dst, uint64_t bytes) {
+    return guarded([&] {
+        Locked l(ctx);
+        if (ctx->capturing) fail("%s", kCaptureRead);
+        void* s = view(ctx, src, offset, bytes, 1, "gq_download");
+        if (bytes) {
+            if (!dst) fail("gq_download: null destination");
+            GQ_CUDA(cudaMemcpyAsync(dst, s, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+        }
+        host_wait(ctx);
+        ctx->stats.downloads++;
+    });
+}
+
+int32_t gq_upload_async(gq_ctx* ctx, gq_buf dst, uint64_t offset, const void* src, uint64_t bytes) {
+    return guarded([&] {
+        Locked l(ctx);
+        void* d = view(ctx, dst, offset, bytes, 1, "gq_upload_async");
+        if (!bytes) return;
+        if (!src) fail("gq_upload_async: null source");
+        GQ_CUDA(cudaMemcpyAsync(d, src, bytes, cudaMemcpyHostToDevice, ctx->stream));
+        ctx->stats.uploads++;
+        if (ctx->capturing) {
+            lookup(ctx, dst, "gq_upload_async").refs++;
+            ctx->capture_retained.push_back(dst);
+            ctx->capture_nodes++;
+        }
+    });
+}
+
+int32_t gq_download_async(gq_ctx* ctx, gq_buf src, uint64_t offset, void* dst, uint64_t bytes) {
+    return guarded([&] {
+        Locked l(ctx);
+        void* s = view(ctx, src, offset, bytes, 1, "gq_download_async");
+        if (!bytes) return;
+        if (!dst) fail("gq_download_async: null destination");
+        GQ_CUDA(cudaMemcpyAsync(dst, s, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+        ctx->stats.downloads++;
+        if (ctx->capturing) {
+            lookup(ctx, src, "gq_download_async").refs++;
+            ctx->capture_retained.push_back(src);
+            ctx->capture_nodes++;
+        }
+    });
+}
+
+int32_t gq_host_alloc(gq_ctx* ctx, uint64_t bytes, void** out) {
+    return guarded([&] {
+        Locked l(ctx);
+        if (!out) fail("gq_host_alloc: null out pointer");
+        *out = nullptr;
+        GQ_CUDA(cudaMallocHost(out, bytes ? bytes : 1));
+    });
+}
+
+int32_t gq_host_free(gq_ctx* ctx, void* ptr) {
+    return guarded([&] {
+        Locked l(ctx);
+        if (ptr) GQ_CUDA(cudaFreeHost(ptr));
+    });
+}
+
+int32_t gq_copy(gq_ctx* ctx, gq_buf src, uint64_t src_offset, gq_buf dst, uint64_t dst_offset, uint64_t bytes) {
+    return guarded([&] {
+        Locked l(ctx);
+        if ((src_offset | dst_offset | bytes) & 3) fail("gq_copy: offsets and size must be multiples of 4");
+        void* s = view(ctx, src, src_offset, bytes, 1, "gq_copy source");
+        void* d = view(ctx, dst, dst_offset, bytes, 1, "gq_copy destination");
+        if (!bytes) return;
+        GQ_CUDA(cudaMemcpyAsync(d, s, bytes, cudaMemcpyDeviceToDevice, ctx->stream));
+        after_launch(ctx, "copy", {src, dst});
+    });
+}
+
+int32_t gq_fill(gq_ctx* ctx, gq_buf dst, uint64_t offset, uint64_t bytes, uint32_t word) {
+    return guarded([&] {
+        Locked l(ctx);
+        if ((offset | bytes) & 3) fail("gq_fill: offset and size must be multiples of 4");
+        void* d = view(ctx, dst, offset, bytes, 1, "gq_fill");
+        if (!bytes) return;
+        launch_fill_u32(ctx->stream, (uint32_t*)d, bytes / 4, word);
+        after_launch(ctx, "fill", {dst});
+    });
+}
+
+int32_t gq_synchronize(gq_ctx* ctx) {
+    return guarded([&] {
+        Locked l(ctx);
+        if (ctx->capturing) fail("%s", kCaptureRead);
+        host_wait(ctx);
+    });
+}
+
+int32_t gq_stats_get(gq_ctx* ctx, gq_stats* out) {
+    return guarded([&] {
+        Locked l(ctx);
+        if (!out) fail("gq_stats_get: null out pointer");
+        *out = ctx->stats;
+    });
+}
+
+int32_t gq_persistent_peak_reset(gq_ctx* ctx) {
+    return guarded([&] {
+        Locked l(ctx);
+        ctx->stats.persistent_peak = ctx->stats.persistent_bytes;
+    });
+}
+
+// ── operators ────────────────────────────────────────────────────────────
+
+static uint64_t words8(uint64_t k) { return (k + 15) / 16 * 4; }
+static uint64_t words4(uint64_t k) { return (k + 31) / 32 * 4; }
+static const uint64_t kMaxDim = 0x7fffffffull;  // kernels index with 32-bit row/column counts
+
+static void check_dims(const char* op, uint64_t a, uint64_t b, uint64_t c = 1) {
+    if (a > kMaxDim || b > kMaxDim || c > kMaxDim) fail("%s: a dimension exceeds 2^31 - 1", op);
+}
+
+static void check_group(uint64_t group) {
+    // crates/grilly-infer/src/quant4.rs:99-103
+    if (group == 0 || group % 32 != 0) fail("int4 group_size must be a positive multiple of 32, got %llu", (unsigned long long)group);
+    if (group > kMaxDim) fail("int4 group_size exceeds 2^31 - 1");
+}
+
+int32_t gq_int8_quantize(gq_ctx* ctx, gq_buf w, uint64_t w_off, uint64_t rows, uint64_t k, gq_buf q, gq_buf scale) {
+    return guarded([&] {
+        Locked l(ctx);
+        check_dims("gq_int8_quantize", rows, k);
+        if (k == 0) fail("cannot quantize a weight with no input features");  // quant.rs:106-110
+        auto wp = (const float*)view(ctx, w, w_off, rows * k, 4, "gq_int8_quantize weight");
+        auto qp = (uint32_t*)view(ctx, q, 0, rows * words8(k), 4, "gq_int8_quantize q");
+        auto sp = (float*)view(ctx, scale, 0, rows, 4, "gq_int8_quantize scale");
+        if (rows == 0) return;
+        launch_quantize_q8(ctx->stream, wp, rows, k, qp, sp);
+        after_launch(ctx, "quantize_q8", {w, q, scale});
+    });
+}
+
+int32_t gq_int8_dequantize(gq_ctx* ctx, gq_buf q, gq_buf scale, uint64_t rows, uint64_t k, gq_buf w) {
+    return guarded([&] {
+        Locked l(ctx);
+        check_dims("gq_int8_dequantize", rows, k);
+        auto qp = (const uint32_t*)view(ctx, q, 0, rows * words8(k), 4, "gq_int8_dequantize q");
+        auto sp = (const float*)view(ctx, scale, 0, rows, 4, "gq_int8_dequantize scale");
+        auto wp = (float*)view(ctx, w, 0, rows * k, 4, "gq_int8_dequantize weight");
+        if (rows == 0 || k == 0) return;
+        launch_dequantize_q8(ctx->stream, qp, sp, rows, k, wp);
+        after_launch(ctx, "dequantize_q8", {q, scale, w});
+    });
+}
+
+int32_t gq_int8_linear(gq_ctx* ctx, gq_buf x, uint64_t x_off, uint64_t m, uint64_t k, gq_buf q, gq_buf scale,
+                       gq_buf bias, uint64_t b_off, uint64_t n, gq_buf y, int32_t kernel) {
+    return guarded([&] {
+        Locked l(ctx);
+        check_dims("gq_int8_linear", m, k, n);
+        if (kernel != GQ_KERNEL_AUTO && kernel != GQ_KERNEL_GEMV && kernel != GQ_KERNEL_TENSOR) fail("gq_int8_linear: unknown kernel selector %d", kernel);
+        auto xp = (const float*)view(ctx, x, x_off, m * k, 4, "gq_int8_linear input");
+        auto qp = (const uint32_t*)view(ctx, q, 0, n * words8(k), 4, "gq_int8_linear q");
+        auto sp = (const float*)view(ctx, scale, 0, n, 4, "gq_int8_linear scale");
+        auto bp = bias ? (const float*)view(ctx, bias, b_off, n, 4, "gq_int8_linear bias") : nullptr;
+        auto yp = (float*)view(ctx, y, 0, m * n, 4, "gq_int8_linear output");
+        if (m == 0 || n == 0) return;  // quant.rs:267-269
+        if (kernel == GQ_KERNEL_TENSOR) fail("gq_int8_linear: the tensor-core kernel is not built into this library");
+        launch_gemv_q8(ctx->stream, ctx->prop.multiProcessorCount, xp, m, k, qp, sp, bp, n, yp);
+        after_launch(ctx, "gemv_q8", {x, q, scale, bias, y});
+    });
+}
+
+int32_t gq_int4_quantize(gq_ctx* ctx, gq_buf w, uint64_t w_off, uint64_t rows, uint64_t k, uint64_t group, gq_buf q,
+                         gq_buf scale, gq_buf zero) {
+    return guarded([&] {
+        Locked l(ctx);
+        check_dims("gq_int4_quantize", rows, k);
+        if (k == 0) fail("cannot quantize a weight with no input features");  // quant4.rs:93-97
+        check_group(group);
+        uint64_t groups = (k + group - 1) / group;
+        auto wp = (const float*)view(ctx, w, w_off, rows * k, 4, "gq_int4_quantize weight");
+        auto qp = (uint32_t*)view(ctx, q, 0, rows * words4(k), 4, "gq_int4_quantize q");
+        auto sp = (float*)view(ctx, scale, 0, rows * groups, 4, "gq_int4_quantize scale");
+        auto zp = (float*)view(ctx, zero, 0, rows * groups, 4, "gq_int4_quantize zero");
+        if (rows == 0) return;
+        launch_quantize_q4(ctx->stream, wp, rows, k, group, qp, sp, zp);
+        after_launch(ctx, "quantize_q4", {w, q, scale, zero});
+    });
+}
+
+int32_t gq_int4_dequantize(gq_ctx* ctx, gq_buf q, gq_buf scale, gq_buf zero, uint64_t rows, uint64_t k,
+                           uint64_t group, gq_buf w) {
+    return guarded([&] {
+        Locked l(ctx);
+        check_dims("gq_int4_dequantize", rows, k);
+        check_group(group);
+        uint64_t groups = (k + group - 1) / group;
+        auto qp = (const uint32_t*)view(ctx, q, 0, rows * words4(k), 4, "gq_int4_dequantize q");
+        auto sp = (const float*)view(ctx, scale, 0, rows * groups, 4, "gq_int4_dequantize scale");
+        auto zp = (const float*)view(ctx, zero, 0, rows * groups, 4, "gq_int4_dequantize zero");
+        auto wp = (float*)view(ctx, w, 0, rows * k, 4, "gq_int4_dequantize weight");
+        if (rows == 0 || k == 0) return;
+        launch_dequantize_q4(ctx->stream, qp, sp, zp, rows, k, group, wp);
+        after_launch(ctx, "dequantize_q4", {q, scale, zero, w});
+    });
+}
+
+int32_t gq_int4_linear(gq_ctx* ctx, gq_buf x, uint64_t x_off, uint64_t m, uint64_t k, gq_buf q, gq_buf scale,
+                       gq_buf zero, gq_buf bias, uint64_t b_off, uint64_t n, uint64_t group, gq_buf y,
+                       int32_t kernel) {
+    return guarded([&] {
+        Locked l(ctx);
+        check_dims("gq_int4_linear", m, k, n);
+        check_group(group);
+        if (kernel != GQ_KERNEL_AUTO && kernel != GQ_KERNEL_GEMV && kernel != GQ_KERNEL_TENSOR) fail("gq_int4_linear: unknown kernel selector %d", kernel);
+        uint64_t groups = (k + group - 1) / group;
+        auto xp = (const float*)view(ctx, x, x_off, m * k, 4, "gq_int4_linear input");
+        auto qp = (const uint32_t*)view(ctx, q, 0, n * words4(k), 4, "gq_int4_linear q");
+        auto sp = (const float*)view(ctx, scale, 0, n * groups, 4, "gq_int4_linear scale");
+        auto zp = (const float*)view(ctx, zero, 0, n * groups, 4, "gq_int4_linear zero");
+        auto bp = bias ? (const float*)view(ctx, bias, b_off, n, 4, "gq_int4_linear bias") : nullptr;
+        auto yp = (float*)view(ctx, y, 0, m * n, 4, "gq_int4_linear output");
+        if (m == 0 || n == 0) return;
+        if (kernel == GQ_KERNEL_TENSOR) fail("gq_int4_linear: there is no tensor-core int4 kernel (the reference has none either, crates/grilly-infer/src/quant4.rs:412-413)");
+        launch_gemv_q4(ctx->stream, ctx->prop.multiProcessorCount, xp, m, k, qp, sp, zp, bp, n, group, yp);
+        after_launch(ctx, "gemv_q4", {x, q, scale, zero, bias, y});
+    });
+}
+
+// ── capture / replay ─────────────────────────────────────────────────────
+
+int32_t gq_begin_capture(gq_ctx* ctx) {
+    return guarded([&] {
+        Locked l(ctx);
+        if (ctx->capturing) fail("a capture is already running on this context");
+        // Relaxed: buffer allocation (cudaMalloc on a pool miss) stays legal while recording.
+        GQ_CUDA(cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeRelaxed));
+        ctx->capturing = true;
+        ctx->capture_nodes = 0;
+        ctx->capture_retained.clear();
+    });
+}
+
+int32_t gq_end_capture(gq_ctx* ctx, gq_graph** out) {
+    return guarded([&] {
+        Locked l(ctx);
+        if (out) *out = nullptr;
+        if (!ctx->capturing) fail("no capture is running on this context");
+        ctx->capturing = false;
+        cudaGraph_t graph = nullptr;
+        cudaError_t e = cudaStreamEndCapture(ctx->stream, &graph);
+        auto retained = std::move(ctx->capture_retained);
+        ctx->capture_retained.clear();
+        auto release_all = [&] {
+            for (gq_buf h : retained) drop_ref(ctx, h);
+        };
+        if (e != cudaSuccess) {
+            release_all();
+            cudaGetLastError();
+            fail("ending the capture: %s", cudaGetErrorString(e));
+        }
+        if (!out) {  // the caller only wanted the capture closed (an exception path)
+            if (graph) cudaGraphDestroy(graph);
+            release_all();
+            return;
+        }
+        if (ctx->capture_nodes == 0) {
+            if (graph) cudaGraphDestroy(graph);
+            release_all();
+            // crates/grilly-core/src/graph.rs:157-161
+            fail("nothing was captured: the callable recorded no GPU work, so there is nothing to replay");
+        }
+        auto g = new gq_graph();
+        g->graph = graph;
+        g->nodes = ctx->capture_nodes;
+        g->retained = std::move(retained);
+        e = cudaGraphInstantiate(&g->exec, graph, 0);
+        if (e != cudaSuccess) {
+            cudaGraphDestroy(graph);
+            for (gq_buf h : g->retained) drop_ref(ctx, h);
+            delete g;
+            fail("instantiating the captured graph: %s", cudaGetErrorString(e));
+        }
+        ctx->stats.captures++;
+        // The reference records while it runs, so the step has happened by the
+        // time its capture ends. A CUDA stream capture only records: run it once.
+        e = cudaGraphLaunch(g->exec, ctx->stream);
+        if (e != cudaSuccess) {
+            cudaGraphExecDestroy(g->exec);
+            cudaGraphDestroy(graph);
+            for (gq_buf h : g->retained) drop_ref(ctx, h);
+            delete g;
+            fail("running the captured graph: %s", cudaGetErrorString(e));
+        }
+        *out = g;
+    });
+}
+
+int32_t gq_capturing(gq_ctx* ctx, uint32_t* out) {
+    return guarded([&] {
+        Locked l(ctx);
+        if (!out) fail("gq_capturing: null out pointer");
+        *out = ctx->capturing ? 1u : 0u;
+    });
+}
+
+int32_t gq_graph_replay(gq_ctx* ctx, gq_graph* graph) {
+    return guarded([&] {
+        Locked l(ctx);
+        if (!graph || !graph->exec) fail("gq_graph_replay: null graph");
+        if (ctx->capturing) fail("gq_graph_replay: a capture is running on this context");
+        GQ_CUDA(cudaGraphLaunch(graph->exec, ctx->stream));
+        ctx->stats.graph_launches++;
+        ctx->stats.graph_nodes_replayed += graph->nodes;
+        if (ctx->launch_blocking) GQ_CUDA(cudaStreamSynchronize(ctx->stream));
+    });
+}
+
+int32_t gq_graph_nodes(gq_graph* graph, uint64_t* out) {
+    return guarded([&] {
+        if (!graph || !out) fail("gq_graph_nodes: null argument");
+        *out = graph->nodes;
+    });
+}
+
+void gq_graph_destroy(gq_ctx* ctx, gq_graph* graph) {
+    if (!ctx || !graph) return;
+    guarded([&] {
+        Locked l(ctx);
+        cudaStreamSynchronize(ctx->stream);  // a replay may still be running
+        if (graph->exec) cudaGraphExecDestroy(graph->exec);
+        if (graph->graph) cudaGraphDestroy(graph->graph);
+        for (gq_buf h : graph->retained) drop_ref(ctx, h);
+        delete graph;
+    });
+}
+
+}  // extern "C"

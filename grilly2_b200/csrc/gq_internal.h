@@ -1,0 +1,92 @@
+// Internal declarations shared by the backend's translation units. Nothing
+// here is part of the ABI; include/gq.h is.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <cstdio>
+#include <map>
+#include <mutex>
+#include <stdexcept>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "gq.h"
+
+namespace gq {
+
+// Thrown inside the library, turned into GQ_ERR + message at the boundary.
+struct Failure : std::runtime_error {
+    using std::runtime_error::runtime_error;
+};
+
+[[noreturn]] void fail(const char* fmt, ...) __attribute__((format(printf, 1, 2)));
+
+#define GQ_CUDA(expr)                                                                         \
+    do {                                                                                      \
+        cudaError_t gq_e_ = (expr);                                                           \
+        if (gq_e_ != cudaSuccess) ::gq::fail("%s: %s", #expr, cudaGetErrorString(gq_e_));     \
+    } while (0)
+
+struct Buffer {
+    void* ptr = nullptr;
+    uint64_t bytes = 0;     // what the caller asked for
+    uint64_t capacity = 0;  // what the allocation holds (pool bucket) — 0 for wrapped memory
+    uint32_t mem = GQ_MEM_DEVICE;
+    bool owned = true;
+    uint32_t refs = 1;  // the handle itself + one per graph that retains it
+    bool released = false;
+};
+
+}  // namespace gq
+
+struct gq_graph {
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    uint64_t nodes = 0;                // operator launches recorded
+    std::vector<gq_buf> retained;      // buffers the recorded work names
+};
+
+struct gq_ctx {
+    std::mutex mutex;
+    int device = 0;
+    cudaDeviceProp prop{};
+    cudaStream_t stream = nullptr;
+    uint64_t next_handle = 1;
+    std::unordered_map<gq_buf, gq::Buffer> buffers;
+    std::multimap<uint64_t, void*> pool;  // capacity -> free block (GQ_MEM_DEVICE only)
+    gq_stats stats{};
+    bool launch_blocking = false;  // GQ_LAUNCH_BLOCKING=1: wait after every launch
+    // capture state
+    bool capturing = false;
+    uint64_t capture_nodes = 0;
+    std::vector<gq_buf> capture_retained;
+    // lazily created device scratch owned by the context (tensor-core paths)
+    void* scratch = nullptr;
+    uint64_t scratch_bytes = 0;
+};
+
+namespace gq {
+
+// A checked view of `count` elements of `elem` bytes at element offset `off`.
+void* view(gq_ctx* ctx, gq_buf buf, uint64_t off, uint64_t count, uint64_t elem, const char* what);
+// Counts a launch, notes buffers for an open capture, honours launch_blocking.
+void after_launch(gq_ctx* ctx, const char* kernel, std::initializer_list<gq_buf> used);
+void* ensure_scratch(gq_ctx* ctx, uint64_t bytes);
+
+// ── kernels (each file states which reference shader it replaces) ─────────
+void launch_quantize_q8(cudaStream_t s, const float* w, uint64_t rows, uint64_t k, uint32_t* q, float* scale);
+void launch_dequantize_q8(cudaStream_t s, const uint32_t* q, const float* scale, uint64_t rows, uint64_t k, float* w);
+void launch_quantize_q4(cudaStream_t s, const float* w, uint64_t rows, uint64_t k, uint64_t group, uint32_t* q,
+                        float* scale, float* zero);
+void launch_dequantize_q4(cudaStream_t s, const uint32_t* q, const float* scale, const float* zero, uint64_t rows,
+                          uint64_t k, uint64_t group, float* w);
+void launch_fill_u32(cudaStream_t s, uint32_t* dst, uint64_t n, uint32_t word);
+void launch_gemv_q8(cudaStream_t s, int sm_count, const float* x, uint64_t m, uint64_t k, const uint32_t* q,
+                    const float* scale, const float* bias, uint64_t n, float* y);
+void launch_gemv_q4(cudaStream_t s, int sm_count, const float* x, uint64_t m, uint64_t k, const uint32_t* q,
+                    const float* scale, const float* zero, const float* bias, uint64_t n, uint64_t group, float* y);
+
+}  // namespace gq

@@ -1,0 +1,198 @@
+/* gq.h — C ABI of the B200 (sm_100a) backend for grilly2's weight-only
+ * quantized linear path: int8 per-row and int4 group-wise weights, their
+ * packers, the dequant-fused linear, and capture/replay as CUDA graphs.
+ *
+ * It takes the place, for these operators only, of the reference's Vulkan
+ * shim: crates/grilly-sys/shim/gc_shim.h:78-126 (gc_create … gc_submit) and
+ * the per-operator "signatures" (binding order + push-constant words) that
+ * crates/grilly-infer/src/quant.rs:18-46 and quant4.rs:26-46 declare for
+ * gc_dispatch. The conventions are that shim's (gc_shim.h:1-16):
+ *
+ *  - every function returns GQ_OK or GQ_ERR; on GQ_ERR the message is
+ *    available from gq_last_error() on the same thread until the next
+ *    failing call on that thread. No C++ exception crosses this boundary,
+ *    and misuse (bad handle, wrong size, bad shape) is reported, never a
+ *    device fault: every operator checks its operands against the sizes of
+ *    the buffers it was given before it launches anything.
+ *  - the context is opaque; buffers are 64-bit handles, 0 is never valid.
+ *    The caller owns the context and every handle it creates and releases
+ *    handles before gq_destroy. Allocations stay on this side.
+ *  - tensors are contiguous row-major float32 / 32-bit words located by an
+ *    ELEMENT offset into a whole buffer, as the reference's kernels receive
+ *    them (crates/grilly-core/src/kernel.rs:26-36), so an input may start at
+ *    any element; aligned fast paths are chosen inside.
+ *  - all work is asynchronous on the context's one CUDA stream, in call
+ *    order. gq_download and gq_synchronize wait for it. There is no batch to
+ *    open or submit.
+ *  - every call on a context is serialised on that context's mutex.
+ *
+ * Packed weight layouts are the reference's, bit for bit
+ * (crates/grilly-infer/src/quant.rs:84-94, quant4.rs:69-81), so a weight
+ * packed by either side is readable by the other:
+ *   int8: q[rows][words8] int32 words, words8 = 4*ceil(k/16); four
+ *         two's-complement int8 per word, little-endian; rows zero padded to
+ *         whole 16-byte vectors; scale[rows] float32.
+ *   int4: q[rows][words4] int32 words, words4 = 4*ceil(k/32); eight 4-bit
+ *         levels per word, low nibble first; zero padded;
+ *         scale[rows][groups], zero[rows][groups] float32,
+ *         groups = ceil(k/group).
+ */
+#ifndef GQ_H
+#define GQ_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+#if defined(GQ_BUILD) && defined(__GNUC__)
+#pragma GCC visibility push(default) /* the library hides everything else */
+#endif
+
+typedef struct gq_ctx gq_ctx;
+typedef struct gq_graph gq_graph;
+typedef uint64_t gq_buf; /* 0 is never a valid handle */
+
+#define GQ_OK 0
+#define GQ_ERR 1
+
+/* Memory classes; the values are gc_shim.h:33-41's. */
+#define GQ_MEM_DEVICE 0            /* pooled device memory (activations, outputs) */
+#define GQ_MEM_DEVICE_PERSISTENT 3 /* exactly the size asked for, never pooled, counted in
+                                      persistent_bytes / persistent_peak: weights and quantized data */
+
+/* Which kernel a linear runs. AUTO picks by shape (see gq_int8_linear). */
+#define GQ_KERNEL_AUTO 0
+#define GQ_KERNEL_GEMV 1   /* dequant-fused GEMV on the CUDA cores, the reference's summation order */
+#define GQ_KERNEL_TENSOR 2 /* tcgen05 tensor-core GEMM (tf32), dequantised in shared memory */
+
+typedef struct gq_caps { /* replaces gc_caps, gc_shim.h:43-50 */
+    char device_name[256];
+    uint32_t cc_major, cc_minor;
+    uint32_t sm_count;
+    uint32_t max_shared_per_block;
+    uint64_t total_memory;
+    uint64_t l2_bytes;
+} gq_caps;
+
+typedef struct gq_stats { /* replaces gc_submit_stats, gc_shim.h:61-76 */
+    uint64_t launches;            /* kernels launched by operators (eager and while capturing) */
+    uint64_t graph_launches;      /* gq_graph_replay calls */
+    uint64_t graph_nodes_replayed;/* kernel nodes those replays ran */
+    uint64_t captures;            /* graphs instantiated */
+    uint64_t syncs;               /* host waits (download, synchronize) */
+    uint64_t wait_ns_total;       /* host time spent in those waits */
+    uint64_t wait_ns_last;
+    uint64_t buffer_allocations;  /* fresh device allocations (pool misses and persistent) */
+    uint64_t buffers_outstanding; /* handles alive */
+    uint64_t pool_reuses;         /* GQ_MEM_DEVICE requests served from the pool */
+    uint64_t persistent_buffers;  /* GQ_MEM_DEVICE_PERSISTENT buffers alive */
+    uint64_t persistent_bytes;    /* and their total size */
+    uint64_t persistent_peak;     /* the most persistent bytes alive at once */
+    uint64_t uploads, downloads;
+} gq_stats;
+
+/* gc_shim.h:78 */
+const char* gq_last_error(void);
+
+/* gc_shim.h:80-82. `device` is the CUDA ordinal. Refuses anything that is not
+ * compute capability 10.x: the kernels are built for sm_100a only. */
+int32_t gq_create(int32_t device, gq_ctx** out);
+void gq_destroy(gq_ctx* ctx);
+int32_t gq_caps_get(gq_ctx* ctx, gq_caps* out);
+
+/* gc_shim.h:96-98 */
+int32_t gq_buffer_create(gq_ctx* ctx, uint64_t bytes, uint32_t mem, gq_buf* out);
+int32_t gq_buffer_release(gq_ctx* ctx, gq_buf buf);
+int32_t gq_buffer_size(gq_ctx* ctx, gq_buf buf, uint64_t* out);
+/* No counterpart in the shim (Vulkan buffers have no address): register
+ * device memory the caller owns (a framework tensor, say) so operators can
+ * use it without a copy. Releasing the handle does not free the memory. */
+int32_t gq_buffer_wrap(gq_ctx* ctx, void* device_ptr, uint64_t bytes, gq_buf* out);
+/* The device address behind a handle, for callers that run their own kernels
+ * on the context's stream. */
+int32_t gq_buffer_ptr(gq_ctx* ctx, gq_buf buf, void** out);
+/* The context's cudaStream_t, as a void*. */
+int32_t gq_stream(gq_ctx* ctx, void** out);
+
+/* gc_shim.h:100-107. Both return after the copy has completed. Refused while
+ * a capture is open, with the reference's messages
+ * (crates/grilly-core/src/device.rs:591-597, 620-628). */
+int32_t gq_upload(gq_ctx* ctx, gq_buf dst, uint64_t offset, const void* src, uint64_t bytes);
+int32_t gq_download(gq_ctx* ctx, gq_buf src, uint64_t offset, void* dst, uint64_t bytes);
+/* Asynchronous forms for pinned host memory (gq_host_alloc): the copy is
+ * ordered on the stream and the host pointer must stay valid until the next
+ * gq_synchronize. These may be captured. */
+int32_t gq_upload_async(gq_ctx* ctx, gq_buf dst, uint64_t offset, const void* pinned_src, uint64_t bytes);
+int32_t gq_download_async(gq_ctx* ctx, gq_buf src, uint64_t offset, void* pinned_dst, uint64_t bytes);
+int32_t gq_host_alloc(gq_ctx* ctx, uint64_t bytes, void** out);
+int32_t gq_host_free(gq_ctx* ctx, void* ptr);
+
+/* gc_shim.h:117-121 (byte offsets; multiples of 4) */
+int32_t gq_copy(gq_ctx* ctx, gq_buf src, uint64_t src_offset, gq_buf dst, uint64_t dst_offset, uint64_t bytes);
+int32_t gq_fill(gq_ctx* ctx, gq_buf dst, uint64_t offset, uint64_t bytes, uint32_t word);
+/* gc_submit's wait, gc_shim.h:122 */
+int32_t gq_synchronize(gq_ctx* ctx);
+/* gc_shim.h:123-125 */
+int32_t gq_stats_get(gq_ctx* ctx, gq_stats* out);
+int32_t gq_persistent_peak_reset(gq_ctx* ctx);
+
+/* ── int8 per-row ──────────────────────────────────────────────────────
+ * Offsets named *_off are in ELEMENTS of the tensor's type. */
+
+/* QUANTIZE{w,q,scale; rows,k,words,w_off} — crates/grilly-infer/src/quant.rs:18-24,98-141
+ * and shaders/g2-quantize-q8.glsl:22-53. w is (rows, k) float32 at w_off;
+ * q must hold rows*words8 words, scale rows floats. */
+int32_t gq_int8_quantize(gq_ctx* ctx, gq_buf w, uint64_t w_off, uint64_t rows, uint64_t k, gq_buf q, gq_buf scale);
+
+/* LINEAR / LINEAR_TILED{x,q,scale,bias,y; m,k,n,vecs,x_off,b_off,has_bias,x_vec4}
+ * — quant.rs:25-39,233-304, g2-linear-q8.glsl:33-95, g2-linear-q8-tiled.glsl:41-100.
+ * y[m][n] = (sum_k x[m][k] * q[n][k]) * scale[n] (+ bias[n]); bias == 0 means none.
+ * AUTO: the GEMV for m < GQ_TENSOR_MIN_ROWS, the tensor-core GEMM from there on
+ * when the shape meets its alignment rules (k % 4 == 0, x_off % 4 == 0). */
+int32_t gq_int8_linear(gq_ctx* ctx, gq_buf x, uint64_t x_off, uint64_t m, uint64_t k, gq_buf q, gq_buf scale,
+                       gq_buf bias, uint64_t b_off, uint64_t n, gq_buf y, int32_t kernel);
+
+/* DEQUANTIZE{q,scale,w; rows,k,words} — quant.rs:40-46,307-322, g2-dequantize-q8.glsl:15-21 */
+int32_t gq_int8_dequantize(gq_ctx* ctx, gq_buf q, gq_buf scale, uint64_t rows, uint64_t k, gq_buf w);
+
+/* ── int4 group-wise ─────────────────────────────────────────────────── */
+
+/* QUANTIZE{w,q,scale,zero; rows,k,group,words,groups,w_off} — quant4.rs:26-32,85-154,
+ * g2-quantize-q4.glsl:30-70. group must be a positive multiple of 32. */
+int32_t gq_int4_quantize(gq_ctx* ctx, gq_buf w, uint64_t w_off, uint64_t rows, uint64_t k, uint64_t group, gq_buf q,
+                         gq_buf scale, gq_buf zero);
+
+/* LINEAR{x,q,scale,zero,bias,y; m,k,n,vecs,group,groups,x_off,b_off,has_bias,x_vec4}
+ * — quant4.rs:33-39,371-442, g2-linear-q4.glsl:43-111. */
+int32_t gq_int4_linear(gq_ctx* ctx, gq_buf x, uint64_t x_off, uint64_t m, uint64_t k, gq_buf q, gq_buf scale,
+                       gq_buf zero, gq_buf bias, uint64_t b_off, uint64_t n, uint64_t group, gq_buf y,
+                       int32_t kernel);
+
+/* DEQUANTIZE{q,scale,zero,w; rows,k,group,words,groups} — quant4.rs:40-46,343-366,
+ * g2-dequantize-q4.glsl:16-24 */
+int32_t gq_int4_dequantize(gq_ctx* ctx, gq_buf q, gq_buf scale, gq_buf zero, uint64_t rows, uint64_t k,
+                           uint64_t group, gq_buf w);
+
+/* ── capture / replay — crates/grilly-core/src/graph.rs:43-164,
+ * device.rs:365-416, as CUDA graphs. Capture is context-wide: capture from
+ * the thread that replays, with nothing else running on the context
+ * (graph.rs:23-26). Buffers an operator touches while capturing are retained
+ * by the graph until gq_graph_destroy, so a replay never writes memory that
+ * has been handed to someone else (kernel.rs:99-117). */
+int32_t gq_begin_capture(gq_ctx* ctx);
+int32_t gq_end_capture(gq_ctx* ctx, gq_graph** out); /* GQ_ERR "nothing was captured" for an empty capture */
+int32_t gq_capturing(gq_ctx* ctx, uint32_t* out);
+int32_t gq_graph_replay(gq_ctx* ctx, gq_graph* graph);
+int32_t gq_graph_nodes(gq_graph* graph, uint64_t* out); /* operator launches the graph holds */
+void gq_graph_destroy(gq_ctx* ctx, gq_graph* graph);
+
+#if defined(GQ_BUILD) && defined(__GNUC__)
+#pragma GCC visibility pop
+#endif
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* GQ_H */

@@ -1,0 +1,167 @@
+"""GPU parity of the dequant-fused linear: CUDA against the CPU oracle on the
+same seeded inputs, through the C ABI.
+
+Tolerances, written here as the tests state them:
+ * against the oracle's float32 evaluation in the reference shader's order:
+   EQUAL (the GEMV reproduces that order), and in any case
+   max|y - y_ref| / max|y_ref| <= 1e-5;
+ * against float64: the reference's own bound
+   (crates/grilly-infer/tests/quant.rs:136-160, quant4.rs:170-196).
+"""
+import numpy as np
+import pytest
+
+import oracle
+
+pytestmark = pytest.mark.gpu
+
+TOL = 1e-5
+
+
+@pytest.fixture(scope="module")
+def g():
+    import grilly2_b200 as g
+    return g
+
+
+def rel(y, ref):
+    return float(np.abs(y - ref).max() / max(np.abs(ref).max(), np.finfo(np.float32).tiny))
+
+
+INT8_SHAPES = [(1, 1, 1), (1, 5, 17), (3, 4, 16), (8, 7, 33), (9, 6, 100), (20, 13, 896), (1, 64, 4864), (16, 5, 33),
+               (2, 37, 1040), (4, 130, 2048), (1, 4864, 896), (5, 1152, 896)]
+
+
+@pytest.mark.parametrize("m,n,k", INT8_SHAPES)
+@pytest.mark.parametrize("with_bias", [False, True], ids=["nobias", "bias"])
+def test_int8_linear(g, m, n, k, with_bias):
+    from grilly2_b200 import _lib
+    from grilly2_b200.infer.quantization import Int8Tensor
+    w = oracle.xorshift_data(n * k, m + n + k, -1.0, 1.0).reshape(n, k)
+    x = oracle.xorshift_data(m * k, m * n * k + 7, -2.0, 2.0).reshape(m, k)
+    b = oracle.xorshift_data(n, 99, -0.5, 0.5) if with_bias else None
+    t = Int8Tensor.from_hp(g.from_numpy(w))
+    q, scale = oracle.quantize_q8(w)
+    y = t._q.linear(g.from_numpy(x)._t, None if b is None else g.from_numpy(b)._t, _lib.KERNEL_GEMV).numpy()
+    ref = oracle.linear_q8(x, q, scale, b, k)
+    assert rel(y, ref) <= TOL
+    np.testing.assert_array_equal(y, ref)  # same summation order as the reference's decode shader
+    want, mag = oracle.linear_q8_f64(x, q, scale, b, k)
+    terms = 16 * -(-(-(-k // 16)) // 64)
+    assert (np.abs(y - want) <= (terms + 8) * 2.0 ** -24 * mag + np.finfo(np.float64).tiny).all()
+
+
+INT4_SHAPES = [(1, 1, 32, 32), (1, 5, 128, 128), (3, 4, 130, 128), (8, 7, 256, 64), (2, 64, 896, 128),
+               (9, 6, 4864, 128), (4, 33, 4096, 128), (16, 40, 1024, 32), (1, 300, 8192, 128), (5, 7, 70, 32)]
+
+
+@pytest.mark.parametrize("m,n,k,group", INT4_SHAPES)
+@pytest.mark.parametrize("with_bias", [False, True], ids=["nobias", "bias"])
+def test_int4_linear(g, m, n, k, group, with_bias):
+    from grilly2_b200 import _lib
+    from grilly2_b200.infer.quantization import Int4Tensor
+    w = oracle.xorshift_data(n * k, m + n + k, -1.0, 1.0, int4_form=True).reshape(n, k)
+    x = oracle.xorshift_data(m * k, m * n * k + 7, -2.0, 2.0, int4_form=True).reshape(m, k)
+    b = oracle.xorshift_data(n, 99, -0.5, 0.5, int4_form=True) if with_bias else None
+    t = Int4Tensor.from_hp(g.from_numpy(w), group)
+    q, scale, zero = oracle.quantize_q4(w, group)
+    y = t._q.linear(g.from_numpy(x)._t, None if b is None else g.from_numpy(b)._t, _lib.KERNEL_GEMV).numpy()
+    ref = oracle.linear_q4(x, q, scale, zero, b, k, group)  # x at offset 0: vec4 iff k % 4 == 0
+    assert rel(y, ref) <= TOL
+    np.testing.assert_array_equal(y, ref)
+    want, mag = oracle.linear_q4_f64(x, q, scale, zero, b, k, group)
+    assert (np.abs(y - want) <= (-(-k // 64) + 14) * 2.0 ** -24 * mag + np.finfo(np.float64).tiny).all()
+
+
+@pytest.mark.parametrize("x_off", [1, 2, 4])
+def test_x_and_bias_at_element_offsets(g, x_off):
+    """x may start at any element (crates/grilly-core/src/kernel.rs:26-36);
+    off a multiple of four the scalar path runs, whose int4 `sum` order is the
+    reference's scalar one (g2-linear-q4.glsl:80-86)."""
+    from grilly2_b200 import _C
+    rng = np.random.default_rng(x_off)
+    m, n, k = 3, 21, 256
+    w = rng.standard_normal((n, k)).astype(np.float32)
+    flat = rng.standard_normal(x_off + m * k).astype(np.float32)
+    bflat = rng.standard_normal(5 + n).astype(np.float32)
+    xs = _C.Tensor(_C.Tensor.from_numpy(flat).storage, (m, k), "float32", x_off)
+    bs = _C.Tensor(_C.Tensor.from_numpy(bflat).storage, (n,), "float32", 5)
+    x, b = flat[x_off:].reshape(m, k), bflat[5:]
+    w8 = _C.Int8Weight.quantize(_C.Tensor.from_numpy(w))
+    q, scale = oracle.quantize_q8(w)
+    np.testing.assert_array_equal(w8.linear(xs, bs).numpy(), oracle.linear_q8(x, q, scale, b, k))
+    w4 = _C.Int4Weight.quantize(_C.Tensor.from_numpy(w), 64)
+    q4, s4, z4 = oracle.quantize_q4(w, 64)
+    ref = oracle.linear_q4(x, q4, s4, z4, b, k, 64, x_vec4=(x_off % 4 == 0))
+    np.testing.assert_array_equal(w4.linear(xs, bs).numpy(), ref)
+
+
+def test_leading_dims_empty_and_refusals(g):
+    """crates/grilly-infer/tests/quant.rs:220-253."""
+    from grilly2_b200.infer.quantization import Int4Tensor, Int8Tensor
+    import grilly2_b200.nn.functional as F
+    rng = np.random.default_rng(6)
+    n, k = 6, 64
+    w = rng.standard_normal((n, k)).astype(np.float32)
+    x = rng.standard_normal((2, 3, k)).astype(np.float32)
+    for t in (Int8Tensor.from_hp(g.from_numpy(w)), Int4Tensor.from_hp(g.from_numpy(w), 32)):
+        flat = F.linear(g.from_numpy(x.reshape(6, k)), t)
+        batched = F.linear(g.from_numpy(x), t)
+        assert tuple(batched.shape) == (2, 3, n)
+        np.testing.assert_array_equal(batched.numpy().reshape(6, n), flat.numpy())
+        assert tuple(F.linear(g.from_numpy(np.zeros((0, k), dtype=np.float32)), t).shape) == (0, n)
+        with pytest.raises(RuntimeError, match="does not end in in_features"):
+            F.linear(g.from_numpy(np.zeros((2, 7), dtype=np.float32)), t)
+        with pytest.raises(RuntimeError, match="bias must be"):
+            F.linear(g.from_numpy(x), t, g.from_numpy(np.zeros(n + 1, dtype=np.float32)))
+
+
+def test_cat_linear_equals_separate_linears(g):
+    """A fused q/k/v projection computes each row exactly as the separate
+    ones did (crates/grilly-infer/tests/fused_ops.rs:194-228)."""
+    from grilly2_b200.infer.quantization import Int4Tensor, Int8Tensor
+    import grilly2_b200.nn.functional as F
+    rng = np.random.default_rng(8)
+    parts = [rng.standard_normal((n, 896)).astype(np.float32) * 0.02 for n in (896, 128, 128)]
+    x = g.from_numpy(rng.standard_normal((1, 896)).astype(np.float32))
+    for cls, extra in ((Int8Tensor, ()), (Int4Tensor, (128,))):
+        qs = [cls.from_hp(g.from_numpy(p), *extra) for p in parts]
+        fused = F.linear(x, cls._cat(qs)).numpy()
+        separate = np.concatenate([F.linear(x, q).numpy() for q in qs], axis=1)
+        np.testing.assert_array_equal(fused, separate)
+
+
+@pytest.mark.parametrize("config", ["c1", "c2", "c3"])
+def test_benchmark_configs_full_size(g, config):
+    """The benchmark's own shapes and seeds. The oracle finishes these in
+    seconds, so the comparison is outright; linearity in x is checked on top
+    as a size-independent property."""
+    from grilly2_b200.infer.quantization import Int4Tensor, Int8Tensor
+    import grilly2_b200.nn.functional as F
+    if config == "c1":
+        rng = np.random.default_rng(0)
+        x = rng.standard_normal((1, 896)).astype(np.float32)
+        w = (rng.standard_normal((4864, 896)) * 0.02).astype(np.float32)
+        t = Int8Tensor.from_hp(g.from_numpy(w))
+        q, scale = oracle.quantize_q8(w)
+        ref = oracle.linear_q8(x, q, scale, None, 896)
+        ms = [1]
+    else:
+        n, k, sigma, seed, ms = (14336, 4096, 0.02, 1, [1, 4, 16]) if config == "c2" else (28672, 8192, 0.015, 2, [1, 8])
+        rng = np.random.default_rng(seed)
+        x = rng.standard_normal((max(ms), k)).astype(np.float32)
+        w = (rng.standard_normal((n, k)) * sigma).astype(np.float32)
+        t = Int4Tensor.from_hp(g.from_numpy(w), 128)
+        q, scale, zero = oracle.quantize_q4(w, 128)
+        np.testing.assert_array_equal(t._q.packed().numpy().view(np.uint32), q)
+    for m in ms:
+        xm = x[:m]
+        y = F.linear(g.from_numpy(xm), t).numpy()
+        if config != "c1":
+            ref = oracle.linear_q4(xm, q, scale, zero, None, xm.shape[1], 128)
+        assert rel(y, ref) <= TOL
+        np.testing.assert_array_equal(y, ref)
+    # linearity: f(2x) == 2 f(x) exactly (scaling by two is exact in binary floating point)
+    y1 = F.linear(g.from_numpy(x[:1]), t).numpy()
+    y2 = F.linear(g.from_numpy(2 * x[:1]), t).numpy()
+    np.testing.assert_array_equal(y2, 2 * y1)

@@ -1,0 +1,193 @@
+"""GPU parity of the packers: CUDA quantize / dequantize / cat / from_parts
+against the CPU oracle and the committed golden vectors, bit for bit, through
+the C ABI (via the package's ctypes binding). Shapes and edge cases are the
+reference tests' (crates/grilly-infer/tests/quant.rs:62-83, quant4.rs:89-96)."""
+import os
+
+import numpy as np
+import pytest
+
+import oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def bits(a):
+    return np.ascontiguousarray(a, dtype=np.float32).view(np.uint32)
+
+
+@pytest.fixture(scope="module")
+def g():
+    import grilly2_b200 as g
+    return g
+
+
+def q8_words(t):
+    return t._q.packed().numpy().view(np.uint32)
+
+
+def test_int8_golden_fixture(g, golden_dir):
+    from grilly2_b200.infer.quantization import Int8Tensor
+    z = np.load(os.path.join(golden_dir, "int8_formula.npz"))
+    for i in range(int(z["count"])):
+        w = z[f"w{i}"]
+        t = Int8Tensor.from_hp(g.from_numpy(w))
+        n, k = w.shape
+        assert tuple(t.shape) == (n, k)
+        got = np.frombuffer(t._q.qdata(), dtype=np.int8).reshape(n, k)
+        np.testing.assert_array_equal(got, z[f"q{i}"], f"case {i} q")
+        np.testing.assert_array_equal(bits(t.scale.numpy()), bits(z[f"scale{i}"]), f"case {i} scale")
+        np.testing.assert_array_equal(bits(t.dequantize().numpy()), bits(z[f"deq{i}"]), f"case {i} dequantize")
+        # the whole packed row, padding included, equals the oracle's
+        np.testing.assert_array_equal(q8_words(t), oracle.quantize_q8(w)[0])
+
+
+@pytest.mark.parametrize("n,k", [(1, 1), (3, 5), (33, 17), (64, 896), (40, 4864), (7, 33), (300, 1000), (2, 20000)])
+def test_int8_matches_the_oracle(g, n, k):
+    from grilly2_b200.infer.quantization import Int8Tensor
+    rng = np.random.default_rng(n * 7919 + k)
+    w = (rng.standard_normal((n, k)) * rng.uniform(0.01, 5, (n, 1))).astype(np.float32)
+    w[0] = 0.0
+    t = Int8Tensor.from_hp(g.from_numpy(w))
+    q, scale = oracle.quantize_q8(w)
+    np.testing.assert_array_equal(q8_words(t), q)
+    np.testing.assert_array_equal(bits(t.scale.numpy()), bits(scale))
+    np.testing.assert_array_equal(bits(t.dequantize().numpy()), bits(oracle.dequantize_q8(q, scale, k)))
+    assert t.nbytes == n * oracle.words8(k) * 4 + n * 4
+
+
+def test_int8_weight_at_an_unaligned_offset(g):
+    """A weight that starts at an odd element of its buffer takes the scalar
+    path and must give the same bits (the reference passes w_off,
+    crates/grilly-infer/src/quant.rs:126)."""
+    from grilly2_b200 import _C
+    rng = np.random.default_rng(9)
+    flat = rng.standard_normal(3 + 6 * 40).astype(np.float32)
+    base = _C.Tensor.from_numpy(flat)
+    view = _C.Tensor(base.storage, (6, 40), "float32", 3)
+    got = _C.Int8Weight.quantize(view)
+    q, scale = oracle.quantize_q8(flat[3:].reshape(6, 40))
+    np.testing.assert_array_equal(got.packed().numpy().view(np.uint32), q)
+    np.testing.assert_array_equal(bits(got.scale().numpy()), bits(scale))
+
+
+@pytest.mark.parametrize("name", ["int4_rtn.npz", "int4_formula.npz"])
+def test_int4_golden_fixtures(g, golden_dir, name):
+    from grilly2_b200.infer.quantization import Int4Tensor
+    z = np.load(os.path.join(golden_dir, name))
+    for i in range(int(z["count"])):
+        w, group = z[f"w{i}"], int(z[f"group{i}"])
+        n, k = w.shape
+        t = Int4Tensor.from_hp(g.from_numpy(w), group)
+        words = t._q.packed().numpy().view(np.uint32)
+        np.testing.assert_array_equal(oracle.unpack_q4(words, k), z[f"levels{i}"], f"{name} case {i} levels")
+        np.testing.assert_array_equal(bits(t.scale.numpy()), bits(z[f"scale{i}"]), f"{name} case {i} scale")
+        np.testing.assert_array_equal(bits(t.zero.numpy()), bits(z[f"zero{i}"]), f"{name} case {i} zero")
+        np.testing.assert_array_equal(words, oracle.pack_levels_q4(z[f"levels{i}"]))  # padding words are zero
+        assert t.group_size == group and tuple(t.shape) == (n, k)
+        assert t.nbytes == n * (oracle.words4(k) * 4 + 8 * (-(-k // group)))
+        q, s, zr = oracle.quantize_q4(w, group)
+        np.testing.assert_array_equal(bits(t.dequantize().numpy()), bits(oracle.dequantize_q4(q, s, zr, k, group)))
+        raw = np.frombuffer(t._q.qdata(), dtype=np.uint8).reshape(n, -(-k // 2))
+        np.testing.assert_array_equal(raw, q.view(np.uint8).reshape(n, -1)[:, :-(-k // 2)])
+
+
+@pytest.mark.parametrize("n,k,group", [(1, 32, 32), (5, 130, 128), (9, 4864, 128), (3, 100, 32), (2, 20000, 128),
+                                       (4, 1024, 1024), (3, 5000, 4096), (6, 33, 64), (2, 70000, 32768)])
+def test_int4_matches_the_oracle(g, n, k, group):
+    from grilly2_b200.infer.quantization import Int4Tensor
+    rng = np.random.default_rng(n + k + group)
+    w = rng.standard_normal((n, k)).astype(np.float32)
+    w[0, : min(k, group)] = 0.25  # a constant group: max == min, the scale is eps
+    t = Int4Tensor.from_hp(g.from_numpy(w), group)
+    q, scale, zero = oracle.quantize_q4(w, group)
+    np.testing.assert_array_equal(t._q.packed().numpy().view(np.uint32), q)
+    np.testing.assert_array_equal(bits(t.scale.numpy()), bits(scale))
+    np.testing.assert_array_equal(bits(t.zero.numpy()), bits(zero))
+    np.testing.assert_array_equal(bits(t.dequantize().numpy()), bits(oracle.dequantize_q4(q, scale, zero, k, group)))
+
+
+def test_int4_weight_at_an_unaligned_offset(g):
+    from grilly2_b200 import _C
+    rng = np.random.default_rng(11)
+    flat = rng.standard_normal(1 + 5 * 130).astype(np.float32)
+    view = _C.Tensor(_C.Tensor.from_numpy(flat).storage, (5, 130), "float32", 1)
+    got = _C.Int4Weight.quantize(view, 128)
+    q, scale, zero = oracle.quantize_q4(flat[1:].reshape(5, 130), 128)
+    np.testing.assert_array_equal(got.packed().numpy().view(np.uint32), q)
+    np.testing.assert_array_equal(bits(got.scale().numpy()), bits(scale))
+    np.testing.assert_array_equal(bits(got.zero().numpy()), bits(zero))
+
+
+def test_from_parts_installs_levels_exactly(g):
+    """python/grilly/infer/quantization.py:226-252; identity GPTQ == RTN
+    (tests/python/test_gptq.py:39-47) reduces to this round trip."""
+    from grilly2_b200.infer.quantization import Int4Tensor
+    rng = np.random.default_rng(4)
+    w = rng.standard_normal((6, 200)).astype(np.float32)
+    q, scale, zero = oracle.quantize_q4(w, 64)
+    levels = oracle.unpack_q4(q, 200)
+    t = Int4Tensor.from_parts(levels, scale, zero, 64)
+    direct = Int4Tensor.from_hp(g.from_numpy(w), 64)
+    np.testing.assert_array_equal(t._q.packed().numpy(), direct._q.packed().numpy())
+    np.testing.assert_array_equal(bits(t.dequantize().numpy()), bits(direct.dequantize().numpy()))
+    with pytest.raises(RuntimeError, match="scale and zero must be"):
+        Int4Tensor.from_parts(levels, scale[:, :2], zero, 64)
+    with pytest.raises(RuntimeError, match="multiple of 32"):
+        Int4Tensor.from_parts(levels, scale, zero, 48)
+
+
+def test_cat_equals_quantizing_the_stacked_weight(g):
+    """crates/grilly-infer/tests/fused_ops.rs:194-228."""
+    from grilly2_b200.infer.quantization import Int4Tensor, Int8Tensor
+    rng = np.random.default_rng(5)
+    parts = [rng.standard_normal((n, 896)).astype(np.float32) for n in (14 * 64, 2 * 64, 2 * 64)]
+    whole = np.concatenate(parts)
+    for cls, extra in ((Int8Tensor, ()), (Int4Tensor, (128,))):
+        fused = cls._cat([cls.from_hp(g.from_numpy(p), *extra) for p in parts])
+        direct = cls.from_hp(g.from_numpy(whole), *extra)
+        np.testing.assert_array_equal(fused._q.packed().numpy(), direct._q.packed().numpy())
+        np.testing.assert_array_equal(bits(fused.scale.numpy()), bits(direct.scale.numpy()))
+        assert fused.nbytes == direct.nbytes and tuple(fused.shape) == whole.shape
+    a = Int8Tensor.from_hp(g.from_numpy(parts[0]))
+    b = Int8Tensor.from_hp(g.from_numpy(rng.standard_normal((4, 100)).astype(np.float32)))
+    with pytest.raises(RuntimeError, match="in_features differ"):
+        Int8Tensor._cat([a, b])
+
+
+def test_refusals(g):
+    """crates/grilly-infer/tests/quant.rs:245-252, quant4.rs:206-218."""
+    from grilly2_b200.infer.quantization import Int4Tensor, Int8Tensor
+    with pytest.raises(RuntimeError, match="2-D weight"):
+        Int8Tensor.from_hp(g.from_numpy(np.zeros(8, dtype=np.float32)))
+    with pytest.raises(RuntimeError, match="no input features"):
+        Int8Tensor.from_hp(g.from_numpy(np.zeros((3, 0), dtype=np.float32)))
+    with pytest.raises(RuntimeError, match="multiple of 32"):
+        Int4Tensor.from_hp(g.zeros(4, 64), 8)
+    with pytest.raises(RuntimeError, match="multiple of 32"):
+        Int4Tensor.from_hp(g.zeros(2, 2), 0)
+    with pytest.raises(NotImplementedError):
+        Int8Tensor.from_hp(g.from_numpy(np.zeros((2, 2), dtype=np.int32)))
+
+
+def test_full_size_quantizers_by_properties(g):
+    """At the benchmark's sizes (14336 x 4096) the oracle still finishes in
+    seconds, so compare outright, then check two size-independent properties:
+    re-quantizing the dequantized int8 weight is idempotent, and int4 levels
+    of every full group span 0 and 15."""
+    from grilly2_b200.infer.quantization import Int4Tensor, Int8Tensor
+    w = (np.random.default_rng(1).standard_normal((14336, 4096)) * 0.02).astype(np.float32)
+    wt = g.from_numpy(w)
+    t8 = Int8Tensor.from_hp(wt)
+    q, scale = oracle.quantize_q8(w)
+    np.testing.assert_array_equal(t8._q.packed().numpy().view(np.uint32), q)
+    np.testing.assert_array_equal(bits(t8.scale.numpy()), bits(scale))
+    again = Int8Tensor.from_hp(t8.dequantize())
+    np.testing.assert_array_equal(again._q.packed().numpy(), t8._q.packed().numpy())
+    t4 = Int4Tensor.from_hp(wt, 128)
+    q4, s4, z4 = oracle.quantize_q4(w, 128)
+    np.testing.assert_array_equal(t4._q.packed().numpy().view(np.uint32), q4)
+    np.testing.assert_array_equal(bits(t4.scale.numpy()), bits(s4))
+    np.testing.assert_array_equal(bits(t4.zero.numpy()), bits(z4))
+    lv = oracle.unpack_q4(t4._q.packed().numpy().view(np.uint32), 4096).reshape(14336, 32, 128)
+    assert (lv.min(axis=2) == 0).all() and (lv.max(axis=2) == 15).all()
