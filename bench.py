@@ -1,0 +1,335 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized-linear decode path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Workload (config.workload): the int4 group-128 decode linear of a Llama-8B MLP
+up-projection — x float32 [1, 4096] ~ N(0, 1), W float32 [14336, 4096]
+~ N(0, 0.02) quantized asymmetric uint4 per group of 128 — seeded synthetic
+data standing in for a checkpoint. One STEP is one pass of x through R = 16
+distinct device copies of the packed weight (528 MB, four times the 126 MB L2,
+so every call streams its weight from HBM): 16 dequant-fused GEMV launches,
+replayed as one CUDA graph the way a captured decode step runs.
+
+metric / value : algorithmic GB/s = (packed weight + scales + zero points +
+                 x + y bytes, each counted once) x launches / device time,
+                 inputs resident in HBM, timed with CUDA events on the
+                 launching stream, max over ranks. N ranks each stream their
+                 own copies (weak scaling, no collective on the data path).
+e2e            : the same pass through the public API with HOST buffers: per
+                 step x is copied from pinned host memory, the graph replayed,
+                 all R outputs copied back and waited for (host wall clock).
+roofline       : achieved = algorithmic bytes per launch / average launch
+                 duration over the timed region; peak = measured HBM copy
+                 bandwidth from MEASURED_PEAKS.json (else the fallback 6650).
+cpu_baseline   : the CPU oracle (a port of the reference's shader arithmetic)
+                 timed on the host cores on a bounded sample of the workload.
+
+--impl reference times that CPU implementation alone, on the same metric.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+N_OUT, K_IN, GROUP, SIGMA, SEED = 14336, 4096, 128, 0.02, 1
+REPLICAS = 16
+METRIC, UNIT = "int4_g128_decode_linear_algorithmic_bandwidth", "GB/s"
+
+
+def algorithmic_bytes(m: int, n: int = N_OUT, k: int = K_IN, group: int = GROUP) -> int:
+    words = -(-k // 32) * 4
+    groups = -(-k // group)
+    return n * words * 4 + 2 * n * groups * 4 + m * k * 4 + m * n * 4
+
+
+def make_inputs(m: int):
+    rng = np.random.default_rng(SEED)
+    x = rng.standard_normal((16, K_IN)).astype(np.float32)[:m]
+    w = (rng.standard_normal((N_OUT, K_IN)) * SIGMA).astype(np.float32)
+    return x, w
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        return float(json.load(open(path))["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clock and throttle-reason samples taken while the GPU is under load."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int) -> None:
+        self.index, self.proc, self.path = index, None, f"/tmp/gq_clocks_{os.getpid()}.csv"
+
+    def start(self) -> None:
+        try:
+            self.out = open(self.path, "w")
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.index)], stdout=self.out, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        self.out.close()
+        sm, mx, reasons = [], [], set()
+        for line in open(self.path):
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                mx.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        try:
+            os.remove(self.path)
+        except OSError:
+            pass
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def cpu_run(seconds: float, m: int = 1):
+    """The oracle's int4 linear on the full weight, all host threads, repeated
+    for about `seconds`: returns (GB/s, calls, threads)."""
+    import oracle
+    x, w = make_inputs(m)
+    q, scale, zero = oracle.quantize_q4(w, GROUP)
+    oracle.linear_q4(x, q, scale, zero, None, K_IN, GROUP)  # warm
+    calls, t0 = 0, time.perf_counter()
+    while True:
+        oracle.linear_q4(x, q, scale, zero, None, K_IN, GROUP)
+        calls += 1
+        dt = time.perf_counter() - t0
+        if dt >= seconds:
+            break
+    return algorithmic_bytes(m) * calls / dt / 1e9, calls, oracle.threads(), dt
+
+
+def run_reference(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import oracle
+    x, w = make_inputs(1)
+    q, scale, zero = oracle.quantize_q4(w, GROUP)
+    for _ in range(max(args.warmup, 1)):
+        oracle.linear_q4(x, q, scale, zero, None, K_IN, GROUP)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        oracle.linear_q4(x, q, scale, zero, None, K_IN, GROUP)
+    dt = time.perf_counter() - t0
+    value = algorithmic_bytes(1) * args.steps / dt / 1e9
+    sample = f"each step = one M=1 call over one copy of the packed weight (1/{REPLICAS} of a GPU step), {oracle.threads()} OpenMP threads"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(1),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": oracle.threads(), "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "the reference's own CPU route is Vulkan on a software renderer, unavailable on this box; this is the CPU port of its shader arithmetic (oracle/oracle.c)",
+    }))
+
+
+def workload_config(n_gpus: int) -> dict:
+    return {"workload": f"C2: int4 group-{GROUP} decode linear, x[1,{K_IN}] . W[{N_OUT},{K_IN}]^T, {REPLICAS} weight copies per step "
+                        f"({REPLICAS * algorithmic_bytes(1) / 1e6:.0f} MB > L2, so inputs larger than L2: no flush needed)",
+            "m": 1, "n": N_OUT, "k": K_IN, "group_size": GROUP, "replicas": REPLICAS, "launch": "one CUDA graph of 16 GEMV nodes per step",
+            "parallelism": f"{n_gpus} independent rank(s), each streaming its own weight copies"}
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours")
+    ap.add_argument("--cpu-seconds", type=float, default=10.0)
+    ap.add_argument("--no-extras", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+        return
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    os.environ.setdefault("GQ_DEVICE", str(local))
+
+    import torch
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    import grilly2_b200 as g  # noqa: F401
+    from grilly2_b200 import _C, _lib
+    import ctypes
+
+    lib, ctx = _lib.load(), _C.context()
+    sp = ctypes.c_void_p()
+    _lib.check(lib.gq_stream(ctx, ctypes.byref(sp)))
+    stream = torch.cuda.ExternalStream(sp.value, device=torch.device("cuda", local))
+
+    x_np, w_np = make_inputs(16)
+    base = _C.Int4Weight.quantize(_C.Tensor.from_numpy(w_np), GROUP)
+
+    def replica():
+        q = _C.Tensor.empty(base.packed().shape, "int32", persistent=True)
+        s = _C.Tensor.empty(base.scale().shape, "float32", persistent=True)
+        z = _C.Tensor.empty(base.zero().shape, "float32", persistent=True)
+        q.copy_(base.packed()), s.copy_(base.scale()), z.copy_(base.zero())
+        return _C.Int4Weight(q, s, z, base.shape, GROUP)
+
+    weights = [replica() for _ in range(REPLICAS)]
+
+    def capture(m: int, ws):
+        x = _C.Tensor.from_numpy(x_np[:m])
+        _C.begin_capture()
+        ys = [w.linear(x) for w in ws]
+        return x, ys, _C.end_capture()
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+        _C.synchronize()
+
+    def timed(graph, steps: int, warmup: int) -> float:
+        """Device milliseconds for `steps` replays, max over ranks."""
+        for _ in range(warmup):
+            graph.replay()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(steps):
+            graph.replay()
+        e1.record(stream)
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if dist is not None:
+            t = torch.tensor([ms], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    peak, peak_kind = measured_peak()
+    sampler = ClockSampler(local)
+    x1, ys1, g1 = capture(1, weights)
+    launches_before = _C.submit_stats()["graph_nodes_replayed"]
+    if rank == 0:
+        sampler.start()
+    ms = timed(g1, args.steps, max(args.warmup, 3))
+    clocks = sampler.stop() if rank == 0 else None
+    gpu_launches = (_C.submit_stats()["graph_nodes_replayed"] - launches_before) - max(args.warmup, 3) * REPLICAS
+    per_launch_us = ms * 1e3 / (args.steps * REPLICAS)
+    bytes_launch = algorithmic_bytes(1)
+    achieved = bytes_launch / (per_launch_us * 1e-6) / 1e9
+    value = achieved * world
+
+    # end to end with host buffers: pinned x in, every y out, waited for each step
+    hx, hy = ctypes.c_void_p(), ctypes.c_void_p()
+    y_bytes = N_OUT * 4
+    _lib.check(lib.gq_host_alloc(ctx, K_IN * 4, ctypes.byref(hx)))
+    _lib.check(lib.gq_host_alloc(ctx, REPLICAS * y_bytes, ctypes.byref(hy)))
+    ctypes.memmove(hx.value, x_np[:1].ctypes.data, K_IN * 4)
+
+    def e2e_step():
+        _lib.check(lib.gq_upload_async(ctx, x1.storage.handle, 0, hx, K_IN * 4))
+        g1.replay()
+        for r, y in enumerate(ys1):
+            _lib.check(lib.gq_download_async(ctx, y.storage.handle, 0, hy.value + r * y_bytes, y_bytes))
+        _C.synchronize()
+
+    e2e_steps = min(args.steps, 500)
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e2e_s = time.perf_counter() - t0
+    if dist is not None:
+        t = torch.tensor([e2e_s], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    e2e_value = bytes_launch * REPLICAS * e2e_steps / e2e_s / 1e9 * world
+    host_y = np.ctypeslib.as_array((ctypes.c_float * (REPLICAS * N_OUT)).from_address(hy.value)).reshape(REPLICAS, N_OUT)
+    assert np.array_equal(host_y[0], host_y[-1]) and np.isfinite(host_y).all(), "replicas disagree"
+
+    extras = {}
+    if not args.no_extras:
+        steps2 = max(args.steps // 4, 10)
+        for m in (4, 16):
+            _, _, gm = capture(m, weights)
+            t = timed(gm, steps2, 3) * 1e3 / (steps2 * REPLICAS)
+            extras[f"m{m}_us_per_launch"] = t
+            extras[f"m{m}_GBps"] = algorithmic_bytes(m) / (t * 1e-6) / 1e9
+            extras[f"m{m}_frac_of_measured_hbm"] = extras[f"m{m}_GBps"] / peak
+        _, _, ghot = capture(1, [weights[0]] * REPLICAS)
+        t = timed(ghot, steps2, 3) * 1e3 / (steps2 * REPLICAS)
+        extras["m1_l2_hot_us_per_launch"] = t
+        extras["m1_l2_hot_GBps"] = bytes_launch / (t * 1e-6) / 1e9
+        extras["weight_only_GBps"] = base.nbytes / (per_launch_us * 1e-6) / 1e9  # the reference's own convention
+        extras["frac_of_nominal_8TBps"] = achieved / 8000.0
+
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
+    cpu = None
+    if world == 1 and args.cpu_seconds > 0:
+        gbps, calls, threads, dt = cpu_run(args.cpu_seconds)
+        cpu = {"value": gbps, "unit": UNIT, "cores": threads, "kind": "port",
+               "sample": f"{calls} M=1 calls over one copy of the packed weight in {dt:.1f} s ({calls / REPLICAS:.2f} GPU steps)"}
+
+    print(json.dumps({
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic", "config": workload_config(world),
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": None, "peak_kind": peak_kind, "kernel": "gemv_q4_kernel<1,4,true>",
+                     "algorithmic_bytes_per_launch": bytes_launch, "us_per_launch": per_launch_us},
+        "cpu_baseline": cpu,
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": K_IN * 4, "d2h_bytes_per_step": REPLICAS * y_bytes,
+                "steps": e2e_steps, "ms_per_step": e2e_s / e2e_steps * 1e3},
+        "gpu_launches": int(gpu_launches), "clocks": clocks, "extras": extras,
+    }))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -172,9 +172,9 @@ def test_refusals(g):
 
 def test_full_size_quantizers_by_properties(g):
     """At the benchmark's sizes (14336 x 4096) the oracle still finishes in
-    seconds, so compare outright, then check two size-independent properties:
-    re-quantizing the dequantized int8 weight is idempotent, and int4 levels
-    of every full group span 0 and 15."""
+    seconds, so compare outright (also on the dequantized weight fed back in),
+    then check a size-independent property: the int4 levels of every full
+    group span 0 and 15."""
     from grilly2_b200.infer.quantization import Int4Tensor, Int8Tensor
     w = (np.random.default_rng(1).standard_normal((14336, 4096)) * 0.02).astype(np.float32)
     wt = g.from_numpy(w)
@@ -182,8 +182,9 @@ def test_full_size_quantizers_by_properties(g):
     q, scale = oracle.quantize_q8(w)
     np.testing.assert_array_equal(t8._q.packed().numpy().view(np.uint32), q)
     np.testing.assert_array_equal(bits(t8.scale.numpy()), bits(scale))
-    again = Int8Tensor.from_hp(t8.dequantize())
-    np.testing.assert_array_equal(again._q.packed().numpy(), t8._q.packed().numpy())
+    deq = t8.dequantize()
+    again = Int8Tensor.from_hp(deq)
+    np.testing.assert_array_equal(again._q.packed().numpy().view(np.uint32), oracle.quantize_q8(deq.numpy())[0])
     t4 = Int4Tensor.from_hp(wt, 128)
     q4, s4, z4 = oracle.quantize_q4(w, 128)
     np.testing.assert_array_equal(t4._q.packed().numpy().view(np.uint32), q4)
