@@ -214,10 +214,10 @@ def main() -> None:
 
     weights = [replica() for _ in range(REPLICAS)]
 
-    def capture(m: int, ws):
+    def capture(m: int, ws, kernel=_lib.KERNEL_AUTO):
         x = _C.Tensor.from_numpy(x_np[:m])
         _C.begin_capture()
-        ys = [w.linear(x) for w in ws]
+        ys = [w.linear(x, None, kernel) for w in ws]
         return x, ys, _C.end_capture()
 
     def barrier():
@@ -301,6 +301,9 @@ def main() -> None:
         t = timed(ghot, steps2, 3) * 1e3 / (steps2 * REPLICAS)
         extras["m1_l2_hot_us_per_launch"] = t
         extras["m1_l2_hot_GBps"] = bytes_launch / (t * 1e-6) / 1e9
+        _, _, gexact = capture(1, weights, _lib.KERNEL_GEMV)
+        t = timed(gexact, max(steps2 // 4, 5), 3) * 1e3 / (max(steps2 // 4, 5) * REPLICAS)
+        extras["m1_reference_order_float_kernel_us_per_launch"] = t
         extras["weight_only_GBps"] = base.nbytes / (per_launch_us * 1e-6) / 1e9  # the reference's own convention
         extras["frac_of_nominal_8TBps"] = achieved / 8000.0
 
@@ -320,7 +323,7 @@ def main() -> None:
         "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic", "config": workload_config(world),
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": None, "peak_kind": peak_kind, "kernel": "gemv_q4_kernel<1,4,true>",
+                     "traffic": None, "peak_kind": peak_kind, "kernel": "gemv_q4_dp4a_kernel<1,4,true>",
                      "algorithmic_bytes_per_launch": bytes_launch, "us_per_launch": per_launch_us},
         "cpu_baseline": cpu,
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": K_IN * 4, "d2h_bytes_per_step": REPLICAS * y_bytes,

@@ -2,10 +2,12 @@
 same seeded inputs, through the C ABI.
 
 Tolerances, written here as the tests state them:
- * against the oracle's float32 evaluation in the reference shader's order:
-   EQUAL (the GEMV reproduces that order), and in any case
+ * GQ_KERNEL_GEMV (float32, the reference shader's summation order) against
+   the oracle's float32 evaluation in that order: EQUAL;
+ * GQ_KERNEL_DP4A (the fast path AUTO picks: exact integer dot products on
+   fixed-point digit planes of x) against the same oracle:
    max|y - y_ref| / max|y_ref| <= 1e-5;
- * against float64: the reference's own bound
+ * both against float64: the reference's own bound
    (crates/grilly-infer/tests/quant.rs:136-160, quant4.rs:170-196).
 """
 import numpy as np
@@ -42,13 +44,18 @@ def test_int8_linear(g, m, n, k, with_bias):
     b = oracle.xorshift_data(n, 99, -0.5, 0.5) if with_bias else None
     t = Int8Tensor.from_hp(g.from_numpy(w))
     q, scale = oracle.quantize_q8(w)
-    y = t._q.linear(g.from_numpy(x)._t, None if b is None else g.from_numpy(b)._t, _lib.KERNEL_GEMV).numpy()
+    xt, bt = g.from_numpy(x)._t, None if b is None else g.from_numpy(b)._t
     ref = oracle.linear_q8(x, q, scale, b, k)
-    assert rel(y, ref) <= TOL
-    np.testing.assert_array_equal(y, ref)  # same summation order as the reference's decode shader
     want, mag = oracle.linear_q8_f64(x, q, scale, b, k)
     terms = 16 * -(-(-(-k // 16)) // 64)
-    assert (np.abs(y - want) <= (terms + 8) * 2.0 ** -24 * mag + np.finfo(np.float64).tiny).all()
+    bound = (terms + 8) * 2.0 ** -24 * mag + np.finfo(np.float64).tiny
+    y = t._q.linear(xt, bt, _lib.KERNEL_GEMV).numpy()
+    np.testing.assert_array_equal(y, ref)  # same summation order as the reference's decode shader
+    assert (np.abs(y - want) <= bound).all()
+    for kernel in (_lib.KERNEL_DP4A, _lib.KERNEL_AUTO):
+        y = t._q.linear(xt, bt, kernel).numpy()
+        assert rel(y, ref) <= TOL
+        assert (np.abs(y - want) <= bound).all()
 
 
 INT4_SHAPES = [(1, 1, 32, 32), (1, 5, 128, 128), (3, 4, 130, 128), (8, 7, 256, 64), (2, 64, 896, 128),
@@ -65,12 +72,17 @@ def test_int4_linear(g, m, n, k, group, with_bias):
     b = oracle.xorshift_data(n, 99, -0.5, 0.5, int4_form=True) if with_bias else None
     t = Int4Tensor.from_hp(g.from_numpy(w), group)
     q, scale, zero = oracle.quantize_q4(w, group)
-    y = t._q.linear(g.from_numpy(x)._t, None if b is None else g.from_numpy(b)._t, _lib.KERNEL_GEMV).numpy()
+    xt, bt = g.from_numpy(x)._t, None if b is None else g.from_numpy(b)._t
     ref = oracle.linear_q4(x, q, scale, zero, b, k, group)  # x at offset 0: vec4 iff k % 4 == 0
-    assert rel(y, ref) <= TOL
-    np.testing.assert_array_equal(y, ref)
     want, mag = oracle.linear_q4_f64(x, q, scale, zero, b, k, group)
-    assert (np.abs(y - want) <= (-(-k // 64) + 14) * 2.0 ** -24 * mag + np.finfo(np.float64).tiny).all()
+    bound = (-(-k // 64) + 14) * 2.0 ** -24 * mag + np.finfo(np.float64).tiny
+    y = t._q.linear(xt, bt, _lib.KERNEL_GEMV).numpy()
+    np.testing.assert_array_equal(y, ref)
+    assert (np.abs(y - want) <= bound).all()
+    for kernel in (_lib.KERNEL_DP4A, _lib.KERNEL_AUTO):
+        y = t._q.linear(xt, bt, kernel).numpy()
+        assert rel(y, ref) <= TOL
+        assert (np.abs(y - want) <= bound).all()
 
 
 @pytest.mark.parametrize("x_off", [1, 2, 4])
@@ -78,7 +90,7 @@ def test_x_and_bias_at_element_offsets(g, x_off):
     """x may start at any element (crates/grilly-core/src/kernel.rs:26-36);
     off a multiple of four the scalar path runs, whose int4 `sum` order is the
     reference's scalar one (g2-linear-q4.glsl:80-86)."""
-    from grilly2_b200 import _C
+    from grilly2_b200 import _C, _lib
     rng = np.random.default_rng(x_off)
     m, n, k = 3, 21, 256
     w = rng.standard_normal((n, k)).astype(np.float32)
@@ -89,11 +101,14 @@ def test_x_and_bias_at_element_offsets(g, x_off):
     x, b = flat[x_off:].reshape(m, k), bflat[5:]
     w8 = _C.Int8Weight.quantize(_C.Tensor.from_numpy(w))
     q, scale = oracle.quantize_q8(w)
-    np.testing.assert_array_equal(w8.linear(xs, bs).numpy(), oracle.linear_q8(x, q, scale, b, k))
+    ref8 = oracle.linear_q8(x, q, scale, b, k)
+    np.testing.assert_array_equal(w8.linear(xs, bs, _lib.KERNEL_GEMV).numpy(), ref8)
+    assert rel(w8.linear(xs, bs, _lib.KERNEL_DP4A).numpy(), ref8) <= TOL
     w4 = _C.Int4Weight.quantize(_C.Tensor.from_numpy(w), 64)
     q4, s4, z4 = oracle.quantize_q4(w, 64)
     ref = oracle.linear_q4(x, q4, s4, z4, b, k, 64, x_vec4=(x_off % 4 == 0))
-    np.testing.assert_array_equal(w4.linear(xs, bs).numpy(), ref)
+    np.testing.assert_array_equal(w4.linear(xs, bs, _lib.KERNEL_GEMV).numpy(), ref)
+    assert rel(w4.linear(xs, bs, _lib.KERNEL_DP4A).numpy(), ref) <= TOL
 
 
 def test_leading_dims_empty_and_refusals(g):
@@ -136,6 +151,7 @@ def test_benchmark_configs_full_size(g, config):
     """The benchmark's own shapes and seeds. The oracle finishes these in
     seconds, so the comparison is outright; linearity in x is checked on top
     as a size-independent property."""
+    from grilly2_b200 import _lib
     from grilly2_b200.infer.quantization import Int4Tensor, Int8Tensor
     import grilly2_b200.nn.functional as F
     if config == "c1":
@@ -156,12 +172,42 @@ def test_benchmark_configs_full_size(g, config):
         np.testing.assert_array_equal(t._q.packed().numpy().view(np.uint32), q)
     for m in ms:
         xm = x[:m]
-        y = F.linear(g.from_numpy(xm), t).numpy()
         if config != "c1":
             ref = oracle.linear_q4(xm, q, scale, zero, None, xm.shape[1], 128)
+        y = F.linear(g.from_numpy(xm), t).numpy()  # AUTO: the fast path
         assert rel(y, ref) <= TOL
-        np.testing.assert_array_equal(y, ref)
+        np.testing.assert_array_equal(t._q.linear(g.from_numpy(xm)._t, None, _lib.KERNEL_GEMV).numpy(), ref)
     # linearity: f(2x) == 2 f(x) exactly (scaling by two is exact in binary floating point)
     y1 = F.linear(g.from_numpy(x[:1]), t).numpy()
     y2 = F.linear(g.from_numpy(2 * x[:1]), t).numpy()
     np.testing.assert_array_equal(y2, 2 * y1)
+
+
+def test_dp4a_digit_planes_on_hard_inputs(g):
+    """The fixed-point copy of x must stay exact enough where float ranges are
+    wide: per-vector outliers (1e4 x the rest), tiny and huge magnitudes,
+    exact zeros, negative zero. Non-finite x makes the affected outputs NaN."""
+    from grilly2_b200 import _C, _lib
+    rng = np.random.default_rng(12)
+    n, k = 50, 1024
+    w = rng.standard_normal((n, k)).astype(np.float32)
+    x = rng.standard_normal((4, k)).astype(np.float32)
+    x[0, ::97] *= 1e4
+    x[1] *= 1e-30
+    x[2] *= 1e30
+    x[3, :512] = 0.0
+    x[3, 600] = -0.0
+    w8 = _C.Int8Weight.quantize(_C.Tensor.from_numpy(w))
+    w4 = _C.Int4Weight.quantize(_C.Tensor.from_numpy(w), 128)
+    q, scale = oracle.quantize_q8(w)
+    q4, s4, z4 = oracle.quantize_q4(w, 128)
+    for r in range(4):
+        xr = x[r:r + 1]
+        xt = _C.Tensor.from_numpy(xr)
+        assert rel(w8.linear(xt, None, _lib.KERNEL_DP4A).numpy(), oracle.linear_q8_f64(xr, q, scale, None, k)[0]) <= TOL
+        assert rel(w4.linear(xt, None, _lib.KERNEL_DP4A).numpy(), oracle.linear_q4_f64(xr, q4, s4, z4, None, k, 128)[0]) <= TOL
+    xbad = x[:1].copy()
+    xbad[0, 5] = np.inf
+    assert np.isnan(w8.linear(_C.Tensor.from_numpy(xbad), None, _lib.KERNEL_DP4A).numpy()).all()
+    xbad[0, 5] = np.nan
+    assert np.isnan(w4.linear(_C.Tensor.from_numpy(xbad), None, _lib.KERNEL_DP4A).numpy()).all()
