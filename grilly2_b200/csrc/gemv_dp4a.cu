@@ -386,6 +386,178 @@ __global__ void __launch_bounds__(kWarpsD * 32) gemv_q8_dp4a_kernel(const float*
 
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
+// ── one row of x, balanced over the whole GPU ─────────────────────────────
+// The decode case proper (a single row of x). One CTA per SM, each owning a
+// contiguous range of output features sized to within one feature of the
+// others, so the GPU runs a single wave with no tail and x is converted once
+// per SM. Inside a CTA each of the 16 warps takes `base` whole features; the
+// CTA's remaining (< 16) features are cut into blocks of 32 vectors that are
+// dealt round-robin to the warps and summed through shared memory in a fixed
+// order, which is also what keeps every warp busy when the layer has few
+// output features. Weight vectors for the next step are requested while the
+// current ones are multiplied, two steps deep.
+static constexpr int kBalWarps = 16;
+
+template <bool IS4>
+struct DigitDot;
+
+template <>
+struct DigitDot<true> {  // int4: 8 chunks per vector (even/odd nibbles of 4 words)
+    static constexpr int kChunks = 8;
+    __device__ __forceinline__ static void run(const uint4& w, const uint4 (&xr)[8], int (&D)[4]) {
+        const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint4 xe = xr[2 * i], xo = xr[2 * i + 1];
+            const uint32_t e = ws[i] & 0x0F0F0F0Fu, o = (ws[i] >> 4) & 0x0F0F0F0Fu;
+            D[0] = dp4a_ss(e, xe.x, D[0]);
+            D[1] = dp4a_ss(e, xe.y, D[1]);
+            D[2] = dp4a_ss(e, xe.z, D[2]);
+            D[3] = dp4a_ss(e, xe.w, D[3]);
+            D[0] = dp4a_ss(o, xo.x, D[0]);
+            D[1] = dp4a_ss(o, xo.y, D[1]);
+            D[2] = dp4a_ss(o, xo.z, D[2]);
+            D[3] = dp4a_ss(o, xo.w, D[3]);
+        }
+    }
+};
+
+template <>
+struct DigitDot<false> {  // int8: 4 chunks per vector (one per word)
+    static constexpr int kChunks = 4;
+    __device__ __forceinline__ static void run(const uint4& w, const uint4 (&xr)[4], int (&D)[4]) {
+        const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint4 xw = xr[i];
+            D[0] = dp4a_ss(ws[i], xw.x, D[0]);
+            D[1] = dp4a_ss(ws[i], xw.y, D[1]);
+            D[2] = dp4a_ss(ws[i], xw.z, D[2]);
+            D[3] = dp4a_ss(ws[i], xw.w, D[3]);
+        }
+    }
+};
+
+template <bool IS4, int C, bool XVEC>
+__global__ void __launch_bounds__(kBalWarps * 32, 1)
+    gemv_dp4a_balanced_kernel(const float* __restrict__ x, const uint4* __restrict__ q, const float* __restrict__ scale,
+                              const float* __restrict__ zero, const float* __restrict__ bias, float* __restrict__ y,
+                              uint32_t k, uint32_t n, uint32_t vecs, uint32_t group, uint32_t groups, uint32_t ublocks) {
+    extern __shared__ __align__(16) uint32_t smem_bal[];
+    constexpr int kWordsPerVec = DigitDot<IS4>::kChunks * 4;
+    const uint4* xd4 = reinterpret_cast<const uint4*>(smem_bal);
+    float* xinv = reinterpret_cast<float*>(smem_bal + kWordsPerVec * vecs);
+    float* xsum = xinv + vecs;                    // int4 only
+    float* partial = xsum + (IS4 ? vecs : 0);     // kBalWarps * ublocks floats
+
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    // this CTA's features [cb, cb + ncols); the first n % gridDim CTAs take one more
+    const uint32_t per = n / gridDim.x, extra = n % gridDim.x;
+    const uint32_t cb = blockIdx.x * per + min(blockIdx.x, extra), ncols = per + (blockIdx.x < extra ? 1u : 0u);
+    const uint32_t base = ncols / kBalWarps, rem = ncols % kBalWarps;
+    const uint32_t wcol = cb + warp * base;  // this warp's whole features [wcol, wcol + base)
+    const uint32_t steps = ((base + C - 1) / C) * ublocks;  // (chunk of C features) x (block of 32 vectors)
+
+    auto load_step = [&](uint32_t step, uint4 (&w)[C]) {
+        const uint32_t c0 = (step / ublocks) * C, v = (step % ublocks) * 32 + lane;
+#pragma unroll
+        for (int c = 0; c < C; ++c)
+            w[c] = (step < steps && c0 + c < base && v < vecs) ? ldg_stream4(q + (size_t)(wcol + c0 + c) * vecs + v)
+                                                               : make_uint4(0, 0, 0, 0);
+    };
+
+    // the first two steps' weights are requested before x is converted
+    uint4 w0[C], w1[C];
+    load_step(0, w0);
+    load_step(1, w1);
+
+    if (IS4)
+        prepare_x_q4<XVEC>(x, k, vecs, smem_bal, xinv, xsum);
+    else
+        prepare_x_q8<XVEC>(x, k, vecs, smem_bal, xinv);
+    __syncthreads();
+
+    float acc[C];
+#pragma unroll
+    for (int c = 0; c < C; ++c) acc[c] = 0.0f;
+
+    auto finish = [&](uint32_t col, float p) {  // lane 0 of the warp that holds a feature's full sum
+        if (IS4) {
+            if (bias) p = __fadd_rn(p, bias[col]);
+        } else {
+            p = __fmul_rn(p, scale[col]);  // the row scale multiplies the finished sum
+            if (bias) p = __fadd_rn(p, bias[col]);
+        }
+        y[col] = p;
+    };
+
+    constexpr int kChunks = DigitDot<IS4>::kChunks;
+    auto load_x = [&](uint32_t v, uint4 (&xr)[kChunks]) {  // one register copy of x's digits serves C features
+#pragma unroll
+        for (int j = 0; j < kChunks; ++j) xr[j] = xd4[j * vecs + v];
+    };
+    auto accumulate = [&](uint32_t col, uint32_t v, const uint4& w, const uint4 (&xr)[kChunks], float& a) {
+        int D[4] = {0, 0, 0, 0};
+        DigitDot<IS4>::run(w, xr, D);
+        const float t = combine_digits(D);
+        if (IS4) {
+            const size_t gi = (size_t)col * groups + (v * 32) / group;
+            const float s = __ldg(scale + gi);
+            const float mn = __fsub_rn(__ldg(zero + gi), __fmul_rn(8.0f, s));  // min = zero - 8 s
+            a = __fmaf_rn(__fmul_rn(s, xinv[v]), t, a);
+            a = __fmaf_rn(mn, xsum[v], a);
+        } else {
+            a = __fmaf_rn(xinv[v], t, a);
+        }
+    };
+
+    for (uint32_t step = 0; step < steps; ++step) {
+        uint4 w2[C];
+        load_step(step + 2, w2);
+        const uint32_t c0 = (step / ublocks) * C, ub = step % ublocks, v = ub * 32 + lane;
+        if (v < vecs) {
+            uint4 xr[kChunks];
+            load_x(v, xr);
+#pragma unroll
+            for (int c = 0; c < C; ++c)
+                if (c0 + c < base) accumulate(wcol + c0 + c, v, w0[c], xr, acc[c]);
+        }
+        if (ub + 1 == ublocks) {  // the chunk's features are complete
+#pragma unroll
+            for (int c = 0; c < C; ++c) {
+                float p = acc[c];
+#pragma unroll
+                for (int s = 16; s > 0; s >>= 1) p += __shfl_xor_sync(0xffffffffu, p, s);
+                if (lane == 0 && c0 + c < base) finish(wcol + c0 + c, p);
+                acc[c] = 0.0f;
+            }
+        }
+#pragma unroll
+        for (int c = 0; c < C; ++c) w0[c] = w1[c], w1[c] = w2[c];
+    }
+
+    // the CTA's leftover features, one (feature, block of 32 vectors) per warp at a time
+    const uint32_t lcol = cb + kBalWarps * base;
+    for (uint32_t idx = warp; idx < rem * ublocks; idx += kBalWarps) {
+        const uint32_t j = idx / ublocks, v = (idx % ublocks) * 32 + lane;
+        float a = 0.0f;
+        if (v < vecs) {
+            uint4 xr[kChunks];
+            load_x(v, xr);
+            accumulate(lcol + j, v, ldg_stream4(q + (size_t)(lcol + j) * vecs + v), xr, a);
+        }
+#pragma unroll
+        for (int s = 16; s > 0; s >>= 1) a += __shfl_xor_sync(0xffffffffu, a, s);
+        if (lane == 0) partial[idx] = a;
+    }
+    __syncthreads();
+    if (threadIdx.x < rem) {
+        float p = 0.0f;
+        for (uint32_t u = 0; u < ublocks; ++u) p += partial[threadIdx.x * ublocks + u];
+        finish(lcol + threadIdx.x, p);
+    }
+}
+
 // Shared memory the digit planes of `rows` rows of x need. The caller falls
 // back to the float kernel when they do not fit.
 size_t dp4a_smem_q4(uint64_t k, int rows) { return (k + 31) / 32 * 36 * 4 * rows; }
@@ -419,8 +591,27 @@ static void run_q8(cudaStream_t s, const float* x, uint64_t m, uint64_t k, const
 }
 
 // Returns false when the shape does not fit (the caller then runs the float kernel).
-bool launch_gemv_q4_dp4a(cudaStream_t s, const float* x, uint64_t m, uint64_t k, const uint32_t* q, const float* scale,
+template <bool IS4>
+static bool run_balanced(cudaStream_t s, int sm_count, const float* x, uint64_t k, const uint32_t* q, const float* scale,
                          const float* zero, const float* bias, uint64_t n, uint64_t group, float* y) {
+    constexpr int C = 4;
+    const uint32_t vecs = (uint32_t)(IS4 ? (k + 31) / 32 : (k + 15) / 16);
+    const uint32_t ublocks = (vecs + 31) / 32;
+    const uint32_t groups = IS4 ? (uint32_t)((k + group - 1) / group) : 0;
+    const size_t smem = ((size_t)vecs * (IS4 ? 34 : 17) + (size_t)kBalWarps * ublocks) * 4;
+    if (smem > kMaxSmem) return false;
+    const uint32_t grid = (uint32_t)(n < (uint64_t)sm_count ? n : (uint64_t)sm_count);
+    const bool xvec = aligned16(x) && k % 4 == 0;
+    auto kernel = xvec ? gemv_dp4a_balanced_kernel<IS4, C, true> : gemv_dp4a_balanced_kernel<IS4, C, false>;
+    if (smem > 48 * 1024) GQ_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kernel<<<grid, kBalWarps * 32, smem, s>>>(x, reinterpret_cast<const uint4*>(q), scale, zero, bias, y, (uint32_t)k, (uint32_t)n,
+                                              vecs, (uint32_t)group, groups, ublocks);
+    return true;
+}
+
+bool launch_gemv_q4_dp4a(cudaStream_t s, int sm_count, const float* x, uint64_t m, uint64_t k, const uint32_t* q, const float* scale,
+                         const float* zero, const float* bias, uint64_t n, uint64_t group, float* y) {
+    if (m == 1 && run_balanced<true>(s, sm_count, x, k, q, scale, zero, bias, n, group, y)) return true;
     if (m >= 3 && dp4a_smem_q4(k, 4) <= kMaxSmem)
         run_q4<4, 2>(s, x, m, k, q, scale, zero, bias, n, group, y);
     else if (m >= 2 && dp4a_smem_q4(k, 2) <= kMaxSmem)
@@ -432,8 +623,9 @@ bool launch_gemv_q4_dp4a(cudaStream_t s, const float* x, uint64_t m, uint64_t k,
     return true;
 }
 
-bool launch_gemv_q8_dp4a(cudaStream_t s, const float* x, uint64_t m, uint64_t k, const uint32_t* q, const float* scale,
+bool launch_gemv_q8_dp4a(cudaStream_t s, int sm_count, const float* x, uint64_t m, uint64_t k, const uint32_t* q, const float* scale,
                          const float* bias, uint64_t n, float* y) {
+    if (m == 1 && run_balanced<false>(s, sm_count, x, k, q, scale, nullptr, bias, n, 32, y)) return true;
     if (m >= 3 && dp4a_smem_q8(k, 4) <= kMaxSmem)
         run_q8<4, 2>(s, x, m, k, q, scale, bias, n, y);
     else if (m >= 2 && dp4a_smem_q8(k, 2) <= kMaxSmem)

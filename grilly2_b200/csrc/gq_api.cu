@@ -486,7 +486,7 @@ int32_t gq_int8_linear(gq_ctx* ctx, gq_buf x, uint64_t x_off, uint64_t m, uint64
         if (kernel == GQ_KERNEL_TENSOR) fail("gq_int8_linear: the tensor-core kernel is not built into this library");
         bool done = false;
         if (kernel != GQ_KERNEL_GEMV) {
-            done = launch_gemv_q8_dp4a(ctx->stream, xp, m, k, qp, sp, bp, n, yp);
+            done = launch_gemv_q8_dp4a(ctx->stream, ctx->prop.multiProcessorCount, xp, m, k, qp, sp, bp, n, yp);
             if (!done && kernel == GQ_KERNEL_DP4A) fail("gq_int8_linear: in_features = %llu is too long for the dp4a kernel's shared-memory digit planes", (unsigned long long)k);
         }
         if (!done) launch_gemv_q8(ctx->stream, ctx->prop.multiProcessorCount, xp, m, k, qp, sp, bp, n, yp);
@@ -548,7 +548,7 @@ int32_t gq_int4_linear(gq_ctx* ctx, gq_buf x, uint64_t x_off, uint64_t m, uint64
         if (kernel == GQ_KERNEL_TENSOR) fail("gq_int4_linear: there is no tensor-core int4 kernel (the reference has none either, crates/grilly-infer/src/quant4.rs:412-413)");
         bool done = false;
         if (kernel != GQ_KERNEL_GEMV) {
-            done = launch_gemv_q4_dp4a(ctx->stream, xp, m, k, qp, sp, zp, bp, n, group, yp);
+            done = launch_gemv_q4_dp4a(ctx->stream, ctx->prop.multiProcessorCount, xp, m, k, qp, sp, zp, bp, n, group, yp);
             if (!done && kernel == GQ_KERNEL_DP4A) fail("gq_int4_linear: in_features = %llu is too long for the dp4a kernel's shared-memory digit planes", (unsigned long long)k);
         }
         if (!done) launch_gemv_q4(ctx->stream, ctx->prop.multiProcessorCount, xp, m, k, qp, sp, zp, bp, n, group, yp);

@@ -40,9 +40,9 @@ struct Buffer {
     bool released = false;
 };
 
-bool launch_gemv_q8_dp4a(cudaStream_t s, const float* x, uint64_t m, uint64_t k, const uint32_t* q, const float* scale,
+bool launch_gemv_q8_dp4a(cudaStream_t s, int sm_count, const float* x, uint64_t m, uint64_t k, const uint32_t* q, const float* scale,
                          const float* bias, uint64_t n, float* y);
-bool launch_gemv_q4_dp4a(cudaStream_t s, const float* x, uint64_t m, uint64_t k, const uint32_t* q, const float* scale,
+bool launch_gemv_q4_dp4a(cudaStream_t s, int sm_count, const float* x, uint64_t m, uint64_t k, const uint32_t* q, const float* scale,
                          const float* zero, const float* bias, uint64_t n, uint64_t group, float* y);
 
 }  // namespace gq
@@ -94,9 +94,9 @@ void launch_gemv_q8(cudaStream_t s, int sm_count, const float* x, uint64_t m, ui
 void launch_gemv_q4(cudaStream_t s, int sm_count, const float* x, uint64_t m, uint64_t k, const uint32_t* q,
                     const float* scale, const float* zero, const float* bias, uint64_t n, uint64_t group, float* y);
 
-bool launch_gemv_q8_dp4a(cudaStream_t s, const float* x, uint64_t m, uint64_t k, const uint32_t* q, const float* scale,
+bool launch_gemv_q8_dp4a(cudaStream_t s, int sm_count, const float* x, uint64_t m, uint64_t k, const uint32_t* q, const float* scale,
                          const float* bias, uint64_t n, float* y);
-bool launch_gemv_q4_dp4a(cudaStream_t s, const float* x, uint64_t m, uint64_t k, const uint32_t* q, const float* scale,
+bool launch_gemv_q4_dp4a(cudaStream_t s, int sm_count, const float* x, uint64_t m, uint64_t k, const uint32_t* q, const float* scale,
                          const float* zero, const float* bias, uint64_t n, uint64_t group, float* y);
 
 }  // namespace gq
