@@ -1,0 +1,361 @@
+// Decode GEMV for one or two rows of x on the warp-level integer tensor
+// instruction (mma.sync m16n8k32, 8-bit operands, int32 accumulate).
+//
+// Same arithmetic as gemv_dp4a.cu: x is held as an exact fixed-point number
+// per block of weights,
+//     x[k] ~= X[k] 2^(e-30),  X = d0 + 256 d1 + 65536 d2 + 2^24 d3  (signed base-256 digits),
+// and the packed weights multiply the four digit planes in exact integer
+// arithmetic. Here the digit planes are the COLUMNS of the MMA's B operand
+// (four per row of x, so two rows fill the eight columns) and sixteen output
+// features are its rows, so one warp instruction performs 16 x 32 x 8
+// multiply-adds: per weight the kernel issues ~0.8 thread instructions — 3/8
+// to split int4 nibbles into bytes, the rest loads and the per-block float32
+// epilogue — against 1.7-3.9 for the dp4a kernel and ~5 for the float one.
+// That is what lets a single row of x run at HBM speed on a B200 (46 int4
+// levels per SM per clock).
+//
+// Mapping. A "block" is 64 bytes of one weight row: four 16-byte vectors, 128
+// int4 levels or 64 int8 values; it is also the block x's exponent is shared
+// over, and for int4 it must lie inside one quantization group (group_size a
+// multiple of 128; other group sizes take the dp4a kernel). Thread (g, t) of a
+// warp, g = lane / 4, t = lane % 4, loads vector t of the block for feature
+// rows g and g + 8 of a 16-row tile — so a warp load covers eight rows x 64
+// contiguous bytes — and word j of those vectors feeds MMA j. The k order
+// inside an MMA is therefore a permutation of the memory order; the digit
+// planes of x are laid out in shared memory in the same permutation, once per
+// CTA, so it costs nothing.
+//
+// Work split. One CTA per SM owns a contiguous range of output features, the
+// ranges differing by at most one feature, taken in panels of 128 rows. The
+// 16 warps of a CTA split K: warp w takes blocks w, w + 16, … of every row in
+// the panel (so the B fragments it loaded for a block serve all the panel's
+// tiles), and the 16 partial sums per output are added through shared memory
+// in a fixed order: the result is deterministic and equal on every replay.
+//
+// Algorithmic bytes per launch: packed weights + scales (+ zero points) + x +
+// y (+ bias), each once. Bound: HBM bandwidth.
+#include "gq_internal.h"
+
+namespace gq {
+
+namespace {
+
+constexpr int kWarps = 16;    // per CTA; they split K
+constexpr int kTiles = 4;     // 16-row tiles a warp keeps in flight per step
+constexpr int kPanel = 128;   // rows a CTA reduces at a time
+
+__device__ __forceinline__ uint4 ldg_stream(const uint4* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+// D(16x8, s32) += A(16x32, u8 row-major) * B(32x8, s8 column-major)
+__device__ __forceinline__ void mma_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mma_s8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// 2^(30-e) and 2^(e-30) for a block whose largest |x| is amax (2^e > amax);
+// (0, 0) for a zero block, (0, NaN) for a non-finite one.
+__device__ __forceinline__ void block_scales(float amax, float& mult, float& inv) {
+    uint32_t b = __float_as_uint(amax) >> 23;
+    if (b == 255) {
+        mult = 0.0f;
+        inv = __uint_as_float(0x7fc00000u);
+        return;
+    }
+    if (amax == 0.0f) {
+        mult = inv = 0.0f;
+        return;
+    }
+    b = max(b, 32u);
+    mult = __uint_as_float((283u - b) << 23);
+    inv = __uint_as_float((b - 29u) << 23);
+}
+
+__device__ __forceinline__ void digits_of(int X, int (&d)[4]) {
+    d[0] = (int)(int8_t)X;
+    X = (X - d[0]) >> 8;
+    d[1] = (int)(int8_t)X;
+    X = (X - d[1]) >> 8;
+    d[2] = (int)(int8_t)X;
+    d[3] = (X - d[2]) >> 8;
+}
+
+__device__ __forceinline__ uint32_t pack4(int a, int b, int c, int d) {
+    return ((uint32_t)a & 0xFFu) | (((uint32_t)b & 0xFFu) << 8) | (((uint32_t)c & 0xFFu) << 16) | ((uint32_t)d << 24);
+}
+
+// One row of x -> B fragments. xb[((blk * 4 + t) * 8 + col) * R + reg], col =
+// 4 * xrow + digit, R = 8 registers per (block, t, col) for int4 (word j,
+// parity p -> 2j + p: the even and the odd nibbles of word j of vector t) and
+// 4 for int8 (word j). One packed word of weights (8 or 4 values of x) per
+// thread; the 16 words of a block sit in 16 adjacent lanes.
+template <bool IS4, bool XVEC>
+__device__ __forceinline__ void prepare_x(const float* __restrict__ xr, uint32_t xrow, uint32_t k, uint32_t nblocks,
+                                          uint32_t* xb, float* xinv, float* xsum) {
+    constexpr int E = IS4 ? 8 : 4;  // values of x per packed word
+    constexpr int R = IS4 ? 8 : 4;
+    for (uint32_t base = 0; base < nblocks * 16; base += blockDim.x) {
+        const uint32_t wd = base + threadIdx.x;
+        const bool live = wd < nblocks * 16;
+        const uint32_t k0 = wd * E, blk = wd >> 4, t = (wd >> 2) & 3, j = wd & 3;
+        float xv[E];
+        if (XVEC) {
+#pragma unroll
+            for (int h = 0; h < E / 4; ++h) {
+                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (live && k0 + 4 * h < k) v = __ldg(reinterpret_cast<const float4*>(xr + k0) + h);
+                xv[4 * h] = v.x, xv[4 * h + 1] = v.y, xv[4 * h + 2] = v.z, xv[4 * h + 3] = v.w;
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < E; ++i) xv[i] = (live && k0 + i < k) ? __ldg(xr + k0 + i) : 0.0f;
+        }
+        float amax = 0.0f, sum = 0.0f;
+        bool bad = false;
+#pragma unroll
+        for (int i = 0; i < E; ++i) {
+            amax = fmaxf(amax, fabsf(xv[i]));
+            bad |= !(fabsf(xv[i]) <= 3.402823466e+38f);
+            sum += xv[i];
+        }
+        if (bad) amax = __uint_as_float(0x7f800000u);
+#pragma unroll
+        for (int o = 1; o < 16; o <<= 1) {
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+            sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        }
+        if (!live) continue;
+        float mult, inv;
+        block_scales(amax, mult, inv);
+        int d[E][4];
+#pragma unroll
+        for (int i = 0; i < E; ++i) digits_of(__float2int_rn(xv[i] * mult), d[i]);
+        uint32_t* dst = xb + ((size_t)(blk * 4 + t) * 8 + 4 * xrow) * R;
+#pragma unroll
+        for (int dg = 0; dg < 4; ++dg) {
+            if (IS4) {
+                dst[dg * R + 2 * j] = pack4(d[0][dg], d[2][dg], d[4][dg], d[6][dg]);
+                dst[dg * R + 2 * j + 1] = pack4(d[1][dg], d[3][dg], d[5][dg], d[7][dg]);
+            } else {
+                dst[dg * R + j] = pack4(d[0][dg], d[1][dg], d[2][dg], d[3][dg]);
+            }
+        }
+        if ((wd & 15) == 0) {
+            xinv[blk] = inv;
+            if (IS4) xsum[blk] = sum;
+        }
+    }
+}
+
+template <bool IS4, int MR, bool XVEC>
+__global__ void __launch_bounds__(kWarps * 32, 1)
+    gemv_imma_kernel(const float* __restrict__ x, const uint4* __restrict__ q, const float* __restrict__ scale,
+                     const float* __restrict__ zero, const float* __restrict__ bias, float* __restrict__ y, uint32_t k,
+                     uint32_t n, uint32_t vecs, uint32_t groups, uint32_t gblocks, uint32_t nblocks) {
+    constexpr int R = IS4 ? 8 : 4;
+    extern __shared__ __align__(16) uint32_t smem_imma[];
+    uint32_t* xb = smem_imma;                                         // nblocks * 4 * 8 * R words
+    float* xinv = reinterpret_cast<float*>(xb + (size_t)nblocks * 32 * R);  // MR * nblocks
+    float* xsum = xinv + MR * nblocks;                                // MR * nblocks (int4)
+    float* partial = xsum + (IS4 ? MR * nblocks : 0);                 // kWarps * kPanel * MR
+
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t g = lane >> 2, t = lane & 3;
+    // this CTA's features [cb, ce); the first n % gridDim CTAs take one more
+    const uint32_t per = n / gridDim.x, extra = n % gridDim.x;
+    const uint32_t cb = blockIdx.x * per + min(blockIdx.x, extra), ce = cb + per + (blockIdx.x < extra ? 1u : 0u);
+    const uint32_t my_blocks = warp < nblocks ? (nblocks - warp + kWarps - 1) / kWarps : 0;  // blocks warp, warp + 16, …
+
+    // weights of rows (row, row + 8) of `tiles` tiles for block `blk`
+    auto load_step = [&](uint32_t row0, uint32_t blk, bool on, uint4 (&w)[kTiles][2]) {
+        const uint32_t v = blk * 4 + t;
+#pragma unroll
+        for (int f = 0; f < kTiles; ++f)
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const uint32_t row = row0 + 16 * f + 8 * h + g;
+                w[f][h] = (on && row < ce && v < vecs) ? ldg_stream(q + (size_t)row * vecs + v) : make_uint4(0, 0, 0, 0);
+            }
+    };
+
+    // Steps of a panel: (chunk of kTiles tiles) x (one of this warp's blocks).
+    // The first step's weights are requested before x is converted.
+    uint4 wa[kTiles][2], wb[kTiles][2];
+    load_step(cb, warp, my_blocks > 0, wa);
+
+#pragma unroll
+    for (int r = 0; r < MR; ++r)
+        prepare_x<IS4, XVEC>(x + (size_t)r * k, r, k, nblocks, xb, xinv + r * nblocks, xsum + r * nblocks);
+    __syncthreads();
+
+    // this thread finishes feature row g (even t) or g + 8 (odd t) of each tile, for row t / 2 of x
+    const uint32_t rowoff = g + 8 * (t & 1), xrow = t >> 1;
+    const bool owner = xrow < MR;
+
+    for (uint32_t p0 = cb; p0 < ce; p0 += kPanel) {
+        const uint32_t prow = min((uint32_t)kPanel, ce - p0);
+        const uint32_t chunks = (prow + 16 * kTiles - 1) / (16 * kTiles);
+        const uint32_t steps = chunks * my_blocks;
+
+        float acc[kTiles];
+        auto compute = [&](uint32_t step, const uint4 (&w)[kTiles][2]) {
+            const uint32_t chunk = step / my_blocks, blk = warp + (step % my_blocks) * kWarps;
+            const uint32_t row0 = p0 + chunk * 16 * kTiles;
+            if (step % my_blocks == 0) {
+#pragma unroll
+                for (int f = 0; f < kTiles; ++f) acc[f] = 0.0f;
+            }
+            // B fragments: this lane's column is g (digit g % 4 of x row g / 4)
+            uint32_t b[R];
+            if (g < 4 * MR) {
+                const uint4* src = reinterpret_cast<const uint4*>(xb + ((size_t)(blk * 4 + t) * 8 + g) * R);
+#pragma unroll
+                for (int i = 0; i < R / 4; ++i) {
+                    const uint4 v = src[i];
+                    b[4 * i] = v.x, b[4 * i + 1] = v.y, b[4 * i + 2] = v.z, b[4 * i + 3] = v.w;
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < R; ++i) b[i] = 0;
+            }
+            const float inv = owner ? xinv[xrow * nblocks + blk] : 0.0f;
+            const float sum = (IS4 && owner) ? xsum[xrow * nblocks + blk] : 0.0f;
+#pragma unroll
+            for (int f = 0; f < kTiles; ++f) {
+                int d[4] = {0, 0, 0, 0};
+                const uint32_t u[4] = {w[f][0].x, w[f][0].y, w[f][0].z, w[f][0].w};  // feature row g
+                const uint32_t l[4] = {w[f][1].x, w[f][1].y, w[f][1].z, w[f][1].w};  // feature row g + 8
+                if (IS4) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        mma_u8s8(d, u[j] & 0x0F0F0F0Fu, l[j] & 0x0F0F0F0Fu, (u[j] >> 4) & 0x0F0F0F0Fu, (l[j] >> 4) & 0x0F0F0F0Fu,
+                                 b[2 * j], b[2 * j + 1]);
+                } else {
+                    mma_s8s8(d, u[0], l[0], u[1], l[1], b[0], b[1]);
+                    mma_s8s8(d, u[2], l[2], u[3], l[3], b[2], b[3]);
+                }
+                // d[0], d[1]: row g, columns 2t, 2t+1; d[2], d[3]: row g + 8. Even t holds digits 0,1
+                // (the low half of X), odd t digits 2,3: swap halves with the neighbour so that each of
+                // the pair ends with one complete row.
+                const int pg = d[0] + (d[1] << 8), ph = d[2] + (d[3] << 8);
+                const int got = __shfl_xor_sync(0xffffffffu, (t & 1) ? pg : ph, 1);
+                const float T = (t & 1) ? __fmaf_rn(65536.0f, (float)ph, (float)got) : __fmaf_rn(65536.0f, (float)got, (float)pg);
+                const uint32_t row = row0 + 16 * f + rowoff;
+                if (owner && row < ce) {
+                    if (IS4) {
+                        const size_t gi = (size_t)row * groups + blk / gblocks;
+                        const float s = __ldg(scale + gi);
+                        const float mn = __fsub_rn(__ldg(zero + gi), __fmul_rn(8.0f, s));  // min = zero - 8 s
+                        acc[f] = __fmaf_rn(__fmul_rn(s, inv), T, acc[f]);
+                        acc[f] = __fmaf_rn(mn, sum, acc[f]);
+                    } else {
+                        acc[f] = __fmaf_rn(inv, T, acc[f]);
+                    }
+                }
+            }
+            if (step % my_blocks == my_blocks - 1 && owner) {  // the chunk is complete for this warp's share of K
+#pragma unroll
+                for (int f = 0; f < kTiles; ++f) {
+                    const uint32_t pr = chunk * 16 * kTiles + 16 * f + rowoff;
+                    if (pr < kPanel) partial[((size_t)warp * kPanel + pr) * MR + xrow] = acc[f];
+                }
+            }
+        };
+        auto next_of = [&](uint32_t step, uint32_t& row0, uint32_t& blk, bool& on) {
+            // the step after `step`: in this panel, or the first of the next panel
+            uint32_t s = step + 1, pp = p0;
+            if (s >= steps) {
+                s = 0;
+                pp = p0 + kPanel;
+            }
+            on = my_blocks > 0 && pp < ce;
+            row0 = pp + (s / max(my_blocks, 1u)) * 16 * kTiles;
+            blk = warp + (s % max(my_blocks, 1u)) * kWarps;
+        };
+
+        for (uint32_t step = 0; step < steps; step += 2) {
+            uint32_t row0, blk;
+            bool on;
+            next_of(step, row0, blk, on);
+            load_step(row0, blk, on, wb);
+            compute(step, wa);
+            if (step + 1 < steps) {
+                next_of(step + 1, row0, blk, on);
+                load_step(row0, blk, on, wa);
+                compute(step + 1, wb);
+            } else {
+#pragma unroll
+                for (int f = 0; f < kTiles; ++f) wa[f][0] = wb[f][0], wa[f][1] = wb[f][1];
+            }
+        }
+        if (steps == 0 || (my_blocks == 0)) {
+            // a warp with no share of K contributes zeros
+            for (uint32_t i = lane; i < kPanel * MR; i += 32) partial[(size_t)warp * kPanel * MR + i] = 0.0f;
+        }
+        __syncthreads();
+        // fixed-order sum of the 16 partials; thread (row, xrow) finishes one output
+        for (uint32_t i = threadIdx.x; i < prow * MR; i += blockDim.x) {
+            const uint32_t pr = i / MR, r = i % MR, col = p0 + pr;
+            float v = 0.0f;
+#pragma unroll
+            for (int w = 0; w < kWarps; ++w) v += partial[((size_t)w * kPanel + pr) * MR + r];
+            if (!IS4) v = __fmul_rn(v, scale[col]);  // the row scale multiplies the finished sum
+            if (bias) v = __fadd_rn(v, bias[col]);
+            y[(size_t)r * n + col] = v;
+        }
+        __syncthreads();
+    }
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+template <bool IS4, int MR>
+bool run(cudaStream_t s, int sm_count, const float* x, uint64_t k, const uint32_t* q, const float* scale, const float* zero,
+         const float* bias, uint64_t n, uint64_t group, float* y) {
+    const uint32_t vecs = (uint32_t)(IS4 ? (k + 31) / 32 : (k + 15) / 16);
+    const uint32_t nblocks = (vecs + 3) / 4;
+    const uint32_t groups = IS4 ? (uint32_t)((k + group - 1) / group) : 0;
+    const uint32_t gblocks = IS4 ? (uint32_t)(group / 128) : 1;
+    constexpr int R = IS4 ? 8 : 4;
+    const size_t smem = ((size_t)nblocks * 32 * R + (size_t)MR * nblocks * (IS4 ? 2 : 1) + (size_t)kWarps * kPanel * MR) * 4;
+    if (smem > 200 * 1024) return false;
+    const uint32_t grid = (uint32_t)(n < (uint64_t)sm_count ? n : (uint64_t)sm_count);
+    const bool xvec = aligned16(x) && k % 4 == 0;
+    auto kernel = xvec ? gemv_imma_kernel<IS4, MR, true> : gemv_imma_kernel<IS4, MR, false>;
+    if (smem > 48 * 1024) GQ_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kernel<<<grid, kWarps * 32, smem, s>>>(x, reinterpret_cast<const uint4*>(q), scale, zero, bias, y, (uint32_t)k, (uint32_t)n, vecs,
+                                           groups, gblocks, nblocks);
+    return true;
+}
+
+}  // namespace
+
+// Returns false when the shape is outside this kernel (more than two rows of
+// x, an int4 group size that is not a multiple of 128, or a row of x too long
+// for shared memory); the caller then takes the dp4a kernel.
+bool launch_gemv_q4_imma(cudaStream_t s, int sm_count, const float* x, uint64_t m, uint64_t k, const uint32_t* q,
+                         const float* scale, const float* zero, const float* bias, uint64_t n, uint64_t group, float* y) {
+    if (group % 128 != 0 || m > 2) return false;
+    return m == 1 ? run<true, 1>(s, sm_count, x, k, q, scale, zero, bias, n, group, y)
+                  : run<true, 2>(s, sm_count, x, k, q, scale, zero, bias, n, group, y);
+}
+
+bool launch_gemv_q8_imma(cudaStream_t s, int sm_count, const float* x, uint64_t m, uint64_t k, const uint32_t* q,
+                         const float* scale, const float* bias, uint64_t n, float* y) {
+    if (m > 2) return false;
+    return m == 1 ? run<false, 1>(s, sm_count, x, k, q, scale, nullptr, bias, n, 0, y)
+                  : run<false, 2>(s, sm_count, x, k, q, scale, nullptr, bias, n, 0, y);
+}
+
+}  // namespace gq

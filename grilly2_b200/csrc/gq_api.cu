@@ -476,7 +476,7 @@ int32_t gq_int8_linear(gq_ctx* ctx, gq_buf x, uint64_t x_off, uint64_t m, uint64
     return guarded([&] {
         Locked l(ctx);
         check_dims("gq_int8_linear", m, k, n);
-        if (kernel < GQ_KERNEL_AUTO || kernel > GQ_KERNEL_DP4A) fail("gq_int8_linear: unknown kernel selector %d", kernel);
+        if (kernel < GQ_KERNEL_AUTO || kernel > GQ_KERNEL_IMMA) fail("gq_int8_linear: unknown kernel selector %d", kernel);
         auto xp = (const float*)view(ctx, x, x_off, m * k, 4, "gq_int8_linear input");
         auto qp = (const uint32_t*)view(ctx, q, 0, n * words8(k), 4, "gq_int8_linear q");
         auto sp = (const float*)view(ctx, scale, 0, n, 4, "gq_int8_linear scale");
@@ -485,12 +485,18 @@ int32_t gq_int8_linear(gq_ctx* ctx, gq_buf x, uint64_t x_off, uint64_t m, uint64
         if (m == 0 || n == 0) return;  // quant.rs:267-269
         if (kernel == GQ_KERNEL_TENSOR) fail("gq_int8_linear: the tensor-core kernel is not built into this library");
         bool done = false;
-        if (kernel != GQ_KERNEL_GEMV) {
+        const char* name = "gemv_q8";
+        if (kernel == GQ_KERNEL_AUTO || kernel == GQ_KERNEL_IMMA) {
+            done = launch_gemv_q8_imma(ctx->stream, ctx->prop.multiProcessorCount, xp, m, k, qp, sp, bp, n, yp);
+            if (done) name = "gemv_q8_imma";
+            if (!done && kernel == GQ_KERNEL_IMMA) fail("gq_int8_linear: the IMMA kernel takes one or two rows of x and rows that fit shared memory (m = %llu, k = %llu)", (unsigned long long)m, (unsigned long long)k);
+        }
+        if (!done && kernel != GQ_KERNEL_GEMV) {
             done = launch_gemv_q8_dp4a(ctx->stream, ctx->prop.multiProcessorCount, xp, m, k, qp, sp, bp, n, yp);
             if (!done && kernel == GQ_KERNEL_DP4A) fail("gq_int8_linear: in_features = %llu is too long for the dp4a kernel's shared-memory digit planes", (unsigned long long)k);
         }
         if (!done) launch_gemv_q8(ctx->stream, ctx->prop.multiProcessorCount, xp, m, k, qp, sp, bp, n, yp);
-        after_launch(ctx, done ? "gemv_q8_dp4a" : "gemv_q8", {x, q, scale, bias, y});
+        after_launch(ctx, name, {x, q, scale, bias, y});
     });
 }
 
@@ -536,7 +542,7 @@ int32_t gq_int4_linear(gq_ctx* ctx, gq_buf x, uint64_t x_off, uint64_t m, uint64
         Locked l(ctx);
         check_dims("gq_int4_linear", m, k, n);
         check_group(group);
-        if (kernel < GQ_KERNEL_AUTO || kernel > GQ_KERNEL_DP4A) fail("gq_int4_linear: unknown kernel selector %d", kernel);
+        if (kernel < GQ_KERNEL_AUTO || kernel > GQ_KERNEL_IMMA) fail("gq_int4_linear: unknown kernel selector %d", kernel);
         uint64_t groups = (k + group - 1) / group;
         auto xp = (const float*)view(ctx, x, x_off, m * k, 4, "gq_int4_linear input");
         auto qp = (const uint32_t*)view(ctx, q, 0, n * words4(k), 4, "gq_int4_linear q");
@@ -547,12 +553,18 @@ int32_t gq_int4_linear(gq_ctx* ctx, gq_buf x, uint64_t x_off, uint64_t m, uint64
         if (m == 0 || n == 0) return;
         if (kernel == GQ_KERNEL_TENSOR) fail("gq_int4_linear: there is no tensor-core int4 kernel (the reference has none either, crates/grilly-infer/src/quant4.rs:412-413)");
         bool done = false;
-        if (kernel != GQ_KERNEL_GEMV) {
+        const char* name = "gemv_q4";
+        if (kernel == GQ_KERNEL_AUTO || kernel == GQ_KERNEL_IMMA) {
+            done = launch_gemv_q4_imma(ctx->stream, ctx->prop.multiProcessorCount, xp, m, k, qp, sp, zp, bp, n, group, yp);
+            if (done) name = "gemv_q4_imma";
+            if (!done && kernel == GQ_KERNEL_IMMA) fail("gq_int4_linear: the IMMA kernel takes one or two rows of x, a group_size that is a multiple of 128 and rows that fit shared memory (m = %llu, k = %llu, group_size = %llu)", (unsigned long long)m, (unsigned long long)k, (unsigned long long)group);
+        }
+        if (!done && kernel != GQ_KERNEL_GEMV) {
             done = launch_gemv_q4_dp4a(ctx->stream, ctx->prop.multiProcessorCount, xp, m, k, qp, sp, zp, bp, n, group, yp);
             if (!done && kernel == GQ_KERNEL_DP4A) fail("gq_int4_linear: in_features = %llu is too long for the dp4a kernel's shared-memory digit planes", (unsigned long long)k);
         }
         if (!done) launch_gemv_q4(ctx->stream, ctx->prop.multiProcessorCount, xp, m, k, qp, sp, zp, bp, n, group, yp);
-        after_launch(ctx, done ? "gemv_q4_dp4a" : "gemv_q4", {x, q, scale, zero, bias, y});
+        after_launch(ctx, name, {x, q, scale, zero, bias, y});
     });
 }
 

@@ -67,8 +67,10 @@ typedef uint64_t gq_buf; /* 0 is never a valid handle */
 #define GQ_KERNEL_GEMV 1   /* dequant-fused float32 GEMV in the reference shader's summation order:
                               bit-identical to the reference's arithmetic, bounded by the FP32 pipes */
 #define GQ_KERNEL_TENSOR 2 /* tcgen05 tensor-core GEMM (tf32), dequantised in shared memory */
-#define GQ_KERNEL_DP4A 3   /* GEMV on integer dot products against exact fixed-point digit planes of x:
-                              the fast decode path, within float32 rounding of GQ_KERNEL_GEMV */
+#define GQ_KERNEL_DP4A 3   /* GEMV on integer dot products (dp4a) against exact fixed-point digit planes of x,
+                              within float32 rounding of GQ_KERNEL_GEMV; any group size, up to 16 rows */
+#define GQ_KERNEL_IMMA 4   /* the same arithmetic on the warp-level int8 tensor instruction: the fast path for
+                              one or two rows of x (int4: group_size a multiple of 128) */
 
 typedef struct gq_caps { /* replaces gc_caps, gc_shim.h:43-50 */
     char device_name[256];
@@ -152,8 +154,9 @@ int32_t gq_int8_quantize(gq_ctx* ctx, gq_buf w, uint64_t w_off, uint64_t rows, u
 /* LINEAR / LINEAR_TILED{x,q,scale,bias,y; m,k,n,vecs,x_off,b_off,has_bias,x_vec4}
  * — quant.rs:25-39,233-304, g2-linear-q8.glsl:33-95, g2-linear-q8-tiled.glsl:41-100.
  * y[m][n] = (sum_k x[m][k] * q[n][k]) * scale[n] (+ bias[n]); bias == 0 means none.
- * AUTO: the dp4a GEMV for few rows; the tensor-core GEMM for many, when the
- * shape meets its alignment rules (k % 4 == 0, x_off % 4 == 0). */
+ * AUTO: IMMA for one or two rows, the dp4a GEMV for a few more; the
+ * tensor-core GEMM for many, when the shape meets its alignment rules
+ * (k % 4 == 0, x_off % 4 == 0). */
 int32_t gq_int8_linear(gq_ctx* ctx, gq_buf x, uint64_t x_off, uint64_t m, uint64_t k, gq_buf q, gq_buf scale,
                        gq_buf bias, uint64_t b_off, uint64_t n, gq_buf y, int32_t kernel);
 

@@ -30,7 +30,7 @@ def rel(y, ref):
     return float(np.abs(y - ref).max() / max(np.abs(ref).max(), np.finfo(np.float32).tiny))
 
 
-INT8_SHAPES = [(1, 1, 1), (1, 5, 17), (3, 4, 16), (8, 7, 33), (9, 6, 100), (20, 13, 896), (1, 64, 4864), (16, 5, 33),
+INT8_SHAPES = [(1, 1, 1), (2, 300, 200), (1, 2500, 64), (2, 151, 4864), (1, 5, 17), (3, 4, 16), (8, 7, 33), (9, 6, 100), (20, 13, 896), (1, 64, 4864), (16, 5, 33),
                (2, 37, 1040), (4, 130, 2048), (1, 4864, 896), (5, 1152, 896)]
 
 
@@ -52,13 +52,15 @@ def test_int8_linear(g, m, n, k, with_bias):
     y = t._q.linear(xt, bt, _lib.KERNEL_GEMV).numpy()
     np.testing.assert_array_equal(y, ref)  # same summation order as the reference's decode shader
     assert (np.abs(y - want) <= bound).all()
-    for kernel in (_lib.KERNEL_DP4A, _lib.KERNEL_AUTO):
+    kernels = [_lib.KERNEL_DP4A, _lib.KERNEL_AUTO] + ([_lib.KERNEL_IMMA] if m <= 2 else [])
+    for kernel in kernels:
         y = t._q.linear(xt, bt, kernel).numpy()
         assert rel(y, ref) <= TOL
         assert (np.abs(y - want) <= bound).all()
 
 
-INT4_SHAPES = [(1, 1, 32, 32), (1, 5, 128, 128), (3, 4, 130, 128), (8, 7, 256, 64), (2, 64, 896, 128),
+INT4_SHAPES = [(1, 1, 32, 32), (2, 300, 384, 128), (1, 2500, 128, 128), (2, 151, 4864, 256), (1, 777, 1000, 128),
+               (1, 5, 128, 128), (3, 4, 130, 128), (8, 7, 256, 64), (2, 64, 896, 128),
                (9, 6, 4864, 128), (4, 33, 4096, 128), (16, 40, 1024, 32), (1, 300, 8192, 128), (5, 7, 70, 32)]
 
 
@@ -79,7 +81,8 @@ def test_int4_linear(g, m, n, k, group, with_bias):
     y = t._q.linear(xt, bt, _lib.KERNEL_GEMV).numpy()
     np.testing.assert_array_equal(y, ref)
     assert (np.abs(y - want) <= bound).all()
-    for kernel in (_lib.KERNEL_DP4A, _lib.KERNEL_AUTO):
+    kernels = [_lib.KERNEL_DP4A, _lib.KERNEL_AUTO] + ([_lib.KERNEL_IMMA] if m <= 2 and group % 128 == 0 else [])
+    for kernel in kernels:
         y = t._q.linear(xt, bt, kernel).numpy()
         assert rel(y, ref) <= TOL
         assert (np.abs(y - want) <= bound).all()
@@ -104,6 +107,7 @@ def test_x_and_bias_at_element_offsets(g, x_off):
     ref8 = oracle.linear_q8(x, q, scale, b, k)
     np.testing.assert_array_equal(w8.linear(xs, bs, _lib.KERNEL_GEMV).numpy(), ref8)
     assert rel(w8.linear(xs, bs, _lib.KERNEL_DP4A).numpy(), ref8) <= TOL
+    assert rel(w8.linear(_C.Tensor(xs.storage, (1, k), "float32", x_off), bs, _lib.KERNEL_IMMA).numpy(), ref8[:1]) <= TOL
     w4 = _C.Int4Weight.quantize(_C.Tensor.from_numpy(w), 64)
     q4, s4, z4 = oracle.quantize_q4(w, 64)
     ref = oracle.linear_q4(x, q4, s4, z4, b, k, 64, x_vec4=(x_off % 4 == 0))
@@ -204,10 +208,13 @@ def test_dp4a_digit_planes_on_hard_inputs(g):
     for r in range(4):
         xr = x[r:r + 1]
         xt = _C.Tensor.from_numpy(xr)
-        assert rel(w8.linear(xt, None, _lib.KERNEL_DP4A).numpy(), oracle.linear_q8_f64(xr, q, scale, None, k)[0]) <= TOL
-        assert rel(w4.linear(xt, None, _lib.KERNEL_DP4A).numpy(), oracle.linear_q4_f64(xr, q4, s4, z4, None, k, 128)[0]) <= TOL
+        for kernel in (_lib.KERNEL_DP4A, _lib.KERNEL_IMMA):
+            assert rel(w8.linear(xt, None, kernel).numpy(), oracle.linear_q8_f64(xr, q, scale, None, k)[0]) <= TOL
+            assert rel(w4.linear(xt, None, kernel).numpy(), oracle.linear_q4_f64(xr, q4, s4, z4, None, k, 128)[0]) <= TOL
     xbad = x[:1].copy()
     xbad[0, 5] = np.inf
-    assert np.isnan(w8.linear(_C.Tensor.from_numpy(xbad), None, _lib.KERNEL_DP4A).numpy()).all()
-    xbad[0, 5] = np.nan
-    assert np.isnan(w4.linear(_C.Tensor.from_numpy(xbad), None, _lib.KERNEL_DP4A).numpy()).all()
+    for kernel in (_lib.KERNEL_DP4A, _lib.KERNEL_IMMA):
+        xbad[0, 5] = np.inf
+        assert np.isnan(w8.linear(_C.Tensor.from_numpy(xbad), None, kernel).numpy()).all()
+        xbad[0, 5] = np.nan
+        assert np.isnan(w4.linear(_C.Tensor.from_numpy(xbad), None, kernel).numpy()).all()
