@@ -164,6 +164,8 @@ __global__ void __launch_bounds__(kWarpsD * 32) gemv_q4_dp4a_kernel(const float*
                                                                      uint32_t group, uint32_t groups) {
     extern __shared__ __align__(16) uint32_t smem_q4[];
     const uint32_t row_words = 36 * vecs;  // per row of x: 32 vecs digit words, vecs scales, vecs sums (+ pad to 16 B)
+    const uint32_t vpg = group >> 5, vpg_shift = __ffs(vpg) - 1;  // vectors per group; a shift when a power of two
+    const bool vpg_pow2 = (vpg & (vpg - 1)) == 0;
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const uint32_t col0 = (blockIdx.x * kWarpsD + warp) * C;
     const uint32_t row0 = blockIdx.y * MR;
@@ -196,7 +198,7 @@ __global__ void __launch_bounds__(kWarpsD * 32) gemv_q4_dp4a_kernel(const float*
         for (int c = 0; c < C; ++c)
             wn[c] = (v + 32 < vecs && col0 + c < n) ? ldg_stream4(q + (size_t)(col0 + c) * vecs + v + 32) : make_uint4(0, 0, 0, 0);
         float sc[C], mn[C];
-        const uint32_t g = (v * 32) / group;
+        const uint32_t g = vpg_pow2 ? v >> vpg_shift : v / vpg;
 #pragma unroll
         for (int c = 0; c < C; ++c) {
             const bool ok = col0 + c < n;
@@ -450,6 +452,8 @@ __global__ void __launch_bounds__(kBalWarps * 32, 1)
     float* xsum = xinv + vecs;                    // int4 only
     float* partial = xsum + (IS4 ? vecs : 0);     // kBalWarps * ublocks floats
 
+    const uint32_t vpg = IS4 ? group >> 5 : 1, vpg_shift = __ffs(vpg) - 1;
+    const bool vpg_pow2 = (vpg & (vpg - 1)) == 0;
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     // this CTA's features [cb, cb + ncols); the first n % gridDim CTAs take one more
     const uint32_t per = n / gridDim.x, extra = n % gridDim.x;
@@ -501,7 +505,7 @@ __global__ void __launch_bounds__(kBalWarps * 32, 1)
         DigitDot<IS4>::run(w, xr, D);
         const float t = combine_digits(D);
         if (IS4) {
-            const size_t gi = (size_t)col * groups + (v * 32) / group;
+            const size_t gi = (size_t)col * groups + (vpg_pow2 ? v >> vpg_shift : v / vpg);
             const float s = __ldg(scale + gi);
             const float mn = __fsub_rn(__ldg(zero + gi), __fmul_rn(8.0f, s));  // min = zero - 8 s
             a = __fmaf_rn(__fmul_rn(s, xinv[v]), t, a);

@@ -162,13 +162,13 @@ template <bool IS4, int MR, bool XVEC>
 __global__ void __launch_bounds__(kWarps * 32, 1)
     gemv_imma_kernel(const float* __restrict__ x, const uint4* __restrict__ q, const float* __restrict__ scale,
                      const float* __restrict__ zero, const float* __restrict__ bias, float* __restrict__ y, uint32_t k,
-                     uint32_t n, uint32_t vecs, uint32_t groups, uint32_t gblocks, uint32_t nblocks) {
+                     uint32_t n, uint32_t vecs, uint32_t groups, uint32_t gshift, uint32_t gblocks, uint32_t nblocks) {
     constexpr int R = IS4 ? 8 : 4;
     extern __shared__ __align__(16) uint32_t smem_imma[];
-    uint32_t* xb = smem_imma;                                         // nblocks * 4 * 8 * R words
+    uint32_t* xb = smem_imma;                                               // nblocks * 4 * 8 * R words
     float* xinv = reinterpret_cast<float*>(xb + (size_t)nblocks * 32 * R);  // MR * nblocks
-    float* xsum = xinv + MR * nblocks;                                // MR * nblocks (int4)
-    float* partial = xsum + (IS4 ? MR * nblocks : 0);                 // kWarps * kPanel * MR
+    float* xsum = xinv + MR * nblocks;                                      // MR * nblocks (int4)
+    float* partial = xsum + (IS4 ? MR * nblocks : 0);                       // kWarps * kPanel * MR
 
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const uint32_t g = lane >> 2, t = lane & 3;
@@ -176,23 +176,31 @@ __global__ void __launch_bounds__(kWarps * 32, 1)
     const uint32_t per = n / gridDim.x, extra = n % gridDim.x;
     const uint32_t cb = blockIdx.x * per + min(blockIdx.x, extra), ce = cb + per + (blockIdx.x < extra ? 1u : 0u);
     const uint32_t my_blocks = warp < nblocks ? (nblocks - warp + kWarps - 1) / kWarps : 0;  // blocks warp, warp + 16, …
+    const size_t half_tile = (size_t)8 * vecs;  // uint4 elements between feature rows r and r + 8
 
-    // weights of rows (row, row + 8) of `tiles` tiles for block `blk`
-    auto load_step = [&](uint32_t row0, uint32_t blk, bool on, uint4 (&w)[kTiles][2]) {
+    // Weights of feature rows row0 + 16 f + 8 h + g (f < kTiles, h < 2), vector 4 blk + t.
+    auto load_step = [&](uint32_t row0, uint32_t blk, uint4 (&w)[kTiles][2]) {
         const uint32_t v = blk * 4 + t;
+        const uint4* p = q + (size_t)(row0 + g) * vecs + v;
+        if (row0 + 16 * kTiles <= ce && v < vecs) {  // the common case: nothing to mask
 #pragma unroll
-        for (int f = 0; f < kTiles; ++f)
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const uint32_t row = row0 + 16 * f + 8 * h + g;
-                w[f][h] = (on && row < ce && v < vecs) ? ldg_stream(q + (size_t)row * vecs + v) : make_uint4(0, 0, 0, 0);
+            for (int f = 0; f < kTiles; ++f) {
+                w[f][0] = ldg_stream(p + (2 * f) * half_tile);
+                w[f][1] = ldg_stream(p + (2 * f + 1) * half_tile);
             }
+        } else {
+            const uint32_t left = (row0 < ce && v < vecs) ? ce - row0 : 0;  // valid rows from row0 on
+#pragma unroll
+            for (int f = 0; f < kTiles; ++f)
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+                    w[f][h] = (16 * f + 8 * h + g < left) ? ldg_stream(p + (2 * f + h) * half_tile) : make_uint4(0, 0, 0, 0);
+        }
     };
 
-    // Steps of a panel: (chunk of kTiles tiles) x (one of this warp's blocks).
     // The first step's weights are requested before x is converted.
     uint4 wa[kTiles][2], wb[kTiles][2];
-    load_step(cb, warp, my_blocks > 0, wa);
+    if (my_blocks) load_step(cb, warp, wa);
 
 #pragma unroll
     for (int r = 0; r < MR; ++r)
@@ -202,109 +210,109 @@ __global__ void __launch_bounds__(kWarps * 32, 1)
     // this thread finishes feature row g (even t) or g + 8 (odd t) of each tile, for row t / 2 of x
     const uint32_t rowoff = g + 8 * (t & 1), xrow = t >> 1;
     const bool owner = xrow < MR;
+    const bool odd = t & 1;
 
+    float acc[kTiles];
+
+    // one (chunk of kTiles tiles) x (block) step: 4 (int4) or 2 (int8) MMAs per tile, then the float32 epilogue
+    auto compute = [&](uint32_t row0, uint32_t blk, const uint4 (&w)[kTiles][2]) {
+        uint32_t b[R];  // B fragments: this lane's column is g (digit g % 4 of x row g / 4)
+        if (g < 4 * MR) {
+            const uint4* src = reinterpret_cast<const uint4*>(xb + ((size_t)(blk * 4 + t) * 8 + g) * R);
+#pragma unroll
+            for (int i = 0; i < R / 4; ++i) {
+                const uint4 v = src[i];
+                b[4 * i] = v.x, b[4 * i + 1] = v.y, b[4 * i + 2] = v.z, b[4 * i + 3] = v.w;
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < R; ++i) b[i] = 0;
+        }
+        const float inv = owner ? xinv[xrow * nblocks + blk] : 0.0f;
+        const float sum = (IS4 && owner) ? xsum[xrow * nblocks + blk] : 0.0f;
+        const uint32_t grp = gblocks == 1 ? blk : (gshift < 32 ? blk >> gshift : blk / gblocks);
+        const uint32_t rbase = row0 + rowoff;
+        const float* sp = scale + (size_t)rbase * groups + grp;
+        const float* zp = zero + (size_t)rbase * groups + grp;
+        const size_t tile_stride = (size_t)16 * groups;
+#pragma unroll
+        for (int f = 0; f < kTiles; ++f) {
+            int d[4] = {0, 0, 0, 0};
+            const uint32_t u[4] = {w[f][0].x, w[f][0].y, w[f][0].z, w[f][0].w};  // feature row g
+            const uint32_t l[4] = {w[f][1].x, w[f][1].y, w[f][1].z, w[f][1].w};  // feature row g + 8
+            if (IS4) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    mma_u8s8(d, u[j] & 0x0F0F0F0Fu, l[j] & 0x0F0F0F0Fu, (u[j] >> 4) & 0x0F0F0F0Fu, (l[j] >> 4) & 0x0F0F0F0Fu,
+                             b[2 * j], b[2 * j + 1]);
+            } else {
+                mma_s8s8(d, u[0], l[0], u[1], l[1], b[0], b[1]);
+                mma_s8s8(d, u[2], l[2], u[3], l[3], b[2], b[3]);
+            }
+            // d[0], d[1]: row g, columns 2t, 2t+1; d[2], d[3]: row g + 8. Even t holds digits 0,1 (the low
+            // half of X), odd t digits 2,3: swap halves with the neighbour so each of the pair ends with
+            // one complete row.
+            const int pg = d[0] + (d[1] << 8), ph = d[2] + (d[3] << 8);
+            const int got = __shfl_xor_sync(0xffffffffu, odd ? pg : ph, 1);
+            const float T = odd ? __fmaf_rn(65536.0f, (float)ph, (float)got) : __fmaf_rn(65536.0f, (float)got, (float)pg);
+            if (owner && rbase + 16 * f < ce) {
+                if (IS4) {
+                    const float s = __ldg(sp + f * tile_stride);
+                    const float mn = __fsub_rn(__ldg(zp + f * tile_stride), __fmul_rn(8.0f, s));  // min = zero - 8 s
+                    acc[f] = __fmaf_rn(__fmul_rn(s, inv), T, acc[f]);
+                    acc[f] = __fmaf_rn(mn, sum, acc[f]);
+                } else {
+                    acc[f] = __fmaf_rn(inv, T, acc[f]);
+                }
+            }
+        }
+    };
+
+    // Steps run chunk-major, this warp's blocks inside; (nrow, nblk) always names the step after the
+    // one being computed — possibly the first of the next panel — whose weights are in flight.
+    uint32_t nrow = cb, nblk = warp;
+    auto advance = [&](uint32_t panel_end) {  // move (nrow, nblk) one step on; returns false past the CTA's last step
+        nblk += kWarps;
+        if (nblk >= nblocks) {
+            nblk = warp;
+            nrow += 16 * kTiles;
+            if (nrow >= panel_end) nrow = panel_end;  // the next panel starts where this one ends
+        }
+        return nrow < ce;
+    };
+
+    bool use_a = true;  // which buffer holds the step about to be computed
     for (uint32_t p0 = cb; p0 < ce; p0 += kPanel) {
-        const uint32_t prow = min((uint32_t)kPanel, ce - p0);
-        const uint32_t chunks = (prow + 16 * kTiles - 1) / (16 * kTiles);
-        const uint32_t steps = chunks * my_blocks;
-
-        float acc[kTiles];
-        auto compute = [&](uint32_t step, const uint4 (&w)[kTiles][2]) {
-            const uint32_t chunk = step / my_blocks, blk = warp + (step % my_blocks) * kWarps;
-            const uint32_t row0 = p0 + chunk * 16 * kTiles;
-            if (step % my_blocks == 0) {
+        const uint32_t pend = min(p0 + (uint32_t)kPanel, ce);
+        if (my_blocks) {
+            for (uint32_t row0 = p0; row0 < pend; row0 += 16 * kTiles) {
 #pragma unroll
                 for (int f = 0; f < kTiles; ++f) acc[f] = 0.0f;
-            }
-            // B fragments: this lane's column is g (digit g % 4 of x row g / 4)
-            uint32_t b[R];
-            if (g < 4 * MR) {
-                const uint4* src = reinterpret_cast<const uint4*>(xb + ((size_t)(blk * 4 + t) * 8 + g) * R);
-#pragma unroll
-                for (int i = 0; i < R / 4; ++i) {
-                    const uint4 v = src[i];
-                    b[4 * i] = v.x, b[4 * i + 1] = v.y, b[4 * i + 2] = v.z, b[4 * i + 3] = v.w;
-                }
-            } else {
-#pragma unroll
-                for (int i = 0; i < R; ++i) b[i] = 0;
-            }
-            const float inv = owner ? xinv[xrow * nblocks + blk] : 0.0f;
-            const float sum = (IS4 && owner) ? xsum[xrow * nblocks + blk] : 0.0f;
-#pragma unroll
-            for (int f = 0; f < kTiles; ++f) {
-                int d[4] = {0, 0, 0, 0};
-                const uint32_t u[4] = {w[f][0].x, w[f][0].y, w[f][0].z, w[f][0].w};  // feature row g
-                const uint32_t l[4] = {w[f][1].x, w[f][1].y, w[f][1].z, w[f][1].w};  // feature row g + 8
-                if (IS4) {
-#pragma unroll
-                    for (int j = 0; j < 4; ++j)
-                        mma_u8s8(d, u[j] & 0x0F0F0F0Fu, l[j] & 0x0F0F0F0Fu, (u[j] >> 4) & 0x0F0F0F0Fu, (l[j] >> 4) & 0x0F0F0F0Fu,
-                                 b[2 * j], b[2 * j + 1]);
-                } else {
-                    mma_s8s8(d, u[0], l[0], u[1], l[1], b[0], b[1]);
-                    mma_s8s8(d, u[2], l[2], u[3], l[3], b[2], b[3]);
-                }
-                // d[0], d[1]: row g, columns 2t, 2t+1; d[2], d[3]: row g + 8. Even t holds digits 0,1
-                // (the low half of X), odd t digits 2,3: swap halves with the neighbour so that each of
-                // the pair ends with one complete row.
-                const int pg = d[0] + (d[1] << 8), ph = d[2] + (d[3] << 8);
-                const int got = __shfl_xor_sync(0xffffffffu, (t & 1) ? pg : ph, 1);
-                const float T = (t & 1) ? __fmaf_rn(65536.0f, (float)ph, (float)got) : __fmaf_rn(65536.0f, (float)got, (float)pg);
-                const uint32_t row = row0 + 16 * f + rowoff;
-                if (owner && row < ce) {
-                    if (IS4) {
-                        const size_t gi = (size_t)row * groups + blk / gblocks;
-                        const float s = __ldg(scale + gi);
-                        const float mn = __fsub_rn(__ldg(zero + gi), __fmul_rn(8.0f, s));  // min = zero - 8 s
-                        acc[f] = __fmaf_rn(__fmul_rn(s, inv), T, acc[f]);
-                        acc[f] = __fmaf_rn(mn, sum, acc[f]);
+                for (uint32_t blk = warp; blk < nblocks; blk += kWarps) {
+                    const bool more = advance(pend);
+                    if (use_a) {
+                        if (more) load_step(nrow, nblk, wb);
+                        compute(row0, blk, wa);
                     } else {
-                        acc[f] = __fmaf_rn(inv, T, acc[f]);
+                        if (more) load_step(nrow, nblk, wa);
+                        compute(row0, blk, wb);
+                    }
+                    use_a = !use_a;
+                }
+                if (owner) {
+#pragma unroll
+                    for (int f = 0; f < kTiles; ++f) {
+                        const uint32_t pr = row0 - p0 + 16 * f + rowoff;
+                        if (pr < kPanel) partial[((size_t)warp * kPanel + pr) * MR + xrow] = acc[f];
                     }
                 }
             }
-            if (step % my_blocks == my_blocks - 1 && owner) {  // the chunk is complete for this warp's share of K
-#pragma unroll
-                for (int f = 0; f < kTiles; ++f) {
-                    const uint32_t pr = chunk * 16 * kTiles + 16 * f + rowoff;
-                    if (pr < kPanel) partial[((size_t)warp * kPanel + pr) * MR + xrow] = acc[f];
-                }
-            }
-        };
-        auto next_of = [&](uint32_t step, uint32_t& row0, uint32_t& blk, bool& on) {
-            // the step after `step`: in this panel, or the first of the next panel
-            uint32_t s = step + 1, pp = p0;
-            if (s >= steps) {
-                s = 0;
-                pp = p0 + kPanel;
-            }
-            on = my_blocks > 0 && pp < ce;
-            row0 = pp + (s / max(my_blocks, 1u)) * 16 * kTiles;
-            blk = warp + (s % max(my_blocks, 1u)) * kWarps;
-        };
-
-        for (uint32_t step = 0; step < steps; step += 2) {
-            uint32_t row0, blk;
-            bool on;
-            next_of(step, row0, blk, on);
-            load_step(row0, blk, on, wb);
-            compute(step, wa);
-            if (step + 1 < steps) {
-                next_of(step + 1, row0, blk, on);
-                load_step(row0, blk, on, wa);
-                compute(step + 1, wb);
-            } else {
-#pragma unroll
-                for (int f = 0; f < kTiles; ++f) wa[f][0] = wb[f][0], wa[f][1] = wb[f][1];
-            }
-        }
-        if (steps == 0 || (my_blocks == 0)) {
-            // a warp with no share of K contributes zeros
+        } else {
             for (uint32_t i = lane; i < kPanel * MR; i += 32) partial[(size_t)warp * kPanel * MR + i] = 0.0f;
         }
         __syncthreads();
-        // fixed-order sum of the 16 partials; thread (row, xrow) finishes one output
+        // fixed-order sum of the 16 partials; one thread per output
+        const uint32_t prow = pend - p0;
         for (uint32_t i = threadIdx.x; i < prow * MR; i += blockDim.x) {
             const uint32_t pr = i / MR, r = i % MR, col = p0 + pr;
             float v = 0.0f;
@@ -327,6 +335,9 @@ bool run(cudaStream_t s, int sm_count, const float* x, uint64_t k, const uint32_
     const uint32_t nblocks = (vecs + 3) / 4;
     const uint32_t groups = IS4 ? (uint32_t)((k + group - 1) / group) : 0;
     const uint32_t gblocks = IS4 ? (uint32_t)(group / 128) : 1;
+    uint32_t gshift = 32;  // log2(gblocks) when it is a power of two, else 32 (the kernel then divides)
+    for (uint32_t sft = 0; sft < 32; ++sft)
+        if ((1u << sft) == gblocks) gshift = sft;
     constexpr int R = IS4 ? 8 : 4;
     const size_t smem = ((size_t)nblocks * 32 * R + (size_t)MR * nblocks * (IS4 ? 2 : 1) + (size_t)kWarps * kPanel * MR) * 4;
     if (smem > 200 * 1024) return false;
@@ -335,7 +346,7 @@ bool run(cudaStream_t s, int sm_count, const float* x, uint64_t k, const uint32_
     auto kernel = xvec ? gemv_imma_kernel<IS4, MR, true> : gemv_imma_kernel<IS4, MR, false>;
     if (smem > 48 * 1024) GQ_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     kernel<<<grid, kWarps * 32, smem, s>>>(x, reinterpret_cast<const uint4*>(q), scale, zero, bias, y, (uint32_t)k, (uint32_t)n, vecs,
-                                           groups, gblocks, nblocks);
+                                           groups, gshift, gblocks, nblocks);
     return true;
 }
 
