@@ -179,6 +179,28 @@ __global__ void __launch_bounds__(kWarps * 32, 1)
     const size_t half_tile = (size_t)8 * vecs;  // uint4 elements between feature rows r and r + 8
 
     // Weights of feature rows row0 + 16 f + 8 h + g (f < kTiles, h < 2), vector 4 blk + t.
+    // this thread finishes feature row g (even t) or g + 8 (odd t) of each tile, for row t / 2 of x
+    const uint32_t rowoff = g + 8 * (t & 1), xrow = t >> 1;
+    const bool owner = xrow < MR;
+    const bool odd = t & 1;
+    const size_t tile_stride = (size_t)16 * groups;
+
+    // The group parameters of the rows this thread finishes are requested with the weights, a step
+    // ahead of their use: they stream from HBM like the weights do.
+    auto load_params = [&](uint32_t row0, uint32_t blk, float (&sc)[kTiles], float (&zr)[kTiles]) {
+        if (!IS4) return;
+        const uint32_t grp = gblocks == 1 ? blk : (gshift < 32 ? blk >> gshift : blk / gblocks);
+        const uint32_t rbase = row0 + rowoff;
+        const float* sp = scale + (size_t)rbase * groups + grp;
+        const float* zp = zero + (size_t)rbase * groups + grp;
+#pragma unroll
+        for (int f = 0; f < kTiles; ++f) {
+            const bool ok = owner && rbase + 16 * f < ce;
+            sc[f] = ok ? __ldg(sp + f * tile_stride) : 0.0f;
+            zr[f] = ok ? __ldg(zp + f * tile_stride) : 0.0f;
+        }
+    };
+
     auto load_step = [&](uint32_t row0, uint32_t blk, uint4 (&w)[kTiles][2]) {
         const uint32_t v = blk * 4 + t;
         const uint4* p = q + (size_t)(row0 + g) * vecs + v;
@@ -200,22 +222,22 @@ __global__ void __launch_bounds__(kWarps * 32, 1)
 
     // The first step's weights are requested before x is converted.
     uint4 wa[kTiles][2], wb[kTiles][2];
-    if (my_blocks) load_step(cb, warp, wa);
+    float sa[kTiles], za[kTiles], sb[kTiles], zb[kTiles];
+    if (my_blocks) {
+        load_step(cb, warp, wa);
+        load_params(cb, warp, sa, za);
+    }
 
 #pragma unroll
     for (int r = 0; r < MR; ++r)
         prepare_x<IS4, XVEC>(x + (size_t)r * k, r, k, nblocks, xb, xinv + r * nblocks, xsum + r * nblocks);
     __syncthreads();
 
-    // this thread finishes feature row g (even t) or g + 8 (odd t) of each tile, for row t / 2 of x
-    const uint32_t rowoff = g + 8 * (t & 1), xrow = t >> 1;
-    const bool owner = xrow < MR;
-    const bool odd = t & 1;
-
     float acc[kTiles];
 
     // one (chunk of kTiles tiles) x (block) step: 4 (int4) or 2 (int8) MMAs per tile, then the float32 epilogue
-    auto compute = [&](uint32_t row0, uint32_t blk, const uint4 (&w)[kTiles][2]) {
+    auto compute = [&](uint32_t row0, uint32_t blk, const uint4 (&w)[kTiles][2], const float (&sc)[kTiles],
+                       const float (&zr)[kTiles]) {
         uint32_t b[R];  // B fragments: this lane's column is g (digit g % 4 of x row g / 4)
         if (g < 4 * MR) {
             const uint4* src = reinterpret_cast<const uint4*>(xb + ((size_t)(blk * 4 + t) * 8 + g) * R);
@@ -230,11 +252,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1)
         }
         const float inv = owner ? xinv[xrow * nblocks + blk] : 0.0f;
         const float sum = (IS4 && owner) ? xsum[xrow * nblocks + blk] : 0.0f;
-        const uint32_t grp = gblocks == 1 ? blk : (gshift < 32 ? blk >> gshift : blk / gblocks);
         const uint32_t rbase = row0 + rowoff;
-        const float* sp = scale + (size_t)rbase * groups + grp;
-        const float* zp = zero + (size_t)rbase * groups + grp;
-        const size_t tile_stride = (size_t)16 * groups;
 #pragma unroll
         for (int f = 0; f < kTiles; ++f) {
             int d[4] = {0, 0, 0, 0};
@@ -257,8 +275,8 @@ __global__ void __launch_bounds__(kWarps * 32, 1)
             const float T = odd ? __fmaf_rn(65536.0f, (float)ph, (float)got) : __fmaf_rn(65536.0f, (float)got, (float)pg);
             if (owner && rbase + 16 * f < ce) {
                 if (IS4) {
-                    const float s = __ldg(sp + f * tile_stride);
-                    const float mn = __fsub_rn(__ldg(zp + f * tile_stride), __fmul_rn(8.0f, s));  // min = zero - 8 s
+                    const float s = sc[f];
+                    const float mn = __fsub_rn(zr[f], __fmul_rn(8.0f, s));  // min = zero - 8 s
                     acc[f] = __fmaf_rn(__fmul_rn(s, inv), T, acc[f]);
                     acc[f] = __fmaf_rn(mn, sum, acc[f]);
                 } else {
@@ -291,11 +309,17 @@ __global__ void __launch_bounds__(kWarps * 32, 1)
                 for (uint32_t blk = warp; blk < nblocks; blk += kWarps) {
                     const bool more = advance(pend);
                     if (use_a) {
-                        if (more) load_step(nrow, nblk, wb);
-                        compute(row0, blk, wa);
+                        if (more) {
+                            load_step(nrow, nblk, wb);
+                            load_params(nrow, nblk, sb, zb);
+                        }
+                        compute(row0, blk, wa, sa, za);
                     } else {
-                        if (more) load_step(nrow, nblk, wa);
-                        compute(row0, blk, wb);
+                        if (more) {
+                            load_step(nrow, nblk, wa);
+                            load_params(nrow, nblk, sa, za);
+                        }
+                        compute(row0, blk, wb, sb, zb);
                     }
                     use_a = !use_a;
                 }
