@@ -34,15 +34,21 @@
 //
 // Algorithmic bytes per launch: packed weights + scales (+ zero points) + x +
 // y (+ bias), each once. Bound: HBM bandwidth.
+#include "async_common.cuh"
 #include "gq_internal.h"
 
 namespace gq {
 
 namespace {
 
-constexpr int kWarps = 16;    // per CTA; they split K
-constexpr int kTiles = 4;     // 16-row tiles a warp keeps in flight per step
-constexpr int kPanel = 128;   // rows a CTA reduces at a time
+constexpr int kWarps = 16;                       // consumer warps per CTA; they split K
+constexpr int kThreads = (kWarps + 1) * 32;      // plus the producer warp
+constexpr int kPanel = 128;                      // rows a CTA reduces at a time
+constexpr uint32_t kPartBytes = 2048;            // bytes of a weight row per stage: 32 blocks, two per consumer warp
+constexpr int kBlocksPerWarp = kPartBytes / 64 / kWarps;
+constexpr uint32_t kRowStride = kPartBytes + 64;  // 64 mod 128: rows land in different banks
+constexpr uint32_t kStageBytes = 16 * kRowStride;
+constexpr int kMaxStages = 5;
 
 __device__ __forceinline__ uint4 ldg_stream(const uint4* p) {
     uint4 v;
@@ -105,7 +111,7 @@ __device__ __forceinline__ void prepare_x(const float* __restrict__ xr, uint32_t
                                           uint32_t* xb, float* xinv, float* xsum) {
     constexpr int E = IS4 ? 8 : 4;  // values of x per packed word
     constexpr int R = IS4 ? 8 : 4;
-    for (uint32_t base = 0; base < nblocks * 16; base += blockDim.x) {
+    for (uint32_t base = 0; base < nblocks * 16; base += kWarps * 32) {  // the consumer threads, 0 … 511, run this
         const uint32_t wd = base + threadIdx.x;
         const bool live = wd < nblocks * 16;
         const uint32_t k0 = wd * E, blk = wd >> 4, t = (wd >> 2) & 3, j = wd & 3;
@@ -158,203 +164,193 @@ __device__ __forceinline__ void prepare_x(const float* __restrict__ xr, uint32_t
     }
 }
 
+// ── the kernel ───────────────────────────────────────────────────────────
+// Warp 16 is the producer: it streams the CTA's weight rows into a ring of
+// shared-memory stages with bulk (TMA) copies, one copy per row so that rows
+// can sit kRowStride bytes apart (a stride that is 64 mod 128 keeps the
+// 16-byte fragment reads of eight different rows in different banks). A
+// stage holds one 16-row tile x up to 2048 bytes of each row. Warps 0-15
+// consume: all of them work on the same stage, each on its own 64-byte
+// blocks, so up to five stages — 160 KB per SM — are in flight while they
+// compute, and HBM never waits for the arithmetic.
 template <bool IS4, int MR, bool XVEC>
-__global__ void __launch_bounds__(kWarps * 32, 1)
-    gemv_imma_kernel(const float* __restrict__ x, const uint4* __restrict__ q, const float* __restrict__ scale,
+__global__ void __launch_bounds__(kThreads, 1)
+    gemv_imma_kernel(const float* __restrict__ x, const uint8_t* __restrict__ q, const float* __restrict__ scale,
                      const float* __restrict__ zero, const float* __restrict__ bias, float* __restrict__ y, uint32_t k,
-                     uint32_t n, uint32_t vecs, uint32_t groups, uint32_t gshift, uint32_t gblocks, uint32_t nblocks) {
+                     uint32_t n, uint32_t vecs, uint32_t groups, uint32_t gshift, uint32_t gblocks, uint32_t nblocks,
+                     uint32_t nstages, uint32_t* status) {
     constexpr int R = IS4 ? 8 : 4;
-    extern __shared__ __align__(16) uint32_t smem_imma[];
-    uint32_t* xb = smem_imma;                                               // nblocks * 4 * 8 * R words
-    float* xinv = reinterpret_cast<float*>(xb + (size_t)nblocks * 32 * R);  // MR * nblocks
-    float* xsum = xinv + MR * nblocks;                                      // MR * nblocks (int4)
-    float* partial = xsum + (IS4 ? MR * nblocks : 0);                       // kWarps * kPanel * MR
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    uint8_t* stages = smem_raw;                                                  // nstages * kStageBytes
+    uint32_t* xb = reinterpret_cast<uint32_t*>(stages + (size_t)nstages * kStageBytes);  // nblocks * 32 * R words
+    float* xinv = reinterpret_cast<float*>(xb + (size_t)nblocks * 32 * R);      // MR * nblocks
+    float* xsum = xinv + MR * nblocks;                                           // MR * nblocks (int4)
+    float* partial = xsum + (IS4 ? MR * nblocks : 0);                            // kWarps * kPanel * MR
+    uint64_t* full = reinterpret_cast<uint64_t*>((reinterpret_cast<uintptr_t>(partial + kWarps * kPanel * MR) + 7) & ~uintptr_t(7));
+    uint64_t* empty = full + kMaxStages;
+    volatile uint32_t* failed = reinterpret_cast<volatile uint32_t*>(empty + kMaxStages);
 
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const uint32_t g = lane >> 2, t = lane & 3;
     // this CTA's features [cb, ce); the first n % gridDim CTAs take one more
     const uint32_t per = n / gridDim.x, extra = n % gridDim.x;
     const uint32_t cb = blockIdx.x * per + min(blockIdx.x, extra), ce = cb + per + (blockIdx.x < extra ? 1u : 0u);
-    const uint32_t my_blocks = warp < nblocks ? (nblocks - warp + kWarps - 1) / kWarps : 0;  // blocks warp, warp + 16, …
-    const size_t half_tile = (size_t)8 * vecs;  // uint4 elements between feature rows r and r + 8
+    const uint32_t rowbytes = vecs * 16;
+    const uint32_t parts = (rowbytes + kPartBytes - 1) / kPartBytes;  // stages per tile
+    const uint32_t tiles = (ce - cb + 15) / 16;
 
-    // Weights of feature rows row0 + 16 f + 8 h + g (f < kTiles, h < 2), vector 4 blk + t.
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < nstages; ++s) {
+            mbar_init(full + s, 1);        // the producer's arrive.expect_tx
+            mbar_init(empty + s, kWarps);  // one arrival per consumer warp
+        }
+        *failed = 0;
+        mbar_fence_init();
+    }
+    __syncthreads();
+
+    if (warp == kWarps) {
+        // ── producer ──
+        uint32_t s = 0, round = 0;
+        for (uint32_t tile = 0; tile < tiles; ++tile) {
+            const uint32_t row0 = cb + 16 * tile, nrows = min(16u, ce - row0);
+            for (uint32_t part = 0; part < parts; ++part) {
+                if (round && !mbar_wait(empty + s, (round - 1) & 1, failed, status, kStatusEmptyWaitTimedOut)) return;
+                const uint32_t bytes = min(kPartBytes, rowbytes - part * kPartBytes);
+                if (lane == 0) mbar_arrive_expect_tx(full + s, nrows * bytes);
+                __syncwarp();
+                if (lane < nrows)
+                    bulk_load(stages + (size_t)s * kStageBytes + lane * kRowStride,
+                              q + (size_t)(row0 + lane) * rowbytes + (size_t)part * kPartBytes, bytes, full + s);
+                if (++s == nstages) s = 0, ++round;
+            }
+        }
+        return;
+    }
+
+    // ── consumers ──
+    const uint32_t g = lane >> 2, t = lane & 3;
+#pragma unroll
+    for (int r = 0; r < MR; ++r)
+        prepare_x<IS4, XVEC>(x + (size_t)r * k, r, k, nblocks, xb, xinv + r * nblocks, xsum + r * nblocks);
+    named_barrier_sync(1, kWarps * 32);
+
     // this thread finishes feature row g (even t) or g + 8 (odd t) of each tile, for row t / 2 of x
     const uint32_t rowoff = g + 8 * (t & 1), xrow = t >> 1;
     const bool owner = xrow < MR;
     const bool odd = t & 1;
-    const size_t tile_stride = (size_t)16 * groups;
 
-    // The group parameters of the rows this thread finishes are requested with the weights, a step
-    // ahead of their use: they stream from HBM like the weights do.
-    auto load_params = [&](uint32_t row0, uint32_t blk, float (&sc)[kTiles], float (&zr)[kTiles]) {
+    // Group parameters of this thread's row for the warp's (up to two) blocks of a stage; requested one
+    // stage ahead of their use, since they stream from HBM as the weights do.
+    auto load_params = [&](uint32_t tile, uint32_t part, float (&sc)[kBlocksPerWarp], float (&zr)[kBlocksPerWarp]) {
         if (!IS4) return;
-        const uint32_t grp = gblocks == 1 ? blk : (gshift < 32 ? blk >> gshift : blk / gblocks);
-        const uint32_t rbase = row0 + rowoff;
-        const float* sp = scale + (size_t)rbase * groups + grp;
-        const float* zp = zero + (size_t)rbase * groups + grp;
+        const uint32_t row = cb + 16 * tile + rowoff;
 #pragma unroll
-        for (int f = 0; f < kTiles; ++f) {
-            const bool ok = owner && rbase + 16 * f < ce;
-            sc[f] = ok ? __ldg(sp + f * tile_stride) : 0.0f;
-            zr[f] = ok ? __ldg(zp + f * tile_stride) : 0.0f;
+        for (int bi = 0; bi < kBlocksPerWarp; ++bi) {
+            const uint32_t blk = part * (kPartBytes / 64) + warp + kWarps * bi;
+            const bool ok = owner && tile < tiles && row < ce && blk < nblocks;
+            const uint32_t grp = gblocks == 1 ? blk : (gshift < 32 ? blk >> gshift : blk / gblocks);
+            sc[bi] = ok ? __ldg(scale + (size_t)row * groups + grp) : 0.0f;
+            zr[bi] = ok ? __ldg(zero + (size_t)row * groups + grp) : 0.0f;
         }
     };
 
-    auto load_step = [&](uint32_t row0, uint32_t blk, uint4 (&w)[kTiles][2]) {
-        const uint32_t v = blk * 4 + t;
-        const uint4* p = q + (size_t)(row0 + g) * vecs + v;
-        if (row0 + 16 * kTiles <= ce && v < vecs) {  // the common case: nothing to mask
-#pragma unroll
-            for (int f = 0; f < kTiles; ++f) {
-                w[f][0] = ldg_stream(p + (2 * f) * half_tile);
-                w[f][1] = ldg_stream(p + (2 * f + 1) * half_tile);
+    float sc[kBlocksPerWarp], zr[kBlocksPerWarp], scn[kBlocksPerWarp], zrn[kBlocksPerWarp];
+    load_params(0, 0, sc, zr);
+
+    float acc = 0.0f;
+    bool ok = true;
+    uint32_t s = 0, round = 0;
+    for (uint32_t tile = 0; tile < tiles; ++tile) {
+        for (uint32_t part = 0; part < parts; ++part) {
+            {  // the next stage's parameters
+                uint32_t nt = tile, np = part + 1;
+                if (np == parts) np = 0, ++nt;
+                load_params(nt, np, scn, zrn);
             }
-        } else {
-            const uint32_t left = (row0 < ce && v < vecs) ? ce - row0 : 0;  // valid rows from row0 on
+            ok = ok && mbar_wait(full + s, round & 1, failed, status, kStatusFullWaitTimedOut);
+            if (ok) {
+                const uint8_t* st = stages + (size_t)s * kStageBytes;
 #pragma unroll
-            for (int f = 0; f < kTiles; ++f)
+                for (int bi = 0; bi < kBlocksPerWarp; ++bi) {
+                    const uint32_t b = warp + kWarps * bi;             // block within the part
+                    const uint32_t blk = part * (kPartBytes / 64) + b;  // block within the row
+                    if (blk >= nblocks) break;
+                    const uint4 u4 = *reinterpret_cast<const uint4*>(st + g * kRowStride + 64 * b + 16 * t);        // row g
+                    const uint4 l4 = *reinterpret_cast<const uint4*>(st + (g + 8) * kRowStride + 64 * b + 16 * t);  // row g + 8
+                    uint32_t bf[R];  // B fragments: this lane's column is g (digit g % 4 of x row g / 4)
+                    if (g < 4 * MR) {
+                        const uint4* src = reinterpret_cast<const uint4*>(xb + ((size_t)(blk * 4 + t) * 8 + g) * R);
 #pragma unroll
-                for (int h = 0; h < 2; ++h)
-                    w[f][h] = (16 * f + 8 * h + g < left) ? ldg_stream(p + (2 * f + h) * half_tile) : make_uint4(0, 0, 0, 0);
-        }
-    };
-
-    // The first step's weights are requested before x is converted.
-    uint4 wa[kTiles][2], wb[kTiles][2];
-    float sa[kTiles], za[kTiles], sb[kTiles], zb[kTiles];
-    if (my_blocks) {
-        load_step(cb, warp, wa);
-        load_params(cb, warp, sa, za);
-    }
-
-#pragma unroll
-    for (int r = 0; r < MR; ++r)
-        prepare_x<IS4, XVEC>(x + (size_t)r * k, r, k, nblocks, xb, xinv + r * nblocks, xsum + r * nblocks);
-    __syncthreads();
-
-    float acc[kTiles];
-
-    // one (chunk of kTiles tiles) x (block) step: 4 (int4) or 2 (int8) MMAs per tile, then the float32 epilogue
-    auto compute = [&](uint32_t row0, uint32_t blk, const uint4 (&w)[kTiles][2], const float (&sc)[kTiles],
-                       const float (&zr)[kTiles]) {
-        uint32_t b[R];  // B fragments: this lane's column is g (digit g % 4 of x row g / 4)
-        if (g < 4 * MR) {
-            const uint4* src = reinterpret_cast<const uint4*>(xb + ((size_t)(blk * 4 + t) * 8 + g) * R);
-#pragma unroll
-            for (int i = 0; i < R / 4; ++i) {
-                const uint4 v = src[i];
-                b[4 * i] = v.x, b[4 * i + 1] = v.y, b[4 * i + 2] = v.z, b[4 * i + 3] = v.w;
-            }
-        } else {
-#pragma unroll
-            for (int i = 0; i < R; ++i) b[i] = 0;
-        }
-        const float inv = owner ? xinv[xrow * nblocks + blk] : 0.0f;
-        const float sum = (IS4 && owner) ? xsum[xrow * nblocks + blk] : 0.0f;
-        const uint32_t rbase = row0 + rowoff;
-#pragma unroll
-        for (int f = 0; f < kTiles; ++f) {
-            int d[4] = {0, 0, 0, 0};
-            const uint32_t u[4] = {w[f][0].x, w[f][0].y, w[f][0].z, w[f][0].w};  // feature row g
-            const uint32_t l[4] = {w[f][1].x, w[f][1].y, w[f][1].z, w[f][1].w};  // feature row g + 8
-            if (IS4) {
-#pragma unroll
-                for (int j = 0; j < 4; ++j)
-                    mma_u8s8(d, u[j] & 0x0F0F0F0Fu, l[j] & 0x0F0F0F0Fu, (u[j] >> 4) & 0x0F0F0F0Fu, (l[j] >> 4) & 0x0F0F0F0Fu,
-                             b[2 * j], b[2 * j + 1]);
-            } else {
-                mma_s8s8(d, u[0], l[0], u[1], l[1], b[0], b[1]);
-                mma_s8s8(d, u[2], l[2], u[3], l[3], b[2], b[3]);
-            }
-            // d[0], d[1]: row g, columns 2t, 2t+1; d[2], d[3]: row g + 8. Even t holds digits 0,1 (the low
-            // half of X), odd t digits 2,3: swap halves with the neighbour so each of the pair ends with
-            // one complete row.
-            const int pg = d[0] + (d[1] << 8), ph = d[2] + (d[3] << 8);
-            const int got = __shfl_xor_sync(0xffffffffu, odd ? pg : ph, 1);
-            const float T = odd ? __fmaf_rn(65536.0f, (float)ph, (float)got) : __fmaf_rn(65536.0f, (float)got, (float)pg);
-            if (owner && rbase + 16 * f < ce) {
-                if (IS4) {
-                    const float s = sc[f];
-                    const float mn = __fsub_rn(zr[f], __fmul_rn(8.0f, s));  // min = zero - 8 s
-                    acc[f] = __fmaf_rn(__fmul_rn(s, inv), T, acc[f]);
-                    acc[f] = __fmaf_rn(mn, sum, acc[f]);
-                } else {
-                    acc[f] = __fmaf_rn(inv, T, acc[f]);
-                }
-            }
-        }
-    };
-
-    // Steps run chunk-major, this warp's blocks inside; (nrow, nblk) always names the step after the
-    // one being computed — possibly the first of the next panel — whose weights are in flight.
-    uint32_t nrow = cb, nblk = warp;
-    auto advance = [&](uint32_t panel_end) {  // move (nrow, nblk) one step on; returns false past the CTA's last step
-        nblk += kWarps;
-        if (nblk >= nblocks) {
-            nblk = warp;
-            nrow += 16 * kTiles;
-            if (nrow >= panel_end) nrow = panel_end;  // the next panel starts where this one ends
-        }
-        return nrow < ce;
-    };
-
-    bool use_a = true;  // which buffer holds the step about to be computed
-    for (uint32_t p0 = cb; p0 < ce; p0 += kPanel) {
-        const uint32_t pend = min(p0 + (uint32_t)kPanel, ce);
-        if (my_blocks) {
-            for (uint32_t row0 = p0; row0 < pend; row0 += 16 * kTiles) {
-#pragma unroll
-                for (int f = 0; f < kTiles; ++f) acc[f] = 0.0f;
-                for (uint32_t blk = warp; blk < nblocks; blk += kWarps) {
-                    const bool more = advance(pend);
-                    if (use_a) {
-                        if (more) {
-                            load_step(nrow, nblk, wb);
-                            load_params(nrow, nblk, sb, zb);
+                        for (int i = 0; i < R / 4; ++i) {
+                            const uint4 v = src[i];
+                            bf[4 * i] = v.x, bf[4 * i + 1] = v.y, bf[4 * i + 2] = v.z, bf[4 * i + 3] = v.w;
                         }
-                        compute(row0, blk, wa, sa, za);
                     } else {
-                        if (more) {
-                            load_step(nrow, nblk, wa);
-                            load_params(nrow, nblk, sa, za);
-                        }
-                        compute(row0, blk, wb, sb, zb);
-                    }
-                    use_a = !use_a;
-                }
-                if (owner) {
 #pragma unroll
-                    for (int f = 0; f < kTiles; ++f) {
-                        const uint32_t pr = row0 - p0 + 16 * f + rowoff;
-                        if (pr < kPanel) partial[((size_t)warp * kPanel + pr) * MR + xrow] = acc[f];
+                        for (int i = 0; i < R; ++i) bf[i] = 0;
+                    }
+                    int d[4] = {0, 0, 0, 0};
+                    const uint32_t u[4] = {u4.x, u4.y, u4.z, u4.w}, l[4] = {l4.x, l4.y, l4.z, l4.w};
+                    if (IS4) {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            mma_u8s8(d, u[j] & 0x0F0F0F0Fu, l[j] & 0x0F0F0F0Fu, (u[j] >> 4) & 0x0F0F0F0Fu,
+                                     (l[j] >> 4) & 0x0F0F0F0Fu, bf[2 * j], bf[2 * j + 1]);
+                    } else {
+                        mma_s8s8(d, u[0], l[0], u[1], l[1], bf[0], bf[1]);
+                        mma_s8s8(d, u[2], l[2], u[3], l[3], bf[2], bf[3]);
+                    }
+                    // d[0], d[1]: row g, columns 2t, 2t+1; d[2], d[3]: row g + 8. Even t holds digits 0,1
+                    // (the low half of X), odd t digits 2,3: swap halves with the neighbour so that each
+                    // of the pair ends with one complete row.
+                    const int pg = d[0] + (d[1] << 8), ph = d[2] + (d[3] << 8);
+                    const int got = __shfl_xor_sync(0xffffffffu, odd ? pg : ph, 1);
+                    const float T = odd ? __fmaf_rn(65536.0f, (float)ph, (float)got) : __fmaf_rn(65536.0f, (float)got, (float)pg);
+                    if (owner) {
+                        const float inv = xinv[xrow * nblocks + blk];
+                        if (IS4) {
+                            const float mn = __fsub_rn(zr[bi], __fmul_rn(8.0f, sc[bi]));  // min = zero - 8 s
+                            acc = __fmaf_rn(__fmul_rn(sc[bi], inv), T, acc);
+                            acc = __fmaf_rn(mn, xsum[xrow * nblocks + blk], acc);
+                        } else {
+                            acc = __fmaf_rn(inv, T, acc);
+                        }
                     }
                 }
             }
-        } else {
-            for (uint32_t i = lane; i < kPanel * MR; i += 32) partial[(size_t)warp * kPanel * MR + i] = 0.0f;
-        }
-        __syncthreads();
-        // fixed-order sum of the 16 partials; one thread per output
-        const uint32_t prow = pend - p0;
-        for (uint32_t i = threadIdx.x; i < prow * MR; i += blockDim.x) {
-            const uint32_t pr = i / MR, r = i % MR, col = p0 + pr;
-            float v = 0.0f;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty + s);  // this warp has read the stage
+            if (++s == nstages) s = 0, ++round;
 #pragma unroll
-            for (int w = 0; w < kWarps; ++w) v += partial[((size_t)w * kPanel + pr) * MR + r];
-            if (!IS4) v = __fmul_rn(v, scale[col]);  // the row scale multiplies the finished sum
-            if (bias) v = __fadd_rn(v, bias[col]);
-            y[(size_t)r * n + col] = v;
+            for (int bi = 0; bi < kBlocksPerWarp; ++bi) sc[bi] = scn[bi], zr[bi] = zrn[bi];
         }
-        __syncthreads();
+        // the tile is complete for this warp's share of K
+        const uint32_t pr = (tile % (kPanel / 16)) * 16 + rowoff;
+        if (owner) partial[((size_t)warp * kPanel + pr) * MR + xrow] = acc;
+        acc = 0.0f;
+        if ((tile + 1) % (kPanel / 16) == 0 || tile + 1 == tiles) {
+            // a panel of up to 128 rows: fixed-order sum of the 16 partials, one thread per output
+            named_barrier_sync(1, kWarps * 32);
+            const uint32_t p0 = cb + (tile / (kPanel / 16)) * kPanel, prow = min((uint32_t)kPanel, ce - p0);
+            for (uint32_t i = threadIdx.x; i < prow * MR; i += kWarps * 32) {
+                const uint32_t prr = i / MR, r = i % MR, col = p0 + prr;
+                float v = 0.0f;
+#pragma unroll
+                for (int w = 0; w < kWarps; ++w) v += partial[((size_t)w * kPanel + prr) * MR + r];
+                if (!IS4) v = __fmul_rn(v, scale[col]);  // the row scale multiplies the finished sum
+                if (bias) v = __fadd_rn(v, bias[col]);
+                y[(size_t)r * n + col] = v;
+            }
+            named_barrier_sync(1, kWarps * 32);
+        }
     }
 }
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 template <bool IS4, int MR>
-bool run(cudaStream_t s, int sm_count, const float* x, uint64_t k, const uint32_t* q, const float* scale, const float* zero,
-         const float* bias, uint64_t n, uint64_t group, float* y) {
+bool run(cudaStream_t s, int sm_count, uint32_t* status, const float* x, uint64_t k, const uint32_t* q, const float* scale,
+         const float* zero, const float* bias, uint64_t n, uint64_t group, float* y) {
     const uint32_t vecs = (uint32_t)(IS4 ? (k + 31) / 32 : (k + 15) / 16);
     const uint32_t nblocks = (vecs + 3) / 4;
     const uint32_t groups = IS4 ? (uint32_t)((k + group - 1) / group) : 0;
@@ -363,14 +359,19 @@ bool run(cudaStream_t s, int sm_count, const float* x, uint64_t k, const uint32_
     for (uint32_t sft = 0; sft < 32; ++sft)
         if ((1u << sft) == gblocks) gshift = sft;
     constexpr int R = IS4 ? 8 : 4;
-    const size_t smem = ((size_t)nblocks * 32 * R + (size_t)MR * nblocks * (IS4 ? 2 : 1) + (size_t)kWarps * kPanel * MR) * 4;
-    if (smem > 200 * 1024) return false;
+    const size_t fixed = ((size_t)nblocks * 32 * R + (size_t)MR * nblocks * (IS4 ? 2 : 1) + (size_t)kWarps * kPanel * MR + 1) * 4 +
+                         2 * kMaxStages * 8 + 16;
+    const size_t budget = 226 * 1024;
+    if (fixed + 2 * (size_t)kStageBytes > budget) return false;
+    uint32_t nstages = (uint32_t)((budget - fixed) / kStageBytes);
+    if (nstages > kMaxStages) nstages = kMaxStages;
+    const size_t smem = fixed + (size_t)nstages * kStageBytes;
     const uint32_t grid = (uint32_t)(n < (uint64_t)sm_count ? n : (uint64_t)sm_count);
     const bool xvec = aligned16(x) && k % 4 == 0;
     auto kernel = xvec ? gemv_imma_kernel<IS4, MR, true> : gemv_imma_kernel<IS4, MR, false>;
-    if (smem > 48 * 1024) GQ_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kernel<<<grid, kWarps * 32, smem, s>>>(x, reinterpret_cast<const uint4*>(q), scale, zero, bias, y, (uint32_t)k, (uint32_t)n, vecs,
-                                           groups, gshift, gblocks, nblocks);
+    GQ_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kernel<<<grid, kThreads, smem, s>>>(x, reinterpret_cast<const uint8_t*>(q), scale, zero, bias, y, (uint32_t)k, (uint32_t)n, vecs,
+                                        groups, gshift, gblocks, nblocks, nstages, status);
     return true;
 }
 
@@ -379,18 +380,18 @@ bool run(cudaStream_t s, int sm_count, const float* x, uint64_t k, const uint32_
 // Returns false when the shape is outside this kernel (more than two rows of
 // x, an int4 group size that is not a multiple of 128, or a row of x too long
 // for shared memory); the caller then takes the dp4a kernel.
-bool launch_gemv_q4_imma(cudaStream_t s, int sm_count, const float* x, uint64_t m, uint64_t k, const uint32_t* q,
+bool launch_gemv_q4_imma(cudaStream_t s, int sm_count, uint32_t* status, const float* x, uint64_t m, uint64_t k, const uint32_t* q,
                          const float* scale, const float* zero, const float* bias, uint64_t n, uint64_t group, float* y) {
     if (group % 128 != 0 || m > 2) return false;
-    return m == 1 ? run<true, 1>(s, sm_count, x, k, q, scale, zero, bias, n, group, y)
-                  : run<true, 2>(s, sm_count, x, k, q, scale, zero, bias, n, group, y);
+    return m == 1 ? run<true, 1>(s, sm_count, status, x, k, q, scale, zero, bias, n, group, y)
+                  : run<true, 2>(s, sm_count, status, x, k, q, scale, zero, bias, n, group, y);
 }
 
-bool launch_gemv_q8_imma(cudaStream_t s, int sm_count, const float* x, uint64_t m, uint64_t k, const uint32_t* q,
+bool launch_gemv_q8_imma(cudaStream_t s, int sm_count, uint32_t* status, const float* x, uint64_t m, uint64_t k, const uint32_t* q,
                          const float* scale, const float* bias, uint64_t n, float* y) {
     if (m > 2) return false;
-    return m == 1 ? run<false, 1>(s, sm_count, x, k, q, scale, nullptr, bias, n, 0, y)
-                  : run<false, 2>(s, sm_count, x, k, q, scale, nullptr, bias, n, 0, y);
+    return m == 1 ? run<false, 1>(s, sm_count, status, x, k, q, scale, nullptr, bias, n, 0, y)
+                  : run<false, 2>(s, sm_count, status, x, k, q, scale, nullptr, bias, n, 0, y);
 }
 
 }  // namespace gq

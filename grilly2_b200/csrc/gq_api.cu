@@ -134,6 +134,12 @@ static void host_wait(gq_ctx* ctx) {
     ctx->stats.wait_ns_total += ns;
     ctx->stats.wait_ns_last = ns;
     if (e != cudaSuccess) fail("the device reported an error while the host waited: %s", cudaGetErrorString(e));
+    if (ctx->status_host && *ctx->status_host) {
+        const uint32_t code = *ctx->status_host;
+        *ctx->status_host = 0;
+        fail("a kernel gave up a bounded wait (code %u: 1 = a bulk copy never landed, 2 = a pipeline stage was never freed, "
+             "3 = the tensor cores never signalled completion); its results are not valid", code);
+    }
 }
 
 static const char* const kCaptureRead =
@@ -171,6 +177,9 @@ int32_t gq_create(int32_t device, gq_ctx** out) {
                 fail("gq_create: device %d (%s) is compute capability %d.%d; the kernels are built for sm_100a (B200) only", device,
                      ctx->prop.name, ctx->prop.major, ctx->prop.minor);
             GQ_CUDA(cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking));
+            GQ_CUDA(cudaHostAlloc((void**)&ctx->status_host, 64, cudaHostAllocMapped));
+            *ctx->status_host = 0;
+            GQ_CUDA(cudaHostGetDevicePointer((void**)&ctx->status_dev, ctx->status_host, 0));
             const char* lb = getenv("GQ_LAUNCH_BLOCKING");
             ctx->launch_blocking = lb && lb[0] == '1';
         } catch (...) {
@@ -192,6 +201,7 @@ void gq_destroy(gq_ctx* ctx) {
                 if (kv.second.owned && kv.second.ptr) cudaFree(kv.second.ptr);
             for (auto& kv : ctx->pool) cudaFree(kv.second);
             if (ctx->scratch) cudaFree(ctx->scratch);
+            if (ctx->status_host) cudaFreeHost(ctx->status_host);
             cudaStreamDestroy(ctx->stream);
         }
         delete ctx;
@@ -487,7 +497,7 @@ int32_t gq_int8_linear(gq_ctx* ctx, gq_buf x, uint64_t x_off, uint64_t m, uint64
         bool done = false;
         const char* name = "gemv_q8";
         if (kernel == GQ_KERNEL_AUTO || kernel == GQ_KERNEL_IMMA) {
-            done = launch_gemv_q8_imma(ctx->stream, ctx->prop.multiProcessorCount, xp, m, k, qp, sp, bp, n, yp);
+            done = launch_gemv_q8_imma(ctx->stream, ctx->prop.multiProcessorCount, ctx->status_dev, xp, m, k, qp, sp, bp, n, yp);
             if (done) name = "gemv_q8_imma";
             if (!done && kernel == GQ_KERNEL_IMMA) fail("gq_int8_linear: the IMMA kernel takes one or two rows of x and rows that fit shared memory (m = %llu, k = %llu)", (unsigned long long)m, (unsigned long long)k);
         }
@@ -555,7 +565,7 @@ int32_t gq_int4_linear(gq_ctx* ctx, gq_buf x, uint64_t x_off, uint64_t m, uint64
         bool done = false;
         const char* name = "gemv_q4";
         if (kernel == GQ_KERNEL_AUTO || kernel == GQ_KERNEL_IMMA) {
-            done = launch_gemv_q4_imma(ctx->stream, ctx->prop.multiProcessorCount, xp, m, k, qp, sp, zp, bp, n, group, yp);
+            done = launch_gemv_q4_imma(ctx->stream, ctx->prop.multiProcessorCount, ctx->status_dev, xp, m, k, qp, sp, zp, bp, n, group, yp);
             if (done) name = "gemv_q4_imma";
             if (!done && kernel == GQ_KERNEL_IMMA) fail("gq_int4_linear: the IMMA kernel takes one or two rows of x, a group_size that is a multiple of 128 and rows that fit shared memory (m = %llu, k = %llu, group_size = %llu)", (unsigned long long)m, (unsigned long long)k, (unsigned long long)group);
         }

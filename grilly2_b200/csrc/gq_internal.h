@@ -68,6 +68,10 @@ struct gq_ctx {
     bool capturing = false;
     uint64_t capture_nodes = 0;
     std::vector<gq_buf> capture_retained;
+    // A word in mapped host memory that kernels with bounded waits write when a wait gives up; the
+    // host checks it whenever it waits for the stream.
+    uint32_t* status_host = nullptr;
+    uint32_t* status_dev = nullptr;
     // lazily created device scratch owned by the context (tensor-core paths)
     void* scratch = nullptr;
     uint64_t scratch_bytes = 0;
@@ -99,9 +103,9 @@ bool launch_gemv_q8_dp4a(cudaStream_t s, int sm_count, const float* x, uint64_t 
 bool launch_gemv_q4_dp4a(cudaStream_t s, int sm_count, const float* x, uint64_t m, uint64_t k, const uint32_t* q, const float* scale,
                          const float* zero, const float* bias, uint64_t n, uint64_t group, float* y);
 
-bool launch_gemv_q8_imma(cudaStream_t s, int sm_count, const float* x, uint64_t m, uint64_t k, const uint32_t* q,
+bool launch_gemv_q8_imma(cudaStream_t s, int sm_count, uint32_t* status, const float* x, uint64_t m, uint64_t k, const uint32_t* q,
                          const float* scale, const float* bias, uint64_t n, float* y);
-bool launch_gemv_q4_imma(cudaStream_t s, int sm_count, const float* x, uint64_t m, uint64_t k, const uint32_t* q,
+bool launch_gemv_q4_imma(cudaStream_t s, int sm_count, uint32_t* status, const float* x, uint64_t m, uint64_t k, const uint32_t* q,
                          const float* scale, const float* zero, const float* bias, uint64_t n, uint64_t group, float* y);
 
 }  // namespace gq
