@@ -11,8 +11,10 @@
 // multiply-adds: per weight the kernel issues ~0.8 thread instructions — 3/8
 // to split int4 nibbles into bytes, the rest loads and the per-block float32
 // epilogue — against 1.7-3.9 for the dp4a kernel and ~5 for the float one.
-// That is what lets a single row of x run at HBM speed on a B200 (46 int4
-// levels per SM per clock).
+// Measured on a B200 the warp-level integer MMA itself is the limit: the
+// tensor pipe retires one m16n8k32 in about 20 cycles per SM, so this kernel
+// tops out near 4.5 TB/s for int8 weights and 2.5 TB/s for int4; the tcgen05
+// kernels exist to lift that.
 //
 // Mapping. A "block" is 64 bytes of one weight row: four 16-byte vectors, 128
 // int4 levels or 64 int8 values; it is also the block x's exponent is shared
@@ -239,34 +241,46 @@ __global__ void __launch_bounds__(kThreads, 1)
     const bool owner = xrow < MR;
     const bool odd = t & 1;
 
-    // Group parameters of this thread's row for the warp's (up to two) blocks of a stage; requested one
-    // stage ahead of their use, since they stream from HBM as the weights do.
-    auto load_params = [&](uint32_t tile, uint32_t part, float (&sc)[kBlocksPerWarp], float (&zr)[kBlocksPerWarp]) {
-        if (!IS4) return;
-        const uint32_t row = cb + 16 * tile + rowoff;
-#pragma unroll
-        for (int bi = 0; bi < kBlocksPerWarp; ++bi) {
-            const uint32_t blk = part * (kPartBytes / 64) + warp + kWarps * bi;
-            const bool ok = owner && tile < tiles && row < ce && blk < nblocks;
-            const uint32_t grp = gblocks == 1 ? blk : (gshift < 32 ? blk >> gshift : blk / gblocks);
-            sc[bi] = ok ? __ldg(scale + (size_t)row * groups + grp) : 0.0f;
-            zr[bi] = ok ? __ldg(zero + (size_t)row * groups + grp) : 0.0f;
-        }
+    // Group parameters (scale, zero) of the rows this warp finishes, for its (up to two) blocks of a
+    // stage. They stream from HBM like the weights, so they are requested kMaxStages stages ahead
+    // with 4-byte cp.async copies into a small per-warp ring and read back from shared memory.
+    float* pring = reinterpret_cast<float*>(const_cast<uint32_t*>(failed) + 4);  // [kMaxStages][kWarps][kBlocksPerWarp][16][2]
+    auto param_slot = [&](uint32_t slot, int bi) {
+        return pring + ((((size_t)slot * kWarps + warp) * kBlocksPerWarp + bi) * 16 + rowoff) * 2;
     };
-
-    float sc[kBlocksPerWarp], zr[kBlocksPerWarp], scn[kBlocksPerWarp], zrn[kBlocksPerWarp];
-    load_params(0, 0, sc, zr);
+    auto issue_params = [&](uint32_t slot, uint32_t tile, uint32_t part) {
+        if (IS4 && t < 2 && tile < tiles) {
+            const uint32_t row = cb + 16 * tile + rowoff;
+#pragma unroll
+            for (int bi = 0; bi < kBlocksPerWarp; ++bi) {
+                const uint32_t blk = part * (kPartBytes / 64) + warp + kWarps * bi;
+                if (row < ce && blk < nblocks) {
+                    const uint32_t grp = gblocks == 1 ? blk : (gshift < 32 ? blk >> gshift : blk / gblocks);
+                    const uint32_t dst = smem_u32(param_slot(slot, bi));
+                    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(scale + (size_t)row * groups + grp) : "memory");
+                    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst + 4), "l"(zero + (size_t)row * groups + grp) : "memory");
+                }
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");  // one group per stage, empty or not
+    };
+    uint32_t ptile = 0, ppart = 0;  // the stage whose parameters are requested next
+    auto advance_params = [&]() {
+        if (++ppart == parts) ppart = 0, ++ptile;
+    };
+    for (uint32_t i = 0; i < (uint32_t)kMaxStages; ++i) {
+        issue_params(i, ptile, ppart);
+        advance_params();
+    }
+    uint32_t pslot = 0;
 
     float acc = 0.0f;
     bool ok = true;
     uint32_t s = 0, round = 0;
     for (uint32_t tile = 0; tile < tiles; ++tile) {
         for (uint32_t part = 0; part < parts; ++part) {
-            {  // the next stage's parameters
-                uint32_t nt = tile, np = part + 1;
-                if (np == parts) np = 0, ++nt;
-                load_params(nt, np, scn, zrn);
-            }
+            asm volatile("cp.async.wait_group %0;" ::"n"(kMaxStages - 1) : "memory");  // this stage's parameters have landed
+            __syncwarp();
             ok = ok && mbar_wait(full + s, round & 1, failed, status, kStatusFullWaitTimedOut);
             if (ok) {
                 const uint8_t* st = stages + (size_t)s * kStageBytes;
@@ -309,8 +323,9 @@ __global__ void __launch_bounds__(kThreads, 1)
                     if (owner) {
                         const float inv = xinv[xrow * nblocks + blk];
                         if (IS4) {
-                            const float mn = __fsub_rn(zr[bi], __fmul_rn(8.0f, sc[bi]));  // min = zero - 8 s
-                            acc = __fmaf_rn(__fmul_rn(sc[bi], inv), T, acc);
+                            const float2 sz = *reinterpret_cast<const float2*>(param_slot(pslot, bi));
+                            const float mn = __fsub_rn(sz.y, __fmul_rn(8.0f, sz.x));  // min = zero - 8 s
+                            acc = __fmaf_rn(__fmul_rn(sz.x, inv), T, acc);
                             acc = __fmaf_rn(mn, xsum[xrow * nblocks + blk], acc);
                         } else {
                             acc = __fmaf_rn(inv, T, acc);
@@ -321,8 +336,9 @@ __global__ void __launch_bounds__(kThreads, 1)
             __syncwarp();
             if (lane == 0) mbar_arrive(empty + s);  // this warp has read the stage
             if (++s == nstages) s = 0, ++round;
-#pragma unroll
-            for (int bi = 0; bi < kBlocksPerWarp; ++bi) sc[bi] = scn[bi], zr[bi] = zrn[bi];
+            issue_params(pslot, ptile, ppart);  // the slot just read is free again (the __syncwarp above orders it)
+            advance_params();
+            if (++pslot == (uint32_t)kMaxStages) pslot = 0;
         }
         // the tile is complete for this warp's share of K
         const uint32_t pr = (tile % (kPanel / 16)) * 16 + rowoff;
@@ -360,7 +376,7 @@ bool run(cudaStream_t s, int sm_count, uint32_t* status, const float* x, uint64_
         if ((1u << sft) == gblocks) gshift = sft;
     constexpr int R = IS4 ? 8 : 4;
     const size_t fixed = ((size_t)nblocks * 32 * R + (size_t)MR * nblocks * (IS4 ? 2 : 1) + (size_t)kWarps * kPanel * MR + 1) * 4 +
-                         2 * kMaxStages * 8 + 16;
+                         2 * kMaxStages * 8 + 32 + (IS4 ? (size_t)kMaxStages * kWarps * kBlocksPerWarp * 16 * 2 * 4 : 0);
     const size_t budget = 226 * 1024;
     if (fixed + 2 * (size_t)kStageBytes > budget) return false;
     uint32_t nstages = (uint32_t)((budget - fixed) / kStageBytes);
