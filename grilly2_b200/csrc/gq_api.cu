@@ -486,7 +486,7 @@ int32_t gq_int8_linear(gq_ctx* ctx, gq_buf x, uint64_t x_off, uint64_t m, uint64
     return guarded([&] {
         Locked l(ctx);
         check_dims("gq_int8_linear", m, k, n);
-        if (kernel < GQ_KERNEL_AUTO || kernel > GQ_KERNEL_IMMA) fail("gq_int8_linear: unknown kernel selector %d", kernel);
+        if (kernel < GQ_KERNEL_AUTO || kernel > GQ_KERNEL_UMMA) fail("gq_int8_linear: unknown kernel selector %d", kernel);
         auto xp = (const float*)view(ctx, x, x_off, m * k, 4, "gq_int8_linear input");
         auto qp = (const uint32_t*)view(ctx, q, 0, n * words8(k), 4, "gq_int8_linear q");
         auto sp = (const float*)view(ctx, scale, 0, n, 4, "gq_int8_linear scale");
@@ -496,7 +496,12 @@ int32_t gq_int8_linear(gq_ctx* ctx, gq_buf x, uint64_t x_off, uint64_t m, uint64
         if (kernel == GQ_KERNEL_TENSOR) fail("gq_int8_linear: the tensor-core kernel is not built into this library");
         bool done = false;
         const char* name = "gemv_q8";
-        if (kernel == GQ_KERNEL_AUTO || kernel == GQ_KERNEL_IMMA) {
+        if (kernel == GQ_KERNEL_AUTO || kernel == GQ_KERNEL_UMMA) {
+            done = launch_gemv_q8_tc(ctx->stream, ctx->prop.multiProcessorCount, ctx->status_dev, xp, m, k, qp, sp, bp, n, yp);
+            if (done) name = "gemv_q8_tc";
+            if (!done && kernel == GQ_KERNEL_UMMA) fail("gq_int8_linear: the tcgen05 decode kernel takes one or two rows of x (m = %llu, k = %llu)", (unsigned long long)m, (unsigned long long)k);
+        }
+        if (!done && (kernel == GQ_KERNEL_AUTO || kernel == GQ_KERNEL_IMMA)) {
             done = launch_gemv_q8_imma(ctx->stream, ctx->prop.multiProcessorCount, ctx->status_dev, xp, m, k, qp, sp, bp, n, yp);
             if (done) name = "gemv_q8_imma";
             if (!done && kernel == GQ_KERNEL_IMMA) fail("gq_int8_linear: the IMMA kernel takes one or two rows of x and rows that fit shared memory (m = %llu, k = %llu)", (unsigned long long)m, (unsigned long long)k);
@@ -552,7 +557,7 @@ int32_t gq_int4_linear(gq_ctx* ctx, gq_buf x, uint64_t x_off, uint64_t m, uint64
         Locked l(ctx);
         check_dims("gq_int4_linear", m, k, n);
         check_group(group);
-        if (kernel < GQ_KERNEL_AUTO || kernel > GQ_KERNEL_IMMA) fail("gq_int4_linear: unknown kernel selector %d", kernel);
+        if (kernel < GQ_KERNEL_AUTO || kernel > GQ_KERNEL_UMMA) fail("gq_int4_linear: unknown kernel selector %d", kernel);
         uint64_t groups = (k + group - 1) / group;
         auto xp = (const float*)view(ctx, x, x_off, m * k, 4, "gq_int4_linear input");
         auto qp = (const uint32_t*)view(ctx, q, 0, n * words4(k), 4, "gq_int4_linear q");

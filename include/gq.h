@@ -69,6 +69,8 @@ typedef uint64_t gq_buf; /* 0 is never a valid handle */
 #define GQ_KERNEL_TENSOR 2 /* tcgen05 tensor-core GEMM (tf32), dequantised in shared memory */
 #define GQ_KERNEL_DP4A 3   /* GEMV on integer dot products (dp4a) against exact fixed-point digit planes of x,
                               within float32 rounding of GQ_KERNEL_GEMV; any group size, up to 16 rows */
+#define GQ_KERNEL_UMMA 5   /* decode GEMV on tcgen05 (kind::i8, accumulators in tensor memory), weights fed to the
+                              tensor core by TMA exactly as they lie in HBM: one or two rows of x */
 #define GQ_KERNEL_IMMA 4   /* the same arithmetic on the warp-level int8 tensor instruction: the fast path for
                               one or two rows of x (int4: group_size a multiple of 128) */
 
