@@ -496,7 +496,7 @@ int32_t gq_int8_linear(gq_ctx* ctx, gq_buf x, uint64_t x_off, uint64_t m, uint64
         if (kernel == GQ_KERNEL_TENSOR) fail("gq_int8_linear: the tensor-core kernel is not built into this library");
         bool done = false;
         const char* name = "gemv_q8";
-        if (kernel == GQ_KERNEL_AUTO || kernel == GQ_KERNEL_UMMA) {
+        if (kernel == GQ_KERNEL_UMMA) {
             done = launch_gemv_q8_tc(ctx->stream, ctx->prop.multiProcessorCount, ctx->status_dev, xp, m, k, qp, sp, bp, n, yp);
             if (done) name = "gemv_q8_tc";
             if (!done && kernel == GQ_KERNEL_UMMA) fail("gq_int8_linear: the tcgen05 decode kernel takes one or two rows of x (m = %llu, k = %llu)", (unsigned long long)m, (unsigned long long)k);

@@ -87,8 +87,8 @@ __device__ __forceinline__ void tmem_st8(uint32_t addr, const uint32_t (&r)[8]) 
 // layout type 2 (128-byte swizzle) in bits 61-63. The tile must start on a
 // 1024-byte boundary; advancing along K inside the atom adds the byte offset
 // >> 4 to the start-address field.
-__device__ __forceinline__ uint64_t umma_desc_k128(uint32_t smem_addr) {
-    return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
+__device__ __forceinline__ uint64_t umma_desc_k128(uint32_t smem_addr, uint32_t sbo_bytes = 1024) {
+    return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(sbo_bytes >> 4) << 32) | ((uint64_t)1 << 46) |
            ((uint64_t)2 << 61);
 }
 
