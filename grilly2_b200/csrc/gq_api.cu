@@ -493,10 +493,16 @@ int32_t gq_int8_linear(gq_ctx* ctx, gq_buf x, uint64_t x_off, uint64_t m, uint64
         auto bp = bias ? (const float*)view(ctx, bias, b_off, n, 4, "gq_int8_linear bias") : nullptr;
         auto yp = (float*)view(ctx, y, 0, m * n, 4, "gq_int8_linear output");
         if (m == 0 || n == 0) return;  // quant.rs:267-269
-        if (kernel == GQ_KERNEL_TENSOR) fail("gq_int8_linear: the tensor-core kernel is not built into this library");
         bool done = false;
         const char* name = "gemv_q8";
-        if (kernel == GQ_KERNEL_UMMA) {
+        if (kernel == GQ_KERNEL_TENSOR || (kernel == GQ_KERNEL_AUTO && m >= kTensorMinRows)) {
+            done = launch_gemm_q8_tc(ctx->stream, ctx->prop.multiProcessorCount, ctx->status_dev, xp, m, k, qp, sp, bp, n, yp);
+            if (done) name = "gemm_tf32_q8";
+            if (!done && kernel == GQ_KERNEL_TENSOR)
+                fail("gq_int8_linear: the tensor-core GEMM needs in_features %% 4 == 0 and x on a 16-byte boundary (k = %llu, x_off = %llu)",
+                     (unsigned long long)k, (unsigned long long)x_off);
+        }
+        if (!done && kernel == GQ_KERNEL_UMMA) {
             done = launch_gemv_q8_tc(ctx->stream, ctx->prop.multiProcessorCount, ctx->status_dev, xp, m, k, qp, sp, bp, n, yp);
             if (done) name = "gemv_q8_tc";
             if (!done && kernel == GQ_KERNEL_UMMA) fail("gq_int8_linear: the tcgen05 decode kernel takes one or two rows of x (m = %llu, k = %llu)", (unsigned long long)m, (unsigned long long)k);
@@ -566,6 +572,7 @@ int32_t gq_int4_linear(gq_ctx* ctx, gq_buf x, uint64_t x_off, uint64_t m, uint64
         auto bp = bias ? (const float*)view(ctx, bias, b_off, n, 4, "gq_int4_linear bias") : nullptr;
         auto yp = (float*)view(ctx, y, 0, m * n, 4, "gq_int4_linear output");
         if (m == 0 || n == 0) return;
+        if (kernel == GQ_KERNEL_UMMA) fail("gq_int4_linear: the tcgen05 decode kernel is built for int8 weights only");
         if (kernel == GQ_KERNEL_TENSOR) fail("gq_int4_linear: there is no tensor-core int4 kernel (the reference has none either, crates/grilly-infer/src/quant4.rs:412-413)");
         bool done = false;
         const char* name = "gemv_q4";

@@ -111,4 +111,9 @@ bool launch_gemv_q4_imma(cudaStream_t s, int sm_count, uint32_t* status, const f
 bool launch_gemv_q8_tc(cudaStream_t s, int sm_count, uint32_t* status, const float* x, uint64_t m, uint64_t k, const uint32_t* q,
                        const float* scale, const float* bias, uint64_t n, float* y);
 
+bool launch_gemm_q8_tc(cudaStream_t s, int sm_count, uint32_t* status, const float* x, uint64_t m, uint64_t k, const uint32_t* q,
+                       const float* scale, const float* bias, uint64_t n, float* y);
+// Rows of x from which AUTO takes the tensor-core GEMM instead of a GEMV.
+constexpr uint64_t kTensorMinRows = 64;
+
 }  // namespace gq
