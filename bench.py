@@ -161,6 +161,68 @@ def run_reference(args) -> None:
     }))
 
 
+def run_prefill(args) -> None:
+    """Config 4: x float32 [rows, 4096] ~ N(0,1), W [14336, 4096] ~ N(0, 0.02) int8 per row; one step = one
+    call of the tensor-core GEMM. 2 M N K flops per step; the peak is half the measured bf16 rate (tf32 runs
+    at half of bf16 on these tensor cores), with cuBLAS's own tf32 rate on the same shape measured beside it."""
+    import ctypes
+    import torch
+    from grilly2_b200 import _C, _lib
+    m, n, k = args.rows, N_OUT, K_IN
+    rng = np.random.default_rng(3)
+    w = (rng.standard_normal((n, k)) * SIGMA).astype(np.float32)
+    x_np = rng.standard_normal((m, k)).astype(np.float32)
+    wt = _C.Int8Weight.quantize(_C.Tensor.from_numpy(w))
+    x = _C.Tensor.from_numpy(x_np)
+    lib, ctx = _lib.load(), _C.context()
+    sp = ctypes.c_void_p()
+    _lib.check(lib.gq_stream(ctx, ctypes.byref(sp)))
+    stream = torch.cuda.ExternalStream(sp.value)
+    for _ in range(max(args.warmup, 3)):
+        y = wt.linear(x, None, _lib.KERNEL_TENSOR)
+    _C.synchronize()
+    steps = min(args.steps, 200)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(steps):
+        y = wt.linear(x, None, _lib.KERNEL_TENSOR)
+    e1.record(stream)
+    _C.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    tflops = 2.0 * m * n * k / ms / 1e9
+    cublas = None
+    if not args.no_extras:
+        torch.backends.cuda.matmul.allow_tf32 = True
+        a, b = torch.from_numpy(x_np).cuda(), torch.from_numpy(w).cuda()
+        for _ in range(3):
+            c = a @ b.t()
+        torch.cuda.synchronize()
+        best = 1e9
+        for _ in range(10):
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record()
+            c = a @ b.t()
+            t1.record()
+            torch.cuda.synchronize()
+            best = min(best, t0.elapsed_time(t1))
+        cublas = 2.0 * m * n * k / best / 1e9
+    try:
+        peak, kind = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops"]) / 2, "measured bf16 / 2"
+    except Exception:
+        peak, kind = 1590.0 / 2, "fallback bf16 / 2"
+    print(json.dumps({
+        "metric": "int8_weight_only_prefill_gemm_tf32", "value": tflops, "unit": "TFLOP/s", "n_gpus": 1, "steps": steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "tf32", "data": "synthetic",
+        "config": {"workload": f"C4: int8 weight-only prefill GEMM, x[{m},{k}] . W[{n},{k}]^T, fp32 out (inputs "
+                               f"{(m * k * 4 + n * k) / 1e6:.0f} MB + output {m * n * 4 / 1e6:.0f} MB per step)", "m": m, "n": n, "k": k},
+        "roofline": {"bound": "tensor", "achieved": tflops, "peak": peak, "unit": "TFLOP/s", "frac": tflops / peak, "traffic": None,
+                     "peak_kind": kind, "kernel": "gemm_tf32_q8_kernel", "flops_per_launch": 2.0 * m * n * k,
+                     "cublas_tf32_same_shape_fp32_weights": cublas},
+        "gpu_launches": steps,
+    }))
+
+
 def workload_config(n_gpus: int) -> dict:
     return {"workload": f"C2: int4 group-{GROUP} decode linear, x[1,{K_IN}] . W[{N_OUT},{K_IN}]^T, {REPLICAS} weight copies per step "
                         f"({REPLICAS * algorithmic_bytes(1) / 1e6:.0f} MB > L2, so inputs larger than L2: no flush needed)",
@@ -176,9 +238,15 @@ def main() -> None:
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
     ap.add_argument("--no-extras", action="store_true")
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill"],
+                    help="decode: the headline int4 GEMV sweep; prefill: the int8 tf32 tensor-core GEMM of config 4")
+    ap.add_argument("--rows", type=int, default=2048, help="rows of x for --workload prefill")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+        return
+    if args.workload == "prefill":
+        run_prefill(args)
         return
 
     rank = int(os.environ.get("RANK", "0"))
