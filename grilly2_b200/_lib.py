@@ -65,8 +65,14 @@ PROTOTYPES = {
     "gq_capturing": [vp, P(u32)],
     "gq_graph_replay": [vp, vp],
     "gq_graph_nodes": [vp, P(u64)],
+    "gq_comm_unique_id": [vp, u64],
+    "gq_comm_create": [vp, i32, i32, vp, P(vp)],
+    "gq_all_gather_columns": [vp, vp, u64, u64, u64, u64],
+    "gq_buffer_ipc_export": [vp, u64, vp, u64],
+    "gq_buffer_ipc_open": [vp, vp, u64, P(u64)],
+    "gq_peer_gather": [vp, u64, u64, u64, i32, i32, P(u64), P(u64)],
 }
-VOID_FUNCTIONS = {"gq_destroy": [vp], "gq_graph_destroy": [vp, vp]}
+VOID_FUNCTIONS = {"gq_destroy": [vp], "gq_graph_destroy": [vp, vp], "gq_comm_destroy": [vp, vp]}
 
 _lib = None
 

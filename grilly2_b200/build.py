@@ -36,7 +36,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     os.makedirs(os.path.dirname(OUT), exist_ok=True)
     cmd = [nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17", "-shared",
            "-Xcompiler", "-fPIC,-fvisibility=hidden,-Wall", "-ccbin", "g++", f"-I{os.path.join(ROOT, 'include')}",
-           f"-I{CSRC}", "-DGQ_BUILD", "-o", OUT] + sources() + ["-ldl"]
+           f"-I{CSRC}", "-DGQ_BUILD", "-I/usr/include", "-o", OUT] + sources() + ["-ldl"]
     if verbose:
         cmd.insert(1, "-Xptxas=-v")
     subprocess.run(cmd, check=True)

@@ -78,6 +78,7 @@ static void drop_ref(gq_ctx* ctx, gq_buf h) {
     if (it == ctx->buffers.end()) return;
     Buffer& b = it->second;
     if (--b.refs > 0) return;
+    if (b.ipc && b.ptr) cudaIpcCloseMemHandle(b.ptr);
     if (b.owned && b.ptr) {
         if (b.mem == GQ_MEM_DEVICE_PERSISTENT) {
             cudaFree(b.ptr);  // waits for the device: nothing recorded can still be using it
@@ -695,6 +696,103 @@ void gq_graph_destroy(gq_ctx* ctx, gq_graph* graph) {
         if (graph->graph) cudaGraphDestroy(graph->graph);
         for (gq_buf h : graph->retained) drop_ref(ctx, h);
         delete graph;
+    });
+}
+
+// ── multi-GPU ────────────────────────────────────────────────────────────
+
+int32_t gq_comm_unique_id(void* out, uint64_t bytes) {
+    return guarded([&] {
+        if (!out || bytes < GQ_COMM_ID_BYTES) fail("gq_comm_unique_id: the id needs %d bytes", GQ_COMM_ID_BYTES);
+        comm_unique_id(out);
+    });
+}
+
+int32_t gq_comm_create(gq_ctx* ctx, int32_t nranks, int32_t rank, const void* unique_id, gq_comm** out) {
+    return guarded([&] {
+        Locked l(ctx);
+        if (!out || !unique_id) fail("gq_comm_create: null argument");
+        *out = nullptr;
+        *out = comm_create(nranks, rank, unique_id);
+    });
+}
+
+void gq_comm_destroy(gq_ctx* ctx, gq_comm* comm) {
+    if (!ctx || !comm) return;
+    guarded([&] {
+        Locked l(ctx);
+        cudaStreamSynchronize(ctx->stream);
+        comm_destroy(comm);
+    });
+}
+
+int32_t gq_all_gather_columns(gq_ctx* ctx, gq_comm* comm, gq_buf src, gq_buf dst, uint64_t m, uint64_t n_shard) {
+    return guarded([&] {
+        Locked l(ctx);
+        if (!comm) fail("gq_all_gather_columns: null communicator");
+        int nranks, rank;
+        comm_info(comm, &nranks, &rank);
+        check_dims("gq_all_gather_columns", m, n_shard * nranks);
+        auto sp = (const float*)view(ctx, src, 0, m * n_shard, 4, "gq_all_gather_columns source");
+        auto dp = (float*)view(ctx, dst, 0, m * n_shard * nranks, 4, "gq_all_gather_columns destination");
+        if (m == 0 || n_shard == 0) return;
+        all_gather_columns(ctx->stream, comm, sp, dp, m, n_shard);
+        after_launch(ctx, "nccl_all_gather", {src, dst});
+    });
+}
+
+int32_t gq_buffer_ipc_export(gq_ctx* ctx, gq_buf buf, void* out, uint64_t bytes) {
+    return guarded([&] {
+        Locked l(ctx);
+        static_assert(sizeof(cudaIpcMemHandle_t) <= GQ_IPC_HANDLE_BYTES, "ipc handle size");
+        if (!out || bytes < GQ_IPC_HANDLE_BYTES) fail("gq_buffer_ipc_export: the handle needs %d bytes", GQ_IPC_HANDLE_BYTES);
+        Buffer& b = lookup(ctx, buf, "gq_buffer_ipc_export");
+        if (!b.owned || b.ipc || !b.ptr) fail("gq_buffer_ipc_export: only non-empty buffers made by gq_buffer_create can be exported");
+        cudaIpcMemHandle_t h;
+        GQ_CUDA(cudaIpcGetMemHandle(&h, b.ptr));
+        memset(out, 0, GQ_IPC_HANDLE_BYTES);
+        memcpy(out, &h, sizeof h);
+    });
+}
+
+int32_t gq_buffer_ipc_open(gq_ctx* ctx, const void* handle, uint64_t buffer_bytes, gq_buf* out) {
+    return guarded([&] {
+        Locked l(ctx);
+        if (!out || !handle) fail("gq_buffer_ipc_open: null argument");
+        *out = 0;
+        cudaIpcMemHandle_t h;
+        memcpy(&h, handle, sizeof h);
+        void* p = nullptr;
+        GQ_CUDA(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+        Buffer b;
+        b.ptr = p;
+        b.bytes = buffer_bytes;
+        b.owned = false;
+        b.ipc = true;
+        gq_buf hnd = ctx->next_handle++;
+        ctx->buffers.emplace(hnd, b);
+        ctx->stats.buffers_outstanding++;
+        *out = hnd;
+    });
+}
+
+int32_t gq_peer_gather(gq_ctx* ctx, gq_buf src, uint64_t m, uint64_t n_shard, int32_t rank, int32_t nranks,
+                       const gq_buf* peer_y, const gq_buf* peer_flag) {
+    return guarded([&] {
+        Locked l(ctx);
+        if (nranks < 1 || nranks > 8 || rank < 0 || rank >= nranks) fail("gq_peer_gather: rank %d of %d is out of range (at most 8 ranks)", rank, nranks);
+        if (!peer_y || !peer_flag) fail("gq_peer_gather: null handle arrays");
+        check_dims("gq_peer_gather", m, n_shard * nranks);
+        auto sp = (const float*)view(ctx, src, 0, m * n_shard, 4, "gq_peer_gather source");
+        float* ys[8];
+        uint32_t* fl[8];
+        for (int i = 0; i < nranks; ++i) {
+            ys[i] = (float*)view(ctx, peer_y[i], 0, m * n_shard * nranks, 4, "gq_peer_gather y_full");
+            fl[i] = (uint32_t*)view(ctx, peer_flag[i], 0, nranks + 1, 4, "gq_peer_gather flags");
+        }
+        if (m == 0 || n_shard == 0) return;
+        launch_peer_gather(ctx->stream, ys, fl, sp, m, n_shard, rank, nranks, ctx->status_dev);
+        after_launch(ctx, "peer_gather", {src, peer_y[rank], peer_flag[rank]});
     });
 }
 

@@ -38,6 +38,7 @@ struct Buffer {
     bool owned = true;
     uint32_t refs = 1;  // the handle itself + one per graph that retains it
     bool released = false;
+    bool ipc = false;  // opened from another process's export: closed, not freed, on release
 };
 
 bool launch_gemv_q8_dp4a(cudaStream_t s, int sm_count, const float* x, uint64_t m, uint64_t k, const uint32_t* q, const float* scale,
@@ -115,5 +116,14 @@ bool launch_gemm_q8_tc(cudaStream_t s, int sm_count, uint32_t* status, const flo
                        const float* scale, const float* bias, uint64_t n, float* y);
 // Rows of x from which AUTO takes the tensor-core GEMM instead of a GEMV.
 constexpr uint64_t kTensorMinRows = 64;
+
+// multi-GPU (sharded.cu)
+void comm_unique_id(void* out128);
+gq_comm* comm_create(int nranks, int rank, const void* id128);
+void comm_destroy(gq_comm* c);
+void comm_info(gq_comm* c, int* nranks, int* rank);
+void all_gather_columns(cudaStream_t s, gq_comm* c, const float* src, float* dst, uint64_t m, uint64_t n_shard);
+void launch_peer_gather(cudaStream_t s, float* const* y, uint32_t* const* flag, const float* src, uint64_t m, uint64_t n_shard,
+                        int rank, int nranks, uint32_t* status);
 
 }  // namespace gq

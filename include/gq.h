@@ -52,6 +52,7 @@ extern "C" {
 
 typedef struct gq_ctx gq_ctx;
 typedef struct gq_graph gq_graph;
+typedef struct gq_comm gq_comm;
 typedef uint64_t gq_buf; /* 0 is never a valid handle */
 
 #define GQ_OK 0
@@ -195,6 +196,41 @@ int32_t gq_capturing(gq_ctx* ctx, uint32_t* out);
 int32_t gq_graph_replay(gq_ctx* ctx, gq_graph* graph);
 int32_t gq_graph_nodes(gq_graph* graph, uint64_t* out); /* operator launches the graph holds */
 void gq_graph_destroy(gq_ctx* ctx, gq_graph* graph);
+
+/* ── multi-GPU: column-sharded linears over the GPUs of one box ──────────
+ * No counterpart in the reference, which runs on a single device. One process
+ * (and one context) per GPU. Rank r owns output features [r n/W, (r+1) n/W):
+ * it quantizes and multiplies its own rows with the functions above, then the
+ * blocks of y are gathered so that every rank holds y[m][n]. */
+
+/* NCCL communicator. Rank 0 makes a 128-byte id (gq_comm_unique_id), the
+ * caller carries it to the other ranks, every rank calls gq_comm_create. */
+#define GQ_COMM_ID_BYTES 128
+int32_t gq_comm_unique_id(void* out, uint64_t bytes);
+int32_t gq_comm_create(gq_ctx* ctx, int32_t nranks, int32_t rank, const void* unique_id, gq_comm** out);
+void gq_comm_destroy(gq_ctx* ctx, gq_comm* comm);
+/* dst[r][rank * n_shard + c] = src(rank)[r][c] for every rank (ncclAllGather per row, one group), on the
+ * context's stream; may be captured. src holds m * n_shard floats, dst m * n_shard * nranks. */
+int32_t gq_all_gather_columns(gq_ctx* ctx, gq_comm* comm, gq_buf src, gq_buf dst, uint64_t m, uint64_t n_shard);
+
+/* Peer-mapped memory (CUDA IPC) for the put-and-signal gather below. Export
+ * fills 64 bytes the caller carries to the other processes of the box; open
+ * maps that memory here and returns a handle (releasing it unmaps). Only
+ * buffers made by gq_buffer_create can be exported. */
+#define GQ_IPC_HANDLE_BYTES 64
+int32_t gq_buffer_ipc_export(gq_ctx* ctx, gq_buf buf, void* out, uint64_t bytes);
+int32_t gq_buffer_ipc_open(gq_ctx* ctx, const void* handle, uint64_t buffer_bytes, gq_buf* out);
+
+/* This library's own gather over NVLink: every rank stores its block into each rank's y_full
+ * (peer_y[i] = a handle to rank i's y_full: its own buffer for i == rank, an ipc-opened one otherwise),
+ * then signals a counter in peer_flag[i] (nranks + 1 uint32 each — one counter per source rank and this
+ * rank's step number — zeroed once before the first call) and waits, at most ~2 s, for every peer's
+ * signal of this step. Every rank must make the same sequence of calls; the step number is kept on the
+ * device, so a captured call keeps counting when replayed. The caller alternates two y_full buffers
+ * between calls (a fast rank may store the next step while a slow one still reads this one). A wait
+ * that gives up is reported by the next host wait (GQ_ERR). */
+int32_t gq_peer_gather(gq_ctx* ctx, gq_buf src, uint64_t m, uint64_t n_shard, int32_t rank, int32_t nranks,
+                       const gq_buf* peer_y, const gq_buf* peer_flag);
 
 #if defined(GQ_BUILD) && defined(__GNUC__)
 #pragma GCC visibility pop
