@@ -223,6 +223,57 @@ def run_prefill(args) -> None:
     }))
 
 
+def sharded_c3(world, rank, dist, timed_fn, capture_mod, lib):
+    """Config 3: int4 g128 W[28672, 8192] column-sharded over `world` ranks, x[1, 8192] replicated. Times, per
+    call, this rank's GEMV alone, GEMV + NCCL all-gather of y, and GEMV + the put-and-signal peer gather (CUDA
+    graphs of 8 calls over distinct weight copies; max over ranks). Weights are seeded per rank: timing only."""
+    from grilly2_b200.sharded import Comm, PeerGather
+    _C = capture_mod
+    n, k, reps = 28672, 8192, 8
+    ns = n // world
+    rng = np.random.default_rng(2000 + rank)
+    w = (rng.standard_normal((ns, k)) * 0.015).astype(np.float32)
+    base = _C.Int4Weight.quantize(_C.Tensor.from_numpy(w), GROUP)
+    del w
+
+    def replica():
+        q = _C.Tensor.empty(base.packed().shape, "int32", persistent=True)
+        sc = _C.Tensor.empty(base.scale().shape, "float32", persistent=True)
+        z = _C.Tensor.empty(base.zero().shape, "float32", persistent=True)
+        q.copy_(base.packed()), sc.copy_(base.scale()), z.copy_(base.zero())
+        return _C.Int4Weight(q, sc, z, base.shape, GROUP)
+
+    ws = [replica() for _ in range(reps)]
+    x = _C.Tensor.from_numpy(np.random.default_rng(2).standard_normal((1, k)).astype(np.float32))
+    comm = Comm.from_torch_distributed()
+
+    def exchange(obj):
+        out = [None] * world
+        dist.all_gather_object(out, obj)
+        return out
+
+    peers = PeerGather(world, rank, 1, n, exchange)
+    out = {"world": world, "rows_per_rank": ns, "bytes_per_rank": base.nbytes + 4 * k + 4 * ns}
+    for name in ("gemv_only", "gemv_nccl_all_gather", "gemv_peer_gather"):
+        _C.begin_capture()
+        for wt in ws:
+            y = wt.linear(x)
+            if name == "gemv_nccl_all_gather":
+                comm.all_gather(y)
+            elif name == "gemv_peer_gather":
+                peers.gather(y)
+        graph = _C.end_capture()
+        us = timed_fn(graph, 200, 5) * 1e3 / (200 * reps)
+        out[name + "_us"] = us
+        out[name + "_GBps_per_rank"] = out["bytes_per_rank"] / (us * 1e-6) / 1e9
+        del graph
+    _C.synchronize()
+    dist.barrier()
+    peers.close()
+    comm.close()
+    return out
+
+
 def workload_config(n_gpus: int) -> dict:
     return {"workload": f"C2: int4 group-{GROUP} decode linear, x[1,{K_IN}] . W[{N_OUT},{K_IN}]^T, {REPLICAS} weight copies per step "
                         f"({REPLICAS * algorithmic_bytes(1) / 1e6:.0f} MB > L2, so inputs larger than L2: no flush needed)",
@@ -377,6 +428,9 @@ def main() -> None:
         extras["m1_reference_order_float_kernel_us_per_launch"] = t
         extras["weight_only_GBps"] = base.nbytes / (per_launch_us * 1e-6) / 1e9  # the reference's own convention
         extras["frac_of_nominal_8TBps"] = achieved / 8000.0
+
+    if world > 1 and not args.no_extras:
+        extras["sharded_c3"] = sharded_c3(world, rank, dist, timed_fn=timed, capture_mod=_C, lib=_lib)
 
     if rank != 0:
         if dist is not None:
