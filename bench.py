@@ -281,6 +281,15 @@ def workload_config(n_gpus: int) -> dict:
             "parallelism": f"{n_gpus} independent rank(s), each streaming its own weight copies"}
 
 
+def _quiet_stdout():
+    """Libraries (NCCL's version banner) write to file descriptor 1; the contract is ONE JSON line on stdout.
+    Point fd 1 at stderr for the run and hand back a file on the real stdout for the result line."""
+    real = os.fdopen(os.dup(1), "w")
+    sys.stdout.flush()
+    os.dup2(2, 1)
+    return real
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -293,6 +302,15 @@ def main() -> None:
                     help="decode: the headline int4 GEMV sweep; prefill: the int8 tf32 tensor-core GEMM of config 4")
     ap.add_argument("--rows", type=int, default=2048, help="rows of x for --workload prefill")
     args = ap.parse_args()
+    global print
+    _real = _quiet_stdout()
+    _builtin_print = print
+
+    def print(*a, **kw):  # noqa: A001 - every result line of this file goes to the real stdout
+        kw.setdefault("file", _real)
+        kw.setdefault("flush", True)
+        _builtin_print(*a, **kw)
+
     if args.impl == "reference":
         run_reference(args)
         return
