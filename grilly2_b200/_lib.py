@@ -65,6 +65,14 @@ PROTOTYPES = {
     "gq_capturing": [vp, P(u32)],
     "gq_graph_replay": [vp, vp],
     "gq_graph_nodes": [vp, P(u64)],
+    "gq_embedding": [vp, u64, u64, u64, u64, u64, u64],
+    "gq_add_rms_norm": [vp, u64, u64, u64, u64, u64, ctypes.c_float, u64, u64],
+    "gq_rope_kv_append": [vp, u64, u64, u64, u64, u64, u64, u64, u64, u64, u64, u64, u64, u64, u64, u64],
+    "gq_kv_advance": [vp, u64, u64, u64],
+    "gq_attn_scratch_bytes": [vp, u64, u64, u64, P(u64)],
+    "gq_attn_decode": [vp, u64, u64, u64, u64, u64, u64, u64, u64, u64, u64, u64, u64, ctypes.c_float, u64, u64],
+    "gq_swiglu": [vp, u64, u64, u64, u64],
+    "gq_argmax_rows": [vp, u64, u64, u64, u64],
     "gq_comm_unique_id": [vp, u64],
     "gq_comm_create": [vp, i32, i32, vp, P(vp)],
     "gq_all_gather_columns": [vp, vp, u64, u64, u64, u64],

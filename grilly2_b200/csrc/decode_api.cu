@@ -1,0 +1,133 @@
+// C ABI of the decode-step operators (include/gq.h, "decode step"): argument
+// checks against buffer sizes, then the launchers of decode_ops.cu.
+#include "gq_internal.h"
+
+using namespace gq;
+
+extern "C" {
+
+int32_t gq_embedding(gq_ctx* ctx, gq_buf table, gq_buf ids, uint64_t rows, uint64_t width, uint64_t vocab, gq_buf out) {
+    return guarded([&] {
+        Locked l(ctx);
+        check_dims("gq_embedding", rows, width, vocab);
+        auto tp = (const float*)view(ctx, table, 0, vocab * width, 4, "gq_embedding table");
+        auto ip = (const int32_t*)view(ctx, ids, 0, rows, 4, "gq_embedding ids");
+        auto op = (float*)view(ctx, out, 0, rows * width, 4, "gq_embedding output");
+        if (rows == 0 || width == 0) return;
+        launch_embedding(ctx->stream, tp, ip, rows, width, vocab, op);
+        after_launch(ctx, "embedding", {table, ids, out});
+    });
+}
+
+int32_t gq_add_rms_norm(gq_ctx* ctx, gq_buf x, gq_buf residual, gq_buf weight, uint64_t rows, uint64_t n, float eps, gq_buf y,
+                        gq_buf h) {
+    return guarded([&] {
+        Locked l(ctx);
+        check_dims("gq_add_rms_norm", rows, n);
+        if (n == 0) fail("gq_add_rms_norm: rows of no elements");
+        auto xp = (const float*)view(ctx, x, 0, rows * n, 4, "gq_add_rms_norm input");
+        auto rp = residual ? (const float*)view(ctx, residual, 0, rows * n, 4, "gq_add_rms_norm residual") : nullptr;
+        auto wp = weight ? (const float*)view(ctx, weight, 0, n, 4, "gq_add_rms_norm weight") : nullptr;
+        auto yp = (float*)view(ctx, y, 0, rows * n, 4, "gq_add_rms_norm output");
+        auto hp = h ? (float*)view(ctx, h, 0, rows * n, 4, "gq_add_rms_norm sum output") : nullptr;
+        if (rows == 0) return;
+        launch_add_rms_norm(ctx->stream, xp, rp, wp, rows, n, eps, yp, hp);
+        after_launch(ctx, "add_rms_norm", {x, residual, weight, y, h});
+    });
+}
+
+static void check_heads(const char* op, uint64_t heads, uint64_t kv_heads, uint64_t dim, uint64_t max_len) {
+    check_dims(op, heads, kv_heads, dim);
+    check_dims(op, max_len, 1);
+    if (heads == 0 || kv_heads == 0 || heads % kv_heads) fail("%s: %llu heads do not group over %llu kv heads", op, (unsigned long long)heads, (unsigned long long)kv_heads);
+    if (dim == 0 || dim > 128 || 128 % dim || dim % 2) fail("%s: head_dim must be 32, 64 or 128, got %llu", op, (unsigned long long)dim);
+    if (max_len == 0) fail("%s: a cache of no positions", op);
+}
+
+int32_t gq_rope_kv_append(gq_ctx* ctx, gq_buf qkv, gq_buf cos, gq_buf sin, gq_buf lens, uint64_t layer, uint64_t layers, uint64_t heads,
+                          uint64_t kv_heads, uint64_t dim, uint64_t max_len, gq_buf q_out, gq_buf kcache, uint64_t k_off, gq_buf vcache,
+                          uint64_t v_off) {
+    return guarded([&] {
+        Locked l(ctx);
+        check_heads("gq_rope_kv_append", heads, kv_heads, dim, max_len);
+        if (layer >= layers) fail("gq_rope_kv_append: layer %llu of %llu", (unsigned long long)layer, (unsigned long long)layers);
+        auto qp = (const float*)view(ctx, qkv, 0, (heads + 2 * kv_heads) * dim, 4, "gq_rope_kv_append qkv");
+        auto cp = (const float*)view(ctx, cos, 0, max_len * dim, 4, "gq_rope_kv_append cos");
+        auto sp = (const float*)view(ctx, sin, 0, max_len * dim, 4, "gq_rope_kv_append sin");
+        auto lp = (const uint32_t*)view(ctx, lens, 0, layers, 4, "gq_rope_kv_append cursor");
+        auto op = (float*)view(ctx, q_out, 0, heads * dim, 4, "gq_rope_kv_append q output");
+        auto kp = (float*)view(ctx, kcache, k_off, kv_heads * max_len * dim, 4, "gq_rope_kv_append key cache");
+        auto vp = (float*)view(ctx, vcache, v_off, kv_heads * max_len * dim, 4, "gq_rope_kv_append value cache");
+        launch_rope_kv_append(ctx->stream, qp, cp, sp, lp, (uint32_t)layer, (uint32_t)heads, (uint32_t)kv_heads, (uint32_t)dim,
+                              (uint32_t)max_len, op, kp, vp);
+        after_launch(ctx, "rope_kv_append", {qkv, cos, sin, lens, q_out, kcache, vcache});
+    });
+}
+
+int32_t gq_kv_advance(gq_ctx* ctx, gq_buf lens, uint64_t layers, uint64_t max_len) {
+    return guarded([&] {
+        Locked l(ctx);
+        check_dims("gq_kv_advance", layers, max_len);
+        auto lp = (uint32_t*)view(ctx, lens, 0, layers, 4, "gq_kv_advance cursor");
+        if (layers == 0) return;
+        launch_kv_advance(ctx->stream, lp, (uint32_t)layers, (uint32_t)max_len);
+        after_launch(ctx, "kv_advance", {lens});
+    });
+}
+
+int32_t gq_attn_scratch_bytes(gq_ctx* ctx, uint64_t heads, uint64_t dim, uint64_t max_len, uint64_t* out) {
+    return guarded([&] {
+        Locked l(ctx);
+        if (!out) fail("gq_attn_scratch_bytes: null out pointer");
+        check_heads("gq_attn_scratch_bytes", heads, heads, dim, max_len);
+        const uint32_t splits = attn_splits((uint32_t)heads, (uint32_t)max_len, ctx->prop.multiProcessorCount);
+        *out = attn_scratch_floats((uint32_t)heads, (uint32_t)dim, splits) * 4;
+    });
+}
+
+int32_t gq_attn_decode(gq_ctx* ctx, gq_buf q, gq_buf kcache, uint64_t k_off, gq_buf vcache, uint64_t v_off, gq_buf lens, uint64_t layer,
+                       uint64_t layers, uint64_t heads, uint64_t kv_heads, uint64_t dim, uint64_t max_len, float scale, gq_buf scratch,
+                       gq_buf out) {
+    return guarded([&] {
+        Locked l(ctx);
+        check_heads("gq_attn_decode", heads, kv_heads, dim, max_len);
+        if (layer >= layers) fail("gq_attn_decode: layer %llu of %llu", (unsigned long long)layer, (unsigned long long)layers);
+        const uint32_t splits = attn_splits((uint32_t)heads, (uint32_t)max_len, ctx->prop.multiProcessorCount);
+        auto qp = (const float*)view(ctx, q, 0, heads * dim, 4, "gq_attn_decode q");
+        auto kp = (const float*)view(ctx, kcache, k_off, kv_heads * max_len * dim, 4, "gq_attn_decode key cache");
+        auto vp = (const float*)view(ctx, vcache, v_off, kv_heads * max_len * dim, 4, "gq_attn_decode value cache");
+        auto lp = (const uint32_t*)view(ctx, lens, 0, layers, 4, "gq_attn_decode cursor");
+        auto sp = (float*)view(ctx, scratch, 0, attn_scratch_floats((uint32_t)heads, (uint32_t)dim, splits), 4, "gq_attn_decode scratch");
+        auto op = (float*)view(ctx, out, 0, heads * dim, 4, "gq_attn_decode output");
+        launch_attn_decode(ctx->stream, qp, kp, vp, lp, (uint32_t)layer, (uint32_t)heads, (uint32_t)kv_heads, (uint32_t)dim,
+                           (uint32_t)max_len, scale, splits, sp, op);
+        after_launch(ctx, "attn_decode", {q, kcache, vcache, lens, scratch, out});
+    });
+}
+
+int32_t gq_swiglu(gq_ctx* ctx, gq_buf gate_up, uint64_t rows, uint64_t width, gq_buf out) {
+    return guarded([&] {
+        Locked l(ctx);
+        check_dims("gq_swiglu", rows, 2 * width);
+        auto gp = (const float*)view(ctx, gate_up, 0, rows * 2 * width, 4, "gq_swiglu input");
+        auto op = (float*)view(ctx, out, 0, rows * width, 4, "gq_swiglu output");
+        if (rows == 0 || width == 0) return;
+        launch_swiglu(ctx->stream, gp, rows, width, op);
+        after_launch(ctx, "swiglu", {gate_up, out});
+    });
+}
+
+int32_t gq_argmax_rows(gq_ctx* ctx, gq_buf v, uint64_t rows, uint64_t n, gq_buf out) {
+    return guarded([&] {
+        Locked l(ctx);
+        check_dims("gq_argmax_rows", rows, n);
+        if (n == 0) fail("gq_argmax_rows: rows of no elements");
+        auto vp = (const float*)view(ctx, v, 0, rows * n, 4, "gq_argmax_rows input");
+        auto op = (int32_t*)view(ctx, out, 0, rows, 4, "gq_argmax_rows output");
+        if (rows == 0) return;
+        launch_argmax_rows(ctx->stream, vp, rows, n, op);
+        after_launch(ctx, "argmax_rows", {v, out});
+    });
+}
+
+}  // extern "C"

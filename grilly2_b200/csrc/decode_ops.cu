@@ -1,0 +1,341 @@
+// The non-linear tenth of a decode step of a Llama/Qwen2-shaped model, for
+// the int8 weight-only full-step configuration: embedding lookup, add +
+// RMSNorm, rotary embedding into the KV cache, grouped-query decode attention
+// (split over the cache length), SwiGLU, greedy argmax. They replace the
+// reference's shaders
+//   g2-index.glsl:22-38, g2-rms-norm.glsl:54-74, g2-rope.glsl:24-40,
+//   g2-kv-write.glsl:43-72, g2-kv-advance.glsl:18-21,
+//   g2-attn-decode{,-split,-merge}.glsl, g2-swiglu.glsl:21-29,
+//   g2-argreduce-rows.glsl:42-77   (all under crates/grilly-core/shaders/).
+//
+// Everything a step needs to know about *where it is* comes from device
+// memory — the token id, the cache cursor (which is also the rotary position
+// of q AND k) — never from a kernel argument, so a captured step replays
+// correctly: the reference pushes q's position from the host
+// (python/grilly/infer/models/llama.py:168-173), which a replay would bake in.
+//
+// All kernels here are small and latency-bound; the step's time is the
+// quantized linears' (97 of them, ~494 of ~522 MB per token).
+#include "gq_internal.h"
+
+namespace gq {
+
+namespace {
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ double warp_sum(double v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// out[r][:] = table[ids[r]][:]; an id outside the table yields a row of NaN
+// (the reference raises a deferred IndexError from a fault buffer).
+__global__ void __launch_bounds__(256) embedding_kernel(const float* __restrict__ table, const int32_t* __restrict__ ids,
+                                                       uint32_t rows, uint32_t width, uint32_t vocab, float* __restrict__ out) {
+    for (uint32_t r = blockIdx.x; r < rows; r += gridDim.x) {
+        const int32_t id = ids[r];
+        const bool ok = id >= 0 && (uint32_t)id < vocab;
+        for (uint32_t c = threadIdx.x; c < width; c += blockDim.x)
+            out[(size_t)r * width + c] = ok ? table[(size_t)id * width + c] : __uint_as_float(0x7fc00000u);
+    }
+}
+
+// h = x (+ residual); y = h * (1 / sqrt(mean(h^2) + eps)) * w, torch's order
+// of operations (g2-rms-norm.glsl:54-74). The sum of squares is taken in
+// float64, which rounds to float32 where the shader's compensated sum does.
+__global__ void __launch_bounds__(256) add_rms_norm_kernel(const float* __restrict__ x, const float* __restrict__ res,
+                                                          const float* __restrict__ w, uint32_t rows, uint32_t n, float eps,
+                                                          float* __restrict__ y, float* __restrict__ h) {
+    __shared__ double s_part[8];
+    __shared__ float s_r;
+    for (uint32_t row = blockIdx.x; row < rows; row += gridDim.x) {
+        const float* xr = x + (size_t)row * n;
+        const float* rr = res ? res + (size_t)row * n : nullptr;
+        double ss = 0.0;
+        for (uint32_t k = threadIdx.x; k < n; k += 256) {
+            const float v = rr ? __fadd_rn(xr[k], rr[k]) : xr[k];
+            ss += (double)__fmul_rn(v, v);
+        }
+        ss = warp_sum(ss);
+        if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = ss;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            double t = 0.0;
+            for (int i = 0; i < 8; ++i) t += s_part[i];
+            const float mean = __fdiv_rn((float)t, (float)n);
+            s_r = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, eps)));
+        }
+        __syncthreads();
+        const float r = s_r;
+        for (uint32_t k = threadIdx.x; k < n; k += 256) {
+            const float v = rr ? __fadd_rn(xr[k], rr[k]) : xr[k];
+            if (h) h[(size_t)row * n + k] = v;
+            float yv = __fmul_rn(v, r);
+            if (w) yv = __fmul_rn(yv, w[k]);
+            y[(size_t)row * n + k] = yv;
+        }
+        __syncthreads();
+    }
+}
+
+// One decode token's q, k, v (the fused projection's output row, q | k | v):
+// rotate q and k at the cursor's position (y = x cos + rotate_half(x) sin, two
+// multiplies and an add as g2-rope.glsl:33-39), write q out, append k and v to
+// the cache at the cursor. A full cache takes nothing more (g2-kv-write.glsl:46-50).
+__global__ void __launch_bounds__(256) rope_kv_append_kernel(const float* __restrict__ qkv, const float* __restrict__ cosv,
+                                                            const float* __restrict__ sinv, const uint32_t* __restrict__ lens,
+                                                            uint32_t layer, uint32_t heads, uint32_t kv_heads, uint32_t dim,
+                                                            uint32_t max_len, float* __restrict__ q_out, float* __restrict__ kc,
+                                                            float* __restrict__ vc) {
+    const uint32_t pos = lens[layer];
+    const uint32_t total = (heads + 2 * kv_heads) * dim, half = dim / 2;
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+        const uint32_t hd = i / dim, d = i % dim;
+        const float xv = qkv[i];
+        if (hd < heads + kv_heads) {  // q or k: rotary
+            const uint32_t p = min(pos, max_len - 1);
+            const float rv = d < half ? -qkv[i + half] : qkv[i - half];
+            const float y = __fadd_rn(__fmul_rn(xv, cosv[(size_t)p * dim + d]), __fmul_rn(rv, sinv[(size_t)p * dim + d]));
+            if (hd < heads)
+                q_out[i] = y;
+            else if (pos < max_len)
+                kc[((size_t)(hd - heads) * max_len + pos) * dim + d] = y;
+        } else if (pos < max_len) {
+            vc[((size_t)(hd - heads - kv_heads) * max_len + pos) * dim + d] = xv;
+        }
+    }
+}
+
+// lens[l] = min(lens[l] + 1, max_len) for every layer: once per step, after the last layer has attended.
+__global__ void kv_advance_kernel(uint32_t* lens, uint32_t layers, uint32_t max_len) {
+    const uint32_t l = blockIdx.x * blockDim.x + threadIdx.x;
+    if (l < layers) lens[l] = min(lens[l] + 1, max_len);
+}
+
+// exp as the reference computes it (Cephes expf, g2-common.glsl:21-31), with
+// every operation rounded on its own so that the CPU oracle can match it.
+__device__ __forceinline__ float exp_cephes(float v) {
+    if (v > 88.72283935546875f) return __uint_as_float(0x7f800000u);
+    if (v < -103.97207641601562f) return 0.0f;
+    const float k = floorf(__fadd_rn(__fmul_rn(v, 1.44269504088896341f), 0.5f));
+    float r = __fsub_rn(v, __fmul_rn(k, 0.693359375f));
+    r = __fadd_rn(r, __fmul_rn(k, 2.12194440e-4f));
+    const float z = __fmul_rn(r, r);
+    float p = 1.9875691500e-4f;
+    p = __fadd_rn(__fmul_rn(p, r), 1.3981999507e-3f);
+    p = __fadd_rn(__fmul_rn(p, r), 8.3334519073e-3f);
+    p = __fadd_rn(__fmul_rn(p, r), 4.1665795894e-2f);
+    p = __fadd_rn(__fmul_rn(p, r), 1.6666665459e-1f);
+    p = __fadd_rn(__fmul_rn(p, r), 5.0000001201e-1f);
+    const float yv = __fadd_rn(__fadd_rn(__fmul_rn(p, z), r), 1.0f);
+    return ldexpf(yv, (int)k);
+}
+
+// out[r][j] = (g * sigmoid(g)) * u with g = gate_up[r][j], u = gate_up[r][width + j] (g2-swiglu.glsl:21-29;
+// sigmoid as g2-common.glsl:163-166).
+__global__ void __launch_bounds__(256) swiglu_kernel(const float* __restrict__ gate_up, uint32_t rows, uint32_t width,
+                                                    float* __restrict__ out) {
+    const size_t total = (size_t)rows * width;
+    for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < total; i += (size_t)gridDim.x * 256) {
+        const size_t r = i / width, j = i % width;
+        const float g = gate_up[r * 2 * width + j], u = gate_up[r * 2 * width + width + j];
+        const float e = exp_cephes(-fabsf(g));
+        const float sg = g >= 0.0f ? __fdiv_rn(1.0f, __fadd_rn(1.0f, e)) : __fdiv_rn(e, __fadd_rn(1.0f, e));
+        out[i] = __fmul_rn(__fmul_rn(g, sg), u);
+    }
+}
+
+// Greedy next token: the index of each row's maximum (the first one on ties).
+__global__ void __launch_bounds__(1024) argmax_rows_kernel(const float* __restrict__ v, uint32_t rows, uint32_t n,
+                                                          int32_t* __restrict__ out) {
+    __shared__ float s_val[32];
+    __shared__ uint32_t s_idx[32];
+    for (uint32_t row = blockIdx.x; row < rows; row += gridDim.x) {
+        float best = -INFINITY;
+        uint32_t idx = 0xffffffffu;
+        for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {
+            const float x = v[(size_t)row * n + i];
+            if (x > best || idx == 0xffffffffu) best = x, idx = i;  // strides ascend, so the first maximum wins
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const uint32_t oi = __shfl_xor_sync(0xffffffffu, idx, o);
+            if (ob > best || (ob == best && oi < idx)) best = ob, idx = oi;
+        }
+        if ((threadIdx.x & 31) == 0) s_val[threadIdx.x >> 5] = best, s_idx[threadIdx.x >> 5] = idx;
+        __syncthreads();
+        if (threadIdx.x < 32) {
+            best = threadIdx.x < blockDim.x / 32 ? s_val[threadIdx.x] : -INFINITY;
+            idx = threadIdx.x < blockDim.x / 32 ? s_idx[threadIdx.x] : 0xffffffffu;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+                const uint32_t oi = __shfl_xor_sync(0xffffffffu, idx, o);
+                if (ob > best || (ob == best && oi < idx)) best = ob, idx = oi;
+            }
+            if (threadIdx.x == 0) out[row] = (int32_t)idx;
+        }
+        __syncthreads();
+    }
+}
+
+// Grouped-query attention of one new token against the cache ("flash decoding"):
+// CTA (split s, head h) scores keys [s * chunk, (s + 1) * chunk) of the head's
+// KV group, keeps (max, sum of exp, weighted sum of values) and writes them to
+// scratch; the last CTA of a head to finish — found with a counter in scratch,
+// which it then resets — merges the splits:
+//   out = sum_s acc_s exp(m_s - M) / sum_s z_s exp(m_s - M),  M = max_s m_s.
+// The length is the cache cursor plus the token just appended, read from
+// device memory. scratch: heads * splits * (dim + 2) floats, then `heads`
+// counters that must be zero before the first call.
+constexpr int kAttnThreads = 128;
+constexpr uint32_t kAttnMaxChunk = 512;  // keys per split (scores live in shared memory)
+
+__global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const float* __restrict__ q, const float* __restrict__ kc,
+                                                                  const float* __restrict__ vc, const uint32_t* __restrict__ lens,
+                                                                  uint32_t layer, uint32_t heads, uint32_t kv_heads, uint32_t dim,
+                                                                  uint32_t max_len, float scale, uint32_t chunk, float* scratch,
+                                                                  float* __restrict__ out) {
+    __shared__ float s_q[128];
+    __shared__ float s_sc[kAttnMaxChunk];
+    __shared__ float s_red[kAttnThreads / 32];
+    __shared__ float s_acc[kAttnThreads];
+    __shared__ bool s_last;
+    const uint32_t split = blockIdx.x, splits = gridDim.x, h = blockIdx.y;
+    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t g = h / (heads / kv_heads);
+    const uint32_t len = min(lens[layer] + 1, max_len);
+    const uint32_t j0 = split * chunk, j1 = min(len, j0 + chunk);
+    const float* kb = kc + (size_t)g * max_len * dim;
+    const float* vb = vc + (size_t)g * max_len * dim;
+    float* part = scratch + ((size_t)h * splits + split) * (dim + 2);
+    uint32_t* counters = reinterpret_cast<uint32_t*>(scratch + (size_t)heads * splits * (dim + 2));
+
+    if (tid < dim) s_q[tid] = q[(size_t)h * dim + tid];
+    __syncthreads();
+
+    // scores: one key per warp at a time, lanes across the head dimension
+    float m = -INFINITY;
+    for (uint32_t j = j0 + warp; j < j1; j += kAttnThreads / 32) {
+        float sdot = 0.0f;
+        for (uint32_t d = lane; d < dim; d += 32) sdot = __fmaf_rn(s_q[d], kb[(size_t)j * dim + d], sdot);
+        sdot = warp_sum(sdot) * scale;
+        if (lane == 0) s_sc[j - j0] = sdot;
+        m = fmaxf(m, sdot);
+    }
+    if (lane == 0) s_red[warp] = m;
+    __syncthreads();
+    m = fmaxf(fmaxf(s_red[0], s_red[1]), fmaxf(s_red[2], s_red[3]));
+    __syncthreads();
+
+    float z = 0.0f;
+    for (uint32_t j = j0 + tid; j < j1; j += kAttnThreads) {
+        const float e = exp_cephes(s_sc[j - j0] - m);
+        s_sc[j - j0] = e;
+        z += e;
+    }
+    z = warp_sum(z);
+    if (lane == 0) s_red[warp] = z;
+    __syncthreads();
+    z = (s_red[0] + s_red[1]) + (s_red[2] + s_red[3]);
+
+    // weighted values: groups of `dim` threads stride over the keys
+    const uint32_t groups = kAttnThreads / dim, d = tid % dim, grp = tid / dim;
+    float acc = 0.0f;
+    if (grp < groups)
+        for (uint32_t j = j0 + grp; j < j1; j += groups) acc = __fmaf_rn(s_sc[j - j0], vb[(size_t)j * dim + d], acc);
+    s_acc[tid] = acc;
+    __syncthreads();
+    if (tid < dim) {
+        float t = 0.0f;
+        for (uint32_t k = 0; k < groups; ++k) t += s_acc[k * dim + tid];
+        part[2 + tid] = t;
+    }
+    if (tid == 0) part[0] = m, part[1] = z;
+
+    // the last split of this head to arrive merges
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        const uint32_t seen = atomicAdd(counters + h, 1u);
+        s_last = seen == splits - 1;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    const float* hp = scratch + (size_t)h * splits * (dim + 2);
+    float M = -INFINITY;
+    for (uint32_t s = 0; s < splits; ++s) M = fmaxf(M, hp[s * (dim + 2)]);
+    if (tid < dim) {
+        float Z = 0.0f, o = 0.0f;
+        for (uint32_t s = 0; s < splits; ++s) {
+            const float ms = hp[s * (dim + 2)];
+            const float wgt = ms == -INFINITY ? 0.0f : exp_cephes(ms - M);  // an empty split contributes nothing
+            Z = __fmaf_rn(hp[s * (dim + 2) + 1], wgt, Z);
+            o = __fmaf_rn(hp[s * (dim + 2) + 2 + tid], wgt, o);
+        }
+        out[(size_t)h * dim + tid] = __fdiv_rn(o, Z);
+    }
+    if (tid == 0) counters[h] = 0;  // ready for the next call
+}
+
+
+}  // namespace
+
+static inline uint32_t blocks_for(size_t items, uint32_t per, uint32_t cap) {
+    size_t b = (items + per - 1) / per;
+    return (uint32_t)(b < 1 ? 1 : b > cap ? cap : b);
+}
+
+void launch_embedding(cudaStream_t s, const float* table, const int32_t* ids, uint64_t rows, uint64_t width, uint64_t vocab, float* out) {
+    embedding_kernel<<<blocks_for(rows, 1, 1024), 256, 0, s>>>(table, ids, (uint32_t)rows, (uint32_t)width, (uint32_t)vocab, out);
+}
+void launch_add_rms_norm(cudaStream_t s, const float* x, const float* res, const float* w, uint64_t rows, uint64_t n, float eps,
+                         float* y, float* h) {
+    add_rms_norm_kernel<<<blocks_for(rows, 1, 1024), 256, 0, s>>>(x, res, w, (uint32_t)rows, (uint32_t)n, eps, y, h);
+}
+void launch_rope_kv_append(cudaStream_t s, const float* qkv, const float* cosv, const float* sinv, const uint32_t* lens, uint32_t layer,
+                           uint32_t heads, uint32_t kv_heads, uint32_t dim, uint32_t max_len, float* q_out, float* kc, float* vc) {
+    const uint32_t total = (heads + 2 * kv_heads) * dim;
+    rope_kv_append_kernel<<<blocks_for(total, 256, 64), 256, 0, s>>>(qkv, cosv, sinv, lens, layer, heads, kv_heads, dim, max_len, q_out,
+                                                                    kc, vc);
+}
+void launch_kv_advance(cudaStream_t s, uint32_t* lens, uint32_t layers, uint32_t max_len) {
+    kv_advance_kernel<<<(layers + 127) / 128, 128, 0, s>>>(lens, layers, max_len);
+}
+// Splits of the cache length: enough CTAs to occupy the GPU, at most kAttnMaxChunk keys each.
+uint32_t attn_splits(uint32_t heads, uint32_t max_len, int sm_count) {
+    uint32_t splits = ((uint32_t)sm_count + heads - 1) / heads;
+    const uint32_t need = (max_len + kAttnMaxChunk - 1) / kAttnMaxChunk;
+    if (splits < need) splits = need;
+    if (splits > (max_len + 31) / 32) splits = (max_len + 31) / 32;
+    return splits < 1 ? 1 : splits;
+}
+uint64_t attn_scratch_floats(uint32_t heads, uint32_t dim, uint32_t splits) { return (uint64_t)heads * splits * (dim + 2) + heads; }
+void launch_attn_decode(cudaStream_t s, const float* q, const float* kc, const float* vc, const uint32_t* lens, uint32_t layer,
+                        uint32_t heads, uint32_t kv_heads, uint32_t dim, uint32_t max_len, float scale, uint32_t splits, float* scratch,
+                        float* out) {
+    const uint32_t chunk = (max_len + splits - 1) / splits;
+    attn_decode_kernel<<<dim3(splits, heads), kAttnThreads, 0, s>>>(q, kc, vc, lens, layer, heads, kv_heads, dim, max_len, scale, chunk,
+                                                                   scratch, out);
+}
+void launch_swiglu(cudaStream_t s, const float* gate_up, uint64_t rows, uint64_t width, float* out) {
+    swiglu_kernel<<<blocks_for(rows * width, 256, 148 * 8), 256, 0, s>>>(gate_up, (uint32_t)rows, (uint32_t)width, out);
+}
+void launch_argmax_rows(cudaStream_t s, const float* v, uint64_t rows, uint64_t n, int32_t* out) {
+    argmax_rows_kernel<<<blocks_for(rows, 1, 1024), 1024, 0, s>>>(v, (uint32_t)rows, (uint32_t)n, out);
+}
+
+
+}  // namespace gq

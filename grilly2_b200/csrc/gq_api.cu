@@ -26,31 +26,9 @@ void fail(const char* fmt, ...) {
     throw Failure(buf);
 }
 
-template <class F>
-static int32_t guarded(F&& f) {
-    try {
-        f();
-        return GQ_OK;
-    } catch (const std::exception& e) {
-        g_last_error = e.what();
-    } catch (...) {
-        g_last_error = "unknown error";
-    }
-    return GQ_ERR;
-}
+void set_last_error(const char* msg) { g_last_error = msg; }
 
-static gq_ctx* need(gq_ctx* ctx) {
-    if (!ctx) fail("null context");
-    return ctx;
-}
-
-struct Locked {
-    gq_ctx* ctx;
-    std::lock_guard<std::mutex> lock;
-    explicit Locked(gq_ctx* c) : ctx(need(c)), lock(c->mutex) { GQ_CUDA(cudaSetDevice(c->device)); }
-};
-
-static Buffer& lookup(gq_ctx* ctx, gq_buf h, const char* what) {
+Buffer& lookup(gq_ctx* ctx, gq_buf h, const char* what) {
     auto it = ctx->buffers.find(h);
     if (h == 0 || it == ctx->buffers.end() || it->second.released) fail("%s: invalid buffer handle %llu", what, (unsigned long long)h);
     return it->second;
@@ -63,6 +41,11 @@ void* view(gq_ctx* ctx, gq_buf h, uint64_t off, uint64_t count, uint64_t elem, c
         fail("%s: needs %llu elements of %llu bytes at element offset %llu, but the buffer holds %llu bytes", what,
              (unsigned long long)count, (unsigned long long)elem, (unsigned long long)off, (unsigned long long)b.bytes);
     return static_cast<char*>(b.ptr) + off * elem;
+}
+
+void check_dims(const char* op, uint64_t a, uint64_t b, uint64_t c) {
+    const uint64_t max_dim = 0x7fffffffull;  // kernels index with 32-bit row/column counts
+    if (a > max_dim || b > max_dim || c > max_dim) fail("%s: a dimension exceeds 2^31 - 1", op);
 }
 
 static uint64_t bucket_of(uint64_t bytes) {
@@ -443,11 +426,7 @@ int32_t gq_persistent_peak_reset(gq_ctx* ctx) {
 
 static uint64_t words8(uint64_t k) { return (k + 15) / 16 * 4; }
 static uint64_t words4(uint64_t k) { return (k + 31) / 32 * 4; }
-static const uint64_t kMaxDim = 0x7fffffffull;  // kernels index with 32-bit row/column counts
-
-static void check_dims(const char* op, uint64_t a, uint64_t b, uint64_t c = 1) {
-    if (a > kMaxDim || b > kMaxDim || c > kMaxDim) fail("%s: a dimension exceeds 2^31 - 1", op);
-}
+static const uint64_t kMaxDim = 0x7fffffffull;
 
 static void check_group(uint64_t group) {
     // crates/grilly-infer/src/quant4.rs:99-103

@@ -80,6 +80,31 @@ struct gq_ctx {
 
 namespace gq {
 
+// Entry-point plumbing shared by the files that define extern "C" functions.
+void set_last_error(const char* msg);
+template <class F>
+int32_t guarded(F&& f) {  // any exception -> GQ_ERR + thread-local message (gc_shim.cpp:343-354)
+    try {
+        f();
+        return GQ_OK;
+    } catch (const std::exception& e) {
+        set_last_error(e.what());
+    } catch (...) {
+        set_last_error("unknown error");
+    }
+    return GQ_ERR;
+}
+struct Locked {  // serialises calls on a context and makes its device current
+    gq_ctx* ctx;
+    std::lock_guard<std::mutex> lock;
+    explicit Locked(gq_ctx* c) : ctx(c ? c : (fail("null context"), c)), lock(c->mutex) {
+        cudaError_t e = cudaSetDevice(c->device);
+        if (e != cudaSuccess) fail("cudaSetDevice: %s", cudaGetErrorString(e));
+    }
+};
+Buffer& lookup(gq_ctx* ctx, gq_buf h, const char* what);
+void check_dims(const char* op, uint64_t a, uint64_t b, uint64_t c = 1);
+
 // A checked view of `count` elements of `elem` bytes at element offset `off`.
 void* view(gq_ctx* ctx, gq_buf buf, uint64_t off, uint64_t count, uint64_t elem, const char* what);
 // Counts a launch, notes buffers for an open capture, honours launch_blocking.
@@ -125,5 +150,20 @@ void comm_info(gq_comm* c, int* nranks, int* rank);
 void all_gather_columns(cudaStream_t s, gq_comm* c, const float* src, float* dst, uint64_t m, uint64_t n_shard);
 void launch_peer_gather(cudaStream_t s, float* const* y, uint32_t* const* flag, const float* src, uint64_t m, uint64_t n_shard,
                         int rank, int nranks, uint32_t* status);
+
+// decode-step operators (decode_ops.cu)
+void launch_embedding(cudaStream_t s, const float* table, const int32_t* ids, uint64_t rows, uint64_t width, uint64_t vocab, float* out);
+void launch_add_rms_norm(cudaStream_t s, const float* x, const float* res, const float* w, uint64_t rows, uint64_t n, float eps,
+                         float* y, float* h);
+void launch_rope_kv_append(cudaStream_t s, const float* qkv, const float* cosv, const float* sinv, const uint32_t* lens, uint32_t layer,
+                           uint32_t heads, uint32_t kv_heads, uint32_t dim, uint32_t max_len, float* q_out, float* kc, float* vc);
+void launch_kv_advance(cudaStream_t s, uint32_t* lens, uint32_t layers, uint32_t max_len);
+uint32_t attn_splits(uint32_t heads, uint32_t max_len, int sm_count);
+uint64_t attn_scratch_floats(uint32_t heads, uint32_t dim, uint32_t splits);
+void launch_attn_decode(cudaStream_t s, const float* q, const float* kc, const float* vc, const uint32_t* lens, uint32_t layer,
+                        uint32_t heads, uint32_t kv_heads, uint32_t dim, uint32_t max_len, float scale, uint32_t splits, float* scratch,
+                        float* out);
+void launch_swiglu(cudaStream_t s, const float* gate_up, uint64_t rows, uint64_t width, float* out);
+void launch_argmax_rows(cudaStream_t s, const float* v, uint64_t rows, uint64_t n, int32_t* out);
 
 }  // namespace gq

@@ -1,0 +1,190 @@
+"""One decode step of a Llama/Qwen2-shaped causal LM with int8 weight-only
+linears — the no-grad fused path of the reference's ``LlamaForCausalLM``
+(python/grilly/infer/models/llama.py:340-366): embedding, then per layer
+add+RMSNorm -> fused q|k|v int8 linear (+bias) -> rotary into the KV cache ->
+grouped-query decode attention -> o_proj int8 -> add+RMSNorm -> fused gate|up
+int8 -> SwiGLU -> down int8; final norm; tied lm_head int8 (the embedding table
+itself stays float32). Fused weights are the rows of the parts stacked
+(``Int8Weight.cat``, exact because scales are per row).
+
+Unlike the reference's step, nothing here depends on a host integer: the token
+id, the cache cursor and with it q's rotary position are read on the device, so
+``grilly2_b200.graphed(model.step)`` replays correctly from the second call on.
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+
+import numpy as np
+
+from .. import _C, _lib
+from .._lib import check
+
+
+@dataclass
+class LlamaConfig:
+    vocab_size: int = 151936
+    hidden_size: int = 896
+    num_hidden_layers: int = 24
+    num_attention_heads: int = 14
+    num_key_value_heads: int = 2
+    head_dim: int = 64
+    intermediate_size: int = 4864
+    rms_norm_eps: float = 1e-6
+    rope_theta: float = 1e6
+    max_cache_len: int = 1024
+    attention_bias: bool = True  # Qwen2: q, k, v carry a bias (python/grilly/huggingface/configuration.py:134)
+
+    @property
+    def q_size(self) -> int:
+        return self.num_attention_heads * self.head_dim
+
+    @property
+    def kv_size(self) -> int:
+        return self.num_key_value_heads * self.head_dim
+
+
+def qwen25_05b(max_cache_len: int = 1024) -> LlamaConfig:
+    """The Qwen2.5-0.5B architecture (weights are random-initialised by the caller)."""
+    return LlamaConfig(max_cache_len=max_cache_len)
+
+
+def rotary_tables(cfg: LlamaConfig):
+    """cos / sin [max_cache_len, head_dim] in float32, as transformers builds them:
+    inv_freq = theta^(-2i/d), angles = position * inv_freq, emb = cat(angles, angles)."""
+    inv = (1.0 / (np.float32(cfg.rope_theta) ** (np.arange(0, cfg.head_dim, 2, dtype=np.float32) / np.float32(cfg.head_dim)))).astype(np.float32)
+    ang = np.arange(cfg.max_cache_len, dtype=np.float32)[:, None] * inv[None, :]
+    emb = np.concatenate([ang, ang], axis=1).astype(np.float32)
+    return np.cos(emb).astype(np.float32), np.sin(emb).astype(np.float32)
+
+
+def random_weights(cfg: LlamaConfig, seed: int = 4, sigma: float = 0.02) -> dict:
+    """Seeded synthetic weights with the architecture's shapes: every matrix ~ N(0, sigma) drawn from
+    numpy.random.default_rng(seed * 1000 + index), norm weights 1."""
+    idx = [0]
+
+    def draw(*shape):
+        rng = np.random.default_rng(seed * 1000 + idx[0])
+        idx[0] += 1
+        return (rng.standard_normal(shape) * sigma).astype(np.float32)
+
+    H, I = cfg.hidden_size, cfg.intermediate_size
+    w = {"embed": draw(cfg.vocab_size, H), "norm": np.ones(H, dtype=np.float32), "layers": []}
+    for _ in range(cfg.num_hidden_layers):
+        w["layers"].append({
+            "input_norm": np.ones(H, dtype=np.float32), "post_norm": np.ones(H, dtype=np.float32),
+            "q": draw(cfg.q_size, H), "k": draw(cfg.kv_size, H), "v": draw(cfg.kv_size, H),
+            "q_bias": draw(cfg.q_size), "k_bias": draw(cfg.kv_size), "v_bias": draw(cfg.kv_size),
+            "o": draw(H, cfg.q_size), "gate": draw(I, H), "up": draw(I, H), "down": draw(H, I),
+        })
+    return w
+
+
+class KvCache:
+    """float32 K and V for every layer, [layers][kv_heads][max_len][head_dim], with the per-layer cursor on
+    the device (crates/grilly-infer/src/kv_cache.rs:21-33)."""
+
+    def __init__(self, cfg: LlamaConfig) -> None:
+        self.cfg = cfg
+        self.layer_elems = cfg.num_key_value_heads * cfg.max_cache_len * cfg.head_dim
+        n = cfg.num_hidden_layers * self.layer_elems
+        self.k = _C.Tensor.empty((n,), "float32", persistent=True)
+        self.v = _C.Tensor.empty((n,), "float32", persistent=True)
+        self.lens = _C.Tensor.from_numpy(np.zeros(cfg.num_hidden_layers, dtype=np.int32), persistent=True)
+        out = ctypes.c_uint64()
+        check(_lib.load().gq_attn_scratch_bytes(_C.context(), cfg.num_attention_heads, cfg.head_dim, cfg.max_cache_len, ctypes.byref(out)))
+        self.scratch = _C.Tensor.from_numpy(np.zeros(out.value // 4, dtype=np.float32), persistent=True)
+
+    def fill(self, k: np.ndarray, v: np.ndarray, length: int) -> None:
+        """Install `length` cached positions: k, v are [layers][kv_heads][length][head_dim]."""
+        c = self.cfg
+        full_k = np.zeros((c.num_hidden_layers, c.num_key_value_heads, c.max_cache_len, c.head_dim), dtype=np.float32)
+        full_v = np.zeros_like(full_k)
+        full_k[:, :, :length], full_v[:, :, :length] = k, v
+        self.k = _C.Tensor.from_numpy(full_k.reshape(-1), persistent=True)
+        self.v = _C.Tensor.from_numpy(full_v.reshape(-1), persistent=True)
+        self.lens = _C.Tensor.from_numpy(np.full(c.num_hidden_layers, length, dtype=np.int32), persistent=True)
+
+    def lengths(self) -> np.ndarray:
+        return self.lens.numpy()
+
+
+class LlamaDecoder:
+    """The quantized model and its cache; ``step(token)`` decodes one token."""
+
+    def __init__(self, cfg: LlamaConfig, weights: dict) -> None:
+        self.cfg = cfg
+        T = _C.Tensor.from_numpy
+
+        def q8(a):
+            return _C.Int8Weight.quantize(T(np.ascontiguousarray(a, dtype=np.float32)))
+
+        self.embed = T(weights["embed"], persistent=True)
+        self.lm_head = q8(weights["embed"])  # tied; the table itself stays float32
+        self.norm = T(weights["norm"], persistent=True)
+        self.layers = []
+        for lw in weights["layers"]:
+            self.layers.append({
+                "input_norm": T(lw["input_norm"], persistent=True), "post_norm": T(lw["post_norm"], persistent=True),
+                "qkv": _C.Int8Weight.cat([q8(lw["q"]), q8(lw["k"]), q8(lw["v"])]),
+                "qkv_bias": T(np.concatenate([lw["q_bias"], lw["k_bias"], lw["v_bias"]]), persistent=True) if cfg.attention_bias else None,
+                "o": q8(lw["o"]),
+                "gate_up": _C.Int8Weight.cat([q8(lw["gate"]), q8(lw["up"])]),
+                "down": q8(lw["down"]),
+            })
+        cos, sin = rotary_tables(cfg)
+        self.cos, self.sin = T(cos, persistent=True), T(sin, persistent=True)
+        self.cache = KvCache(cfg)
+
+    # the operators, as thin calls into the C ABI
+    def _norm(self, x, residual, weight, want_sum: bool):
+        H = self.cfg.hidden_size
+        y = _C.Tensor.empty((1, H), "float32")
+        h = _C.Tensor.empty((1, H), "float32") if want_sum else None
+        check(_lib.load().gq_add_rms_norm(_C.context(), x.storage.handle, residual.storage.handle if residual is not None else 0,
+                                          weight.storage.handle, 1, H, self.cfg.rms_norm_eps, y.storage.handle,
+                                          h.storage.handle if h is not None else 0))
+        return y, h
+
+    def step(self, token: "_C.Tensor"):
+        """token: int32 [1]. Returns (logits [1, vocab], next_token int32 [1]); advances the cache."""
+        c, lib, ctx = self.cfg, _lib.load(), _C.context()
+        L, Hq, Hkv, D = c.num_hidden_layers, c.num_attention_heads, c.num_key_value_heads, c.head_dim
+        hidden = _C.Tensor.empty((1, c.hidden_size), "float32")
+        check(lib.gq_embedding(ctx, self.embed.storage.handle, token.storage.handle, 1, c.hidden_size, c.vocab_size, hidden.storage.handle))
+        delta = None  # what the last block produced; added to `hidden` by the next norm
+        for li, lw in enumerate(self.layers):
+            x, summed = self._norm(hidden, delta, lw["input_norm"], delta is not None)
+            if summed is not None:
+                hidden = summed
+            qkv = lw["qkv"].linear(x, lw["qkv_bias"])
+            q = _C.Tensor.empty((1, c.q_size), "float32")
+            off = li * self.cache.layer_elems
+            check(lib.gq_rope_kv_append(ctx, qkv.storage.handle, self.cos.storage.handle, self.sin.storage.handle,
+                                        self.cache.lens.storage.handle, li, L, Hq, Hkv, D, c.max_cache_len, q.storage.handle,
+                                        self.cache.k.storage.handle, off, self.cache.v.storage.handle, off))
+            attn = _C.Tensor.empty((1, c.q_size), "float32")
+            check(lib.gq_attn_decode(ctx, q.storage.handle, self.cache.k.storage.handle, off, self.cache.v.storage.handle, off,
+                                     self.cache.lens.storage.handle, li, L, Hq, Hkv, D, c.max_cache_len, float(D) ** -0.5,
+                                     self.cache.scratch.storage.handle, attn.storage.handle))
+            o = lw["o"].linear(attn)
+            x, hidden = self._norm(hidden, o, lw["post_norm"], True)
+            gu = lw["gate_up"].linear(x)
+            act = _C.Tensor.empty((1, c.intermediate_size), "float32")
+            check(lib.gq_swiglu(ctx, gu.storage.handle, 1, c.intermediate_size, act.storage.handle))
+            delta = lw["down"].linear(act)
+        x, _ = self._norm(hidden, delta, self.norm, False)
+        logits = self.lm_head.linear(x)
+        nxt = _C.Tensor.empty((1,), "int32")
+        check(lib.gq_argmax_rows(ctx, logits.storage.handle, 1, c.vocab_size, nxt.storage.handle))
+        check(lib.gq_kv_advance(ctx, self.cache.lens.storage.handle, L, c.max_cache_len))
+        return logits, nxt
+
+    def bytes_per_token(self) -> dict:
+        """Algorithmic bytes one decode step touches at the cache's current length."""
+        c = self.cfg
+        lin = sum(sum(lw[k].nbytes for k in ("qkv", "o", "gate_up", "down")) for lw in self.layers) + self.lm_head.nbytes
+        kv = 2 * c.num_hidden_layers * c.num_key_value_heads * c.max_cache_len * c.head_dim * 4
+        other = 4 * (c.vocab_size + 40 * c.hidden_size * c.num_hidden_layers)
+        return {"linear_weights": lin, "kv_cache_at_full_length": kv, "other": other, "total": lin + kv + other}

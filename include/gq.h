@@ -197,6 +197,41 @@ int32_t gq_graph_replay(gq_ctx* ctx, gq_graph* graph);
 int32_t gq_graph_nodes(gq_graph* graph, uint64_t* out); /* operator launches the graph holds */
 void gq_graph_destroy(gq_ctx* ctx, gq_graph* graph);
 
+/* ── the rest of a decode step (the int8 full-step configuration) ───────
+ * The operators between the quantized linears of a Llama/Qwen2-shaped decode
+ * step, one new token, batch 1. What a step must know about where it is — the
+ * token id, the cache cursor, which is also q's and k's rotary position — is
+ * read from device memory, so a captured step replays correctly. float32
+ * tensors at offset 0 unless an offset is given. */
+
+/* out[r][:] = table[ids[r]][:] — python/grilly/infer/models/llama.py:348 (g2-index.glsl:22-38). ids int32. */
+int32_t gq_embedding(gq_ctx* ctx, gq_buf table, gq_buf ids, uint64_t rows, uint64_t width, uint64_t vocab, gq_buf out);
+/* h = x (+ residual); y = h / sqrt(mean(h^2) + eps) * weight — crates/grilly-infer/src/ops.rs rms_norm /
+ * add_rms_norm, g2-rms-norm.glsl:54-74. residual, weight and h may be 0 (absent). */
+int32_t gq_add_rms_norm(gq_ctx* ctx, gq_buf x, gq_buf residual, gq_buf weight, uint64_t rows, uint64_t n, float eps, gq_buf y,
+                        gq_buf h);
+/* One token's fused q|k|v row: rotary on q and k at position lens[layer] (cos/sin tables [max_len][dim]), q
+ * to q_out, k and v appended to the layer's cache [kv_heads][max_len][dim] at that position —
+ * crates/grilly-infer/src/ops.rs:120-133 (rope), kv_cache.rs:378-432 (append_rotary), g2-rope.glsl:24-40,
+ * g2-kv-write.glsl:43-72. A full cache takes nothing more. lens: uint32 per layer. */
+int32_t gq_rope_kv_append(gq_ctx* ctx, gq_buf qkv, gq_buf cos, gq_buf sin, gq_buf lens, uint64_t layer, uint64_t layers, uint64_t heads,
+                          uint64_t kv_heads, uint64_t dim, uint64_t max_len, gq_buf q_out, gq_buf kcache, uint64_t k_off, gq_buf vcache,
+                          uint64_t v_off);
+/* lens[l] = min(lens[l] + 1, max_len) for all layers, once per step — g2-kv-advance.glsl:18-21. */
+int32_t gq_kv_advance(gq_ctx* ctx, gq_buf lens, uint64_t layers, uint64_t max_len);
+/* Grouped-query attention of the new token over the cache's first lens[layer] + 1 positions, split over
+ * the length and merged in one launch — kv_cache.rs:454-568, g2-attn-decode{,-split,-merge}.glsl.
+ * `scratch` holds gq_attn_scratch_bytes bytes, zeroed once before the first call; calls sharing a scratch
+ * buffer must not overlap on the GPU. */
+int32_t gq_attn_scratch_bytes(gq_ctx* ctx, uint64_t heads, uint64_t dim, uint64_t max_len, uint64_t* out);
+int32_t gq_attn_decode(gq_ctx* ctx, gq_buf q, gq_buf kcache, uint64_t k_off, gq_buf vcache, uint64_t v_off, gq_buf lens, uint64_t layer,
+                       uint64_t layers, uint64_t heads, uint64_t kv_heads, uint64_t dim, uint64_t max_len, float scale, gq_buf scratch,
+                       gq_buf out);
+/* out[r][j] = silu(gate_up[r][j]) * gate_up[r][width + j] — ops.rs:148-212, g2-swiglu.glsl:21-29. */
+int32_t gq_swiglu(gq_ctx* ctx, gq_buf gate_up, uint64_t rows, uint64_t width, gq_buf out);
+/* out[r] = index of the maximum of row r (int32; the first on ties) — g2-argreduce-rows.glsl:42-77. */
+int32_t gq_argmax_rows(gq_ctx* ctx, gq_buf v, uint64_t rows, uint64_t n, gq_buf out);
+
 /* ── multi-GPU: column-sharded linears over the GPUs of one box ──────────
  * No counterpart in the reference, which runs on a single device. One process
  * (and one context) per GPU. Rank r owns output features [r n/W, (r+1) n/W):
