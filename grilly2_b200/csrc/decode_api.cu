@@ -40,7 +40,7 @@ static void check_heads(const char* op, uint64_t heads, uint64_t kv_heads, uint6
     check_dims(op, heads, kv_heads, dim);
     check_dims(op, max_len, 1);
     if (heads == 0 || kv_heads == 0 || heads % kv_heads) fail("%s: %llu heads do not group over %llu kv heads", op, (unsigned long long)heads, (unsigned long long)kv_heads);
-    if (dim == 0 || dim > 128 || 128 % dim || dim % 2) fail("%s: head_dim must be 32, 64 or 128, got %llu", op, (unsigned long long)dim);
+    if (dim != 32 && dim != 64 && dim != 128) fail("%s: head_dim must be 32, 64 or 128, got %llu", op, (unsigned long long)dim);
     if (max_len == 0) fail("%s: a cache of no positions", op);
 }
 
@@ -125,7 +125,7 @@ int32_t gq_argmax_rows(gq_ctx* ctx, gq_buf v, uint64_t rows, uint64_t n, gq_buf 
         auto vp = (const float*)view(ctx, v, 0, rows * n, 4, "gq_argmax_rows input");
         auto op = (int32_t*)view(ctx, out, 0, rows, 4, "gq_argmax_rows output");
         if (rows == 0) return;
-        launch_argmax_rows(ctx->stream, vp, rows, n, op);
+        launch_argmax_rows(ctx->stream, vp, rows, n, op, ctx->argmax_state);
         after_launch(ctx, "argmax_rows", {v, out});
     });
 }

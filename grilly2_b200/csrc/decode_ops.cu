@@ -155,38 +155,42 @@ __global__ void __launch_bounds__(256) swiglu_kernel(const float* __restrict__ g
     }
 }
 
-// Greedy next token: the index of each row's maximum (the first one on ties).
-__global__ void __launch_bounds__(1024) argmax_rows_kernel(const float* __restrict__ v, uint32_t rows, uint32_t n,
-                                                          int32_t* __restrict__ out) {
-    __shared__ float s_val[32];
-    __shared__ uint32_t s_idx[32];
-    for (uint32_t row = blockIdx.x; row < rows; row += gridDim.x) {
-        float best = -INFINITY;
-        uint32_t idx = 0xffffffffu;
-        for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {
-            const float x = v[(size_t)row * n + i];
-            if (x > best || idx == 0xffffffffu) best = x, idx = i;  // strides ascend, so the first maximum wins
-        }
+// Greedy next token: the index of each row's maximum (the first one on ties; NaN ranks below every number).
+// CTAs (b, row) each reduce a slice to one 64-bit key — the value's bits made monotone in the upper word, the
+// complemented index in the lower — and atomicMax it into state[row]; the last CTA of a row to arrive (a counter
+// after the 1024 keys of `state`) decodes the winner and puts both words back to zero for the next call.
+constexpr uint32_t kArgmaxRows = 1024;  // rows one launch handles (and the size of the state)
+__global__ void __launch_bounds__(256) argmax_rows_kernel(const float* __restrict__ v, uint32_t n, int32_t* __restrict__ out,
+                                                         unsigned long long* state) {
+    __shared__ unsigned long long s_key[8];
+    const uint32_t row = blockIdx.y;
+    const float* vr = v + (size_t)row * n;
+    unsigned long long best = 0;
+    for (uint32_t i = blockIdx.x * 256 + threadIdx.x; i < n; i += gridDim.x * 256) {
+        const float x = vr[i];
+        const uint32_t bits = __float_as_uint(x);
+        const uint32_t ord = x != x ? 1u : (bits & 0x80000000u) ? ~bits : (bits | 0x80000000u);
+        const unsigned long long key = ((unsigned long long)ord << 32) | (0xffffffffu - i);
+        best = key > best ? key : best;
+    }
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
-            const uint32_t oi = __shfl_xor_sync(0xffffffffu, idx, o);
-            if (ob > best || (ob == best && oi < idx)) best = ob, idx = oi;
+    for (int o = 16; o > 0; o >>= 1) {
+        const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+        best = other > best ? other : best;
+    }
+    if ((threadIdx.x & 31) == 0) s_key[threadIdx.x >> 5] = best;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < 8; ++w) best = s_key[w] > best ? s_key[w] : best;
+        atomicMax(state + row, best);
+        __threadfence();
+        uint32_t* counters = reinterpret_cast<uint32_t*>(state + kArgmaxRows);
+        if (atomicAdd(counters + row, 1u) == gridDim.x - 1) {
+            __threadfence();
+            const unsigned long long win = atomicExch(state + row, 0ull);
+            out[row] = (int32_t)(0xffffffffu - (uint32_t)win);
+            counters[row] = 0;
         }
-        if ((threadIdx.x & 31) == 0) s_val[threadIdx.x >> 5] = best, s_idx[threadIdx.x >> 5] = idx;
-        __syncthreads();
-        if (threadIdx.x < 32) {
-            best = threadIdx.x < blockDim.x / 32 ? s_val[threadIdx.x] : -INFINITY;
-            idx = threadIdx.x < blockDim.x / 32 ? s_idx[threadIdx.x] : 0xffffffffu;
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
-                const float ob = __shfl_xor_sync(0xffffffffu, best, o);
-                const uint32_t oi = __shfl_xor_sync(0xffffffffu, idx, o);
-                if (ob > best || (ob == best && oi < idx)) best = ob, idx = oi;
-            }
-            if (threadIdx.x == 0) out[row] = (int32_t)idx;
-        }
-        __syncthreads();
     }
 }
 
@@ -201,39 +205,54 @@ __global__ void __launch_bounds__(1024) argmax_rows_kernel(const float* __restri
 // counters that must be zero before the first call.
 constexpr int kAttnThreads = 128;
 constexpr uint32_t kAttnMaxChunk = 512;  // keys per split (scores live in shared memory)
+constexpr uint32_t kAttnChunk = 32;      // keys per split aimed at: short dependent chains, many CTAs
+constexpr uint32_t kAttnMaxSplits = 64;
 
+// L = dim / 4 lanes share a key (one float4 of the row each), so a CTA takes 128 / L keys per pass with every
+// load of the pass independent of the others.
+template <uint32_t L>
 __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const float* __restrict__ q, const float* __restrict__ kc,
                                                                   const float* __restrict__ vc, const uint32_t* __restrict__ lens,
-                                                                  uint32_t layer, uint32_t heads, uint32_t kv_heads, uint32_t dim,
-                                                                  uint32_t max_len, float scale, uint32_t chunk, float* scratch,
-                                                                  float* __restrict__ out) {
-    __shared__ float s_q[128];
+                                                                  uint32_t layer, uint32_t heads, uint32_t kv_heads, uint32_t max_len,
+                                                                  float scale, uint32_t chunk, float* scratch, float* __restrict__ out) {
+    constexpr uint32_t dim = 4 * L, KP = kAttnThreads / L;
     __shared__ float s_sc[kAttnMaxChunk];
     __shared__ float s_red[kAttnThreads / 32];
-    __shared__ float s_acc[kAttnThreads];
+    __shared__ float4 s_acc[kAttnThreads];
     __shared__ bool s_last;
     const uint32_t split = blockIdx.x, splits = gridDim.x, h = blockIdx.y;
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t sub = tid % L, grp = tid / L;
     const uint32_t g = h / (heads / kv_heads);
     const uint32_t len = min(lens[layer] + 1, max_len);
     const uint32_t j0 = split * chunk, j1 = min(len, j0 + chunk);
-    const float* kb = kc + (size_t)g * max_len * dim;
-    const float* vb = vc + (size_t)g * max_len * dim;
+    const float4* kb = reinterpret_cast<const float4*>(kc + (size_t)g * max_len * dim);
+    const float4* vb = reinterpret_cast<const float4*>(vc + (size_t)g * max_len * dim);
     float* part = scratch + ((size_t)h * splits + split) * (dim + 2);
     uint32_t* counters = reinterpret_cast<uint32_t*>(scratch + (size_t)heads * splits * (dim + 2));
 
-    if (tid < dim) s_q[tid] = q[(size_t)h * dim + tid];
-    __syncthreads();
+    const float4 q4 = reinterpret_cast<const float4*>(q + (size_t)h * dim)[sub];
 
-    // scores: one key per warp at a time, lanes across the head dimension
+    // Every lane of a warp runs the same number of passes (the shuffles below name the whole warp): a lane
+    // whose key lies past the end computes on zeros and keeps nothing.
     float m = -INFINITY;
-    for (uint32_t j = j0 + warp; j < j1; j += kAttnThreads / 32) {
-        float sdot = 0.0f;
-        for (uint32_t d = lane; d < dim; d += 32) sdot = __fmaf_rn(s_q[d], kb[(size_t)j * dim + d], sdot);
-        sdot = warp_sum(sdot) * scale;
-        if (lane == 0) s_sc[j - j0] = sdot;
-        m = fmaxf(m, sdot);
+    const uint32_t passes = j1 > j0 ? (j1 - j0 + KP - 1) / KP : 0;
+#pragma unroll 4
+    for (uint32_t pass = 0; pass < passes; ++pass) {
+        const uint32_t j = j0 + pass * KP + grp;
+        const bool live = j < j1;
+        const float4 k4 = live ? kb[(size_t)j * L + sub] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        float sdot = __fmaf_rn(q4.w, k4.w, __fmaf_rn(q4.z, k4.z, __fmaf_rn(q4.y, k4.y, __fmul_rn(q4.x, k4.x))));
+#pragma unroll
+        for (uint32_t o = L / 2; o > 0; o >>= 1) sdot += __shfl_xor_sync(0xffffffffu, sdot, o);
+        sdot *= scale;
+        if (live) {
+            if (sub == 0) s_sc[j - j0] = sdot;
+            m = fmaxf(m, sdot);
+        }
     }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
     if (lane == 0) s_red[warp] = m;
     __syncthreads();
     m = fmaxf(fmaxf(s_red[0], s_red[1]), fmaxf(s_red[2], s_red[3]));
@@ -250,17 +269,24 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const float* 
     __syncthreads();
     z = (s_red[0] + s_red[1]) + (s_red[2] + s_red[3]);
 
-    // weighted values: groups of `dim` threads stride over the keys
-    const uint32_t groups = kAttnThreads / dim, d = tid % dim, grp = tid / dim;
-    float acc = 0.0f;
-    if (grp < groups)
-        for (uint32_t j = j0 + grp; j < j1; j += groups) acc = __fmaf_rn(s_sc[j - j0], vb[(size_t)j * dim + d], acc);
+    // weighted values: group `grp` strides over the keys, lane `sub` owns one float4 of the output
+    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll 4
+    for (uint32_t j = j0 + grp; j < j1; j += KP) {
+        const float4 v4 = vb[(size_t)j * L + sub];
+        const float p = s_sc[j - j0];
+        acc.x = __fmaf_rn(p, v4.x, acc.x), acc.y = __fmaf_rn(p, v4.y, acc.y);
+        acc.z = __fmaf_rn(p, v4.z, acc.z), acc.w = __fmaf_rn(p, v4.w, acc.w);
+    }
     s_acc[tid] = acc;
     __syncthreads();
-    if (tid < dim) {
-        float t = 0.0f;
-        for (uint32_t k = 0; k < groups; ++k) t += s_acc[k * dim + tid];
-        part[2 + tid] = t;
+    if (tid < L) {
+        float4 t = s_acc[tid];
+        for (uint32_t k = 1; k < KP; ++k) {
+            const float4 o = s_acc[k * L + tid];
+            t.x += o.x, t.y += o.y, t.z += o.z, t.w += o.w;
+        }
+        part[2 + 4 * tid] = t.x, part[3 + 4 * tid] = t.y, part[4 + 4 * tid] = t.z, part[5 + 4 * tid] = t.w;
     }
     if (tid == 0) part[0] = m, part[1] = z;
 
@@ -275,21 +301,26 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const float* 
     if (!s_last) return;
     __threadfence();
     const float* hp = scratch + (size_t)h * splits * (dim + 2);
+    // the weights exp(m_s - M) once, in shared memory (the scores are no longer needed)
     float M = -INFINITY;
-    for (uint32_t s = 0; s < splits; ++s) M = fmaxf(M, hp[s * (dim + 2)]);
+    for (uint32_t s = 0; s < splits; ++s) M = fmaxf(M, __ldcg(hp + s * (dim + 2)));
+    for (uint32_t s = tid; s < splits; s += kAttnThreads) {
+        const float ms = __ldcg(hp + s * (dim + 2));
+        s_sc[s] = ms == -INFINITY ? 0.0f : exp_cephes(ms - M);  // an empty split contributes nothing
+    }
+    __syncthreads();
     if (tid < dim) {
         float Z = 0.0f, o = 0.0f;
+#pragma unroll 4
         for (uint32_t s = 0; s < splits; ++s) {
-            const float ms = hp[s * (dim + 2)];
-            const float wgt = ms == -INFINITY ? 0.0f : exp_cephes(ms - M);  // an empty split contributes nothing
-            Z = __fmaf_rn(hp[s * (dim + 2) + 1], wgt, Z);
-            o = __fmaf_rn(hp[s * (dim + 2) + 2 + tid], wgt, o);
+            const float wgt = s_sc[s];
+            Z = __fmaf_rn(__ldcg(hp + s * (dim + 2) + 1), wgt, Z);
+            o = __fmaf_rn(__ldcg(hp + s * (dim + 2) + 2 + tid), wgt, o);
         }
         out[(size_t)h * dim + tid] = __fdiv_rn(o, Z);
     }
     if (tid == 0) counters[h] = 0;  // ready for the next call
 }
-
 
 }  // namespace
 
@@ -314,12 +345,14 @@ void launch_rope_kv_append(cudaStream_t s, const float* qkv, const float* cosv, 
 void launch_kv_advance(cudaStream_t s, uint32_t* lens, uint32_t layers, uint32_t max_len) {
     kv_advance_kernel<<<(layers + 127) / 128, 128, 0, s>>>(lens, layers, max_len);
 }
-// Splits of the cache length: enough CTAs to occupy the GPU, at most kAttnMaxChunk keys each.
+// Splits of the cache length: about kAttnChunk keys each, at most kAttnMaxSplits (more only where a split would
+// otherwise exceed the kAttnMaxChunk scores that fit in shared memory).
 uint32_t attn_splits(uint32_t heads, uint32_t max_len, int sm_count) {
-    uint32_t splits = ((uint32_t)sm_count + heads - 1) / heads;
+    (void)heads, (void)sm_count;
+    uint32_t splits = (max_len + kAttnChunk - 1) / kAttnChunk;
+    if (splits > kAttnMaxSplits) splits = kAttnMaxSplits;
     const uint32_t need = (max_len + kAttnMaxChunk - 1) / kAttnMaxChunk;
     if (splits < need) splits = need;
-    if (splits > (max_len + 31) / 32) splits = (max_len + 31) / 32;
     return splits < 1 ? 1 : splits;
 }
 uint64_t attn_scratch_floats(uint32_t heads, uint32_t dim, uint32_t splits) { return (uint64_t)heads * splits * (dim + 2) + heads; }
@@ -327,15 +360,28 @@ void launch_attn_decode(cudaStream_t s, const float* q, const float* kc, const f
                         uint32_t heads, uint32_t kv_heads, uint32_t dim, uint32_t max_len, float scale, uint32_t splits, float* scratch,
                         float* out) {
     const uint32_t chunk = (max_len + splits - 1) / splits;
-    attn_decode_kernel<<<dim3(splits, heads), kAttnThreads, 0, s>>>(q, kc, vc, lens, layer, heads, kv_heads, dim, max_len, scale, chunk,
-                                                                   scratch, out);
+    if (splits > kAttnMaxChunk || chunk > kAttnMaxChunk)
+        fail("attention: a cache of %u positions is beyond this kernel (%u splits of %u keys)", max_len, splits, chunk);
+    const dim3 grid(splits, heads);
+    if (dim == 32)
+        attn_decode_kernel<8><<<grid, kAttnThreads, 0, s>>>(q, kc, vc, lens, layer, heads, kv_heads, max_len, scale, chunk, scratch, out);
+    else if (dim == 64)
+        attn_decode_kernel<16><<<grid, kAttnThreads, 0, s>>>(q, kc, vc, lens, layer, heads, kv_heads, max_len, scale, chunk, scratch, out);
+    else if (dim == 128)
+        attn_decode_kernel<32><<<grid, kAttnThreads, 0, s>>>(q, kc, vc, lens, layer, heads, kv_heads, max_len, scale, chunk, scratch, out);
+    else
+        fail("attention: head_dim must be 32, 64 or 128, got %u", dim);
 }
 void launch_swiglu(cudaStream_t s, const float* gate_up, uint64_t rows, uint64_t width, float* out) {
     swiglu_kernel<<<blocks_for(rows * width, 256, 148 * 8), 256, 0, s>>>(gate_up, (uint32_t)rows, (uint32_t)width, out);
 }
-void launch_argmax_rows(cudaStream_t s, const float* v, uint64_t rows, uint64_t n, int32_t* out) {
-    argmax_rows_kernel<<<blocks_for(rows, 1, 1024), 1024, 0, s>>>(v, (uint32_t)rows, (uint32_t)n, out);
+uint64_t argmax_state_bytes() { return kArgmaxRows * 12ull; }
+void launch_argmax_rows(cudaStream_t s, const float* v, uint64_t rows, uint64_t n, int32_t* out, void* state) {
+    const uint32_t per_row = blocks_for(n, 1024, rows >= 64 ? 4 : 148);
+    for (uint64_t r0 = 0; r0 < rows; r0 += kArgmaxRows) {
+        const uint32_t now = (uint32_t)(rows - r0 < kArgmaxRows ? rows - r0 : kArgmaxRows);
+        argmax_rows_kernel<<<dim3(per_row, now), 256, 0, s>>>(v + r0 * n, (uint32_t)n, out + r0, (unsigned long long*)state);
+    }
 }
-
 
 }  // namespace gq

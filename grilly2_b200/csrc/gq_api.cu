@@ -164,6 +164,8 @@ int32_t gq_create(int32_t device, gq_ctx** out) {
             GQ_CUDA(cudaHostAlloc((void**)&ctx->status_host, 64, cudaHostAllocMapped));
             *ctx->status_host = 0;
             GQ_CUDA(cudaHostGetDevicePointer((void**)&ctx->status_dev, ctx->status_host, 0));
+            GQ_CUDA(cudaMalloc(&ctx->argmax_state, argmax_state_bytes()));
+            GQ_CUDA(cudaMemset(ctx->argmax_state, 0, argmax_state_bytes()));
             const char* lb = getenv("GQ_LAUNCH_BLOCKING");
             ctx->launch_blocking = lb && lb[0] == '1';
         } catch (...) {
@@ -185,6 +187,7 @@ void gq_destroy(gq_ctx* ctx) {
                 if (kv.second.owned && kv.second.ptr) cudaFree(kv.second.ptr);
             for (auto& kv : ctx->pool) cudaFree(kv.second);
             if (ctx->scratch) cudaFree(ctx->scratch);
+            if (ctx->argmax_state) cudaFree(ctx->argmax_state);
             if (ctx->status_host) cudaFreeHost(ctx->status_host);
             cudaStreamDestroy(ctx->stream);
         }

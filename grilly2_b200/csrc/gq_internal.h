@@ -75,6 +75,7 @@ struct gq_ctx {
     uint32_t* status_dev = nullptr;
     // lazily created device scratch owned by the context (tensor-core paths)
     void* scratch = nullptr;
+    void* argmax_state = nullptr;  // keys and counters of gq_argmax_rows, zero between calls
     uint64_t scratch_bytes = 0;
 };
 
@@ -164,6 +165,7 @@ void launch_attn_decode(cudaStream_t s, const float* q, const float* kc, const f
                         uint32_t heads, uint32_t kv_heads, uint32_t dim, uint32_t max_len, float scale, uint32_t splits, float* scratch,
                         float* out);
 void launch_swiglu(cudaStream_t s, const float* gate_up, uint64_t rows, uint64_t width, float* out);
-void launch_argmax_rows(cudaStream_t s, const float* v, uint64_t rows, uint64_t n, int32_t* out);
+uint64_t argmax_state_bytes();
+void launch_argmax_rows(cudaStream_t s, const float* v, uint64_t rows, uint64_t n, int32_t* out, void* state);
 
 }  // namespace gq

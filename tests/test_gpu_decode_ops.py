@@ -1,0 +1,68 @@
+"""The decode-step operators one by one, through the C ABI, against float64 numpy."""
+import ctypes
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def _env():
+    from grilly2_b200 import _C, _lib
+    return _C, _lib, _lib.load(), _C.context()
+
+
+@pytest.mark.parametrize("rows,n", [(1, 151936), (3, 1000), (70, 257), (1, 1)])
+def test_argmax_rows_first_maximum_wins(rows, n):
+    _C, _lib, lib, ctx = _env()
+    rng = np.random.default_rng(rows * 1000 + n)
+    v = rng.standard_normal((rows, n)).astype(np.float32)
+    if n > 10:
+        v[0, 7] = v[0, n - 2] = 50.0           # a tie: the first index wins
+        v[-1, :] = -np.abs(v[-1, :]) - 1.0     # an all-negative row
+        v[-1, 3] = np.nan                      # NaN ranks below every number
+    want = np.array([int(np.nanargmax(r)) for r in v], dtype=np.int32)
+    t, out = _C.Tensor.from_numpy(v), _C.Tensor.empty((rows,), "int32")
+    for _ in range(2):  # the state must return to zero between calls
+        _lib.check(lib.gq_argmax_rows(ctx, t.storage.handle, rows, n, out.storage.handle))
+        np.testing.assert_array_equal(out.numpy(), want)
+
+
+@pytest.mark.parametrize("dim,heads,kv_heads,max_len,length", [(64, 14, 2, 1024, 1023), (64, 14, 2, 1024, 0), (32, 4, 2, 48, 20),
+                                                               (128, 8, 8, 300, 299), (64, 2, 1, 40000, 33333)])
+def test_attention_against_float64(dim, heads, kv_heads, max_len, length):
+    """`length` positions are cached and the cursor says so; the kernel attends over length + 1 (the appended one)."""
+    _C, _lib, lib, ctx = _env()
+    rng = np.random.default_rng(dim + length)
+    k = rng.standard_normal((kv_heads, max_len, dim)).astype(np.float32)
+    v = rng.standard_normal((kv_heads, max_len, dim)).astype(np.float32)
+    q = rng.standard_normal((heads, dim)).astype(np.float32)
+    layers, layer = 3, 1
+    lens = np.array([5, length, 9], dtype=np.int32)
+    nbytes = ctypes.c_uint64()
+    _lib.check(lib.gq_attn_scratch_bytes(ctx, heads, dim, max_len, ctypes.byref(nbytes)))
+    scratch = _C.Tensor.from_numpy(np.zeros(nbytes.value // 4, dtype=np.float32))
+    tq, tk, tv, tl = (_C.Tensor.from_numpy(a) for a in (q, k.reshape(-1), v.reshape(-1), lens))
+    out = _C.Tensor.empty((heads, dim), "float32")
+    n = min(length + 1, max_len)
+    want = np.zeros((heads, dim))
+    for h in range(heads):
+        g = h // (heads // kv_heads)
+        s = k[g, :n].astype(np.float64) @ q[h].astype(np.float64) / np.sqrt(dim)
+        e = np.exp(s - s.max())
+        want[h] = (e / e.sum()) @ v[g, :n].astype(np.float64)
+    for _ in range(2):  # the counters in scratch reset themselves
+        _lib.check(lib.gq_attn_decode(ctx, tq.storage.handle, tk.storage.handle, 0, tv.storage.handle, 0, tl.storage.handle, layer,
+                                      layers, heads, kv_heads, dim, max_len, float(dim) ** -0.5, scratch.storage.handle,
+                                      out.storage.handle))
+        got = out.numpy()
+        assert np.abs(got - want).max() <= 2e-6 * max(1.0, np.abs(want).max())
+
+
+def test_attention_refuses_other_head_sizes():
+    _C, _lib, lib, ctx = _env()
+    t = _C.Tensor.from_numpy(np.zeros(4096, dtype=np.float32))
+    ti = _C.Tensor.from_numpy(np.zeros(1, dtype=np.int32))
+    rc = lib.gq_attn_decode(ctx, t.storage.handle, t.storage.handle, 0, t.storage.handle, 0, ti.storage.handle, 0, 1, 2, 1, 48, 8,
+                            1.0, t.storage.handle, t.storage.handle)
+    assert rc != 0 and b"head_dim" in lib.gq_last_error()
