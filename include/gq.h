@@ -227,6 +227,15 @@ int32_t gq_attn_scratch_bytes(gq_ctx* ctx, uint64_t heads, uint64_t dim, uint64_
 int32_t gq_attn_decode(gq_ctx* ctx, gq_buf q, gq_buf kcache, uint64_t k_off, gq_buf vcache, uint64_t v_off, gq_buf lens, uint64_t layer,
                        uint64_t layers, uint64_t heads, uint64_t kv_heads, uint64_t dim, uint64_t max_len, float scale, gq_buf scratch,
                        gq_buf out);
+/* gq_attn_decode with the scratch in a fixed 2 MiB array of the library's own device memory: takes no scratch
+ * buffer and allocates nothing, on the first call or later. No counterpart in the reference (its scratch is
+ * a pooled buffer, kv_cache.rs:502-528). The first call on a device does the set-up (an address look-up):
+ * make it before a stream capture begins. Refuses shapes whose heads * splits * (dim + 2) + heads floats exceed
+ * the array. Every call on a device shares the array, so calls that overlap on the GPU race; calls on one
+ * context are stream-ordered and do not. */
+int32_t gq_attn_decode_static(gq_ctx* ctx, gq_buf q, gq_buf kcache, uint64_t k_off, gq_buf vcache, uint64_t v_off, gq_buf lens,
+                              uint64_t layer, uint64_t layers, uint64_t heads, uint64_t kv_heads, uint64_t dim, uint64_t max_len,
+                              float scale, gq_buf out);
 /* out[r][j] = silu(gate_up[r][j]) * gate_up[r][width + j] — ops.rs:148-212, g2-swiglu.glsl:21-29. */
 int32_t gq_swiglu(gq_ctx* ctx, gq_buf gate_up, uint64_t rows, uint64_t width, gq_buf out);
 /* out[r] = index of the maximum of row r (int32; the first on ties) — g2-argreduce-rows.glsl:42-77. */
