@@ -560,6 +560,13 @@ def main() -> None:
         t = timed(ghot, steps2, 3) * 1e3 / (steps2 * REPLICAS)
         extras["m1_l2_hot_us_per_launch"] = t
         extras["m1_l2_hot_GBps"] = bytes_launch / (t * 1e-6) / 1e9
+        _, _, gim = capture(1, weights, _lib.KERNEL_IMMA)
+        t = timed(gim, max(steps2 // 4, 5), 3) * 1e3 / (max(steps2 // 4, 5) * REPLICAS)
+        extras["m1_imma_streaming_kernel_us_per_launch"] = t
+        _, _, g2 = capture(2, weights)
+        t = timed(g2, steps2, 3) * 1e3 / (steps2 * REPLICAS)
+        extras["m2_us_per_launch"] = t
+        extras["m2_GBps"] = algorithmic_bytes(2) / (t * 1e-6) / 1e9
         _, _, gdp = capture(1, weights, _lib.KERNEL_DP4A)
         t = timed(gdp, max(steps2 // 4, 5), 3) * 1e3 / (max(steps2 // 4, 5) * REPLICAS)
         extras["m1_dp4a_kernel_us_per_launch"] = t
@@ -588,7 +595,7 @@ def main() -> None:
         "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic", "config": workload_config(world),
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": None, "peak_kind": peak_kind, "kernel": "gemv_imma_kernel<int4, 1 row>",
+                     "traffic": None, "peak_kind": peak_kind, "kernel": "gemv_q4_ring_kernel<1 row of x, 2 groups per warp>",
                      "algorithmic_bytes_per_launch": bytes_launch, "us_per_launch": per_launch_us},
         "cpu_baseline": cpu,
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": K_IN * 4, "d2h_bytes_per_step": REPLICAS * y_bytes,

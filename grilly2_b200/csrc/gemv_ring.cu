@@ -1,0 +1,320 @@
+// Decode GEMV for int4 group-128 weights and one or two rows of x on the
+// warp-level integer tensor instruction (mma.sync m16n8k32, u8 x s8 -> s32),
+// organised so that a weight costs few instructions and no CTA-wide barrier
+// stands between the launch and the first multiply.
+//
+// Arithmetic (as gemv_imma.cu): within each group of 128 k, x is held as an
+// exact fixed-point integer X = rint(x 2^(30-e)), 2^e > max|x| of the group,
+// split into four signed base-256 digits. The digits are the columns of the
+// MMA's B operand (four per row of x), sixteen output features are the rows
+// of A, and the int4 levels enter as bytes 0..15: per group and feature the
+// four digit sums are exact int32, recombined and scaled in float32:
+//   y[f] = sum_g  s[f][g] * (sum_k level x) + (zero[f][g] - 8 s[f][g]) * (sum_k x).
+// The only approximation is X (2^-31 of the group's max |x|). A non-finite x
+// gives NaN outputs.
+//
+// Ownership: K is split by group over the 16 consumer warps (warp w owns
+// groups w, w + 16, ...). A warp converts only its own groups of x, straight
+// into the B fragments it keeps in registers for the whole kernel — no
+// CTA-wide barrier, and nothing of x is re-read from shared memory in the
+// main loop. It then walks the CTA's output features in blocks of 16: per
+// block and group two 16-byte shared-memory reads per lane feed four MMAs
+// (lane (g, t) reads bytes 16 t .. 16 t + 15 of the group's 64 bytes of features
+// 2 g and 2 g + 1; word i of those 16 bytes, split in even and odd nibbles, is
+// the A fragment of MMA i, and the B fragments are laid out to match), then
+// ~12 instructions fold the int32 sums into two float accumulators. After
+// its groups the warp leaves a partial sum per feature in shared memory; the
+// last warp to arrive for a block adds the 16 partials in warp order (so the
+// result does not depend on timing) and writes y.
+//
+// Data movement: one producer warp fills a ring of 16-row blocks with 1-D bulk (TMA)
+// copies of two weight rows each (MMA rows g and g + 8 are features 2 g and 2 g + 1,
+// read by different instructions, and each pair is followed by 16 bytes of padding so
+// that one instruction's reads of 8 pairs x 4 chunks spread over all banks; a bulk
+// copy costs the copy engine ~40 ns whatever its size, so nothing smaller than
+// a row goes that way). The block's scales and zero points come as 2-D TMA
+// tiles (16 features x 32 groups, 128-byte swizzle, so that the eight features
+// a quarter-warp reads for one group fall in eight different banks). Three or
+// more blocks (>= 100 KB) are in flight per SM.
+//
+// Algorithmic bytes per launch: packed weights + scales + zeros + x + y
+// (+ bias). Bound: HBM bandwidth.
+#include "gq_internal.h"
+#include "tc_common.cuh"
+
+namespace gq {
+
+namespace {
+
+constexpr int kWarps = 16;                  // consumer warps
+constexpr int kThreads = (kWarps + 1) * 32; // + the producer warp
+constexpr uint32_t kBlockRows = 16;         // output features per MMA and per ring stage
+constexpr uint32_t kRowPad = 16;            // bytes added to a row's pitch in shared memory
+constexpr int kMaxStages = 8;
+constexpr uint32_t kScratchWords = 8 * 4 * 4 * 2;  // per warp: [column][t][mma][parity] digit words of one group
+
+__device__ __forceinline__ void mma_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+
+// One group of one row of x -> digit words in the warp's scratch, plus 2^(e-30) and the group's sum of x.
+// Lane L converts x[128 G + 32 tt + 8 i + 2 b + par], b = 0..3, with tt = L / 8, i = (L / 2) % 4, par = L % 2:
+// the four values one packed weight word's even (par = 0) or odd (par = 1) nibbles of chunk tt meet in MMA i.
+__device__ __forceinline__ void load_group(const float* __restrict__ xr, uint32_t k, uint32_t G, uint32_t lane, float (&v)[4]) {
+    const uint32_t kb = G * 128 + 32 * (lane >> 3) + 8 * ((lane >> 1) & 3u) + (lane & 1u);
+#pragma unroll
+    for (int b = 0; b < 4; ++b) v[b] = kb + 2 * b < k ? __ldg(xr + kb + 2 * b) : 0.0f;
+}
+__device__ __forceinline__ void convert_group(const float (&v)[4], uint32_t lane, uint32_t col0, uint32_t* scratch, float& inv, float& xs) {
+    const uint32_t tt = lane >> 3, i = (lane >> 1) & 3u, par = lane & 1u;
+    float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+    const bool bad = !(fabsf(v[0]) <= 3.402823466e+38f) | !(fabsf(v[1]) <= 3.402823466e+38f) | !(fabsf(v[2]) <= 3.402823466e+38f) |
+                     !(fabsf(v[3]) <= 3.402823466e+38f);
+    if (bad) amax = __uint_as_float(0x7f800000u);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    uint32_t e = __float_as_uint(amax) >> 23;
+    float mult;
+    if (e == 255) {
+        mult = 0.0f, inv = __uint_as_float(0x7fc00000u);
+    } else if (amax == 0.0f) {
+        mult = inv = 0.0f;
+    } else {
+        e = max(e, 32u);
+        mult = __uint_as_float((283u - e) << 23);  // 2^(30 - e)
+        inv = __uint_as_float((e - 29u) << 23);    // 2^(e - 30)
+    }
+    uint32_t word[4] = {0u, 0u, 0u, 0u};
+    int sum_lo = 0, sum_hi = 0;  // X = lo + 65536 hi with lo a signed 16-bit number: both sums stay far inside int32
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+        int X = __float2int_rn(v[b] * mult);
+        const int xl = (int)(int16_t)X;
+        sum_lo += xl, sum_hi += (X - xl) >> 16;
+        const int d0 = (int)(int8_t)X;
+        X = (X - d0) >> 8;
+        const int d1 = (int)(int8_t)X;
+        X = (X - d1) >> 8;
+        const int d2 = (int)(int8_t)X;
+        const int d3 = (X - d2) >> 8;
+        word[0] |= ((uint32_t)d0 & 0xFFu) << (8 * b), word[1] |= ((uint32_t)d1 & 0xFFu) << (8 * b);
+        word[2] |= ((uint32_t)d2 & 0xFFu) << (8 * b), word[3] |= ((uint32_t)d3 & 0xFFu) << (8 * b);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        sum_lo += __shfl_xor_sync(0xffffffffu, sum_lo, o);
+        sum_hi += __shfl_xor_sync(0xffffffffu, sum_hi, o);
+    }
+    xs = __fmaf_rn((float)sum_hi, 65536.0f, (float)sum_lo) * inv;
+#pragma unroll
+    for (int p = 0; p < 4; ++p) scratch[(((col0 + p) * 4 + tt) * 4 + i) * 2 + par] = word[p];
+}
+
+// Shared memory: [stages x (16 padded rows | scale tiles | zero tiles)] [partials: stages x 16 warps x 32] [scratch: 16 warps x 256
+// words] [counts: stages] [barriers] [failed].
+template <int MR, int GPW>
+__global__ void __launch_bounds__(kThreads, 1)
+    gemv_q4_ring_kernel(const __grid_constant__ CUtensorMap smap, const __grid_constant__ CUtensorMap zmap, const uint32_t* __restrict__ q,
+                        const float* __restrict__ x, const float* __restrict__ bias, float* __restrict__ y, uint32_t k, uint32_t n,
+                        uint32_t groups, uint32_t nstages, uint32_t stage_stride, uint32_t* status) {
+    extern __shared__ uint8_t smem_unaligned[];
+    uint8_t* smem = smem_unaligned + ((1024u - (smem_u32(smem_unaligned) & 1023u)) & 1023u);  // swizzle atoms are 1 KB
+    const uint32_t row_bytes = k >> 1, pitch = 2 * row_bytes + kRowPad;  // two consecutive features share a copy; 16 bytes of padding follow
+    const uint32_t nbox = groups >> 5;                                      // 32 groups of scales (128 bytes) per box row
+    const uint32_t sz_off = ((kBlockRows / 2) * pitch + 1023u) & ~1023u;          // a block's scales: nbox boxes of 16 rows x 128 bytes,
+    const uint32_t zr_off = sz_off + nbox * 2048u;                          // then its zero points, each box 128-byte swizzled
+    float* partials = reinterpret_cast<float*>(smem + (size_t)nstages * stage_stride);
+    uint32_t* scratch_all = reinterpret_cast<uint32_t*>(partials + (size_t)nstages * kWarps * 32);
+    uint32_t* counts = scratch_all + kWarps * kScratchWords;
+    uint64_t* full = reinterpret_cast<uint64_t*>(counts + kMaxStages);
+    uint64_t* empty = full + kMaxStages;
+    volatile uint32_t* failed = reinterpret_cast<volatile uint32_t*>(empty + kMaxStages);
+
+    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t row_begin = (uint32_t)((uint64_t)n * blockIdx.x / gridDim.x), row_end = (uint32_t)((uint64_t)n * (blockIdx.x + 1) / gridDim.x);
+    const uint32_t nrows = row_end - row_begin;
+    const uint32_t blocks = (nrows + kBlockRows - 1) / kBlockRows;
+
+    if (tid < nstages) {
+        mbar_init(full + tid, 1);
+        mbar_init(empty + tid, kWarps);
+        counts[tid] = 0;
+    }
+    if (tid == 0) {
+        *failed = 0;
+        mbar_fence_init();
+    }
+    __syncthreads();
+
+    if (warp == kWarps) {
+        // ── producer: lanes 0-7 bulk-copy a block's weight rows two at a time, lanes 16.. and 24.. fetch its scale and zero-point tiles ──
+        for (uint32_t rb = 0; rb < blocks; ++rb) {
+            const uint32_t s = rb % nstages, round = rb / nstages;
+            bool ok = true;
+            if (round && lane == 0) ok = mbar_wait(empty + s, (round - 1) & 1, failed, status, kStatusEmptyWaitTimedOut);
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) break;
+            const uint32_t rows_here = min(kBlockRows, nrows - rb * kBlockRows);
+            if (lane == 0) mbar_arrive_expect_tx(full + s, rows_here * row_bytes + 2 * nbox * 2048u);
+            __syncwarp();
+            uint8_t* dst = smem + (size_t)s * stage_stride;
+            const size_t row0 = (size_t)row_begin + (size_t)rb * kBlockRows;
+            if (2 * lane < rows_here)  // lanes 0-7: features 2 lane and 2 lane + 1 (the last pair of the CTA may be a single row)
+                bulk_load(dst + lane * pitch, reinterpret_cast<const uint8_t*>(q) + (row0 + 2 * lane) * row_bytes,
+                          min(2u, rows_here - 2 * lane) * row_bytes, full + s);
+            else if (lane >= 16 && lane < 16 + nbox)
+                tma_load_2d(dst + sz_off + (lane - 16) * 2048u, &smap, (int32_t)((lane - 16) * 32), (int32_t)row0, full + s);
+            else if (lane >= 24 && lane < 24 + nbox)
+                tma_load_2d(dst + zr_off + (lane - 24) * 2048u, &zmap, (int32_t)((lane - 24) * 32), (int32_t)row0, full + s);
+        }
+        return;
+    }
+
+    // ── consumers: B fragments of this warp's groups, once ──
+    const uint32_t g8 = lane >> 2, t = lane & 3u;  // MMA row (and B column) index, thread-in-group
+    const uint32_t xrow = t >> 1, high = t & 1u;   // this lane's accumulator columns: digits 2 high, 2 high + 1 of row xrow of x
+    uint32_t* scratch = scratch_all + warp * kScratchWords;
+    uint32_t bf[GPW][8];
+    float coef[GPW], zcoef[GPW];
+    float xv[GPW][MR][4];  // every load of x is requested before the first conversion waits for one
+#pragma unroll
+    for (int gi = 0; gi < GPW; ++gi)
+#pragma unroll
+        for (int r = 0; r < MR; ++r)
+            if (warp + gi * kWarps < groups) load_group(x + (size_t)r * k, k, warp + gi * kWarps, lane, xv[gi][r]);
+#pragma unroll
+    for (int gi = 0; gi < GPW; ++gi) {
+        const uint32_t G = warp + gi * kWarps;
+        coef[gi] = zcoef[gi] = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) bf[gi][j] = 0u;
+        if (G >= groups) continue;  // uniform over the warp
+        float inv[MR], xs[MR];
+#pragma unroll
+        for (int r = 0; r < MR; ++r) convert_group(xv[gi][r], lane, 4 * r, scratch, inv[r], xs[r]);
+        __syncwarp();
+        if (g8 < 4 * MR) {
+            const uint4 lo = *reinterpret_cast<const uint4*>(scratch + (g8 * 4 + t) * 8), hi = *reinterpret_cast<const uint4*>(scratch + (g8 * 4 + t) * 8 + 4);
+            bf[gi][0] = lo.x, bf[gi][1] = lo.y, bf[gi][2] = lo.z, bf[gi][3] = lo.w;
+            bf[gi][4] = hi.x, bf[gi][5] = hi.y, bf[gi][6] = hi.z, bf[gi][7] = hi.w;
+        }
+        __syncwarp();
+        if (xrow < MR) {
+            const float iv = MR == 2 && xrow == 1 ? inv[MR - 1] : inv[0];
+            coef[gi] = high ? iv * 65536.0f : iv;
+            zcoef[gi] = high ? 0.0f : (MR == 2 && xrow == 1 ? xs[MR - 1] : xs[0]);
+        }
+    }
+
+    const uint32_t smem_base = smem_u32(smem);
+    for (uint32_t rb = 0; rb < blocks; ++rb) {
+        const uint32_t s = rb % nstages, round = rb / nstages;
+        if (!mbar_wait(full + s, round & 1, failed, status, kStatusFullWaitTimedOut)) break;
+        const uint32_t stage = smem_base + s * stage_stride;
+        float acc0 = 0.0f, acc1 = 0.0f;  // MMA rows g8 and g8 + 8 are features 2 g8 and 2 g8 + 1 of the block
+#pragma unroll
+        for (int gi = 0; gi < GPW; ++gi) {
+            const uint32_t G = warp + gi * kWarps;
+            if (G >= groups) continue;
+            const uint4 wa = lds128(stage + g8 * pitch + G * 64 + t * 16), wb = lds128(stage + g8 * pitch + row_bytes + G * 64 + t * 16);
+            const uint32_t a[4] = {wa.x, wa.y, wa.z, wa.w}, b[4] = {wb.x, wb.y, wb.z, wb.w};
+            int c[4] = {0, 0, 0, 0};
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                mma_u8s8(c, a[i] & 0x0f0f0f0fu, b[i] & 0x0f0f0f0fu, (a[i] >> 4) & 0x0f0f0f0fu, (b[i] >> 4) & 0x0f0f0f0fu, bf[gi][2 * i],
+                         bf[gi][2 * i + 1]);
+            // (row r, group G) of a tile lies at r * 128 + ((G % 32 / 4) ^ (r % 8)) * 16 + G % 4 * 4 of box G / 32
+            const uint32_t r0 = 2 * g8, r1 = r0 + 1, gc = (G & 31u) >> 2, gb = (G >> 5) * 2048u + (G & 3u) * 4u;
+            const uint32_t so0 = gb + r0 * 128u + ((gc ^ (r0 & 7u)) << 4), so1 = gb + r1 * 128u + ((gc ^ (r1 & 7u)) << 4);
+            const uint8_t* st_p = smem + (size_t)s * stage_stride;
+            const float s0 = *reinterpret_cast<const float*>(st_p + sz_off + so0), s1 = *reinterpret_cast<const float*>(st_p + sz_off + so1);
+            const float z0 = *reinterpret_cast<const float*>(st_p + zr_off + so0), z1 = *reinterpret_cast<const float*>(st_p + zr_off + so1);
+            const float v0 = (float)(c[0] + (c[1] << 8)) * coef[gi], v1 = (float)(c[2] + (c[3] << 8)) * coef[gi];
+            acc0 = __fmaf_rn(s0, v0, acc0), acc1 = __fmaf_rn(s1, v1, acc1);
+            acc0 = __fmaf_rn(__fmaf_rn(-8.0f, s0, z0), zcoef[gi], acc0), acc1 = __fmaf_rn(__fmaf_rn(-8.0f, s1, z1), zcoef[gi], acc1);
+        }
+        // low + high digit pairs; lanes with t even then hold this warp's share of (row xrow of x, features 2 g8, 2 g8 + 1)
+        acc0 += __shfl_xor_sync(0xffffffffu, acc0, 1);
+        acc1 += __shfl_xor_sync(0xffffffffu, acc1, 1);
+        float* part = partials + ((size_t)s * kWarps + warp) * 32;
+        if (!high) part[xrow * 16 + 2 * g8] = acc0, part[xrow * 16 + 2 * g8 + 1] = acc1;
+        __syncwarp();
+        uint32_t last = 0;
+        if (lane == 0) {
+            __threadfence_block();
+            last = atomicAdd(counts + s, 1u) == kWarps - 1;
+        }
+        last = __shfl_sync(0xffffffffu, last, 0);
+        if (last) {
+            __threadfence_block();
+            const uint32_t xr = lane >> 4, f = lane & 15u, j = rb * kBlockRows + f;
+            const volatile float* p = partials + (size_t)s * kWarps * 32 + lane;
+            float tot = p[0];
+#pragma unroll
+            for (int w = 1; w < kWarps; ++w) tot = __fadd_rn(tot, p[w * 32]);
+            if (xr < MR && j < nrows) y[(size_t)xr * n + row_begin + j] = bias ? __fadd_rn(tot, bias[row_begin + j]) : tot;
+            __syncwarp();
+            if (lane == 0) counts[s] = 0;
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty + s);  // everything this warp does with the block is done
+    }
+}
+
+template <int MR, int GPW>
+void launch(cudaStream_t s, uint32_t grid, uint64_t smem, const uint32_t* q, const float* x, const float* scale, const float* zero,
+            const float* bias, float* y, uint64_t k, uint64_t n, uint64_t groups, uint64_t nstages, uint64_t stage_stride, uint32_t* status) {
+    // scales and zero points as (n x groups) float matrices, fetched in tiles of 16 rows x 32 groups; rows past n read zeros
+    const CUtensorMap smap = make_tensor_map_2d(scale, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, groups, n, groups * 4, 32, kBlockRows, Swizzle::B128);
+    const CUtensorMap zmap = make_tensor_map_2d(zero, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, groups, n, groups * 4, 32, kBlockRows, Swizzle::B128);
+    GQ_CUDA(cudaFuncSetAttribute(gemv_q4_ring_kernel<MR, GPW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    gemv_q4_ring_kernel<MR, GPW><<<grid, kThreads, smem, s>>>(smap, zmap, q, x, bias, y, (uint32_t)k, (uint32_t)n, (uint32_t)groups,
+                                                             (uint32_t)nstages, (uint32_t)stage_stride, status);
+}
+
+}  // namespace
+
+// One or two rows of x, group_size 128, K a multiple of 4096 (so that a row of scales is whole 128-byte tile rows) of which two
+// 16-row blocks fit shared memory (K <= 8192).
+// Returns false when the shape is not this kernel's.
+bool launch_gemv_q4_ring(cudaStream_t s, int sm_count, uint32_t* status, const float* x, uint64_t m, uint64_t k, const uint32_t* q,
+                         const float* scale, const float* zero, const float* bias, uint64_t n, uint64_t group, float* y) {
+    if (m < 1 || m > 2 || group != 128 || k == 0 || (k & 4095) || k > 16384 || n == 0 || n > 0x7fffffffull) return false;
+    if (((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(scale) | reinterpret_cast<uintptr_t>(zero)) & 15) != 0) return false;
+    const uint64_t groups = k / 128, row_bytes = k / 2;
+    const uint64_t gpw = (groups + kWarps - 1) / kWarps;
+    const uint64_t blocks_total = (n + kBlockRows - 1) / kBlockRows;
+    const uint32_t grid = (uint32_t)(blocks_total < (uint64_t)sm_count ? blocks_total : (uint64_t)sm_count);
+    const uint64_t rows_per_cta = (n + grid - 1) / grid;
+    const uint64_t blocks = (rows_per_cta + kBlockRows - 1) / kBlockRows;
+    const uint64_t stage_stride = ((kBlockRows / 2) * (2 * row_bytes + kRowPad) + 1023) / 1024 * 1024 + 2 * (groups / 32) * 2048;
+    const uint64_t per_stage = stage_stride + kWarps * 32 * 4;
+    const uint64_t fixed = 1024 + kWarps * kScratchWords * 4 + kMaxStages * 4 + 2 * kMaxStages * 8 + 64;
+    const uint64_t budget = 226 * 1024;
+    if (fixed + 2 * per_stage > budget) return false;
+    uint64_t nstages = (budget - fixed) / per_stage;
+    if (nstages > kMaxStages) nstages = kMaxStages;
+    if (nstages > blocks) nstages = blocks;
+    const uint64_t smem = fixed + nstages * per_stage;
+#define GQ_RING(MRV, GPWV) launch<MRV, GPWV>(s, grid, smem, q, x, scale, zero, bias, y, k, n, groups, nstages, stage_stride, status)
+    if (m == 1) {
+        if (gpw <= 2) GQ_RING(1, 2);
+        else if (gpw <= 4) GQ_RING(1, 4);
+        else GQ_RING(1, 8);
+    } else {
+        if (gpw <= 2) GQ_RING(2, 2);
+        else if (gpw <= 4) GQ_RING(2, 4);
+        else GQ_RING(2, 8);
+    }
+#undef GQ_RING
+    return true;
+}
+
+}  // namespace gq

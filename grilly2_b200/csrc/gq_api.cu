@@ -546,7 +546,7 @@ int32_t gq_int4_linear(gq_ctx* ctx, gq_buf x, uint64_t x_off, uint64_t m, uint64
         Locked l(ctx);
         check_dims("gq_int4_linear", m, k, n);
         check_group(group);
-        if (kernel < GQ_KERNEL_AUTO || kernel > GQ_KERNEL_UMMA) fail("gq_int4_linear: unknown kernel selector %d", kernel);
+        if (kernel < GQ_KERNEL_AUTO || kernel > GQ_KERNEL_RING) fail("gq_int4_linear: unknown kernel selector %d", kernel);
         uint64_t groups = (k + group - 1) / group;
         auto xp = (const float*)view(ctx, x, x_off, m * k, 4, "gq_int4_linear input");
         auto qp = (const uint32_t*)view(ctx, q, 0, n * words4(k), 4, "gq_int4_linear q");
@@ -559,7 +559,12 @@ int32_t gq_int4_linear(gq_ctx* ctx, gq_buf x, uint64_t x_off, uint64_t m, uint64
         if (kernel == GQ_KERNEL_TENSOR) fail("gq_int4_linear: there is no tensor-core int4 kernel (the reference has none either, crates/grilly-infer/src/quant4.rs:412-413)");
         bool done = false;
         const char* name = "gemv_q4";
-        if (kernel == GQ_KERNEL_AUTO || kernel == GQ_KERNEL_IMMA) {
+        if (kernel == GQ_KERNEL_AUTO || kernel == GQ_KERNEL_RING) {
+            done = launch_gemv_q4_ring(ctx->stream, ctx->prop.multiProcessorCount, ctx->status_dev, xp, m, k, qp, sp, zp, bp, n, group, yp);
+            if (done) name = "gemv_q4_ring";
+            if (!done && kernel == GQ_KERNEL_RING) fail("gq_int4_linear: the ring kernel takes one or two rows of x, group_size 128 and in_features 4096 or 8192 (m = %llu, k = %llu, group_size = %llu)", (unsigned long long)m, (unsigned long long)k, (unsigned long long)group);
+        }
+        if (!done && (kernel == GQ_KERNEL_AUTO || kernel == GQ_KERNEL_IMMA)) {
             done = launch_gemv_q4_imma(ctx->stream, ctx->prop.multiProcessorCount, ctx->status_dev, xp, m, k, qp, sp, zp, bp, n, group, yp);
             if (done) name = "gemv_q4_imma";
             if (!done && kernel == GQ_KERNEL_IMMA) fail("gq_int4_linear: the IMMA kernel takes one or two rows of x, a group_size that is a multiple of 128 and rows that fit shared memory (m = %llu, k = %llu, group_size = %llu)", (unsigned long long)m, (unsigned long long)k, (unsigned long long)group);

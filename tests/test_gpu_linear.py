@@ -61,7 +61,9 @@ def test_int8_linear(g, m, n, k, with_bias):
 
 INT4_SHAPES = [(1, 1, 32, 32), (2, 300, 384, 128), (1, 2500, 128, 128), (2, 151, 4864, 256), (1, 777, 1000, 128),
                (1, 5, 128, 128), (3, 4, 130, 128), (8, 7, 256, 64), (2, 64, 896, 128),
-               (9, 6, 4864, 128), (4, 33, 4096, 128), (16, 40, 1024, 32), (1, 300, 8192, 128), (5, 7, 70, 32)]
+               (9, 6, 4864, 128), (4, 33, 4096, 128), (16, 40, 1024, 32), (1, 300, 8192, 128), (5, 7, 70, 32),
+               (1, 2500, 512, 128), (1, 333, 4096, 128), (1, 97, 14336, 128), (2, 1500, 1024, 128), (2, 40, 12288, 128), (2, 700, 4096, 128),
+               (1, 3000, 16384, 128)]
 
 
 @pytest.mark.parametrize("m,n,k,group", INT4_SHAPES)
@@ -82,6 +84,7 @@ def test_int4_linear(g, m, n, k, group, with_bias):
     np.testing.assert_array_equal(y, ref)
     assert (np.abs(y - want) <= bound).all()
     kernels = [_lib.KERNEL_DP4A, _lib.KERNEL_AUTO] + ([_lib.KERNEL_IMMA] if m <= 2 and group % 128 == 0 else [])
+    kernels += [_lib.KERNEL_RING] if m <= 2 and group == 128 and k % 4096 == 0 and k <= 8192 else []
     for kernel in kernels:
         y = t._q.linear(xt, bt, kernel).numpy()
         assert rel(y, ref) <= TOL
@@ -95,7 +98,7 @@ def test_x_and_bias_at_element_offsets(g, x_off):
     reference's scalar one (g2-linear-q4.glsl:80-86)."""
     from grilly2_b200 import _C, _lib
     rng = np.random.default_rng(x_off)
-    m, n, k = 3, 21, 256
+    m, n, k = 3, 21, 4096
     w = rng.standard_normal((n, k)).astype(np.float32)
     flat = rng.standard_normal(x_off + m * k).astype(np.float32)
     bflat = rng.standard_normal(5 + n).astype(np.float32)
@@ -113,6 +116,10 @@ def test_x_and_bias_at_element_offsets(g, x_off):
     ref = oracle.linear_q4(x, q4, s4, z4, b, k, 64, x_vec4=(x_off % 4 == 0))
     np.testing.assert_array_equal(w4.linear(xs, bs, _lib.KERNEL_GEMV).numpy(), ref)
     assert rel(w4.linear(xs, bs, _lib.KERNEL_DP4A).numpy(), ref) <= TOL
+    w4g = _C.Int4Weight.quantize(_C.Tensor.from_numpy(w), 128)
+    q4, s4, z4 = oracle.quantize_q4(w, 128)
+    ref = oracle.linear_q4(x[:1], q4, s4, z4, b, k, 128, x_vec4=(x_off % 4 == 0))
+    assert rel(w4g.linear(_C.Tensor(xs.storage, (1, k), "float32", x_off), bs, _lib.KERNEL_RING).numpy(), ref) <= TOL
 
 
 def test_leading_dims_empty_and_refusals(g):
@@ -193,7 +200,7 @@ def test_dp4a_digit_planes_on_hard_inputs(g):
     exact zeros, negative zero. Non-finite x makes the affected outputs NaN."""
     from grilly2_b200 import _C, _lib
     rng = np.random.default_rng(12)
-    n, k = 50, 1024
+    n, k = 50, 4096
     w = rng.standard_normal((n, k)).astype(np.float32)
     x = rng.standard_normal((4, k)).astype(np.float32)
     x[0, ::97] *= 1e4
@@ -211,6 +218,7 @@ def test_dp4a_digit_planes_on_hard_inputs(g):
         for kernel in (_lib.KERNEL_DP4A, _lib.KERNEL_IMMA):
             assert rel(w8.linear(xt, None, kernel).numpy(), oracle.linear_q8_f64(xr, q, scale, None, k)[0]) <= TOL
             assert rel(w4.linear(xt, None, kernel).numpy(), oracle.linear_q4_f64(xr, q4, s4, z4, None, k, 128)[0]) <= TOL
+        assert rel(w4.linear(xt, None, _lib.KERNEL_RING).numpy(), oracle.linear_q4_f64(xr, q4, s4, z4, None, k, 128)[0]) <= TOL
     xbad = x[:1].copy()
     xbad[0, 5] = np.inf
     for kernel in (_lib.KERNEL_DP4A, _lib.KERNEL_IMMA):
@@ -218,3 +226,6 @@ def test_dp4a_digit_planes_on_hard_inputs(g):
         assert np.isnan(w8.linear(_C.Tensor.from_numpy(xbad), None, kernel).numpy()).all()
         xbad[0, 5] = np.nan
         assert np.isnan(w4.linear(_C.Tensor.from_numpy(xbad), None, kernel).numpy()).all()
+    for bad in (np.inf, np.nan):
+        xbad[0, 5] = bad
+        assert np.isnan(w4.linear(_C.Tensor.from_numpy(xbad), None, _lib.KERNEL_RING).numpy()).all()
