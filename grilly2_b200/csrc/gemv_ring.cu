@@ -1,4 +1,4 @@
-// Decode GEMV for int4 group-128 weights and one or two rows of x on the
+// Decode GEMV for int4 group-128 weights and one to four rows of x on the
 // warp-level integer tensor instruction (mma.sync m16n8k32, u8 x s8 -> s32),
 // organised so that a weight costs few instructions and no CTA-wide barrier
 // stands between the launch and the first multiply.
@@ -51,7 +51,7 @@ constexpr int kThreads = (kWarps + 1) * 32; // + the producer warp
 constexpr uint32_t kBlockRows = 16;         // output features per MMA and per ring stage
 constexpr uint32_t kRowPad = 16;            // bytes added to a row's pitch in shared memory
 constexpr int kMaxStages = 8;
-constexpr uint32_t kScratchWords = 8 * 4 * 4 * 2;  // per warp: [column][t][mma][parity] digit words of one group
+constexpr uint32_t kScratchWords = 8 * 4 * 4 * 2;  // per warp and 8-column tile: [column][t][mma][parity] digit words of one group
 
 __device__ __forceinline__ void mma_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
@@ -131,8 +131,9 @@ __global__ void __launch_bounds__(kThreads, 1)
     const uint32_t sz_off = ((kBlockRows / 2) * pitch + 1023u) & ~1023u;          // a block's scales: nbox boxes of 16 rows x 128 bytes,
     const uint32_t zr_off = sz_off + nbox * 2048u;                          // then its zero points, each box 128-byte swizzled
     float* partials = reinterpret_cast<float*>(smem + (size_t)nstages * stage_stride);
-    uint32_t* scratch_all = reinterpret_cast<uint32_t*>(partials + (size_t)nstages * kWarps * 32);
-    uint32_t* counts = scratch_all + kWarps * kScratchWords;
+    constexpr int kTiles = (MR + 1) / 2;
+    uint32_t* scratch_all = reinterpret_cast<uint32_t*>(partials + (size_t)nstages * kWarps * 32 * kTiles);
+    uint32_t* counts = scratch_all + kWarps * kScratchWords * kTiles;
     uint64_t* full = reinterpret_cast<uint64_t*>(counts + kMaxStages);
     uint64_t* empty = full + kMaxStages;
     volatile uint32_t* failed = reinterpret_cast<volatile uint32_t*>(empty + kMaxStages);
@@ -178,11 +179,12 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
 
     // ── consumers: B fragments of this warp's groups, once ──
+    constexpr int NT = (MR + 1) / 2;               // 8-column tiles of B: two rows of x (4 digits each) per tile
     const uint32_t g8 = lane >> 2, t = lane & 3u;  // MMA row (and B column) index, thread-in-group
-    const uint32_t xrow = t >> 1, high = t & 1u;   // this lane's accumulator columns: digits 2 high, 2 high + 1 of row xrow of x
-    uint32_t* scratch = scratch_all + warp * kScratchWords;
-    uint32_t bf[GPW][8];
-    float coef[GPW], zcoef[GPW];
+    const uint32_t xloc = t >> 1, high = t & 1u;   // this lane's accumulator columns: digits 2 high, 2 high + 1 of row 2 nt + xloc of x
+    uint32_t* scratch = scratch_all + warp * (kScratchWords * NT);
+    uint32_t bf[GPW][NT][8];
+    float coef[GPW][NT], zcoef[GPW][NT];
     float xv[GPW][MR][4];  // every load of x is requested before the first conversion waits for one
 #pragma unroll
     for (int gi = 0; gi < GPW; ++gi)
@@ -192,25 +194,33 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
     for (int gi = 0; gi < GPW; ++gi) {
         const uint32_t G = warp + gi * kWarps;
-        coef[gi] = zcoef[gi] = 0.0f;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) bf[gi][j] = 0u;
+        for (int nt = 0; nt < NT; ++nt) {
+            coef[gi][nt] = zcoef[gi][nt] = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) bf[gi][nt][j] = 0u;
+        }
         if (G >= groups) continue;  // uniform over the warp
         float inv[MR], xs[MR];
 #pragma unroll
         for (int r = 0; r < MR; ++r) convert_group(xv[gi][r], lane, 4 * r, scratch, inv[r], xs[r]);
         __syncwarp();
-        if (g8 < 4 * MR) {
-            const uint4 lo = *reinterpret_cast<const uint4*>(scratch + (g8 * 4 + t) * 8), hi = *reinterpret_cast<const uint4*>(scratch + (g8 * 4 + t) * 8 + 4);
-            bf[gi][0] = lo.x, bf[gi][1] = lo.y, bf[gi][2] = lo.z, bf[gi][3] = lo.w;
-            bf[gi][4] = hi.x, bf[gi][5] = hi.y, bf[gi][6] = hi.z, bf[gi][7] = hi.w;
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            const uint32_t col = nt * 8 + g8;
+            if (col < 4 * MR) {
+                const uint4 lo = *reinterpret_cast<const uint4*>(scratch + (col * 4 + t) * 8), hi = *reinterpret_cast<const uint4*>(scratch + (col * 4 + t) * 8 + 4);
+                bf[gi][nt][0] = lo.x, bf[gi][nt][1] = lo.y, bf[gi][nt][2] = lo.z, bf[gi][nt][3] = lo.w;
+                bf[gi][nt][4] = hi.x, bf[gi][nt][5] = hi.y, bf[gi][nt][6] = hi.z, bf[gi][nt][7] = hi.w;
+            }
+#pragma unroll
+            for (int r = 0; r < MR; ++r)
+                if ((uint32_t)r == 2 * nt + xloc) {
+                    coef[gi][nt] = high ? inv[r] * 65536.0f : inv[r];
+                    zcoef[gi][nt] = high ? 0.0f : xs[r];
+                }
         }
         __syncwarp();
-        if (xrow < MR) {
-            const float iv = MR == 2 && xrow == 1 ? inv[MR - 1] : inv[0];
-            coef[gi] = high ? iv * 65536.0f : iv;
-            zcoef[gi] = high ? 0.0f : (MR == 2 && xrow == 1 ? xs[MR - 1] : xs[0]);
-        }
     }
 
     const uint32_t smem_base = smem_u32(smem);
@@ -218,33 +228,46 @@ __global__ void __launch_bounds__(kThreads, 1)
         const uint32_t s = rb % nstages, round = rb / nstages;
         if (!mbar_wait(full + s, round & 1, failed, status, kStatusFullWaitTimedOut)) break;
         const uint32_t stage = smem_base + s * stage_stride;
-        float acc0 = 0.0f, acc1 = 0.0f;  // MMA rows g8 and g8 + 8 are features 2 g8 and 2 g8 + 1 of the block
+        float acc0[NT], acc1[NT];  // MMA rows g8 and g8 + 8 are features 2 g8 and 2 g8 + 1 of the block
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) acc0[nt] = acc1[nt] = 0.0f;
 #pragma unroll
         for (int gi = 0; gi < GPW; ++gi) {
             const uint32_t G = warp + gi * kWarps;
             if (G >= groups) continue;
             const uint4 wa = lds128(stage + g8 * pitch + G * 64 + t * 16), wb = lds128(stage + g8 * pitch + row_bytes + G * 64 + t * 16);
             const uint32_t a[4] = {wa.x, wa.y, wa.z, wa.w}, b[4] = {wb.x, wb.y, wb.z, wb.w};
-            int c[4] = {0, 0, 0, 0};
+            int c[NT][4];
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
-                mma_u8s8(c, a[i] & 0x0f0f0f0fu, b[i] & 0x0f0f0f0fu, (a[i] >> 4) & 0x0f0f0f0fu, (b[i] >> 4) & 0x0f0f0f0fu, bf[gi][2 * i],
-                         bf[gi][2 * i + 1]);
+            for (int nt = 0; nt < NT; ++nt) c[nt][0] = c[nt][1] = c[nt][2] = c[nt][3] = 0;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const uint32_t a0 = a[i] & 0x0f0f0f0fu, a1 = b[i] & 0x0f0f0f0fu, a2 = (a[i] >> 4) & 0x0f0f0f0fu, a3 = (b[i] >> 4) & 0x0f0f0f0fu;
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) mma_u8s8(c[nt], a0, a1, a2, a3, bf[gi][nt][2 * i], bf[gi][nt][2 * i + 1]);
+            }
             // (row r, group G) of a tile lies at r * 128 + ((G % 32 / 4) ^ (r % 8)) * 16 + G % 4 * 4 of box G / 32
             const uint32_t r0 = 2 * g8, r1 = r0 + 1, gc = (G & 31u) >> 2, gb = (G >> 5) * 2048u + (G & 3u) * 4u;
             const uint32_t so0 = gb + r0 * 128u + ((gc ^ (r0 & 7u)) << 4), so1 = gb + r1 * 128u + ((gc ^ (r1 & 7u)) << 4);
             const uint8_t* st_p = smem + (size_t)s * stage_stride;
             const float s0 = *reinterpret_cast<const float*>(st_p + sz_off + so0), s1 = *reinterpret_cast<const float*>(st_p + sz_off + so1);
             const float z0 = *reinterpret_cast<const float*>(st_p + zr_off + so0), z1 = *reinterpret_cast<const float*>(st_p + zr_off + so1);
-            const float v0 = (float)(c[0] + (c[1] << 8)) * coef[gi], v1 = (float)(c[2] + (c[3] << 8)) * coef[gi];
-            acc0 = __fmaf_rn(s0, v0, acc0), acc1 = __fmaf_rn(s1, v1, acc1);
-            acc0 = __fmaf_rn(__fmaf_rn(-8.0f, s0, z0), zcoef[gi], acc0), acc1 = __fmaf_rn(__fmaf_rn(-8.0f, s1, z1), zcoef[gi], acc1);
+            const float zm0 = __fmaf_rn(-8.0f, s0, z0), zm1 = __fmaf_rn(-8.0f, s1, z1);
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                const float v0 = (float)(c[nt][0] + (c[nt][1] << 8)) * coef[gi][nt], v1 = (float)(c[nt][2] + (c[nt][3] << 8)) * coef[gi][nt];
+                acc0[nt] = __fmaf_rn(zm0, zcoef[gi][nt], __fmaf_rn(s0, v0, acc0[nt]));
+                acc1[nt] = __fmaf_rn(zm1, zcoef[gi][nt], __fmaf_rn(s1, v1, acc1[nt]));
+            }
         }
-        // low + high digit pairs; lanes with t even then hold this warp's share of (row xrow of x, features 2 g8, 2 g8 + 1)
-        acc0 += __shfl_xor_sync(0xffffffffu, acc0, 1);
-        acc1 += __shfl_xor_sync(0xffffffffu, acc1, 1);
-        float* part = partials + ((size_t)s * kWarps + warp) * 32;
-        if (!high) part[xrow * 16 + 2 * g8] = acc0, part[xrow * 16 + 2 * g8 + 1] = acc1;
+        // low + high digit pairs; lanes with t even then hold this warp's share of (row 2 nt + xloc of x, features 2 g8, 2 g8 + 1)
+        float* part = partials + ((size_t)s * kWarps + warp) * (32 * NT);
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            acc0[nt] += __shfl_xor_sync(0xffffffffu, acc0[nt], 1);
+            acc1[nt] += __shfl_xor_sync(0xffffffffu, acc1[nt], 1);
+            if (!high) part[nt * 32 + xloc * 16 + 2 * g8] = acc0[nt], part[nt * 32 + xloc * 16 + 2 * g8 + 1] = acc1[nt];
+        }
         __syncwarp();
         uint32_t last = 0;
         if (lane == 0) {
@@ -254,12 +277,16 @@ __global__ void __launch_bounds__(kThreads, 1)
         last = __shfl_sync(0xffffffffu, last, 0);
         if (last) {
             __threadfence_block();
-            const uint32_t xr = lane >> 4, f = lane & 15u, j = rb * kBlockRows + f;
-            const volatile float* p = partials + (size_t)s * kWarps * 32 + lane;
-            float tot = p[0];
+            const uint32_t f = lane & 15u, j = rb * kBlockRows + f;
 #pragma unroll
-            for (int w = 1; w < kWarps; ++w) tot = __fadd_rn(tot, p[w * 32]);
-            if (xr < MR && j < nrows) y[(size_t)xr * n + row_begin + j] = bias ? __fadd_rn(tot, bias[row_begin + j]) : tot;
+            for (int nt = 0; nt < NT; ++nt) {
+                const uint32_t xr = 2 * nt + (lane >> 4);
+                const volatile float* p = partials + (size_t)s * kWarps * (32 * NT) + nt * 32 + lane;
+                float tot = p[0];
+#pragma unroll
+                for (int w = 1; w < kWarps; ++w) tot = __fadd_rn(tot, p[w * 32 * NT]);
+                if (xr < MR && j < nrows) y[(size_t)xr * n + row_begin + j] = bias ? __fadd_rn(tot, bias[row_begin + j]) : tot;
+            }
             __syncwarp();
             if (lane == 0) counts[s] = 0;
         }
@@ -281,12 +308,12 @@ void launch(cudaStream_t s, uint32_t grid, uint64_t smem, const uint32_t* q, con
 
 }  // namespace
 
-// One or two rows of x, group_size 128, K a multiple of 4096 (so that a row of scales is whole 128-byte tile rows) of which two
+// Up to four rows of x (three or four: K = 4096 only), group_size 128, K a multiple of 4096 (so that a row of scales is whole 128-byte tile rows) of which two
 // 16-row blocks fit shared memory (K <= 8192).
 // Returns false when the shape is not this kernel's.
 bool launch_gemv_q4_ring(cudaStream_t s, int sm_count, uint32_t* status, const float* x, uint64_t m, uint64_t k, const uint32_t* q,
                          const float* scale, const float* zero, const float* bias, uint64_t n, uint64_t group, float* y) {
-    if (m < 1 || m > 2 || group != 128 || k == 0 || (k & 4095) || k > 16384 || n == 0 || n > 0x7fffffffull) return false;
+    if (m < 1 || m > 4 || group != 128 || k == 0 || (k & 4095) || k > 16384 || n == 0 || n > 0x7fffffffull) return false;
     if (((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(scale) | reinterpret_cast<uintptr_t>(zero)) & 15) != 0) return false;
     const uint64_t groups = k / 128, row_bytes = k / 2;
     const uint64_t gpw = (groups + kWarps - 1) / kWarps;
@@ -295,8 +322,10 @@ bool launch_gemv_q4_ring(cudaStream_t s, int sm_count, uint32_t* status, const f
     const uint64_t rows_per_cta = (n + grid - 1) / grid;
     const uint64_t blocks = (rows_per_cta + kBlockRows - 1) / kBlockRows;
     const uint64_t stage_stride = ((kBlockRows / 2) * (2 * row_bytes + kRowPad) + 1023) / 1024 * 1024 + 2 * (groups / 32) * 2048;
-    const uint64_t per_stage = stage_stride + kWarps * 32 * 4;
-    const uint64_t fixed = 1024 + kWarps * kScratchWords * 4 + kMaxStages * 4 + 2 * kMaxStages * 8 + 64;
+    const uint64_t tiles = (m + 1) / 2;
+    if (m > 2 && gpw > 2) return false;  // the B fragments of three or four rows of x fit the registers for K = 4096 only
+    const uint64_t per_stage = stage_stride + kWarps * 32 * 4 * tiles;
+    const uint64_t fixed = 1024 + kWarps * kScratchWords * 4 * tiles + kMaxStages * 4 + 2 * kMaxStages * 8 + 64;
     const uint64_t budget = 226 * 1024;
     if (fixed + 2 * per_stage > budget) return false;
     uint64_t nstages = (budget - fixed) / per_stage;
@@ -308,10 +337,14 @@ bool launch_gemv_q4_ring(cudaStream_t s, int sm_count, uint32_t* status, const f
         if (gpw <= 2) GQ_RING(1, 2);
         else if (gpw <= 4) GQ_RING(1, 4);
         else GQ_RING(1, 8);
-    } else {
+    } else if (m == 2) {
         if (gpw <= 2) GQ_RING(2, 2);
         else if (gpw <= 4) GQ_RING(2, 4);
         else GQ_RING(2, 8);
+    } else if (m == 3) {
+        GQ_RING(3, 2);
+    } else {
+        GQ_RING(4, 2);
     }
 #undef GQ_RING
     return true;
