@@ -42,6 +42,7 @@ __device__ __forceinline__ float warp_max(float v) {
 // (the reference raises a deferred IndexError from a fault buffer).
 __global__ void __launch_bounds__(256) embedding_kernel(const float* __restrict__ table, const int32_t* __restrict__ ids,
                                                        uint32_t rows, uint32_t width, uint32_t vocab, float* __restrict__ out) {
+    GQ_GRID_DEP_SYNC();
     for (uint32_t r = blockIdx.x; r < rows; r += gridDim.x) {
         const int32_t id = ids[r];
         const bool ok = id >= 0 && (uint32_t)id < vocab;
@@ -56,6 +57,7 @@ __global__ void __launch_bounds__(256) embedding_kernel(const float* __restrict_
 __global__ void __launch_bounds__(256) add_rms_norm_kernel(const float* __restrict__ x, const float* __restrict__ res,
                                                           const float* __restrict__ w, uint32_t rows, uint32_t n, float eps,
                                                           float* __restrict__ y, float* __restrict__ h) {
+    GQ_GRID_DEP_SYNC();
     __shared__ double s_part[8];
     __shared__ float s_r;
     for (uint32_t row = blockIdx.x; row < rows; row += gridDim.x) {
@@ -97,6 +99,7 @@ __global__ void __launch_bounds__(256) rope_kv_append_kernel(const float* __rest
                                                             uint32_t layer, uint32_t heads, uint32_t kv_heads, uint32_t dim,
                                                             uint32_t max_len, float* __restrict__ q_out, float* __restrict__ kc,
                                                             float* __restrict__ vc) {
+    GQ_GRID_DEP_SYNC();
     const uint32_t pos = lens[layer];
     const uint32_t total = (heads + 2 * kv_heads) * dim, half = dim / 2;
     for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
@@ -118,6 +121,7 @@ __global__ void __launch_bounds__(256) rope_kv_append_kernel(const float* __rest
 
 // lens[l] = min(lens[l] + 1, max_len) for every layer: once per step, after the last layer has attended.
 __global__ void kv_advance_kernel(uint32_t* lens, uint32_t layers, uint32_t max_len) {
+    GQ_GRID_DEP_SYNC();
     const uint32_t l = blockIdx.x * blockDim.x + threadIdx.x;
     if (l < layers) lens[l] = min(lens[l] + 1, max_len);
 }
@@ -145,6 +149,7 @@ __device__ __forceinline__ float exp_cephes(float v) {
 // sigmoid as g2-common.glsl:163-166).
 __global__ void __launch_bounds__(256) swiglu_kernel(const float* __restrict__ gate_up, uint32_t rows, uint32_t width,
                                                     float* __restrict__ out) {
+    GQ_GRID_DEP_SYNC();
     const size_t total = (size_t)rows * width;
     for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < total; i += (size_t)gridDim.x * 256) {
         const size_t r = i / width, j = i % width;
@@ -162,6 +167,7 @@ __global__ void __launch_bounds__(256) swiglu_kernel(const float* __restrict__ g
 constexpr uint32_t kArgmaxRows = 1024;  // rows one launch handles (and the size of the state)
 __global__ void __launch_bounds__(256) argmax_rows_kernel(const float* __restrict__ v, uint32_t n, int32_t* __restrict__ out,
                                                          unsigned long long* state) {
+    GQ_GRID_DEP_SYNC();
     __shared__ unsigned long long s_key[8];
     const uint32_t row = blockIdx.y;
     const float* vr = v + (size_t)row * n;
@@ -215,6 +221,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const float* 
                                                                   const float* __restrict__ vc, const uint32_t* __restrict__ lens,
                                                                   uint32_t layer, uint32_t heads, uint32_t kv_heads, uint32_t max_len,
                                                                   float scale, uint32_t chunk, float* scratch, float* __restrict__ out) {
+    GQ_GRID_DEP_SYNC();
     constexpr uint32_t dim = 4 * L, KP = kAttnThreads / L;
     __shared__ float s_sc[kAttnMaxChunk];
     __shared__ float s_red[kAttnThreads / 32];
@@ -330,20 +337,20 @@ static inline uint32_t blocks_for(size_t items, uint32_t per, uint32_t cap) {
 }
 
 void launch_embedding(cudaStream_t s, const float* table, const int32_t* ids, uint64_t rows, uint64_t width, uint64_t vocab, float* out) {
-    embedding_kernel<<<blocks_for(rows, 1, 1024), 256, 0, s>>>(table, ids, (uint32_t)rows, (uint32_t)width, (uint32_t)vocab, out);
+    launch_after(embedding_kernel, dim3(blocks_for(rows, 1, 1024)), dim3(256), 0, s, table, ids, (uint32_t)rows, (uint32_t)width, (uint32_t)vocab, out);
 }
 void launch_add_rms_norm(cudaStream_t s, const float* x, const float* res, const float* w, uint64_t rows, uint64_t n, float eps,
                          float* y, float* h) {
-    add_rms_norm_kernel<<<blocks_for(rows, 1, 1024), 256, 0, s>>>(x, res, w, (uint32_t)rows, (uint32_t)n, eps, y, h);
+    launch_after(add_rms_norm_kernel, dim3(blocks_for(rows, 1, 1024)), dim3(256), 0, s, x, res, w, (uint32_t)rows, (uint32_t)n, eps, y, h);
 }
 void launch_rope_kv_append(cudaStream_t s, const float* qkv, const float* cosv, const float* sinv, const uint32_t* lens, uint32_t layer,
                            uint32_t heads, uint32_t kv_heads, uint32_t dim, uint32_t max_len, float* q_out, float* kc, float* vc) {
     const uint32_t total = (heads + 2 * kv_heads) * dim;
-    rope_kv_append_kernel<<<blocks_for(total, 256, 64), 256, 0, s>>>(qkv, cosv, sinv, lens, layer, heads, kv_heads, dim, max_len, q_out,
-                                                                    kc, vc);
+    launch_after(rope_kv_append_kernel, dim3(blocks_for(total, 256, 64)), dim3(256), 0, s, qkv, cosv, sinv, lens, layer, heads, kv_heads, dim, max_len,
+                 q_out, kc, vc);
 }
 void launch_kv_advance(cudaStream_t s, uint32_t* lens, uint32_t layers, uint32_t max_len) {
-    kv_advance_kernel<<<(layers + 127) / 128, 128, 0, s>>>(lens, layers, max_len);
+    launch_after(kv_advance_kernel, dim3((layers + 127) / 128), dim3(128), 0, s, lens, layers, max_len);
 }
 // Splits of the cache length: about kAttnChunk keys each, at most kAttnMaxSplits (more only where a split would
 // otherwise exceed the kAttnMaxChunk scores that fit in shared memory).
@@ -364,23 +371,23 @@ void launch_attn_decode(cudaStream_t s, const float* q, const float* kc, const f
         fail("attention: a cache of %u positions is beyond this kernel (%u splits of %u keys)", max_len, splits, chunk);
     const dim3 grid(splits, heads);
     if (dim == 32)
-        attn_decode_kernel<8><<<grid, kAttnThreads, 0, s>>>(q, kc, vc, lens, layer, heads, kv_heads, max_len, scale, chunk, scratch, out);
+        launch_after(attn_decode_kernel<8>, grid, dim3(kAttnThreads), 0, s, q, kc, vc, lens, layer, heads, kv_heads, max_len, scale, chunk, scratch, out);
     else if (dim == 64)
-        attn_decode_kernel<16><<<grid, kAttnThreads, 0, s>>>(q, kc, vc, lens, layer, heads, kv_heads, max_len, scale, chunk, scratch, out);
+        launch_after(attn_decode_kernel<16>, grid, dim3(kAttnThreads), 0, s, q, kc, vc, lens, layer, heads, kv_heads, max_len, scale, chunk, scratch, out);
     else if (dim == 128)
-        attn_decode_kernel<32><<<grid, kAttnThreads, 0, s>>>(q, kc, vc, lens, layer, heads, kv_heads, max_len, scale, chunk, scratch, out);
+        launch_after(attn_decode_kernel<32>, grid, dim3(kAttnThreads), 0, s, q, kc, vc, lens, layer, heads, kv_heads, max_len, scale, chunk, scratch, out);
     else
         fail("attention: head_dim must be 32, 64 or 128, got %u", dim);
 }
 void launch_swiglu(cudaStream_t s, const float* gate_up, uint64_t rows, uint64_t width, float* out) {
-    swiglu_kernel<<<blocks_for(rows * width, 256, 148 * 8), 256, 0, s>>>(gate_up, (uint32_t)rows, (uint32_t)width, out);
+    launch_after(swiglu_kernel, dim3(blocks_for(rows * width, 256, 148 * 8)), dim3(256), 0, s, gate_up, (uint32_t)rows, (uint32_t)width, out);
 }
 uint64_t argmax_state_bytes() { return kArgmaxRows * 12ull; }
 void launch_argmax_rows(cudaStream_t s, const float* v, uint64_t rows, uint64_t n, int32_t* out, void* state) {
     const uint32_t per_row = blocks_for(n, 1024, rows >= 64 ? 4 : 148);
     for (uint64_t r0 = 0; r0 < rows; r0 += kArgmaxRows) {
         const uint32_t now = (uint32_t)(rows - r0 < kArgmaxRows ? rows - r0 : kArgmaxRows);
-        argmax_rows_kernel<<<dim3(per_row, now), 256, 0, s>>>(v + r0 * n, (uint32_t)n, out + r0, (unsigned long long*)state);
+        launch_after(argmax_rows_kernel, dim3(per_row, now), dim3(256), 0, s, v + r0 * n, (uint32_t)n, out + r0, (unsigned long long*)state);
     }
 }
 

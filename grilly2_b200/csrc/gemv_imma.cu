@@ -181,6 +181,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                      const float* __restrict__ zero, const float* __restrict__ bias, float* __restrict__ y, uint32_t k,
                      uint32_t n, uint32_t vecs, uint32_t groups, uint32_t gshift, uint32_t gblocks, uint32_t nblocks,
                      uint32_t nstages, uint32_t* status) {
+    GQ_GRID_DEP_SYNC();
     constexpr int R = IS4 ? 8 : 4;
     extern __shared__ __align__(128) uint8_t smem_raw[];
     uint8_t* stages = smem_raw;                                                  // nstages * kStageBytes
@@ -386,8 +387,8 @@ bool run(cudaStream_t s, int sm_count, uint32_t* status, const float* x, uint64_
     const bool xvec = aligned16(x) && k % 4 == 0;
     auto kernel = xvec ? gemv_imma_kernel<IS4, MR, true> : gemv_imma_kernel<IS4, MR, false>;
     GQ_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kernel<<<grid, kThreads, smem, s>>>(x, reinterpret_cast<const uint8_t*>(q), scale, zero, bias, y, (uint32_t)k, (uint32_t)n, vecs,
-                                        groups, gshift, gblocks, nblocks, nstages, status);
+    launch_after(kernel, dim3(grid), dim3(kThreads), smem, s, x, reinterpret_cast<const uint8_t*>(q), scale, zero, bias, y, (uint32_t)k,
+                 (uint32_t)n, vecs, groups, gshift, gblocks, nblocks, nstages, status);
     return true;
 }
 

@@ -139,6 +139,8 @@ __global__ void __launch_bounds__(kThreads, 1)
     volatile uint32_t* failed = reinterpret_cast<volatile uint32_t*>(empty + kMaxStages);
 
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    // A following launch that asked for it may start its CTAs as ours exit; it still waits (below) before touching x or y.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const uint32_t row_begin = (uint32_t)((uint64_t)n * blockIdx.x / gridDim.x), row_end = (uint32_t)((uint64_t)n * (blockIdx.x + 1) / gridDim.x);
     const uint32_t nrows = row_end - row_begin;
     const uint32_t blocks = (nrows + kBlockRows - 1) / kBlockRows;
@@ -186,6 +188,9 @@ __global__ void __launch_bounds__(kThreads, 1)
     uint32_t bf[GPW][NT][8];
     float coef[GPW][NT], zcoef[GPW][NT];
     float xv[GPW][MR][4];  // every load of x is requested before the first conversion waits for one
+    // x may be the previous launch's output, and y or the partial sums' readers its input: wait for it to finish. The
+    // producer warp did not: the weights it fetches are not written by that launch.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 #pragma unroll
     for (int gi = 0; gi < GPW; ++gi)
 #pragma unroll
@@ -297,13 +302,20 @@ __global__ void __launch_bounds__(kThreads, 1)
 
 template <int MR, int GPW>
 void launch(cudaStream_t s, uint32_t grid, uint64_t smem, const uint32_t* q, const float* x, const float* scale, const float* zero,
-            const float* bias, float* y, uint64_t k, uint64_t n, uint64_t groups, uint64_t nstages, uint64_t stage_stride, uint32_t* status) {
+            const float* bias, float* y, uint64_t k, uint64_t n, uint64_t groups, uint64_t nstages, uint64_t stage_stride, uint32_t* status,
+            bool overlap) {
     // scales and zero points as (n x groups) float matrices, fetched in tiles of 16 rows x 32 groups; rows past n read zeros
     const CUtensorMap smap = make_tensor_map_2d(scale, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, groups, n, groups * 4, 32, kBlockRows, Swizzle::B128);
     const CUtensorMap zmap = make_tensor_map_2d(zero, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, groups, n, groups * 4, 32, kBlockRows, Swizzle::B128);
     GQ_CUDA(cudaFuncSetAttribute(gemv_q4_ring_kernel<MR, GPW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-    gemv_q4_ring_kernel<MR, GPW><<<grid, kThreads, smem, s>>>(smap, zmap, q, x, bias, y, (uint32_t)k, (uint32_t)n, (uint32_t)groups,
-                                                             (uint32_t)nstages, (uint32_t)stage_stride, status);
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(grid), cfg.blockDim = dim3(kThreads), cfg.dynamicSmemBytes = smem, cfg.stream = s;
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr, cfg.numAttrs = overlap ? 1 : 0;
+    GQ_CUDA(cudaLaunchKernelEx(&cfg, gemv_q4_ring_kernel<MR, GPW>, smap, zmap, q, x, bias, y, (uint32_t)k, (uint32_t)n, (uint32_t)groups,
+                               (uint32_t)nstages, (uint32_t)stage_stride, status));
 }
 
 }  // namespace
@@ -312,7 +324,8 @@ void launch(cudaStream_t s, uint32_t grid, uint64_t smem, const uint32_t* q, con
 // 16-row blocks fit shared memory (K <= 8192).
 // Returns false when the shape is not this kernel's.
 bool launch_gemv_q4_ring(cudaStream_t s, int sm_count, uint32_t* status, const float* x, uint64_t m, uint64_t k, const uint32_t* q,
-                         const float* scale, const float* zero, const float* bias, uint64_t n, uint64_t group, float* y) {
+                         const float* scale, const float* zero, const float* bias, uint64_t n, uint64_t group, float* y,
+                         bool overlap_previous) {
     if (m < 1 || m > 4 || group != 128 || k == 0 || (k & 4095) || k > 16384 || n == 0 || n > 0x7fffffffull) return false;
     if (((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(scale) | reinterpret_cast<uintptr_t>(zero)) & 15) != 0) return false;
     const uint64_t groups = k / 128, row_bytes = k / 2;
@@ -332,7 +345,7 @@ bool launch_gemv_q4_ring(cudaStream_t s, int sm_count, uint32_t* status, const f
     if (nstages > kMaxStages) nstages = kMaxStages;
     if (nstages > blocks) nstages = blocks;
     const uint64_t smem = fixed + nstages * per_stage;
-#define GQ_RING(MRV, GPWV) launch<MRV, GPWV>(s, grid, smem, q, x, scale, zero, bias, y, k, n, groups, nstages, stage_stride, status)
+#define GQ_RING(MRV, GPWV) launch<MRV, GPWV>(s, grid, smem, q, x, scale, zero, bias, y, k, n, groups, nstages, stage_stride, status, overlap_previous)
     if (m == 1) {
         if (gpw <= 2) GQ_RING(1, 2);
         else if (gpw <= 4) GQ_RING(1, 4);

@@ -75,6 +75,7 @@ struct gq_ctx {
     uint32_t* status_dev = nullptr;
     // lazily created device scratch owned by the context (tensor-core paths)
     void* scratch = nullptr;
+    gq_buf ring_prev_y = 0;        // output of the ring GEMV that was the last operation put on the stream, else 0
     void* argmax_state = nullptr;  // keys and counters of gq_argmax_rows, zero between calls
     uint64_t scratch_bytes = 0;
 };
@@ -106,6 +107,31 @@ struct Locked {  // serialises calls on a context and makes its device current
 Buffer& lookup(gq_ctx* ctx, gq_buf h, const char* what);
 void check_dims(const char* op, uint64_t a, uint64_t b, uint64_t c = 1);
 
+
+// ── launches that hide the launch latency behind the previous kernel ─────
+// A kernel whose FIRST statement is GQ_GRID_DEP_SYNC() may be launched with launch_after(): its CTAs are scheduled
+// as soon as the kernel before it in the stream lets them (programmatic stream serialization) and then wait, in
+// hardware, until that kernel has finished and its writes are visible. Stream-order semantics are unchanged (nothing
+// is read or written before the wait); what is saved is the launch gap. Inside a capture the edge is recorded as such.
+#ifdef __CUDACC__
+#define GQ_GRID_DEP_SYNC()                                                  \
+    do {                                                                    \
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");     \
+        asm volatile("griddepcontrol.wait;" ::: "memory");                  \
+    } while (0)
+
+template <typename... KArgs, typename... Args>
+void launch_after(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid, cfg.blockDim = block, cfg.dynamicSmemBytes = smem, cfg.stream = s;
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr, cfg.numAttrs = 1;
+    GQ_CUDA(cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...));
+}
+#endif
+
 // A checked view of `count` elements of `elem` bytes at element offset `off`.
 void* view(gq_ctx* ctx, gq_buf buf, uint64_t off, uint64_t count, uint64_t elem, const char* what);
 // Counts a launch, notes buffers for an open capture, honours launch_blocking.
@@ -133,7 +159,8 @@ bool launch_gemv_q4_dp4a(cudaStream_t s, int sm_count, const float* x, uint64_t 
 bool launch_gemv_q8_imma(cudaStream_t s, int sm_count, uint32_t* status, const float* x, uint64_t m, uint64_t k, const uint32_t* q,
                          const float* scale, const float* bias, uint64_t n, float* y);
 bool launch_gemv_q4_ring(cudaStream_t s, int sm_count, uint32_t* status, const float* x, uint64_t m, uint64_t k, const uint32_t* q,
-                          const float* scale, const float* zero, const float* bias, uint64_t n, uint64_t group, float* y);
+                          const float* scale, const float* zero, const float* bias, uint64_t n, uint64_t group, float* y,
+                         bool overlap_previous);
 bool launch_gemv_q4_imma(cudaStream_t s, int sm_count, uint32_t* status, const float* x, uint64_t m, uint64_t k, const uint32_t* q,
                          const float* scale, const float* zero, const float* bias, uint64_t n, uint64_t group, float* y);
 
