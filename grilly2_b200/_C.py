@@ -240,6 +240,32 @@ class Int8Weight:
                                   bias.offset if bias is not None else 0, n, y.storage.handle, kernel))
         return y
 
+    def linear_norm(self, x: Tensor, residual: Tensor | None, norm_weight: Tensor, eps: float, bias: Tensor | None = None,
+                    want_sum: bool = False):
+        """One row: h = x + residual; returns (W . rms_norm(h) * norm_weight + bias, h if want_sum else None) in one launch."""
+        n, k = self._shape
+        if x.numel() != k or x.offset or (residual is not None and (residual.numel() != k or residual.offset)):
+            raise RuntimeError(f"linear_norm takes one row of {k} values at offset 0")
+        y = Tensor.empty((1, n), F32)
+        h = Tensor.empty((1, k), F32) if want_sum else None
+        check(_l().gq_int8_linear_norm(context(), x.storage.handle, residual.storage.handle if residual is not None else 0,
+                                       norm_weight.storage.handle, eps, h.storage.handle if h is not None else 0, k,
+                                       self._qt.storage.handle, self._scale.storage.handle,
+                                       bias.storage.handle if bias is not None else 0, bias.offset if bias is not None else 0, n,
+                                       y.storage.handle))
+        return y, h
+
+    def linear_swiglu(self, gate_up: Tensor, bias: Tensor | None = None) -> Tensor:
+        """One row of gate | up (2 k values): W . (silu(gate) * up) + bias in one launch."""
+        n, k = self._shape
+        if gate_up.numel() != 2 * k or gate_up.offset:
+            raise RuntimeError(f"linear_swiglu takes one row of {2 * k} values at offset 0")
+        y = Tensor.empty((1, n), F32)
+        check(_l().gq_int8_linear_swiglu(context(), gate_up.storage.handle, k, self._qt.storage.handle, self._scale.storage.handle,
+                                         bias.storage.handle if bias is not None else 0, bias.offset if bias is not None else 0, n,
+                                         y.storage.handle))
+        return y
+
 
 class Int4Weight:
     """A linear layer's weight, int4 with a float32 scale and zero point per

@@ -1,6 +1,7 @@
 // C ABI of the decode-step operators (include/gq.h, "decode step"): argument
 // checks against buffer sizes, then the launchers of decode_ops.cu.
 #include "gq_internal.h"
+#include "math_common.cuh"
 
 using namespace gq;
 
@@ -127,6 +128,45 @@ int32_t gq_argmax_rows(gq_ctx* ctx, gq_buf v, uint64_t rows, uint64_t n, gq_buf 
         if (rows == 0) return;
         launch_argmax_rows(ctx->stream, vp, rows, n, op, ctx->argmax_state);
         after_launch(ctx, "argmax_rows", {v, out});
+    });
+}
+
+int32_t gq_int8_linear_norm(gq_ctx* ctx, gq_buf x, gq_buf residual, gq_buf norm_weight, float eps, gq_buf h_out, uint64_t k, gq_buf q,
+                            gq_buf scale, gq_buf bias, uint64_t b_off, uint64_t n, gq_buf y) {
+    return guarded([&] {
+        Locked l(ctx);
+        check_dims("gq_int8_linear_norm", 1, k, n);
+        if (k == 0 || n == 0) fail("gq_int8_linear_norm: an empty layer");
+        Prologue pro;
+        auto xp = (const float*)view(ctx, x, 0, k, 4, "gq_int8_linear_norm input");
+        pro.res = residual ? (const float*)view(ctx, residual, 0, k, 4, "gq_int8_linear_norm residual") : nullptr;
+        pro.w = (const float*)view(ctx, norm_weight, 0, k, 4, "gq_int8_linear_norm norm weight");
+        pro.h_out = h_out ? (float*)view(ctx, h_out, 0, k, 4, "gq_int8_linear_norm sum output") : nullptr;
+        pro.eps = eps;
+        auto qp = (const uint32_t*)view(ctx, q, 0, n * 4 * ((k + 15) / 16), 4, "gq_int8_linear_norm q");
+        auto sp = (const float*)view(ctx, scale, 0, n, 4, "gq_int8_linear_norm scale");
+        auto bp = bias ? (const float*)view(ctx, bias, b_off, n, 4, "gq_int8_linear_norm bias") : nullptr;
+        auto yp = (float*)view(ctx, y, 0, n, 4, "gq_int8_linear_norm output");
+        if (!launch_gemv_q8_imma_fused(ctx->stream, ctx->prop.multiProcessorCount, ctx->status_dev, xp, k, qp, sp, bp, n, yp, 1, pro))
+            fail("gq_int8_linear_norm: in_features = %llu must be a multiple of 4 that fits shared memory, and the buffers 16-byte aligned", (unsigned long long)k);
+        after_launch(ctx, "gemv_q8_imma_norm", {x, residual, norm_weight, h_out, q, scale, bias, y});
+    });
+}
+
+int32_t gq_int8_linear_swiglu(gq_ctx* ctx, gq_buf gate_up, uint64_t k, gq_buf q, gq_buf scale, gq_buf bias, uint64_t b_off, uint64_t n,
+                              gq_buf y) {
+    return guarded([&] {
+        Locked l(ctx);
+        check_dims("gq_int8_linear_swiglu", 1, 2 * k, n);
+        if (k == 0 || n == 0) fail("gq_int8_linear_swiglu: an empty layer");
+        auto xp = (const float*)view(ctx, gate_up, 0, 2 * k, 4, "gq_int8_linear_swiglu input");
+        auto qp = (const uint32_t*)view(ctx, q, 0, n * 4 * ((k + 15) / 16), 4, "gq_int8_linear_swiglu q");
+        auto sp = (const float*)view(ctx, scale, 0, n, 4, "gq_int8_linear_swiglu scale");
+        auto bp = bias ? (const float*)view(ctx, bias, b_off, n, 4, "gq_int8_linear_swiglu bias") : nullptr;
+        auto yp = (float*)view(ctx, y, 0, n, 4, "gq_int8_linear_swiglu output");
+        if (!launch_gemv_q8_imma_fused(ctx->stream, ctx->prop.multiProcessorCount, ctx->status_dev, xp, k, qp, sp, bp, n, yp, 2, Prologue()))
+            fail("gq_int8_linear_swiglu: in_features = %llu must be a multiple of 4 that fits shared memory, and the input 16-byte aligned", (unsigned long long)k);
+        after_launch(ctx, "gemv_q8_imma_swiglu", {gate_up, q, scale, bias, y});
     });
 }
 

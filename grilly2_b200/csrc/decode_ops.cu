@@ -17,6 +17,7 @@
 // All kernels here are small and latency-bound; the step's time is the
 // quantized linears' (97 of them, ~494 of ~522 MB per token).
 #include "gq_internal.h"
+#include "math_common.cuh"
 
 namespace gq {
 
@@ -126,25 +127,6 @@ __global__ void kv_advance_kernel(uint32_t* lens, uint32_t layers, uint32_t max_
     if (l < layers) lens[l] = min(lens[l] + 1, max_len);
 }
 
-// exp as the reference computes it (Cephes expf, g2-common.glsl:21-31), with
-// every operation rounded on its own so that the CPU oracle can match it.
-__device__ __forceinline__ float exp_cephes(float v) {
-    if (v > 88.72283935546875f) return __uint_as_float(0x7f800000u);
-    if (v < -103.97207641601562f) return 0.0f;
-    const float k = floorf(__fadd_rn(__fmul_rn(v, 1.44269504088896341f), 0.5f));
-    float r = __fsub_rn(v, __fmul_rn(k, 0.693359375f));
-    r = __fadd_rn(r, __fmul_rn(k, 2.12194440e-4f));
-    const float z = __fmul_rn(r, r);
-    float p = 1.9875691500e-4f;
-    p = __fadd_rn(__fmul_rn(p, r), 1.3981999507e-3f);
-    p = __fadd_rn(__fmul_rn(p, r), 8.3334519073e-3f);
-    p = __fadd_rn(__fmul_rn(p, r), 4.1665795894e-2f);
-    p = __fadd_rn(__fmul_rn(p, r), 1.6666665459e-1f);
-    p = __fadd_rn(__fmul_rn(p, r), 5.0000001201e-1f);
-    const float yv = __fadd_rn(__fadd_rn(__fmul_rn(p, z), r), 1.0f);
-    return ldexpf(yv, (int)k);
-}
-
 // out[r][j] = (g * sigmoid(g)) * u with g = gate_up[r][j], u = gate_up[r][width + j] (g2-swiglu.glsl:21-29;
 // sigmoid as g2-common.glsl:163-166).
 __global__ void __launch_bounds__(256) swiglu_kernel(const float* __restrict__ gate_up, uint32_t rows, uint32_t width,
@@ -154,9 +136,7 @@ __global__ void __launch_bounds__(256) swiglu_kernel(const float* __restrict__ g
     for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < total; i += (size_t)gridDim.x * 256) {
         const size_t r = i / width, j = i % width;
         const float g = gate_up[r * 2 * width + j], u = gate_up[r * 2 * width + width + j];
-        const float e = exp_cephes(-fabsf(g));
-        const float sg = g >= 0.0f ? __fdiv_rn(1.0f, __fadd_rn(1.0f, e)) : __fdiv_rn(e, __fadd_rn(1.0f, e));
-        out[i] = __fmul_rn(__fmul_rn(g, sg), u);
+        out[i] = silu_mul(g, u);
     }
 }
 
@@ -231,24 +211,32 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const float* 
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t sub = tid % L, grp = tid / L;
     const uint32_t g = h / (heads / kv_heads);
-    const uint32_t len = min(lens[layer] + 1, max_len);
-    const uint32_t j0 = split * chunk, j1 = min(len, j0 + chunk);
+    const uint32_t j0 = split * chunk, jcap = min(j0 + chunk, max_len);  // where this split's keys lie, whatever the cursor says
     const float4* kb = reinterpret_cast<const float4*>(kc + (size_t)g * max_len * dim);
     const float4* vb = reinterpret_cast<const float4*>(vc + (size_t)g * max_len * dim);
     float* part = scratch + ((size_t)h * splits + split) * (dim + 2);
     uint32_t* counters = reinterpret_cast<uint32_t*>(scratch + (size_t)heads * splits * (dim + 2));
 
+    // The first passes' keys AND values are requested at once, before the cursor is known (rows past it are valid
+    // memory and are masked below): q, the cursor, K and V then cost one memory latency instead of four in a row.
+    constexpr int kPre = 4;
     const float4 q4 = reinterpret_cast<const float4*>(q + (size_t)h * dim)[sub];
+    float4 kpre[kPre], vpre[kPre];
+#pragma unroll
+    for (int p = 0; p < kPre; ++p) {
+        const uint32_t j = j0 + p * KP + grp;
+        const bool in = j < jcap;
+        kpre[p] = in ? kb[(size_t)j * L + sub] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        vpre[p] = in ? vb[(size_t)j * L + sub] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    }
+    const uint32_t len = min(lens[layer] + 1, max_len);
+    const uint32_t j1 = min(len, j0 + chunk);
 
     // Every lane of a warp runs the same number of passes (the shuffles below name the whole warp): a lane
     // whose key lies past the end computes on zeros and keeps nothing.
     float m = -INFINITY;
     const uint32_t passes = j1 > j0 ? (j1 - j0 + KP - 1) / KP : 0;
-#pragma unroll 4
-    for (uint32_t pass = 0; pass < passes; ++pass) {
-        const uint32_t j = j0 + pass * KP + grp;
-        const bool live = j < j1;
-        const float4 k4 = live ? kb[(size_t)j * L + sub] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    auto score = [&](uint32_t j, bool live, const float4& k4) {
         float sdot = __fmaf_rn(q4.w, k4.w, __fmaf_rn(q4.z, k4.z, __fmaf_rn(q4.y, k4.y, __fmul_rn(q4.x, k4.x))));
 #pragma unroll
         for (uint32_t o = L / 2; o > 0; o >>= 1) sdot += __shfl_xor_sync(0xffffffffu, sdot, o);
@@ -257,6 +245,20 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const float* 
             if (sub == 0) s_sc[j - j0] = sdot;
             m = fmaxf(m, sdot);
         }
+    };
+#pragma unroll
+    for (int p = 0; p < kPre; ++p) {
+        if ((uint32_t)p < passes) {  // uniform over the CTA
+            const uint32_t j = j0 + p * KP + grp;
+            const bool live = j < j1;
+            score(j, live, live ? kpre[p] : make_float4(0.0f, 0.0f, 0.0f, 0.0f));
+        }
+    }
+#pragma unroll 4
+    for (uint32_t pass = kPre; pass < passes; ++pass) {
+        const uint32_t j = j0 + pass * KP + grp;
+        const bool live = j < j1;
+        score(j, live, live ? kb[(size_t)j * L + sub] : make_float4(0.0f, 0.0f, 0.0f, 0.0f));
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
@@ -278,13 +280,18 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const float* 
 
     // weighted values: group `grp` strides over the keys, lane `sub` owns one float4 of the output
     float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-#pragma unroll 4
-    for (uint32_t j = j0 + grp; j < j1; j += KP) {
-        const float4 v4 = vb[(size_t)j * L + sub];
+    auto weigh = [&](uint32_t j, const float4& v4) {
         const float p = s_sc[j - j0];
         acc.x = __fmaf_rn(p, v4.x, acc.x), acc.y = __fmaf_rn(p, v4.y, acc.y);
         acc.z = __fmaf_rn(p, v4.z, acc.z), acc.w = __fmaf_rn(p, v4.w, acc.w);
+    };
+#pragma unroll
+    for (int p = 0; p < kPre; ++p) {
+        const uint32_t j = j0 + p * KP + grp;
+        if (j < j1) weigh(j, vpre[p]);
     }
+#pragma unroll 4
+    for (uint32_t j = j0 + kPre * KP + grp; j < j1; j += KP) weigh(j, vb[(size_t)j * L + sub]);
     s_acc[tid] = acc;
     __syncthreads();
     if (tid < L) {

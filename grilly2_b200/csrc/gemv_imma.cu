@@ -38,6 +38,7 @@
 // y (+ bias), each once. Bound: HBM bandwidth.
 #include "async_common.cuh"
 #include "gq_internal.h"
+#include "math_common.cuh"
 
 namespace gq {
 
@@ -108,9 +109,10 @@ __device__ __forceinline__ uint32_t pack4(int a, int b, int c, int d) {
 // parity p -> 2j + p: the even and the odd nibbles of word j of vector t) and
 // 4 for int8 (word j). One packed word of weights (8 or 4 values of x) per
 // thread; the 16 words of a block sit in 16 adjacent lanes.
-template <bool IS4, bool XVEC>
+template <bool IS4, bool XVEC, int PRO>
 __device__ __forceinline__ void prepare_x(const float* __restrict__ xr, uint32_t xrow, uint32_t k, uint32_t nblocks,
-                                          uint32_t* xb, float* xinv, float* xsum) {
+                                          uint32_t* xb, float* xinv, float* xsum, const Prologue& pro, float rinv) {
+    static_assert(PRO == 0 || (!IS4 && XVEC), "prologues are built for int8 weights and an aligned row of x");
     constexpr int E = IS4 ? 8 : 4;  // values of x per packed word
     constexpr int R = IS4 ? 8 : 4;
     for (uint32_t base = 0; base < nblocks * 16; base += kWarps * 32) {  // the consumer threads, 0 … 511, run this
@@ -118,7 +120,24 @@ __device__ __forceinline__ void prepare_x(const float* __restrict__ xr, uint32_t
         const bool live = wd < nblocks * 16;
         const uint32_t k0 = wd * E, blk = wd >> 4, t = (wd >> 2) & 3, j = wd & 3;
         float xv[E];
-        if (XVEC) {
+        if (PRO == 1) {  // x' = (x + residual) * rinv * w; CTA 0 also stores x + residual
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f), w4 = v;
+            if (live && k0 < k) {
+                v = __ldg(reinterpret_cast<const float4*>(xr + k0));
+                if (pro.res) {
+                    const float4 r4 = __ldg(reinterpret_cast<const float4*>(pro.res + k0));
+                    v.x = __fadd_rn(v.x, r4.x), v.y = __fadd_rn(v.y, r4.y), v.z = __fadd_rn(v.z, r4.z), v.w = __fadd_rn(v.w, r4.w);
+                }
+                if (pro.h_out && blockIdx.x == 0) *reinterpret_cast<float4*>(pro.h_out + k0) = v;
+                w4 = __ldg(reinterpret_cast<const float4*>(pro.w + k0));
+            }
+            xv[0] = __fmul_rn(__fmul_rn(v.x, rinv), w4.x), xv[1] = __fmul_rn(__fmul_rn(v.y, rinv), w4.y);
+            xv[2] = __fmul_rn(__fmul_rn(v.z, rinv), w4.z), xv[3] = __fmul_rn(__fmul_rn(v.w, rinv), w4.w);
+        } else if (PRO == 2) {  // x'[j] = silu(x[j]) * x[k + j]
+            float4 g4 = make_float4(0.f, 0.f, 0.f, 0.f), u4 = g4;
+            if (live && k0 < k) g4 = __ldg(reinterpret_cast<const float4*>(xr + k0)), u4 = __ldg(reinterpret_cast<const float4*>(xr + k + k0));
+            xv[0] = silu_mul(g4.x, u4.x), xv[1] = silu_mul(g4.y, u4.y), xv[2] = silu_mul(g4.z, u4.z), xv[3] = silu_mul(g4.w, u4.w);
+        } else if (XVEC) {
 #pragma unroll
             for (int h = 0; h < E / 4; ++h) {
                 float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -175,12 +194,35 @@ __device__ __forceinline__ void prepare_x(const float* __restrict__ xr, uint32_t
 // consume: all of them work on the same stage, each on its own 64-byte
 // blocks, so up to five stages — 160 KB per SM — are in flight while they
 // compute, and HBM never waits for the arithmetic.
-template <bool IS4, int MR, bool XVEC>
+// 1 / sqrt(mean((x + residual)^2) + eps) over one row of k values, by the 512 consumer threads (add_rms_norm_kernel's
+// arithmetic: squares in float32, their sum in float64). `red` is 16 doubles of shared memory.
+__device__ __forceinline__ float row_rms_inverse(const float* __restrict__ xr, const Prologue& pro, uint32_t k, double* red) {
+    double ss = 0.0;
+    for (uint32_t i = threadIdx.x * 4; i < k; i += kWarps * 32 * 4) {
+        float4 v = __ldg(reinterpret_cast<const float4*>(xr + i));
+        if (pro.res) {
+            const float4 r4 = __ldg(reinterpret_cast<const float4*>(pro.res + i));
+            v.x = __fadd_rn(v.x, r4.x), v.y = __fadd_rn(v.y, r4.y), v.z = __fadd_rn(v.z, r4.z), v.w = __fadd_rn(v.w, r4.w);
+        }
+        ss += (double)__fmul_rn(v.x, v.x), ss += (double)__fmul_rn(v.y, v.y), ss += (double)__fmul_rn(v.z, v.z), ss += (double)__fmul_rn(v.w, v.w);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    named_barrier_sync(2, kWarps * 32);
+    double t = 0.0;
+#pragma unroll
+    for (int i = 0; i < kWarps; ++i) t += red[i];
+    const float mean = __fdiv_rn((float)t, (float)k);
+    return __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, pro.eps)));
+}
+
+template <bool IS4, int MR, bool XVEC, int PRO>
 __global__ void __launch_bounds__(kThreads, 1)
     gemv_imma_kernel(const float* __restrict__ x, const uint8_t* __restrict__ q, const float* __restrict__ scale,
                      const float* __restrict__ zero, const float* __restrict__ bias, float* __restrict__ y, uint32_t k,
                      uint32_t n, uint32_t vecs, uint32_t groups, uint32_t gshift, uint32_t gblocks, uint32_t nblocks,
-                     uint32_t nstages, uint32_t* status) {
+                     uint32_t nstages, uint32_t* status, Prologue pro) {
     GQ_GRID_DEP_SYNC();
     constexpr int R = IS4 ? 8 : 4;
     extern __shared__ __align__(128) uint8_t smem_raw[];
@@ -232,9 +274,12 @@ __global__ void __launch_bounds__(kThreads, 1)
 
     // ── consumers ──
     const uint32_t g = lane >> 2, t = lane & 3;
+    __shared__ double s_red[kWarps];
+    float rinv = 0.0f;
+    if (PRO == 1) rinv = row_rms_inverse(x, pro, k, s_red);
 #pragma unroll
     for (int r = 0; r < MR; ++r)
-        prepare_x<IS4, XVEC>(x + (size_t)r * k, r, k, nblocks, xb, xinv + r * nblocks, xsum + r * nblocks);
+        prepare_x<IS4, XVEC, PRO>(x + (size_t)r * k, r, k, nblocks, xb, xinv + r * nblocks, xsum + r * nblocks, pro, rinv);
     named_barrier_sync(1, kWarps * 32);
 
     // this thread finishes feature row g (even t) or g + 8 (odd t) of each tile, for row t / 2 of x
@@ -367,7 +412,7 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 
 template <bool IS4, int MR>
 bool run(cudaStream_t s, int sm_count, uint32_t* status, const float* x, uint64_t k, const uint32_t* q, const float* scale,
-         const float* zero, const float* bias, uint64_t n, uint64_t group, float* y) {
+         const float* zero, const float* bias, uint64_t n, uint64_t group, float* y, int kind = 0, Prologue pro = Prologue()) {
     const uint32_t vecs = (uint32_t)(IS4 ? (k + 31) / 32 : (k + 15) / 16);
     const uint32_t nblocks = (vecs + 3) / 4;
     const uint32_t groups = IS4 ? (uint32_t)((k + group - 1) / group) : 0;
@@ -385,10 +430,17 @@ bool run(cudaStream_t s, int sm_count, uint32_t* status, const float* x, uint64_
     const size_t smem = fixed + (size_t)nstages * kStageBytes;
     const uint32_t grid = (uint32_t)(n < (uint64_t)sm_count ? n : (uint64_t)sm_count);
     const bool xvec = aligned16(x) && k % 4 == 0;
-    auto kernel = xvec ? gemv_imma_kernel<IS4, MR, true> : gemv_imma_kernel<IS4, MR, false>;
+    using Kernel = void (*)(const float*, const uint8_t*, const float*, const float*, const float*, float*, uint32_t, uint32_t, uint32_t,
+                            uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t*, Prologue);
+    Kernel kernel = xvec ? gemv_imma_kernel<IS4, MR, true, 0> : gemv_imma_kernel<IS4, MR, false, 0>;
+    if (kind != 0) {
+        if (IS4 || MR != 1 || !xvec) return false;  // prologues: int8 weights, one aligned row of x
+        if (kind == 1 && (!aligned16(pro.w) || (pro.res && !aligned16(pro.res)) || (pro.h_out && !aligned16(pro.h_out)))) return false;
+        if constexpr (!IS4 && MR == 1) kernel = kind == 1 ? gemv_imma_kernel<false, 1, true, 1> : gemv_imma_kernel<false, 1, true, 2>;
+    }
     GQ_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     launch_after(kernel, dim3(grid), dim3(kThreads), smem, s, x, reinterpret_cast<const uint8_t*>(q), scale, zero, bias, y, (uint32_t)k,
-                 (uint32_t)n, vecs, groups, gshift, gblocks, nblocks, nstages, status);
+                 (uint32_t)n, vecs, groups, gshift, gblocks, nblocks, nstages, status, pro);
     return true;
 }
 
@@ -402,6 +454,12 @@ bool launch_gemv_q4_imma(cudaStream_t s, int sm_count, uint32_t* status, const f
     if (group % 128 != 0 || m > 2) return false;
     return m == 1 ? run<true, 1>(s, sm_count, status, x, k, q, scale, zero, bias, n, group, y)
                   : run<true, 2>(s, sm_count, status, x, k, q, scale, zero, bias, n, group, y);
+}
+
+// y = W . f(x) for one row of x, f the prologue `kind` (math_common.cuh). False when the shape or alignment is not this kernel's.
+bool launch_gemv_q8_imma_fused(cudaStream_t s, int sm_count, uint32_t* status, const float* x, uint64_t k, const uint32_t* q,
+                               const float* scale, const float* bias, uint64_t n, float* y, int kind, const Prologue& pro) {
+    return run<false, 1>(s, sm_count, status, x, k, q, scale, nullptr, bias, n, 0, y, kind, pro);
 }
 
 bool launch_gemv_q8_imma(cudaStream_t s, int sm_count, uint32_t* status, const float* x, uint64_t m, uint64_t k, const uint32_t* q,

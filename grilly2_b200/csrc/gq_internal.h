@@ -158,6 +158,9 @@ bool launch_gemv_q4_dp4a(cudaStream_t s, int sm_count, const float* x, uint64_t 
 
 bool launch_gemv_q8_imma(cudaStream_t s, int sm_count, uint32_t* status, const float* x, uint64_t m, uint64_t k, const uint32_t* q,
                          const float* scale, const float* bias, uint64_t n, float* y);
+struct Prologue;
+bool launch_gemv_q8_imma_fused(cudaStream_t s, int sm_count, uint32_t* status, const float* x, uint64_t k, const uint32_t* q,
+                               const float* scale, const float* bias, uint64_t n, float* y, int kind, const Prologue& pro);
 bool launch_gemv_q4_ring(cudaStream_t s, int sm_count, uint32_t* status, const float* x, uint64_t m, uint64_t k, const uint32_t* q,
                           const float* scale, const float* zero, const float* bias, uint64_t n, uint64_t group, float* y,
                          bool overlap_previous);

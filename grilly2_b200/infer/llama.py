@@ -113,8 +113,10 @@ class KvCache:
 class LlamaDecoder:
     """The quantized model and its cache; ``step(token)`` decodes one token."""
 
-    def __init__(self, cfg: LlamaConfig, weights: dict) -> None:
+    def __init__(self, cfg: LlamaConfig, weights: dict, fused: bool = True) -> None:
         self.cfg = cfg
+        # fused: norms and SwiGLU run inside the following projection (one launch each); needs row lengths that are multiples of 4
+        self.fused = fused and cfg.hidden_size % 4 == 0 and cfg.intermediate_size % 4 == 0
         T = _C.Tensor.from_numpy
 
         def q8(a):
@@ -154,11 +156,15 @@ class LlamaDecoder:
         hidden = _C.Tensor.empty((1, c.hidden_size), "float32")
         check(lib.gq_embedding(ctx, self.embed.storage.handle, token.storage.handle, 1, c.hidden_size, c.vocab_size, hidden.storage.handle))
         delta = None  # what the last block produced; added to `hidden` by the next norm
+        fused = self.fused
         for li, lw in enumerate(self.layers):
-            x, summed = self._norm(hidden, delta, lw["input_norm"], delta is not None)
+            if fused:  # the norm runs inside the projection's conversion of its input row
+                qkv, summed = lw["qkv"].linear_norm(hidden, delta, lw["input_norm"], c.rms_norm_eps, lw["qkv_bias"], delta is not None)
+            else:
+                x, summed = self._norm(hidden, delta, lw["input_norm"], delta is not None)
+                qkv = lw["qkv"].linear(x, lw["qkv_bias"])
             if summed is not None:
                 hidden = summed
-            qkv = lw["qkv"].linear(x, lw["qkv_bias"])
             q = _C.Tensor.empty((1, c.q_size), "float32")
             off = li * self.cache.layer_elems
             check(lib.gq_rope_kv_append(ctx, qkv.storage.handle, self.cos.storage.handle, self.sin.storage.handle,
@@ -169,13 +175,20 @@ class LlamaDecoder:
                                      self.cache.lens.storage.handle, li, L, Hq, Hkv, D, c.max_cache_len, float(D) ** -0.5,
                                      self.cache.scratch.storage.handle, attn.storage.handle))
             o = lw["o"].linear(attn)
-            x, hidden = self._norm(hidden, o, lw["post_norm"], True)
-            gu = lw["gate_up"].linear(x)
-            act = _C.Tensor.empty((1, c.intermediate_size), "float32")
-            check(lib.gq_swiglu(ctx, gu.storage.handle, 1, c.intermediate_size, act.storage.handle))
-            delta = lw["down"].linear(act)
-        x, _ = self._norm(hidden, delta, self.norm, False)
-        logits = self.lm_head.linear(x)
+            if fused:
+                gu, hidden = lw["gate_up"].linear_norm(hidden, o, lw["post_norm"], c.rms_norm_eps, None, True)
+                delta = lw["down"].linear_swiglu(gu)
+            else:
+                x, hidden = self._norm(hidden, o, lw["post_norm"], True)
+                gu = lw["gate_up"].linear(x)
+                act = _C.Tensor.empty((1, c.intermediate_size), "float32")
+                check(lib.gq_swiglu(ctx, gu.storage.handle, 1, c.intermediate_size, act.storage.handle))
+                delta = lw["down"].linear(act)
+        if fused:
+            logits, _ = self.lm_head.linear_norm(hidden, delta, self.norm, c.rms_norm_eps)
+        else:
+            x, _ = self._norm(hidden, delta, self.norm, False)
+            logits = self.lm_head.linear(x)
         nxt = _C.Tensor.empty((1,), "int32")
         check(lib.gq_argmax_rows(ctx, logits.storage.handle, 1, c.vocab_size, nxt.storage.handle))
         check(lib.gq_kv_advance(ctx, self.cache.lens.storage.handle, L, c.max_cache_len))

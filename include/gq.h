@@ -230,6 +230,16 @@ int32_t gq_attn_scratch_bytes(gq_ctx* ctx, uint64_t heads, uint64_t dim, uint64_
 int32_t gq_attn_decode(gq_ctx* ctx, gq_buf q, gq_buf kcache, uint64_t k_off, gq_buf vcache, uint64_t v_off, gq_buf lens, uint64_t layer,
                        uint64_t layers, uint64_t heads, uint64_t kv_heads, uint64_t dim, uint64_t max_len, float scale, gq_buf scratch,
                        gq_buf out);
+/* Fused forms for one decode token (one row): the operator before a linear runs inside the linear's conversion of x,
+ * saving a launch and a round trip of the row. No counterpart in the reference, which launches them one by one.
+ * gq_int8_linear_norm:   h = x + residual (residual 0: h = x); h_out = h (if not 0); y = W . (h / sqrt(mean(h^2) + eps) * w) + bias
+ *                        — gq_add_rms_norm then gq_int8_linear.
+ * gq_int8_linear_swiglu: y = W . (silu(gate_up[0:k]) * gate_up[k:2k]) + bias — gq_swiglu then gq_int8_linear.
+ * k = in_features of the layer, a multiple of 4; x, residual, w, h_out and gate_up at offset 0. */
+int32_t gq_int8_linear_norm(gq_ctx* ctx, gq_buf x, gq_buf residual, gq_buf norm_weight, float eps, gq_buf h_out, uint64_t k, gq_buf q,
+                            gq_buf scale, gq_buf bias, uint64_t b_off, uint64_t n, gq_buf y);
+int32_t gq_int8_linear_swiglu(gq_ctx* ctx, gq_buf gate_up, uint64_t k, gq_buf q, gq_buf scale, gq_buf bias, uint64_t b_off, uint64_t n,
+                              gq_buf y);
 /* gq_attn_decode with the scratch in a fixed 2 MiB array of the library's own device memory: takes no scratch
  * buffer and allocates nothing, on the first call or later. No counterpart in the reference (its scratch is
  * a pooled buffer, kv_cache.rs:502-528). The first call on a device does the set-up (an address look-up):

@@ -66,3 +66,38 @@ def test_attention_refuses_other_head_sizes():
     rc = lib.gq_attn_decode(ctx, t.storage.handle, t.storage.handle, 0, t.storage.handle, 0, ti.storage.handle, 0, 1, 2, 1, 48, 8,
                             1.0, t.storage.handle, t.storage.handle)
     assert rc != 0 and b"head_dim" in lib.gq_last_error()
+
+
+@pytest.mark.parametrize("k,n", [(896, 1152), (4864, 896), (896, 151936), (64, 5)])
+def test_fused_norm_and_swiglu_linears_equal_the_separate_operators(k, n):
+    """gq_int8_linear_norm == gq_add_rms_norm then gq_int8_linear; gq_int8_linear_swiglu == gq_swiglu then gq_int8_linear."""
+    _C, _lib, lib, ctx = _env()
+    rng = np.random.default_rng(k + n)
+    w = _C.Int8Weight.quantize(_C.Tensor.from_numpy((rng.standard_normal((n, k)) * 0.05).astype(np.float32)))
+    x, res = (_C.Tensor.from_numpy(rng.standard_normal((1, k)).astype(np.float32)) for _ in range(2))
+    nw = _C.Tensor.from_numpy((1 + 0.1 * rng.standard_normal(k)).astype(np.float32))
+    bias = _C.Tensor.from_numpy(rng.standard_normal(n).astype(np.float32))
+    for residual in (res, None):
+        xn, h = _C.Tensor.empty((1, k), "float32"), _C.Tensor.empty((1, k), "float32")
+        _lib.check(lib.gq_add_rms_norm(ctx, x.storage.handle, residual.storage.handle if residual is not None else 0, nw.storage.handle, 1, k,
+                                       1e-6, xn.storage.handle, h.storage.handle))
+        want = w.linear(xn, bias, _lib.KERNEL_IMMA).numpy()
+        got, hs = w.linear_norm(x, residual, nw, 1e-6, bias, True)
+        np.testing.assert_array_equal(hs.numpy(), h.numpy())
+        assert np.abs(got.numpy() - want).max() <= 1e-6 * np.abs(want).max()
+        got2, none = w.linear_norm(x, residual, nw, 1e-6, bias, False)
+        assert none is None
+        np.testing.assert_array_equal(got2.numpy(), got.numpy())
+    gu = _C.Tensor.from_numpy((rng.standard_normal((1, 2 * k)) * 3).astype(np.float32))
+    act = _C.Tensor.empty((1, k), "float32")
+    _lib.check(lib.gq_swiglu(ctx, gu.storage.handle, 1, k, act.storage.handle))
+    want = w.linear(act, None, _lib.KERNEL_IMMA).numpy()
+    np.testing.assert_array_equal(w.linear_swiglu(gu).numpy(), want)
+
+
+def test_fused_linears_refuse_row_lengths_that_are_not_multiples_of_four():
+    _C, _lib, lib, ctx = _env()
+    w = _C.Int8Weight.quantize(_C.Tensor.from_numpy(np.ones((3, 6), dtype=np.float32)))
+    x = _C.Tensor.from_numpy(np.ones((1, 6), dtype=np.float32))
+    with pytest.raises(RuntimeError, match="multiple of 4"):
+        w.linear_norm(x, None, x, 1e-6)

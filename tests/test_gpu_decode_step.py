@@ -19,13 +19,13 @@ def small_config():
                        head_dim=32, intermediate_size=256, max_cache_len=48)
 
 
-def build(cfg, seed, prefill):
+def build(cfg, seed, prefill, fused=True):
     from grilly2_b200.infer import llama
     from oracle.llama_ref import DecoderRef
     w = llama.random_weights(cfg, seed=seed, sigma=0.05)
     for i, lw in enumerate(w["layers"]):  # non-trivial norm weights
         lw["input_norm"] = (1 + 0.1 * np.random.default_rng(100 + i).standard_normal(cfg.hidden_size)).astype(np.float32)
-    model = llama.LlamaDecoder(cfg, w)
+    model = llama.LlamaDecoder(cfg, w, fused=fused)
     cos, sin = llama.rotary_tables(cfg)
     ref = DecoderRef(cfg, w, cos, sin)
     if prefill:
@@ -37,11 +37,12 @@ def build(cfg, seed, prefill):
     return model, ref
 
 
-@pytest.mark.parametrize("prefill", [0, 20])
-def test_decode_steps_match_the_float64_model(prefill):
+@pytest.mark.parametrize("prefill,fused", [(0, True), (20, True), (20, False)])
+def test_decode_steps_match_the_float64_model(prefill, fused):
     from grilly2_b200 import _C
     cfg = small_config()
-    model, ref = build(cfg, 4, prefill)
+    model, ref = build(cfg, 4, prefill, fused)
+    assert model.fused == fused
     token = 7
     for step in range(4):
         logits, nxt = model.step(_C.Tensor.from_numpy(np.array([token], dtype=np.int32)))
