@@ -72,6 +72,7 @@ PROTOTYPES = {
     "gq_attn_scratch_bytes": [vp, u64, u64, u64, P(u64)],
     "gq_attn_decode": [vp, u64, u64, u64, u64, u64, u64, u64, u64, u64, u64, u64, u64, ctypes.c_float, u64, u64],
     "gq_attn_decode_static": [vp, u64, u64, u64, u64, u64, u64, u64, u64, u64, u64, u64, u64, ctypes.c_float, u64],
+    "gq_attn_decode_rope": [vp, u64, u64, u64, u64, u64, u64, u64, u64, u64, u64, u64, u64, u64, u64, ctypes.c_float, u64, u64],
     "gq_int8_linear_norm": [vp, u64, u64, u64, ctypes.c_float, u64, u64, u64, u64, u64, u64, u64, u64],
     "gq_int8_linear_swiglu": [vp, u64, u64, u64, u64, u64, u64, u64, u64],
     "gq_swiglu": [vp, u64, u64, u64, u64],

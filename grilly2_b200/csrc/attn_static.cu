@@ -62,13 +62,13 @@ extern "C" int32_t gq_attn_decode_static(gq_ctx* ctx, gq_buf q, gq_buf kcache, u
                  (unsigned long long)heads, splits, (unsigned long long)dim, (unsigned long long)(need * 4),
                  (unsigned long long)(kStaticScratchFloats * 4));
         auto qp = (const float*)view(ctx, q, 0, heads * dim, 4, "gq_attn_decode_static q");
-        auto kp = (const float*)view(ctx, kcache, k_off, kv_heads * max_len * dim, 4, "gq_attn_decode_static key cache");
-        auto vp = (const float*)view(ctx, vcache, v_off, kv_heads * max_len * dim, 4, "gq_attn_decode_static value cache");
+        auto kp = (float*)view(ctx, kcache, k_off, kv_heads * max_len * dim, 4, "gq_attn_decode_static key cache");
+        auto vp = (float*)view(ctx, vcache, v_off, kv_heads * max_len * dim, 4, "gq_attn_decode_static value cache");
         auto lp = (const uint32_t*)view(ctx, lens, 0, layers, 4, "gq_attn_decode_static cursor");
         auto op = (float*)view(ctx, out, 0, heads * dim, 4, "gq_attn_decode_static output");
         float* sp = static_scratch(ctx->device);
         launch_attn_decode(ctx->stream, qp, kp, vp, lp, (uint32_t)layer, (uint32_t)heads, (uint32_t)kv_heads, (uint32_t)dim,
                            (uint32_t)max_len, scale, splits, sp, op);
-        after_launch(ctx, "attn_decode_static", {q, kcache, vcache, lens, out});
+        after_launch(ctx, "attn_decode_static", {q, kcache, vcache, lens, out}, {out});
     });
 }

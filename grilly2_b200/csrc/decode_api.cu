@@ -16,7 +16,7 @@ int32_t gq_embedding(gq_ctx* ctx, gq_buf table, gq_buf ids, uint64_t rows, uint6
         auto op = (float*)view(ctx, out, 0, rows * width, 4, "gq_embedding output");
         if (rows == 0 || width == 0) return;
         launch_embedding(ctx->stream, tp, ip, rows, width, vocab, op);
-        after_launch(ctx, "embedding", {table, ids, out});
+        after_launch(ctx, "embedding", {table, ids, out}, {out});
     });
 }
 
@@ -33,7 +33,7 @@ int32_t gq_add_rms_norm(gq_ctx* ctx, gq_buf x, gq_buf residual, gq_buf weight, u
         auto hp = h ? (float*)view(ctx, h, 0, rows * n, 4, "gq_add_rms_norm sum output") : nullptr;
         if (rows == 0) return;
         launch_add_rms_norm(ctx->stream, xp, rp, wp, rows, n, eps, yp, hp);
-        after_launch(ctx, "add_rms_norm", {x, residual, weight, y, h});
+        after_launch(ctx, "add_rms_norm", {x, residual, weight, y, h}, {y, h});
     });
 }
 
@@ -61,7 +61,7 @@ int32_t gq_rope_kv_append(gq_ctx* ctx, gq_buf qkv, gq_buf cos, gq_buf sin, gq_bu
         auto vp = (float*)view(ctx, vcache, v_off, kv_heads * max_len * dim, 4, "gq_rope_kv_append value cache");
         launch_rope_kv_append(ctx->stream, qp, cp, sp, lp, (uint32_t)layer, (uint32_t)heads, (uint32_t)kv_heads, (uint32_t)dim,
                               (uint32_t)max_len, op, kp, vp);
-        after_launch(ctx, "rope_kv_append", {qkv, cos, sin, lens, q_out, kcache, vcache});
+        after_launch(ctx, "rope_kv_append", {qkv, cos, sin, lens, q_out, kcache, vcache}, {q_out, kcache, vcache});
     });
 }
 
@@ -72,7 +72,7 @@ int32_t gq_kv_advance(gq_ctx* ctx, gq_buf lens, uint64_t layers, uint64_t max_le
         auto lp = (uint32_t*)view(ctx, lens, 0, layers, 4, "gq_kv_advance cursor");
         if (layers == 0) return;
         launch_kv_advance(ctx->stream, lp, (uint32_t)layers, (uint32_t)max_len);
-        after_launch(ctx, "kv_advance", {lens});
+        after_launch(ctx, "kv_advance", {lens}, {lens});
     });
 }
 
@@ -95,14 +95,37 @@ int32_t gq_attn_decode(gq_ctx* ctx, gq_buf q, gq_buf kcache, uint64_t k_off, gq_
         if (layer >= layers) fail("gq_attn_decode: layer %llu of %llu", (unsigned long long)layer, (unsigned long long)layers);
         const uint32_t splits = attn_splits((uint32_t)heads, (uint32_t)max_len, ctx->prop.multiProcessorCount);
         auto qp = (const float*)view(ctx, q, 0, heads * dim, 4, "gq_attn_decode q");
-        auto kp = (const float*)view(ctx, kcache, k_off, kv_heads * max_len * dim, 4, "gq_attn_decode key cache");
-        auto vp = (const float*)view(ctx, vcache, v_off, kv_heads * max_len * dim, 4, "gq_attn_decode value cache");
+        auto kp = (float*)view(ctx, kcache, k_off, kv_heads * max_len * dim, 4, "gq_attn_decode key cache");
+        auto vp = (float*)view(ctx, vcache, v_off, kv_heads * max_len * dim, 4, "gq_attn_decode value cache");
         auto lp = (const uint32_t*)view(ctx, lens, 0, layers, 4, "gq_attn_decode cursor");
         auto sp = (float*)view(ctx, scratch, 0, attn_scratch_floats((uint32_t)heads, (uint32_t)dim, splits), 4, "gq_attn_decode scratch");
         auto op = (float*)view(ctx, out, 0, heads * dim, 4, "gq_attn_decode output");
         launch_attn_decode(ctx->stream, qp, kp, vp, lp, (uint32_t)layer, (uint32_t)heads, (uint32_t)kv_heads, (uint32_t)dim,
                            (uint32_t)max_len, scale, splits, sp, op);
-        after_launch(ctx, "attn_decode", {q, kcache, vcache, lens, scratch, out});
+        after_launch(ctx, "attn_decode", {q, kcache, vcache, lens, scratch, out}, {scratch, out});
+    });
+}
+
+int32_t gq_attn_decode_rope(gq_ctx* ctx, gq_buf qkv, gq_buf cos, gq_buf sin, gq_buf kcache, uint64_t k_off, gq_buf vcache, uint64_t v_off,
+                            gq_buf lens, uint64_t layer, uint64_t layers, uint64_t heads, uint64_t kv_heads, uint64_t dim, uint64_t max_len,
+                            float scale, gq_buf scratch, gq_buf out) {
+    return guarded([&] {
+        Locked l(ctx);
+        check_heads("gq_attn_decode_rope", heads, kv_heads, dim, max_len);
+        if (layer >= layers) fail("gq_attn_decode_rope: layer %llu of %llu", (unsigned long long)layer, (unsigned long long)layers);
+        const uint32_t splits = attn_splits((uint32_t)heads, (uint32_t)max_len, ctx->prop.multiProcessorCount);
+        auto qp = (const float*)view(ctx, qkv, 0, (heads + 2 * kv_heads) * dim, 4, "gq_attn_decode_rope qkv");
+        auto cp = (const float*)view(ctx, cos, 0, max_len * dim, 4, "gq_attn_decode_rope cos");
+        auto sp = (const float*)view(ctx, sin, 0, max_len * dim, 4, "gq_attn_decode_rope sin");
+        auto kp = (float*)view(ctx, kcache, k_off, kv_heads * max_len * dim, 4, "gq_attn_decode_rope key cache");
+        auto vp = (float*)view(ctx, vcache, v_off, kv_heads * max_len * dim, 4, "gq_attn_decode_rope value cache");
+        auto lp = (const uint32_t*)view(ctx, lens, 0, layers, 4, "gq_attn_decode_rope cursor");
+        auto scp = (float*)view(ctx, scratch, 0, attn_scratch_floats((uint32_t)heads, (uint32_t)dim, splits), 4, "gq_attn_decode_rope scratch");
+        auto op = (float*)view(ctx, out, 0, heads * dim, 4, "gq_attn_decode_rope output");
+        if (((uintptr_t)qp | (uintptr_t)cp | (uintptr_t)sp | (uintptr_t)kp | (uintptr_t)vp) & 15) fail("gq_attn_decode_rope: buffers and cache offsets must be 16-byte aligned");
+        launch_attn_decode(ctx->stream, qp, kp, vp, lp, (uint32_t)layer, (uint32_t)heads, (uint32_t)kv_heads, (uint32_t)dim,
+                           (uint32_t)max_len, scale, splits, scp, op, cp, sp);
+        after_launch(ctx, "attn_decode_rope", {qkv, cos, sin, kcache, vcache, lens, scratch, out}, {kcache, vcache, scratch, out});
     });
 }
 
@@ -114,7 +137,7 @@ int32_t gq_swiglu(gq_ctx* ctx, gq_buf gate_up, uint64_t rows, uint64_t width, gq
         auto op = (float*)view(ctx, out, 0, rows * width, 4, "gq_swiglu output");
         if (rows == 0 || width == 0) return;
         launch_swiglu(ctx->stream, gp, rows, width, op);
-        after_launch(ctx, "swiglu", {gate_up, out});
+        after_launch(ctx, "swiglu", {gate_up, out}, {out});
     });
 }
 
@@ -127,7 +150,7 @@ int32_t gq_argmax_rows(gq_ctx* ctx, gq_buf v, uint64_t rows, uint64_t n, gq_buf 
         auto op = (int32_t*)view(ctx, out, 0, rows, 4, "gq_argmax_rows output");
         if (rows == 0) return;
         launch_argmax_rows(ctx->stream, vp, rows, n, op, ctx->argmax_state);
-        after_launch(ctx, "argmax_rows", {v, out});
+        after_launch(ctx, "argmax_rows", {v, out}, {out});
     });
 }
 
@@ -147,9 +170,10 @@ int32_t gq_int8_linear_norm(gq_ctx* ctx, gq_buf x, gq_buf residual, gq_buf norm_
         auto sp = (const float*)view(ctx, scale, 0, n, 4, "gq_int8_linear_norm scale");
         auto bp = bias ? (const float*)view(ctx, bias, b_off, n, 4, "gq_int8_linear_norm bias") : nullptr;
         auto yp = (float*)view(ctx, y, 0, n, 4, "gq_int8_linear_norm output");
-        if (!launch_gemv_q8_imma_fused(ctx->stream, ctx->prop.multiProcessorCount, ctx->status_dev, xp, k, qp, sp, bp, n, yp, 1, pro))
+        if (!launch_gemv_q8_imma_fused(ctx->stream, ctx->prop.multiProcessorCount, ctx->status_dev, xp, k, qp, sp, bp, n, yp, 1, pro,
+                                       weights_settled(ctx, {q, scale})))
             fail("gq_int8_linear_norm: in_features = %llu must be a multiple of 4 that fits shared memory, and the buffers 16-byte aligned", (unsigned long long)k);
-        after_launch(ctx, "gemv_q8_imma_norm", {x, residual, norm_weight, h_out, q, scale, bias, y});
+        after_launch(ctx, "gemv_q8_imma_norm", {x, residual, norm_weight, h_out, q, scale, bias, y}, {y, h_out});
     });
 }
 
@@ -164,9 +188,10 @@ int32_t gq_int8_linear_swiglu(gq_ctx* ctx, gq_buf gate_up, uint64_t k, gq_buf q,
         auto sp = (const float*)view(ctx, scale, 0, n, 4, "gq_int8_linear_swiglu scale");
         auto bp = bias ? (const float*)view(ctx, bias, b_off, n, 4, "gq_int8_linear_swiglu bias") : nullptr;
         auto yp = (float*)view(ctx, y, 0, n, 4, "gq_int8_linear_swiglu output");
-        if (!launch_gemv_q8_imma_fused(ctx->stream, ctx->prop.multiProcessorCount, ctx->status_dev, xp, k, qp, sp, bp, n, yp, 2, Prologue()))
+        if (!launch_gemv_q8_imma_fused(ctx->stream, ctx->prop.multiProcessorCount, ctx->status_dev, xp, k, qp, sp, bp, n, yp, 2, Prologue(),
+                                       weights_settled(ctx, {q, scale})))
             fail("gq_int8_linear_swiglu: in_features = %llu must be a multiple of 4 that fits shared memory, and the input 16-byte aligned", (unsigned long long)k);
-        after_launch(ctx, "gemv_q8_imma_swiglu", {gate_up, q, scale, bias, y});
+        after_launch(ctx, "gemv_q8_imma_swiglu", {gate_up, q, scale, bias, y}, {y});
     });
 }
 

@@ -196,11 +196,17 @@ constexpr uint32_t kAttnMaxSplits = 64;
 
 // L = dim / 4 lanes share a key (one float4 of the row each), so a CTA takes 128 / L keys per pass with every
 // load of the pass independent of the others.
-template <uint32_t L>
-__global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const float* __restrict__ q, const float* __restrict__ kc,
-                                                                  const float* __restrict__ vc, const uint32_t* __restrict__ lens,
-                                                                  uint32_t layer, uint32_t heads, uint32_t kv_heads, uint32_t max_len,
-                                                                  float scale, uint32_t chunk, float* scratch, float* __restrict__ out) {
+//
+// ROPE: `q` is the fused projection's raw row q | k | v instead. The CTA rotates its head of q itself at the cursor's
+// position, the new token's key (rotated) and value are taken from that row wherever the cursor's position is needed —
+// the cache row is stale there — and the first head of each KV group, in the split that holds the position, appends
+// them to the cache: rope_kv_append_kernel's arithmetic and attn_decode_kernel's in one launch.
+template <uint32_t L, bool ROPE>
+__global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const float* __restrict__ q, float* kc, float* vc,
+                                                                  const uint32_t* __restrict__ lens, uint32_t layer, uint32_t heads,
+                                                                  uint32_t kv_heads, uint32_t max_len, float scale, uint32_t chunk,
+                                                                  float* scratch, float* __restrict__ out, const float* __restrict__ cosv,
+                                                                  const float* __restrict__ sinv) {
     GQ_GRID_DEP_SYNC();
     constexpr uint32_t dim = 4 * L, KP = kAttnThreads / L;
     __shared__ float s_sc[kAttnMaxChunk];
@@ -220,7 +226,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const float* 
     // The first passes' keys AND values are requested at once, before the cursor is known (rows past it are valid
     // memory and are masked below): q, the cursor, K and V then cost one memory latency instead of four in a row.
     constexpr int kPre = 4;
-    const float4 q4 = reinterpret_cast<const float4*>(q + (size_t)h * dim)[sub];
+    float4 q4 = reinterpret_cast<const float4*>(q + (size_t)h * dim)[sub];
     float4 kpre[kPre], vpre[kPre];
 #pragma unroll
     for (int p = 0; p < kPre; ++p) {
@@ -229,8 +235,33 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const float* 
         kpre[p] = in ? kb[(size_t)j * L + sub] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
         vpre[p] = in ? vb[(size_t)j * L + sub] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
     }
-    const uint32_t len = min(lens[layer] + 1, max_len);
+    const uint32_t pos = lens[layer];
+    const uint32_t len = min(pos + 1, max_len);
     const uint32_t j1 = min(len, j0 + chunk);
+    float4 knew = make_float4(0.0f, 0.0f, 0.0f, 0.0f), vnew = knew;
+    if (ROPE) {
+        // y = x cos + rotate_half(x) sin; rotate_half(x)[d] = -x[d + dim/2] below dim/2, x[d - dim/2] above
+        const uint32_t p = min(pos, max_len - 1), partner = (sub + L / 2) % L;
+        const float sign = sub < L / 2 ? -1.0f : 1.0f;
+        const float4 c4 = reinterpret_cast<const float4*>(cosv + (size_t)p * dim)[sub], s4 = reinterpret_cast<const float4*>(sinv + (size_t)p * dim)[sub];
+        auto rotate = [&](const float4& xv, const float4& pv) {
+            float4 r;
+            r.x = __fadd_rn(__fmul_rn(xv.x, c4.x), __fmul_rn(sign * pv.x, s4.x)), r.y = __fadd_rn(__fmul_rn(xv.y, c4.y), __fmul_rn(sign * pv.y, s4.y));
+            r.z = __fadd_rn(__fmul_rn(xv.z, c4.z), __fmul_rn(sign * pv.z, s4.z)), r.w = __fadd_rn(__fmul_rn(xv.w, c4.w), __fmul_rn(sign * pv.w, s4.w));
+            return r;
+        };
+        q4 = rotate(q4, reinterpret_cast<const float4*>(q + (size_t)h * dim)[partner]);
+        if (pos < max_len && pos >= j0 && pos < j0 + chunk) {  // this split holds the new token (uniform over the CTA)
+            const float4* kraw = reinterpret_cast<const float4*>(q + (size_t)(heads + g) * dim);
+            knew = rotate(kraw[sub], kraw[partner]);
+            vnew = reinterpret_cast<const float4*>(q + (size_t)(heads + kv_heads + g) * dim)[sub];
+            if (h % (heads / kv_heads) == 0 && grp == 0) {
+                reinterpret_cast<float4*>(kc + ((size_t)g * max_len + pos) * dim)[sub] = knew;
+                reinterpret_cast<float4*>(vc + ((size_t)g * max_len + pos) * dim)[sub] = vnew;
+            }
+        }
+    }
+    const uint32_t jnew = ROPE && pos < max_len ? pos : 0xffffffffu;  // the key whose cache row must not be used
 
     // Every lane of a warp runs the same number of passes (the shuffles below name the whole warp): a lane
     // whose key lies past the end computes on zeros and keeps nothing.
@@ -251,14 +282,14 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const float* 
         if ((uint32_t)p < passes) {  // uniform over the CTA
             const uint32_t j = j0 + p * KP + grp;
             const bool live = j < j1;
-            score(j, live, live ? kpre[p] : make_float4(0.0f, 0.0f, 0.0f, 0.0f));
+            score(j, live, !live ? make_float4(0.0f, 0.0f, 0.0f, 0.0f) : j == jnew ? knew : kpre[p]);
         }
     }
 #pragma unroll 4
     for (uint32_t pass = kPre; pass < passes; ++pass) {
         const uint32_t j = j0 + pass * KP + grp;
         const bool live = j < j1;
-        score(j, live, live ? kb[(size_t)j * L + sub] : make_float4(0.0f, 0.0f, 0.0f, 0.0f));
+        score(j, live, !live ? make_float4(0.0f, 0.0f, 0.0f, 0.0f) : j == jnew ? knew : kb[(size_t)j * L + sub]);
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
@@ -288,10 +319,10 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const float* 
 #pragma unroll
     for (int p = 0; p < kPre; ++p) {
         const uint32_t j = j0 + p * KP + grp;
-        if (j < j1) weigh(j, vpre[p]);
+        if (j < j1) weigh(j, j == jnew ? vnew : vpre[p]);
     }
 #pragma unroll 4
-    for (uint32_t j = j0 + kPre * KP + grp; j < j1; j += KP) weigh(j, vb[(size_t)j * L + sub]);
+    for (uint32_t j = j0 + kPre * KP + grp; j < j1; j += KP) weigh(j, j == jnew ? vnew : vb[(size_t)j * L + sub]);
     s_acc[tid] = acc;
     __syncthreads();
     if (tid < L) {
@@ -370,21 +401,33 @@ uint32_t attn_splits(uint32_t heads, uint32_t max_len, int sm_count) {
     return splits < 1 ? 1 : splits;
 }
 uint64_t attn_scratch_floats(uint32_t heads, uint32_t dim, uint32_t splits) { return (uint64_t)heads * splits * (dim + 2) + heads; }
-void launch_attn_decode(cudaStream_t s, const float* q, const float* kc, const float* vc, const uint32_t* lens, uint32_t layer,
-                        uint32_t heads, uint32_t kv_heads, uint32_t dim, uint32_t max_len, float scale, uint32_t splits, float* scratch,
-                        float* out) {
+// cosv == nullptr: q is the rotated query and the cache already holds the new token (after rope_kv_append). Otherwise q is the raw
+// q | k | v row, rotated and appended here.
+void launch_attn_decode(cudaStream_t s, const float* q, float* kc, float* vc, const uint32_t* lens, uint32_t layer, uint32_t heads,
+                        uint32_t kv_heads, uint32_t dim, uint32_t max_len, float scale, uint32_t splits, float* scratch, float* out,
+                        const float* cosv, const float* sinv) {
     const uint32_t chunk = (max_len + splits - 1) / splits;
     if (splits > kAttnMaxChunk || chunk > kAttnMaxChunk)
         fail("attention: a cache of %u positions is beyond this kernel (%u splits of %u keys)", max_len, splits, chunk);
     const dim3 grid(splits, heads);
+#define GQ_ATTN(LV)                                                                                                                   \
+    do {                                                                                                                              \
+        if (cosv)                                                                                                                     \
+            launch_after(attn_decode_kernel<LV, true>, grid, dim3(kAttnThreads), 0, s, q, kc, vc, lens, layer, heads, kv_heads, max_len, \
+                         scale, chunk, scratch, out, cosv, sinv);                                                                     \
+        else                                                                                                                          \
+            launch_after(attn_decode_kernel<LV, false>, grid, dim3(kAttnThreads), 0, s, q, kc, vc, lens, layer, heads, kv_heads, max_len, \
+                         scale, chunk, scratch, out, cosv, sinv);                                                                     \
+    } while (0)
     if (dim == 32)
-        launch_after(attn_decode_kernel<8>, grid, dim3(kAttnThreads), 0, s, q, kc, vc, lens, layer, heads, kv_heads, max_len, scale, chunk, scratch, out);
+        GQ_ATTN(8);
     else if (dim == 64)
-        launch_after(attn_decode_kernel<16>, grid, dim3(kAttnThreads), 0, s, q, kc, vc, lens, layer, heads, kv_heads, max_len, scale, chunk, scratch, out);
+        GQ_ATTN(16);
     else if (dim == 128)
-        launch_after(attn_decode_kernel<32>, grid, dim3(kAttnThreads), 0, s, q, kc, vc, lens, layer, heads, kv_heads, max_len, scale, chunk, scratch, out);
+        GQ_ATTN(32);
     else
         fail("attention: head_dim must be 32, 64 or 128, got %u", dim);
+#undef GQ_ATTN
 }
 void launch_swiglu(cudaStream_t s, const float* gate_up, uint64_t rows, uint64_t width, float* out) {
     launch_after(swiglu_kernel, dim3(blocks_for(rows * width, 256, 148 * 8)), dim3(256), 0, s, gate_up, (uint32_t)rows, (uint32_t)width, out);

@@ -222,8 +222,10 @@ __global__ void __launch_bounds__(kThreads, 1)
     gemv_imma_kernel(const float* __restrict__ x, const uint8_t* __restrict__ q, const float* __restrict__ scale,
                      const float* __restrict__ zero, const float* __restrict__ bias, float* __restrict__ y, uint32_t k,
                      uint32_t n, uint32_t vecs, uint32_t groups, uint32_t gshift, uint32_t gblocks, uint32_t nblocks,
-                     uint32_t nstages, uint32_t* status, Prologue pro) {
-    GQ_GRID_DEP_SYNC();
+                     uint32_t nstages, uint32_t* status, Prologue pro, bool early) {
+    // Launched so that it may start before the kernel ahead of it has finished: nothing below touches global memory
+    // before a griddepcontrol.wait, except the producer's weight copies when `early` says that kernel did not write them.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     constexpr int R = IS4 ? 8 : 4;
     extern __shared__ __align__(128) uint8_t smem_raw[];
     uint8_t* stages = smem_raw;                                                  // nstages * kStageBytes
@@ -255,6 +257,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 
     if (warp == kWarps) {
         // ── producer ──
+        if (!early) asm volatile("griddepcontrol.wait;" ::: "memory");
         uint32_t s = 0, round = 0;
         for (uint32_t tile = 0; tile < tiles; ++tile) {
             const uint32_t row0 = cb + 16 * tile, nrows = min(16u, ce - row0);
@@ -273,6 +276,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
 
     // ── consumers ──
+    asm volatile("griddepcontrol.wait;" ::: "memory");  // x may be the output of the kernel ahead
     const uint32_t g = lane >> 2, t = lane & 3;
     __shared__ double s_red[kWarps];
     float rinv = 0.0f;
@@ -412,7 +416,7 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 
 template <bool IS4, int MR>
 bool run(cudaStream_t s, int sm_count, uint32_t* status, const float* x, uint64_t k, const uint32_t* q, const float* scale,
-         const float* zero, const float* bias, uint64_t n, uint64_t group, float* y, int kind = 0, Prologue pro = Prologue()) {
+         const float* zero, const float* bias, uint64_t n, uint64_t group, float* y, bool early, int kind = 0, Prologue pro = Prologue()) {
     const uint32_t vecs = (uint32_t)(IS4 ? (k + 31) / 32 : (k + 15) / 16);
     const uint32_t nblocks = (vecs + 3) / 4;
     const uint32_t groups = IS4 ? (uint32_t)((k + group - 1) / group) : 0;
@@ -431,7 +435,7 @@ bool run(cudaStream_t s, int sm_count, uint32_t* status, const float* x, uint64_
     const uint32_t grid = (uint32_t)(n < (uint64_t)sm_count ? n : (uint64_t)sm_count);
     const bool xvec = aligned16(x) && k % 4 == 0;
     using Kernel = void (*)(const float*, const uint8_t*, const float*, const float*, const float*, float*, uint32_t, uint32_t, uint32_t,
-                            uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t*, Prologue);
+                            uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t*, Prologue, bool);
     Kernel kernel = xvec ? gemv_imma_kernel<IS4, MR, true, 0> : gemv_imma_kernel<IS4, MR, false, 0>;
     if (kind != 0) {
         if (IS4 || MR != 1 || !xvec) return false;  // prologues: int8 weights, one aligned row of x
@@ -440,7 +444,7 @@ bool run(cudaStream_t s, int sm_count, uint32_t* status, const float* x, uint64_
     }
     GQ_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     launch_after(kernel, dim3(grid), dim3(kThreads), smem, s, x, reinterpret_cast<const uint8_t*>(q), scale, zero, bias, y, (uint32_t)k,
-                 (uint32_t)n, vecs, groups, gshift, gblocks, nblocks, nstages, status, pro);
+                 (uint32_t)n, vecs, groups, gshift, gblocks, nblocks, nstages, status, pro, early);
     return true;
 }
 
@@ -450,23 +454,24 @@ bool run(cudaStream_t s, int sm_count, uint32_t* status, const float* x, uint64_
 // x, an int4 group size that is not a multiple of 128, or a row of x too long
 // for shared memory); the caller then takes the dp4a kernel.
 bool launch_gemv_q4_imma(cudaStream_t s, int sm_count, uint32_t* status, const float* x, uint64_t m, uint64_t k, const uint32_t* q,
-                         const float* scale, const float* zero, const float* bias, uint64_t n, uint64_t group, float* y) {
+                         const float* scale, const float* zero, const float* bias, uint64_t n, uint64_t group, float* y,
+                         bool weights_settled) {
     if (group % 128 != 0 || m > 2) return false;
-    return m == 1 ? run<true, 1>(s, sm_count, status, x, k, q, scale, zero, bias, n, group, y)
-                  : run<true, 2>(s, sm_count, status, x, k, q, scale, zero, bias, n, group, y);
+    return m == 1 ? run<true, 1>(s, sm_count, status, x, k, q, scale, zero, bias, n, group, y, weights_settled)
+                  : run<true, 2>(s, sm_count, status, x, k, q, scale, zero, bias, n, group, y, weights_settled);
 }
 
 // y = W . f(x) for one row of x, f the prologue `kind` (math_common.cuh). False when the shape or alignment is not this kernel's.
 bool launch_gemv_q8_imma_fused(cudaStream_t s, int sm_count, uint32_t* status, const float* x, uint64_t k, const uint32_t* q,
-                               const float* scale, const float* bias, uint64_t n, float* y, int kind, const Prologue& pro) {
-    return run<false, 1>(s, sm_count, status, x, k, q, scale, nullptr, bias, n, 0, y, kind, pro);
+                               const float* scale, const float* bias, uint64_t n, float* y, int kind, const Prologue& pro, bool weights_settled) {
+    return run<false, 1>(s, sm_count, status, x, k, q, scale, nullptr, bias, n, 0, y, weights_settled, kind, pro);
 }
 
 bool launch_gemv_q8_imma(cudaStream_t s, int sm_count, uint32_t* status, const float* x, uint64_t m, uint64_t k, const uint32_t* q,
-                         const float* scale, const float* bias, uint64_t n, float* y) {
+                         const float* scale, const float* bias, uint64_t n, float* y, bool weights_settled) {
     if (m > 2) return false;
-    return m == 1 ? run<false, 1>(s, sm_count, status, x, k, q, scale, nullptr, bias, n, 0, y)
-                  : run<false, 2>(s, sm_count, status, x, k, q, scale, nullptr, bias, n, 0, y);
+    return m == 1 ? run<false, 1>(s, sm_count, status, x, k, q, scale, nullptr, bias, n, 0, y, weights_settled)
+                  : run<false, 2>(s, sm_count, status, x, k, q, scale, nullptr, bias, n, 0, y, weights_settled);
 }
 
 }  // namespace gq

@@ -228,11 +228,24 @@ __global__ void __launch_bounds__(kThreads, 1)
         __syncwarp();
     }
 
+    // Offsets that do not change from block to block: this lane's 16 bytes of each of its groups within a stage, and
+    // its two features' scale / zero-point words within the stage's tiles. (Row r, group G) of a tile lies at
+    // r * 128 + ((G % 32 / 4) ^ (r % 8)) * 16 + G % 4 * 4 of box G / 32.
+    uint32_t woff[GPW], so0[GPW], so1[GPW];
+#pragma unroll
+    for (int gi = 0; gi < GPW; ++gi) {
+        const uint32_t G = warp + gi * kWarps;
+        woff[gi] = g8 * pitch + G * 64 + t * 16;
+        const uint32_t r0 = 2 * g8, r1 = r0 + 1, gc = (G & 31u) >> 2, gb = (G >> 5) * 2048u + (G & 3u) * 4u;
+        so0[gi] = sz_off + gb + r0 * 128u + ((gc ^ (r0 & 7u)) << 4), so1[gi] = sz_off + gb + r1 * 128u + ((gc ^ (r1 & 7u)) << 4);
+    }
+    const uint32_t zr_delta = zr_off - sz_off;
     const uint32_t smem_base = smem_u32(smem);
     for (uint32_t rb = 0; rb < blocks; ++rb) {
         const uint32_t s = rb % nstages, round = rb / nstages;
         if (!mbar_wait(full + s, round & 1, failed, status, kStatusFullWaitTimedOut)) break;
         const uint32_t stage = smem_base + s * stage_stride;
+        const uint8_t* st_p = smem + (size_t)s * stage_stride;
         float acc0[NT], acc1[NT];  // MMA rows g8 and g8 + 8 are features 2 g8 and 2 g8 + 1 of the block
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) acc0[nt] = acc1[nt] = 0.0f;
@@ -240,7 +253,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         for (int gi = 0; gi < GPW; ++gi) {
             const uint32_t G = warp + gi * kWarps;
             if (G >= groups) continue;
-            const uint4 wa = lds128(stage + g8 * pitch + G * 64 + t * 16), wb = lds128(stage + g8 * pitch + row_bytes + G * 64 + t * 16);
+            const uint4 wa = lds128(stage + woff[gi]), wb = lds128(stage + woff[gi] + row_bytes);
             const uint32_t a[4] = {wa.x, wa.y, wa.z, wa.w}, b[4] = {wb.x, wb.y, wb.z, wb.w};
             int c[NT][4];
 #pragma unroll
@@ -251,12 +264,8 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt) mma_u8s8(c[nt], a0, a1, a2, a3, bf[gi][nt][2 * i], bf[gi][nt][2 * i + 1]);
             }
-            // (row r, group G) of a tile lies at r * 128 + ((G % 32 / 4) ^ (r % 8)) * 16 + G % 4 * 4 of box G / 32
-            const uint32_t r0 = 2 * g8, r1 = r0 + 1, gc = (G & 31u) >> 2, gb = (G >> 5) * 2048u + (G & 3u) * 4u;
-            const uint32_t so0 = gb + r0 * 128u + ((gc ^ (r0 & 7u)) << 4), so1 = gb + r1 * 128u + ((gc ^ (r1 & 7u)) << 4);
-            const uint8_t* st_p = smem + (size_t)s * stage_stride;
-            const float s0 = *reinterpret_cast<const float*>(st_p + sz_off + so0), s1 = *reinterpret_cast<const float*>(st_p + sz_off + so1);
-            const float z0 = *reinterpret_cast<const float*>(st_p + zr_off + so0), z1 = *reinterpret_cast<const float*>(st_p + zr_off + so1);
+            const float s0 = *reinterpret_cast<const float*>(st_p + so0[gi]), s1 = *reinterpret_cast<const float*>(st_p + so1[gi]);
+            const float z0 = *reinterpret_cast<const float*>(st_p + so0[gi] + zr_delta), z1 = *reinterpret_cast<const float*>(st_p + so1[gi] + zr_delta);
             const float zm0 = __fmaf_rn(-8.0f, s0, z0), zm1 = __fmaf_rn(-8.0f, s1, z1);
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {

@@ -75,11 +75,16 @@ static void drop_ref(gq_ctx* ctx, gq_buf h) {
     ctx->buffers.erase(it);
 }
 
-void after_launch(gq_ctx* ctx, const char* kernel, std::initializer_list<gq_buf> used) {
+void after_launch(gq_ctx* ctx, const char* kernel, std::initializer_list<gq_buf> used, std::initializer_list<gq_buf> written) {
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) fail("launching %s: %s", kernel, cudaGetErrorString(e));
     ctx->stats.launches++;
-    ctx->ring_prev_y = 0;  // only gq_int4_linear's ring path sets it again, after this call
+    ctx->prev_known = written.size() > 0 && written.size() <= 4;
+    for (auto& w : ctx->prev_written) w = 0;
+    if (ctx->prev_known) {
+        int i = 0;
+        for (gq_buf h : written) ctx->prev_written[i++] = h;
+    }
     if (ctx->capturing) {
         ctx->capture_nodes++;
         for (gq_buf h : used) {
@@ -93,6 +98,14 @@ void after_launch(gq_ctx* ctx, const char* kernel, std::initializer_list<gq_buf>
         e = cudaStreamSynchronize(ctx->stream);
         if (e != cudaSuccess) fail("%s failed on the device: %s", kernel, cudaGetErrorString(e));
     }
+}
+
+bool weights_settled(const gq_ctx* ctx, std::initializer_list<gq_buf> weights) {
+    if (!ctx->prev_known) return false;
+    for (gq_buf w : weights)
+        for (gq_buf p : ctx->prev_written)
+            if (w != 0 && w == p) return false;
+    return true;
 }
 
 void* ensure_scratch(gq_ctx* ctx, uint64_t bytes) {
@@ -312,7 +325,7 @@ int32_t gq_upload(gq_ctx* ctx, gq_buf dst, uint64_t offset, const void* src, uin
         void* d = view(ctx, dst, offset, bytes, 1, "gq_upload");
         if (!bytes) return;
         if (!src) fail("gq_upload: null source");
-        ctx->ring_prev_y = 0;
+        ctx->prev_known = false;
         GQ_CUDA(cudaMemcpyAsync(d, src, bytes, cudaMemcpyHostToDevice, ctx->stream));
         GQ_CUDA(cudaStreamSynchronize(ctx->stream));
         ctx->stats.uploads++;
@@ -326,8 +339,8 @@ int32_t gq_download(gq_ctx* ctx, gq_buf src, uint64_t offset, void* dst, uint64_
         void* s = view(ctx, src, offset, bytes, 1, "gq_download");
         if (bytes) {
             if (!dst) fail("gq_download: null destination");
-            ctx->ring_prev_y = 0;
-            ctx->ring_prev_y = 0;
+            ctx->prev_known = false;
+            ctx->prev_known = false;
         GQ_CUDA(cudaMemcpyAsync(dst, s, bytes, cudaMemcpyDeviceToHost, ctx->stream));
         }
         host_wait(ctx);
@@ -341,7 +354,7 @@ int32_t gq_upload_async(gq_ctx* ctx, gq_buf dst, uint64_t offset, const void* sr
         void* d = view(ctx, dst, offset, bytes, 1, "gq_upload_async");
         if (!bytes) return;
         if (!src) fail("gq_upload_async: null source");
-        ctx->ring_prev_y = 0;
+        ctx->prev_known = false;
         GQ_CUDA(cudaMemcpyAsync(d, src, bytes, cudaMemcpyHostToDevice, ctx->stream));
         ctx->stats.uploads++;
         if (ctx->capturing) {
@@ -358,7 +371,7 @@ int32_t gq_download_async(gq_ctx* ctx, gq_buf src, uint64_t offset, void* dst, u
         void* s = view(ctx, src, offset, bytes, 1, "gq_download_async");
         if (!bytes) return;
         if (!dst) fail("gq_download_async: null destination");
-        ctx->ring_prev_y = 0;
+        ctx->prev_known = false;
         GQ_CUDA(cudaMemcpyAsync(dst, s, bytes, cudaMemcpyDeviceToHost, ctx->stream));
         ctx->stats.downloads++;
         if (ctx->capturing) {
@@ -392,7 +405,7 @@ int32_t gq_copy(gq_ctx* ctx, gq_buf src, uint64_t src_offset, gq_buf dst, uint64
         void* s = view(ctx, src, src_offset, bytes, 1, "gq_copy source");
         void* d = view(ctx, dst, dst_offset, bytes, 1, "gq_copy destination");
         if (!bytes) return;
-        ctx->ring_prev_y = 0;
+        ctx->prev_known = false;
         GQ_CUDA(cudaMemcpyAsync(d, s, bytes, cudaMemcpyDeviceToDevice, ctx->stream));
         after_launch(ctx, "copy", {src, dst});
     });
@@ -498,7 +511,7 @@ int32_t gq_int8_linear(gq_ctx* ctx, gq_buf x, uint64_t x_off, uint64_t m, uint64
             if (!done && kernel == GQ_KERNEL_UMMA) fail("gq_int8_linear: the tcgen05 decode kernel takes one or two rows of x (m = %llu, k = %llu)", (unsigned long long)m, (unsigned long long)k);
         }
         if (!done && (kernel == GQ_KERNEL_AUTO || kernel == GQ_KERNEL_IMMA)) {
-            done = launch_gemv_q8_imma(ctx->stream, ctx->prop.multiProcessorCount, ctx->status_dev, xp, m, k, qp, sp, bp, n, yp);
+            done = launch_gemv_q8_imma(ctx->stream, ctx->prop.multiProcessorCount, ctx->status_dev, xp, m, k, qp, sp, bp, n, yp, weights_settled(ctx, {q, scale}));
             if (done) name = "gemv_q8_imma";
             if (!done && kernel == GQ_KERNEL_IMMA) fail("gq_int8_linear: the IMMA kernel takes one or two rows of x and rows that fit shared memory (m = %llu, k = %llu)", (unsigned long long)m, (unsigned long long)k);
         }
@@ -507,7 +520,7 @@ int32_t gq_int8_linear(gq_ctx* ctx, gq_buf x, uint64_t x_off, uint64_t m, uint64
             if (!done && kernel == GQ_KERNEL_DP4A) fail("gq_int8_linear: in_features = %llu is too long for the dp4a kernel's shared-memory digit planes", (unsigned long long)k);
         }
         if (!done) launch_gemv_q8(ctx->stream, ctx->prop.multiProcessorCount, xp, m, k, qp, sp, bp, n, yp);
-        after_launch(ctx, name, {x, q, scale, bias, y});
+        after_launch(ctx, name, {x, q, scale, bias, y}, {y});
     });
 }
 
@@ -564,20 +577,19 @@ int32_t gq_int4_linear(gq_ctx* ctx, gq_buf x, uint64_t x_off, uint64_t m, uint64
         if (m == 0 || n == 0) return;
         if (kernel == GQ_KERNEL_UMMA) fail("gq_int4_linear: the tcgen05 decode kernel is built for int8 weights only");
         if (kernel == GQ_KERNEL_TENSOR) fail("gq_int4_linear: there is no tensor-core int4 kernel (the reference has none either, crates/grilly-infer/src/quant4.rs:412-413)");
-        bool done = false, ring = false;
+        bool done = false;
         const char* name = "gemv_q4";
         if (kernel == GQ_KERNEL_AUTO || kernel == GQ_KERNEL_RING) {
-            // A ring launch straight after another ring launch on this stream may begin while the first drains (its
-            // weight copies only; it waits for the first to finish before it reads x or writes y), provided its
-            // weights are not what the first one wrote.
-            const gq_buf prev_y = ctx->ring_prev_y;
-            const bool overlap = prev_y != 0 && prev_y != q && prev_y != scale && prev_y != zero;
+            // Straight after another kernel of this library whose outputs are known, the launch may begin while that one
+            // drains (its weight copies only; it waits for it to finish before it reads x or writes y), provided its
+            // weights are not what that kernel wrote.
+            const bool overlap = weights_settled(ctx, {q, scale, zero});
             done = launch_gemv_q4_ring(ctx->stream, ctx->prop.multiProcessorCount, ctx->status_dev, xp, m, k, qp, sp, zp, bp, n, group, yp, overlap);
-            if (done) name = "gemv_q4_ring", ring = true;
+            if (done) name = "gemv_q4_ring";
             if (!done && kernel == GQ_KERNEL_RING) fail("gq_int4_linear: the ring kernel takes one or two rows of x, group_size 128 and in_features 4096 or 8192 (m = %llu, k = %llu, group_size = %llu)", (unsigned long long)m, (unsigned long long)k, (unsigned long long)group);
         }
         if (!done && (kernel == GQ_KERNEL_AUTO || kernel == GQ_KERNEL_IMMA)) {
-            done = launch_gemv_q4_imma(ctx->stream, ctx->prop.multiProcessorCount, ctx->status_dev, xp, m, k, qp, sp, zp, bp, n, group, yp);
+            done = launch_gemv_q4_imma(ctx->stream, ctx->prop.multiProcessorCount, ctx->status_dev, xp, m, k, qp, sp, zp, bp, n, group, yp, weights_settled(ctx, {q, scale, zero}));
             if (done) name = "gemv_q4_imma";
             if (!done && kernel == GQ_KERNEL_IMMA) fail("gq_int4_linear: the IMMA kernel takes one or two rows of x, a group_size that is a multiple of 128 and rows that fit shared memory (m = %llu, k = %llu, group_size = %llu)", (unsigned long long)m, (unsigned long long)k, (unsigned long long)group);
         }
@@ -586,8 +598,7 @@ int32_t gq_int4_linear(gq_ctx* ctx, gq_buf x, uint64_t x_off, uint64_t m, uint64
             if (!done && kernel == GQ_KERNEL_DP4A) fail("gq_int4_linear: in_features = %llu is too long for the dp4a kernel's shared-memory digit planes", (unsigned long long)k);
         }
         if (!done) launch_gemv_q4(ctx->stream, ctx->prop.multiProcessorCount, xp, m, k, qp, sp, zp, bp, n, group, yp);
-        after_launch(ctx, name, {x, q, scale, zero, bias, y});
-        if (ring) ctx->ring_prev_y = y;
+        after_launch(ctx, name, {x, q, scale, zero, bias, y}, {y});
     });
 }
 
@@ -598,7 +609,7 @@ int32_t gq_begin_capture(gq_ctx* ctx) {
         Locked l(ctx);
         if (ctx->capturing) fail("a capture is already running on this context");
         // Relaxed: buffer allocation (cudaMalloc on a pool miss) stays legal while recording.
-        ctx->ring_prev_y = 0;
+        ctx->prev_known = false;
         GQ_CUDA(cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeRelaxed));
         ctx->capturing = true;
         ctx->capture_nodes = 0;
@@ -613,7 +624,7 @@ int32_t gq_end_capture(gq_ctx* ctx, gq_graph** out) {
         if (!ctx->capturing) fail("no capture is running on this context");
         ctx->capturing = false;
         cudaGraph_t graph = nullptr;
-        ctx->ring_prev_y = 0;
+        ctx->prev_known = false;
         cudaError_t e = cudaStreamEndCapture(ctx->stream, &graph);
         auto retained = std::move(ctx->capture_retained);
         ctx->capture_retained.clear();
@@ -650,7 +661,7 @@ int32_t gq_end_capture(gq_ctx* ctx, gq_graph** out) {
         ctx->stats.captures++;
         // The reference records while it runs, so the step has happened by the
         // time its capture ends. A CUDA stream capture only records: run it once.
-        ctx->ring_prev_y = 0;
+        ctx->prev_known = false;
         e = cudaGraphLaunch(g->exec, ctx->stream);
         if (e != cudaSuccess) {
             cudaGraphExecDestroy(g->exec);
@@ -676,7 +687,7 @@ int32_t gq_graph_replay(gq_ctx* ctx, gq_graph* graph) {
         Locked l(ctx);
         if (!graph || !graph->exec) fail("gq_graph_replay: null graph");
         if (ctx->capturing) fail("gq_graph_replay: a capture is running on this context");
-        ctx->ring_prev_y = 0;
+        ctx->prev_known = false;
         GQ_CUDA(cudaGraphLaunch(graph->exec, ctx->stream));
         ctx->stats.graph_launches++;
         ctx->stats.graph_nodes_replayed += graph->nodes;

@@ -75,7 +75,11 @@ struct gq_ctx {
     uint32_t* status_dev = nullptr;
     // lazily created device scratch owned by the context (tensor-core paths)
     void* scratch = nullptr;
-    gq_buf ring_prev_y = 0;        // output of the ring GEMV that was the last operation put on the stream, else 0
+    // What the last operation put on the stream wrote, when that operation was one of this library's kernels whose
+    // outputs are known (prev_known): a GEMV that follows may then fetch its weights before that kernel has finished,
+    // provided they are none of these buffers.
+    bool prev_known = false;
+    gq_buf prev_written[4] = {0, 0, 0, 0};
     void* argmax_state = nullptr;  // keys and counters of gq_argmax_rows, zero between calls
     uint64_t scratch_bytes = 0;
 };
@@ -135,7 +139,9 @@ void launch_after(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, 
 // A checked view of `count` elements of `elem` bytes at element offset `off`.
 void* view(gq_ctx* ctx, gq_buf buf, uint64_t off, uint64_t count, uint64_t elem, const char* what);
 // Counts a launch, notes buffers for an open capture, honours launch_blocking.
-void after_launch(gq_ctx* ctx, const char* kernel, std::initializer_list<gq_buf> used);
+void after_launch(gq_ctx* ctx, const char* kernel, std::initializer_list<gq_buf> used, std::initializer_list<gq_buf> written = {});
+// True when none of `weights` was written by the operation before this one on the stream (and that operation is known).
+bool weights_settled(const gq_ctx* ctx, std::initializer_list<gq_buf> weights);
 void* ensure_scratch(gq_ctx* ctx, uint64_t bytes);
 
 // ── kernels (each file states which reference shader it replaces) ─────────
@@ -157,15 +163,16 @@ bool launch_gemv_q4_dp4a(cudaStream_t s, int sm_count, const float* x, uint64_t 
                          const float* zero, const float* bias, uint64_t n, uint64_t group, float* y);
 
 bool launch_gemv_q8_imma(cudaStream_t s, int sm_count, uint32_t* status, const float* x, uint64_t m, uint64_t k, const uint32_t* q,
-                         const float* scale, const float* bias, uint64_t n, float* y);
+                         const float* scale, const float* bias, uint64_t n, float* y, bool weights_settled);
 struct Prologue;
 bool launch_gemv_q8_imma_fused(cudaStream_t s, int sm_count, uint32_t* status, const float* x, uint64_t k, const uint32_t* q,
-                               const float* scale, const float* bias, uint64_t n, float* y, int kind, const Prologue& pro);
+                               const float* scale, const float* bias, uint64_t n, float* y, int kind, const Prologue& pro, bool weights_settled);
 bool launch_gemv_q4_ring(cudaStream_t s, int sm_count, uint32_t* status, const float* x, uint64_t m, uint64_t k, const uint32_t* q,
                           const float* scale, const float* zero, const float* bias, uint64_t n, uint64_t group, float* y,
                          bool overlap_previous);
 bool launch_gemv_q4_imma(cudaStream_t s, int sm_count, uint32_t* status, const float* x, uint64_t m, uint64_t k, const uint32_t* q,
-                         const float* scale, const float* zero, const float* bias, uint64_t n, uint64_t group, float* y);
+                         const float* scale, const float* zero, const float* bias, uint64_t n, uint64_t group, float* y,
+                         bool weights_settled);
 
 bool launch_gemv_q8_tc(cudaStream_t s, int sm_count, uint32_t* status, const float* x, uint64_t m, uint64_t k, const uint32_t* q,
                        const float* scale, const float* bias, uint64_t n, float* y);
@@ -193,9 +200,9 @@ void launch_rope_kv_append(cudaStream_t s, const float* qkv, const float* cosv, 
 void launch_kv_advance(cudaStream_t s, uint32_t* lens, uint32_t layers, uint32_t max_len);
 uint32_t attn_splits(uint32_t heads, uint32_t max_len, int sm_count);
 uint64_t attn_scratch_floats(uint32_t heads, uint32_t dim, uint32_t splits);
-void launch_attn_decode(cudaStream_t s, const float* q, const float* kc, const float* vc, const uint32_t* lens, uint32_t layer,
-                        uint32_t heads, uint32_t kv_heads, uint32_t dim, uint32_t max_len, float scale, uint32_t splits, float* scratch,
-                        float* out);
+void launch_attn_decode(cudaStream_t s, const float* q, float* kc, float* vc, const uint32_t* lens, uint32_t layer, uint32_t heads,
+                        uint32_t kv_heads, uint32_t dim, uint32_t max_len, float scale, uint32_t splits, float* scratch, float* out,
+                        const float* cosv = nullptr, const float* sinv = nullptr);
 void launch_swiglu(cudaStream_t s, const float* gate_up, uint64_t rows, uint64_t width, float* out);
 uint64_t argmax_state_bytes();
 void launch_argmax_rows(cudaStream_t s, const float* v, uint64_t rows, uint64_t n, int32_t* out, void* state);

@@ -165,15 +165,21 @@ class LlamaDecoder:
                 qkv = lw["qkv"].linear(x, lw["qkv_bias"])
             if summed is not None:
                 hidden = summed
-            q = _C.Tensor.empty((1, c.q_size), "float32")
             off = li * self.cache.layer_elems
-            check(lib.gq_rope_kv_append(ctx, qkv.storage.handle, self.cos.storage.handle, self.sin.storage.handle,
-                                        self.cache.lens.storage.handle, li, L, Hq, Hkv, D, c.max_cache_len, q.storage.handle,
-                                        self.cache.k.storage.handle, off, self.cache.v.storage.handle, off))
             attn = _C.Tensor.empty((1, c.q_size), "float32")
-            check(lib.gq_attn_decode(ctx, q.storage.handle, self.cache.k.storage.handle, off, self.cache.v.storage.handle, off,
-                                     self.cache.lens.storage.handle, li, L, Hq, Hkv, D, c.max_cache_len, float(D) ** -0.5,
-                                     self.cache.scratch.storage.handle, attn.storage.handle))
+            if fused:  # rotary, the cache append and attention in one launch
+                check(lib.gq_attn_decode_rope(ctx, qkv.storage.handle, self.cos.storage.handle, self.sin.storage.handle,
+                                              self.cache.k.storage.handle, off, self.cache.v.storage.handle, off,
+                                              self.cache.lens.storage.handle, li, L, Hq, Hkv, D, c.max_cache_len, float(D) ** -0.5,
+                                              self.cache.scratch.storage.handle, attn.storage.handle))
+            else:
+                q = _C.Tensor.empty((1, c.q_size), "float32")
+                check(lib.gq_rope_kv_append(ctx, qkv.storage.handle, self.cos.storage.handle, self.sin.storage.handle,
+                                            self.cache.lens.storage.handle, li, L, Hq, Hkv, D, c.max_cache_len, q.storage.handle,
+                                            self.cache.k.storage.handle, off, self.cache.v.storage.handle, off))
+                check(lib.gq_attn_decode(ctx, q.storage.handle, self.cache.k.storage.handle, off, self.cache.v.storage.handle, off,
+                                         self.cache.lens.storage.handle, li, L, Hq, Hkv, D, c.max_cache_len, float(D) ** -0.5,
+                                         self.cache.scratch.storage.handle, attn.storage.handle))
             o = lw["o"].linear(attn)
             if fused:
                 gu, hidden = lw["gate_up"].linear_norm(hidden, o, lw["post_norm"], c.rms_norm_eps, None, True)

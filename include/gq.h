@@ -230,6 +230,12 @@ int32_t gq_attn_scratch_bytes(gq_ctx* ctx, uint64_t heads, uint64_t dim, uint64_
 int32_t gq_attn_decode(gq_ctx* ctx, gq_buf q, gq_buf kcache, uint64_t k_off, gq_buf vcache, uint64_t v_off, gq_buf lens, uint64_t layer,
                        uint64_t layers, uint64_t heads, uint64_t kv_heads, uint64_t dim, uint64_t max_len, float scale, gq_buf scratch,
                        gq_buf out);
+/* gq_rope_kv_append and gq_attn_decode in one launch: `qkv` is the raw q | k | v row; every CTA rotates its head of q at the
+ * cursor's position, the new token's rotated key and its value are used where that position is attended to and are appended to
+ * the cache by one CTA per KV head. No counterpart in the reference (two launches there). Buffers 16-byte aligned. */
+int32_t gq_attn_decode_rope(gq_ctx* ctx, gq_buf qkv, gq_buf cos, gq_buf sin, gq_buf kcache, uint64_t k_off, gq_buf vcache, uint64_t v_off,
+                            gq_buf lens, uint64_t layer, uint64_t layers, uint64_t heads, uint64_t kv_heads, uint64_t dim, uint64_t max_len,
+                            float scale, gq_buf scratch, gq_buf out);
 /* Fused forms for one decode token (one row): the operator before a linear runs inside the linear's conversion of x,
  * saving a launch and a round trip of the row. No counterpart in the reference, which launches them one by one.
  * gq_int8_linear_norm:   h = x + residual (residual 0: h = x); h_out = h (if not 0); y = W . (h / sqrt(mean(h^2) + eps) * w) + bias

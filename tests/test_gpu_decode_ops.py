@@ -101,3 +101,36 @@ def test_fused_linears_refuse_row_lengths_that_are_not_multiples_of_four():
     x = _C.Tensor.from_numpy(np.ones((1, 6), dtype=np.float32))
     with pytest.raises(RuntimeError, match="multiple of 4"):
         w.linear_norm(x, None, x, 1e-6)
+
+
+@pytest.mark.parametrize("dim,heads,kv_heads,max_len,length", [(64, 14, 2, 1024, 1023), (64, 14, 2, 1024, 0), (64, 14, 2, 1024, 1024),
+                                                               (32, 4, 2, 48, 20), (128, 8, 4, 300, 37), (64, 4, 1, 2500, 1700)])
+def test_rope_attention_in_one_launch_equals_the_two_operators(dim, heads, kv_heads, max_len, length):
+    """gq_attn_decode_rope == gq_rope_kv_append then gq_attn_decode: same output, same cache afterwards."""
+    _C, _lib, lib, ctx = _env()
+    rng = np.random.default_rng(dim + length + heads)
+    k = rng.standard_normal(kv_heads * max_len * dim).astype(np.float32)
+    v = rng.standard_normal(kv_heads * max_len * dim).astype(np.float32)
+    qkv = rng.standard_normal((heads + 2 * kv_heads) * dim).astype(np.float32)
+    ang = rng.uniform(0, 6.28, (max_len, dim)).astype(np.float32)
+    cos, sin = _C.Tensor.from_numpy(np.cos(ang)), _C.Tensor.from_numpy(np.sin(ang))
+    lens = _C.Tensor.from_numpy(np.array([length, 7], dtype=np.int32))
+    nbytes = ctypes.c_uint64()
+    _lib.check(lib.gq_attn_scratch_bytes(ctx, heads, dim, max_len, ctypes.byref(nbytes)))
+    scratch = _C.Tensor.from_numpy(np.zeros(nbytes.value // 4, dtype=np.float32))
+    tq = _C.Tensor.from_numpy(qkv)
+    k1, v1, k2, v2 = (_C.Tensor.from_numpy(a) for a in (k, v, k, v))
+    q = _C.Tensor.empty((heads * dim,), "float32")
+    want, got = _C.Tensor.empty((heads, dim), "float32"), _C.Tensor.empty((heads, dim), "float32")
+    _lib.check(lib.gq_rope_kv_append(ctx, tq.storage.handle, cos.storage.handle, sin.storage.handle, lens.storage.handle, 0, 2, heads, kv_heads,
+                                     dim, max_len, q.storage.handle, k1.storage.handle, 0, v1.storage.handle, 0))
+    _lib.check(lib.gq_attn_decode(ctx, q.storage.handle, k1.storage.handle, 0, v1.storage.handle, 0, lens.storage.handle, 0, 2, heads,
+                                  kv_heads, dim, max_len, dim ** -0.5, scratch.storage.handle, want.storage.handle))
+    _lib.check(lib.gq_attn_decode_rope(ctx, tq.storage.handle, cos.storage.handle, sin.storage.handle, k2.storage.handle, 0, v2.storage.handle,
+                                       0, lens.storage.handle, 0, 2, heads, kv_heads, dim, max_len, dim ** -0.5, scratch.storage.handle,
+                                       got.storage.handle))
+    np.testing.assert_array_equal(k2.numpy(), k1.numpy())
+    np.testing.assert_array_equal(v2.numpy(), v1.numpy())
+    if length < max_len:
+        assert not np.array_equal(k1.numpy(), k)  # something was appended
+    np.testing.assert_array_equal(got.numpy(), want.numpy())
