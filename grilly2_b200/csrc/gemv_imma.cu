@@ -431,8 +431,12 @@ bool run(cudaStream_t s, int sm_count, uint32_t* status, const float* x, uint64_
     if (fixed + 2 * (size_t)kStageBytes > budget) return false;
     uint32_t nstages = (uint32_t)((budget - fixed) / kStageBytes);
     if (nstages > kMaxStages) nstages = kMaxStages;
-    const size_t smem = fixed + (size_t)nstages * kStageBytes;
     const uint32_t grid = (uint32_t)(n < (uint64_t)sm_count ? n : (uint64_t)sm_count);
+    // A small layer asks only for the stages a CTA fills (a kernel launched behind it can then be resident beside it).
+    const uint64_t rows_per_cta = (n + grid - 1) / grid, rowbytes64 = (uint64_t)vecs * 16;
+    const uint64_t used = ((rows_per_cta + 15) / 16 + 1) * ((rowbytes64 + kPartBytes - 1) / kPartBytes);
+    if (used < nstages) nstages = (uint32_t)(used < 2 ? 2 : used);
+    const size_t smem = fixed + (size_t)nstages * kStageBytes;
     const bool xvec = aligned16(x) && k % 4 == 0;
     using Kernel = void (*)(const float*, const uint8_t*, const float*, const float*, const float*, float*, uint32_t, uint32_t, uint32_t,
                             uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t*, Prologue, bool);

@@ -123,7 +123,7 @@ template <int MR, int GPW>
 __global__ void __launch_bounds__(kThreads, 1)
     gemv_q4_ring_kernel(const __grid_constant__ CUtensorMap smap, const __grid_constant__ CUtensorMap zmap, const uint32_t* __restrict__ q,
                         const float* __restrict__ x, const float* __restrict__ bias, float* __restrict__ y, uint32_t k, uint32_t n,
-                        uint32_t groups, uint32_t nstages, uint32_t stage_stride, uint32_t* status) {
+                        uint32_t groups, uint32_t nstages, uint32_t stage_stride, uint32_t* status, bool x_settled) {
     extern __shared__ uint8_t smem_unaligned[];
     uint8_t* smem = smem_unaligned + ((1024u - (smem_u32(smem_unaligned) & 1023u)) & 1023u);  // swizzle atoms are 1 KB
     const uint32_t row_bytes = k >> 1, pitch = 2 * row_bytes + kRowPad;  // two consecutive features share a copy; 16 bytes of padding follow
@@ -141,9 +141,13 @@ __global__ void __launch_bounds__(kThreads, 1)
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     // A following launch that asked for it may start its CTAs as ours exit; it still waits (below) before touching x or y.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    const uint32_t row_begin = (uint32_t)((uint64_t)n * blockIdx.x / gridDim.x), row_end = (uint32_t)((uint64_t)n * (blockIdx.x + 1) / gridDim.x);
+    // Output features are dealt out in whole 16-row blocks (a CTA gets floor or ceil of blocks / CTAs of them), so no CTA
+    // pays a block's latency for a few rows.
+    const uint32_t blocks_total = (n + kBlockRows - 1) / kBlockRows;
+    const uint32_t b0 = (uint32_t)((uint64_t)blocks_total * blockIdx.x / gridDim.x), b1 = (uint32_t)((uint64_t)blocks_total * (blockIdx.x + 1) / gridDim.x);
+    const uint32_t row_begin = b0 * kBlockRows, row_end = min(b1 * kBlockRows, n);
     const uint32_t nrows = row_end - row_begin;
-    const uint32_t blocks = (nrows + kBlockRows - 1) / kBlockRows;
+    const uint32_t blocks = b1 - b0;
 
     if (tid < nstages) {
         mbar_init(full + tid, 1);
@@ -188,9 +192,10 @@ __global__ void __launch_bounds__(kThreads, 1)
     uint32_t bf[GPW][NT][8];
     float coef[GPW][NT], zcoef[GPW][NT];
     float xv[GPW][MR][4];  // every load of x is requested before the first conversion waits for one
-    // x may be the previous launch's output, and y or the partial sums' readers its input: wait for it to finish. The
-    // producer warp did not: the weights it fetches are not written by that launch.
-    asm volatile("griddepcontrol.wait;" ::: "memory");
+    // x may be the previous launch's output: wait for that launch to finish, unless the caller knows that it is not
+    // (x_settled); y is only written after a wait in either case. The producer warp did not wait: the weights it fetches
+    // are not written by that launch.
+    if (!x_settled) asm volatile("griddepcontrol.wait;" ::: "memory");
 #pragma unroll
     for (int gi = 0; gi < GPW; ++gi)
 #pragma unroll
@@ -291,6 +296,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         last = __shfl_sync(0xffffffffu, last, 0);
         if (last) {
             __threadfence_block();
+            asm volatile("griddepcontrol.wait;" ::: "memory");  // y (and bias) may be buffers the launch ahead still uses
             const uint32_t f = lane & 15u, j = rb * kBlockRows + f;
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
@@ -312,7 +318,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 template <int MR, int GPW>
 void launch(cudaStream_t s, uint32_t grid, uint64_t smem, const uint32_t* q, const float* x, const float* scale, const float* zero,
             const float* bias, float* y, uint64_t k, uint64_t n, uint64_t groups, uint64_t nstages, uint64_t stage_stride, uint32_t* status,
-            bool overlap) {
+            bool overlap, bool x_settled) {
     // scales and zero points as (n x groups) float matrices, fetched in tiles of 16 rows x 32 groups; rows past n read zeros
     const CUtensorMap smap = make_tensor_map_2d(scale, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, groups, n, groups * 4, 32, kBlockRows, Swizzle::B128);
     const CUtensorMap zmap = make_tensor_map_2d(zero, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, groups, n, groups * 4, 32, kBlockRows, Swizzle::B128);
@@ -324,7 +330,7 @@ void launch(cudaStream_t s, uint32_t grid, uint64_t smem, const uint32_t* q, con
     attr.val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = &attr, cfg.numAttrs = overlap ? 1 : 0;
     GQ_CUDA(cudaLaunchKernelEx(&cfg, gemv_q4_ring_kernel<MR, GPW>, smap, zmap, q, x, bias, y, (uint32_t)k, (uint32_t)n, (uint32_t)groups,
-                               (uint32_t)nstages, (uint32_t)stage_stride, status));
+                               (uint32_t)nstages, (uint32_t)stage_stride, status, overlap && x_settled));
 }
 
 }  // namespace
@@ -334,15 +340,14 @@ void launch(cudaStream_t s, uint32_t grid, uint64_t smem, const uint32_t* q, con
 // Returns false when the shape is not this kernel's.
 bool launch_gemv_q4_ring(cudaStream_t s, int sm_count, uint32_t* status, const float* x, uint64_t m, uint64_t k, const uint32_t* q,
                          const float* scale, const float* zero, const float* bias, uint64_t n, uint64_t group, float* y,
-                         bool overlap_previous) {
+                         bool overlap_previous, bool x_settled) {
     if (m < 1 || m > 4 || group != 128 || k == 0 || (k & 4095) || k > 16384 || n == 0 || n > 0x7fffffffull) return false;
     if (((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(scale) | reinterpret_cast<uintptr_t>(zero)) & 15) != 0) return false;
     const uint64_t groups = k / 128, row_bytes = k / 2;
     const uint64_t gpw = (groups + kWarps - 1) / kWarps;
     const uint64_t blocks_total = (n + kBlockRows - 1) / kBlockRows;
     const uint32_t grid = (uint32_t)(blocks_total < (uint64_t)sm_count ? blocks_total : (uint64_t)sm_count);
-    const uint64_t rows_per_cta = (n + grid - 1) / grid;
-    const uint64_t blocks = (rows_per_cta + kBlockRows - 1) / kBlockRows;
+    const uint64_t blocks = (blocks_total + grid - 1) / grid;  // the most 16-row blocks a CTA gets
     const uint64_t stage_stride = ((kBlockRows / 2) * (2 * row_bytes + kRowPad) + 1023) / 1024 * 1024 + 2 * (groups / 32) * 2048;
     const uint64_t tiles = (m + 1) / 2;
     if (m > 2 && gpw > 2) return false;  // the B fragments of three or four rows of x fit the registers for K = 4096 only
@@ -354,7 +359,7 @@ bool launch_gemv_q4_ring(cudaStream_t s, int sm_count, uint32_t* status, const f
     if (nstages > kMaxStages) nstages = kMaxStages;
     if (nstages > blocks) nstages = blocks;
     const uint64_t smem = fixed + nstages * per_stage;
-#define GQ_RING(MRV, GPWV) launch<MRV, GPWV>(s, grid, smem, q, x, scale, zero, bias, y, k, n, groups, nstages, stage_stride, status, overlap_previous)
+#define GQ_RING(MRV, GPWV) launch<MRV, GPWV>(s, grid, smem, q, x, scale, zero, bias, y, k, n, groups, nstages, stage_stride, status, overlap_previous, x_settled)
     if (m == 1) {
         if (gpw <= 2) GQ_RING(1, 2);
         else if (gpw <= 4) GQ_RING(1, 4);

@@ -584,7 +584,8 @@ int32_t gq_int4_linear(gq_ctx* ctx, gq_buf x, uint64_t x_off, uint64_t m, uint64
             // drains (its weight copies only; it waits for it to finish before it reads x or writes y), provided its
             // weights are not what that kernel wrote.
             const bool overlap = weights_settled(ctx, {q, scale, zero});
-            done = launch_gemv_q4_ring(ctx->stream, ctx->prop.multiProcessorCount, ctx->status_dev, xp, m, k, qp, sp, zp, bp, n, group, yp, overlap);
+            done = launch_gemv_q4_ring(ctx->stream, ctx->prop.multiProcessorCount, ctx->status_dev, xp, m, k, qp, sp, zp, bp, n, group, yp, overlap,
+                                       weights_settled(ctx, {x}));
             if (done) name = "gemv_q4_ring";
             if (!done && kernel == GQ_KERNEL_RING) fail("gq_int4_linear: the ring kernel takes one or two rows of x, group_size 128 and in_features 4096 or 8192 (m = %llu, k = %llu, group_size = %llu)", (unsigned long long)m, (unsigned long long)k, (unsigned long long)group);
         }

@@ -169,7 +169,7 @@ bool launch_gemv_q8_imma_fused(cudaStream_t s, int sm_count, uint32_t* status, c
                                const float* scale, const float* bias, uint64_t n, float* y, int kind, const Prologue& pro, bool weights_settled);
 bool launch_gemv_q4_ring(cudaStream_t s, int sm_count, uint32_t* status, const float* x, uint64_t m, uint64_t k, const uint32_t* q,
                           const float* scale, const float* zero, const float* bias, uint64_t n, uint64_t group, float* y,
-                         bool overlap_previous);
+                         bool overlap_previous, bool x_settled);
 bool launch_gemv_q4_imma(cudaStream_t s, int sm_count, uint32_t* status, const float* x, uint64_t m, uint64_t k, const uint32_t* q,
                          const float* scale, const float* zero, const float* bias, uint64_t n, uint64_t group, float* y,
                          bool weights_settled);
