@@ -343,8 +343,8 @@ def run_decode_step(args) -> None:
 
 def sharded_c3(world, rank, dist, timed_fn, capture_mod, lib):
     """Config 3: int4 g128 W[28672, 8192] column-sharded over `world` ranks, x[1, 8192] replicated. Times, per
-    call, this rank's GEMV alone, GEMV + NCCL all-gather of y, and GEMV + the put-and-signal peer gather (CUDA
-    graphs of 8 calls over distinct weight copies; max over ranks). Weights are seeded per rank: timing only."""
+    call, this rank's GEMV alone, GEMV + NCCL all-gather of y, GEMV + the put-and-signal peer gather, and the GEMV
+    whose epilogue does the gather itself (CUDA graphs of 8 calls over distinct weight copies; max over ranks). Weights are seeded per rank: timing only."""
     from grilly2_b200.sharded import Comm, PeerGather
     _C = capture_mod
     n, k, reps = 28672, 8192, 8
@@ -372,9 +372,12 @@ def sharded_c3(world, rank, dist, timed_fn, capture_mod, lib):
 
     peers = PeerGather(world, rank, 1, n, exchange)
     out = {"world": world, "rows_per_rank": ns, "bytes_per_rank": base.nbytes + 4 * k + 4 * ns}
-    for name in ("gemv_only", "gemv_nccl_all_gather", "gemv_peer_gather"):
+    for name in ("gemv_only", "gemv_nccl_all_gather", "gemv_peer_gather", "gemv_fused_gather"):
         _C.begin_capture()
         for wt in ws:
+            if name == "gemv_fused_gather":  # one kernel: the GEMV's epilogue stores into every rank's y_full and signals
+                peers.linear_gather(wt, x)
+                continue
             y = wt.linear(x)
             if name == "gemv_nccl_all_gather":
                 comm.all_gather(y)

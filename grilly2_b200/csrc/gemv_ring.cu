@@ -119,11 +119,11 @@ __device__ __forceinline__ void convert_group(const float (&v)[4], uint32_t lane
 
 // Shared memory: [stages x (16 padded rows | scale tiles | zero tiles)] [partials: stages x 16 warps x 32] [scratch: 16 warps x 256
 // words] [counts: stages] [barriers] [failed].
-template <int MR, int GPW>
+template <int MR, int GPW, bool PEER>
 __global__ void __launch_bounds__(kThreads, 1)
     gemv_q4_ring_kernel(const __grid_constant__ CUtensorMap smap, const __grid_constant__ CUtensorMap zmap, const uint32_t* __restrict__ q,
                         const float* __restrict__ x, const float* __restrict__ bias, float* __restrict__ y, uint32_t k, uint32_t n,
-                        uint32_t groups, uint32_t nstages, uint32_t stage_stride, uint32_t* status, bool x_settled) {
+                        uint32_t groups, uint32_t nstages, uint32_t stage_stride, uint32_t* status, bool x_settled, PeerOut peer) {
     extern __shared__ uint8_t smem_unaligned[];
     uint8_t* smem = smem_unaligned + ((1024u - (smem_u32(smem_unaligned) & 1023u)) & 1023u);  // swizzle atoms are 1 KB
     const uint32_t row_bytes = k >> 1, pitch = 2 * row_bytes + kRowPad;  // two consecutive features share a copy; 16 bytes of padding follow
@@ -305,7 +305,14 @@ __global__ void __launch_bounds__(kThreads, 1)
                 float tot = p[0];
 #pragma unroll
                 for (int w = 1; w < kWarps; ++w) tot = __fadd_rn(tot, p[w * 32 * NT]);
-                if (xr < MR && j < nrows) y[(size_t)xr * n + row_begin + j] = bias ? __fadd_rn(tot, bias[row_begin + j]) : tot;
+                if (xr < MR && j < nrows) {
+                    const float val = bias ? __fadd_rn(tot, bias[row_begin + j]) : tot;
+                    if (PEER) {  // this rank's block of columns, stored straight into every rank's y_full
+                        for (uint32_t pr = 0; pr < peer.nranks; ++pr) peer.y[pr][(size_t)xr * peer.n_full + (size_t)peer.rank * n + row_begin + j] = val;
+                    } else {
+                        y[(size_t)xr * n + row_begin + j] = val;
+                    }
+                }
             }
             __syncwarp();
             if (lane == 0) counts[s] = 0;
@@ -313,24 +320,57 @@ __global__ void __launch_bounds__(kThreads, 1)
         __syncwarp();
         if (lane == 0) mbar_arrive(empty + s);  // everything this warp does with the block is done
     }
+    if (PEER) {
+        // Put-and-signal: when the last CTA of the grid has seen every CTA's stores fenced, it bumps this rank's counter
+        // in every rank's flag words, then waits (bounded) until every rank's counter here has reached this step, so that
+        // y_full is complete on this GPU when the kernel ends. The step word makes a captured launch count on by itself.
+        __threadfence_system();
+        __syncwarp();
+        __shared__ uint32_t s_warps_done;
+        if (tid == 0) s_warps_done = 0;
+        named_barrier_sync(3, kWarps * 32);
+        bool finisher = false;
+        if (lane == 0) finisher = atomicAdd(&s_warps_done, 1u) == kWarps - 1;
+        if (finisher) {
+            uint32_t* mine = peer.flag[peer.rank];
+            if (atomicAdd(mine + peer.nranks + 1, 1u) == gridDim.x - 1) {
+                mine[peer.nranks + 1] = 0;
+                __threadfence_system();
+                for (uint32_t pr = 0; pr < peer.nranks; ++pr) atomicAdd_system(peer.flag[pr] + peer.rank, 1u);
+                const uint32_t step = mine[peer.nranks] + 1;
+                const long long start = clock64();
+                for (uint32_t src = 0; src < peer.nranks; ++src) {
+                    volatile uint32_t* f = mine + src;
+                    while ((int32_t)(*f - step) < 0) {
+                        if (clock64() - start > 4000000000ll) {  // ~2 s: give up, tell the host
+                            atomicCAS(status, 0u, 16u + src);
+                            break;
+                        }
+                    }
+                }
+                __threadfence_system();
+                mine[peer.nranks] = step;
+            }
+        }
+    }
 }
 
-template <int MR, int GPW>
+template <int MR, int GPW, bool PEER>
 void launch(cudaStream_t s, uint32_t grid, uint64_t smem, const uint32_t* q, const float* x, const float* scale, const float* zero,
             const float* bias, float* y, uint64_t k, uint64_t n, uint64_t groups, uint64_t nstages, uint64_t stage_stride, uint32_t* status,
-            bool overlap, bool x_settled) {
+            bool overlap, bool x_settled, const PeerOut& peer) {
     // scales and zero points as (n x groups) float matrices, fetched in tiles of 16 rows x 32 groups; rows past n read zeros
     const CUtensorMap smap = make_tensor_map_2d(scale, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, groups, n, groups * 4, 32, kBlockRows, Swizzle::B128);
     const CUtensorMap zmap = make_tensor_map_2d(zero, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, groups, n, groups * 4, 32, kBlockRows, Swizzle::B128);
-    GQ_CUDA(cudaFuncSetAttribute(gemv_q4_ring_kernel<MR, GPW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    GQ_CUDA(cudaFuncSetAttribute(gemv_q4_ring_kernel<MR, GPW, PEER>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(grid), cfg.blockDim = dim3(kThreads), cfg.dynamicSmemBytes = smem, cfg.stream = s;
     cudaLaunchAttribute attr{};
     attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr.val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = &attr, cfg.numAttrs = overlap ? 1 : 0;
-    GQ_CUDA(cudaLaunchKernelEx(&cfg, gemv_q4_ring_kernel<MR, GPW>, smap, zmap, q, x, bias, y, (uint32_t)k, (uint32_t)n, (uint32_t)groups,
-                               (uint32_t)nstages, (uint32_t)stage_stride, status, overlap && x_settled));
+    GQ_CUDA(cudaLaunchKernelEx(&cfg, gemv_q4_ring_kernel<MR, GPW, PEER>, smap, zmap, q, x, bias, y, (uint32_t)k, (uint32_t)n, (uint32_t)groups,
+                               (uint32_t)nstages, (uint32_t)stage_stride, status, overlap && x_settled, peer));
 }
 
 }  // namespace
@@ -340,7 +380,7 @@ void launch(cudaStream_t s, uint32_t grid, uint64_t smem, const uint32_t* q, con
 // Returns false when the shape is not this kernel's.
 bool launch_gemv_q4_ring(cudaStream_t s, int sm_count, uint32_t* status, const float* x, uint64_t m, uint64_t k, const uint32_t* q,
                          const float* scale, const float* zero, const float* bias, uint64_t n, uint64_t group, float* y,
-                         bool overlap_previous, bool x_settled) {
+                         bool overlap_previous, bool x_settled, const PeerOut* peer) {
     if (m < 1 || m > 4 || group != 128 || k == 0 || (k & 4095) || k > 16384 || n == 0 || n > 0x7fffffffull) return false;
     if (((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(scale) | reinterpret_cast<uintptr_t>(zero)) & 15) != 0) return false;
     const uint64_t groups = k / 128, row_bytes = k / 2;
@@ -359,7 +399,15 @@ bool launch_gemv_q4_ring(cudaStream_t s, int sm_count, uint32_t* status, const f
     if (nstages > kMaxStages) nstages = kMaxStages;
     if (nstages > blocks) nstages = blocks;
     const uint64_t smem = fixed + nstages * per_stage;
-#define GQ_RING(MRV, GPWV) launch<MRV, GPWV>(s, grid, smem, q, x, scale, zero, bias, y, k, n, groups, nstages, stage_stride, status, overlap_previous, x_settled)
+#define GQ_RING(MRV, GPWV)                                                                                                              \
+    do {                                                                                                                                \
+        if (peer)                                                                                                                       \
+            launch<MRV, GPWV, true>(s, grid, smem, q, x, scale, zero, bias, y, k, n, groups, nstages, stage_stride, status, overlap_previous, \
+                                    x_settled, *peer);                                                                                  \
+        else                                                                                                                            \
+            launch<MRV, GPWV, false>(s, grid, smem, q, x, scale, zero, bias, y, k, n, groups, nstages, stage_stride, status,            \
+                                     overlap_previous, x_settled, PeerOut());                                                           \
+    } while (0)
     if (m == 1) {
         if (gpw <= 2) GQ_RING(1, 2);
         else if (gpw <= 4) GQ_RING(1, 4);

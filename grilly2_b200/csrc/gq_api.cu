@@ -812,4 +812,34 @@ int32_t gq_peer_gather(gq_ctx* ctx, gq_buf src, uint64_t m, uint64_t n_shard, in
     });
 }
 
+int32_t gq_int4_linear_gather(gq_ctx* ctx, gq_buf x, uint64_t x_off, uint64_t m, uint64_t k, gq_buf q, gq_buf scale, gq_buf zero, gq_buf bias,
+                              uint64_t b_off, uint64_t n_shard, uint64_t group, int32_t rank, int32_t nranks, const gq_buf* peer_y,
+                              const gq_buf* peer_flag) {
+    return guarded([&] {
+        Locked l(ctx);
+        if (nranks < 1 || nranks > 8 || rank < 0 || rank >= nranks) fail("gq_int4_linear_gather: rank %d of %d is out of range (at most 8 ranks)", rank, nranks);
+        if (!peer_y || !peer_flag) fail("gq_int4_linear_gather: null handle arrays");
+        check_dims("gq_int4_linear_gather", m, k, n_shard * nranks);
+        check_group(group);
+        if (m == 0 || n_shard == 0) fail("gq_int4_linear_gather: an empty layer");
+        const uint64_t groups = (k + group - 1) / group;
+        auto xp = (const float*)view(ctx, x, x_off, m * k, 4, "gq_int4_linear_gather input");
+        auto qp = (const uint32_t*)view(ctx, q, 0, n_shard * words4(k), 4, "gq_int4_linear_gather q");
+        auto sp = (const float*)view(ctx, scale, 0, n_shard * groups, 4, "gq_int4_linear_gather scale");
+        auto zp = (const float*)view(ctx, zero, 0, n_shard * groups, 4, "gq_int4_linear_gather zero");
+        auto bp = bias ? (const float*)view(ctx, bias, b_off, n_shard, 4, "gq_int4_linear_gather bias") : nullptr;
+        PeerOut peer;
+        peer.nranks = (uint32_t)nranks, peer.rank = (uint32_t)rank, peer.n_full = (uint32_t)(n_shard * nranks);
+        for (int i = 0; i < nranks; ++i) {
+            peer.y[i] = (float*)view(ctx, peer_y[i], 0, m * n_shard * nranks, 4, "gq_int4_linear_gather y_full");
+            peer.flag[i] = (uint32_t*)view(ctx, peer_flag[i], 0, nranks + 2, 4, "gq_int4_linear_gather flags");
+        }
+        if (!launch_gemv_q4_ring(ctx->stream, ctx->prop.multiProcessorCount, ctx->status_dev, xp, m, k, qp, sp, zp, bp, n_shard, group, nullptr,
+                                 weights_settled(ctx, {q, scale, zero}), false, &peer))
+            fail("gq_int4_linear_gather: the fused kernel takes up to four rows of x, group_size 128 and in_features 4096 or 8192 (m = %llu, k = %llu, group_size = %llu)",
+                 (unsigned long long)m, (unsigned long long)k, (unsigned long long)group);
+        after_launch(ctx, "gemv_q4_ring_gather", {x, q, scale, zero, bias, peer_y[rank], peer_flag[rank]}, {peer_y[rank], peer_flag[rank]});
+    });
+}
+
 }  // extern "C"

@@ -165,11 +165,18 @@ bool launch_gemv_q4_dp4a(cudaStream_t s, int sm_count, const float* x, uint64_t 
 bool launch_gemv_q8_imma(cudaStream_t s, int sm_count, uint32_t* status, const float* x, uint64_t m, uint64_t k, const uint32_t* q,
                          const float* scale, const float* bias, uint64_t n, float* y, bool weights_settled);
 struct Prologue;
+// Where a column-sharded layer's outputs go when the gather is fused into the GEMV: every rank's y_full (peer-mapped,
+// this rank's own included) and every rank's flag words (one counter per source rank, a step word, a CTA counter).
+struct PeerOut {
+    float* y[8] = {};
+    uint32_t* flag[8] = {};
+    uint32_t nranks = 0, rank = 0, n_full = 0;
+};
 bool launch_gemv_q8_imma_fused(cudaStream_t s, int sm_count, uint32_t* status, const float* x, uint64_t k, const uint32_t* q,
                                const float* scale, const float* bias, uint64_t n, float* y, int kind, const Prologue& pro, bool weights_settled);
 bool launch_gemv_q4_ring(cudaStream_t s, int sm_count, uint32_t* status, const float* x, uint64_t m, uint64_t k, const uint32_t* q,
                           const float* scale, const float* zero, const float* bias, uint64_t n, uint64_t group, float* y,
-                         bool overlap_previous, bool x_settled);
+                         bool overlap_previous, bool x_settled, const PeerOut* peer = nullptr);
 bool launch_gemv_q4_imma(cudaStream_t s, int sm_count, uint32_t* status, const float* x, uint64_t m, uint64_t k, const uint32_t* q,
                          const float* scale, const float* zero, const float* bias, uint64_t n, uint64_t group, float* y,
                          bool weights_settled);

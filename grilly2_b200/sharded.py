@@ -84,6 +84,8 @@ class PeerGather:
         self.world, self.rank, self.m, self.n_full, self.step = world, rank, m, n_full, 0
         self.y = [_C.Tensor.empty((m, n_full), "float32", persistent=True) for _ in range(2)]
         self.flags = _C.Tensor.from_numpy(np.zeros(world + 1, dtype=np.int32), persistent=True)
+        # the fused linear + gather signals once per rank and step and keeps a CTA counter: flag words of its own
+        self.fused_flags = _C.Tensor.from_numpy(np.zeros(world + 2, dtype=np.int32), persistent=True)
         _C.synchronize()
 
         def export(t):
@@ -91,7 +93,7 @@ class PeerGather:
             check(lib.gq_buffer_ipc_export(ctx, t.storage.handle, buf, 64))
             return buf.raw
 
-        mine = {"y": [export(t) for t in self.y], "flags": export(self.flags)}
+        mine = {"y": [export(t) for t in self.y], "flags": export(self.flags), "fused_flags": export(self.fused_flags)}
         everyone = exchange(mine)
         self._opened = []
 
@@ -105,6 +107,8 @@ class PeerGather:
                             for r in range(world)] for b in range(2)]
         self._flag_handles = [self.flags.storage.handle if r == rank else open_(everyone[r]["flags"], (world + 1) * 4)
                               for r in range(world)]
+        self._fused_flag_handles = [self.fused_flags.storage.handle if r == rank else open_(everyone[r]["fused_flags"], (world + 2) * 4)
+                                    for r in range(world)]
 
     def gather(self, y_shard: "_C.Tensor") -> "_C.Tensor":
         lib, ctx = _lib.load(), _C.context()
@@ -114,6 +118,23 @@ class PeerGather:
         m = y_shard.numel() // y_shard.shape[-1]
         check(lib.gq_peer_gather(ctx, y_shard.storage.handle, m, y_shard.shape[-1], self.rank, self.world,
                                  arr(*self._y_handles[b]), arr(*self._flag_handles)))
+        return self.y[b]
+
+    def linear_gather(self, weight: "_C.Int4Weight", x: "_C.Tensor", bias: "_C.Tensor | None" = None) -> "_C.Tensor":
+        """This rank's int4 block times x, stored from the GEMV's epilogue into every rank's y_full: one kernel for the
+        linear and the gather (group size 128, in_features 4096 or 8192, up to four rows of x)."""
+        lib, ctx = _lib.load(), _C.context()
+        self.step += 1
+        b = self.step & 1
+        arr = ctypes.c_uint64 * self.world
+        n_shard, k = weight.shape
+        m = x.numel() // k
+        if m != self.m or n_shard * self.world != self.n_full:
+            raise RuntimeError(f"linear_gather: {m} x {n_shard} x {self.world} ranks does not fill y_full {self.m} x {self.n_full}")
+        check(lib.gq_int4_linear_gather(ctx, x.storage.handle, x.offset, m, k, weight._qt.storage.handle, weight._scale.storage.handle,
+                                        weight._zero.storage.handle, bias.storage.handle if bias is not None else 0,
+                                        bias.offset if bias is not None else 0, n_shard, weight._group, self.rank, self.world,
+                                        arr(*self._y_handles[b]), arr(*self._fused_flag_handles)))
         return self.y[b]
 
     def close(self) -> None:

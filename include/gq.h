@@ -294,6 +294,14 @@ int32_t gq_buffer_ipc_open(gq_ctx* ctx, const void* handle, uint64_t buffer_byte
  * that gives up is reported by the next host wait (GQ_ERR). */
 int32_t gq_peer_gather(gq_ctx* ctx, gq_buf src, uint64_t m, uint64_t n_shard, int32_t rank, int32_t nranks,
                        const gq_buf* peer_y, const gq_buf* peer_flag);
+/* gq_int4_linear and the gather in ONE kernel: this rank's block of columns is stored from the GEMV's epilogue straight into every
+ * rank's y_full (plain peer stores), the grid's last CTA then signals every rank and waits (bounded, ~2 s, reported through the
+ * context's status) until every rank has signalled this step. peer_y / peer_flag as for gq_peer_gather, except that the flag
+ * buffers hold nranks + 2 words and one signal per rank and step, so a flag buffer serves one of the two collectives only.
+ * Shapes: the ring kernel's (group_size 128, in_features 4096 or 8192, up to four rows of x). */
+int32_t gq_int4_linear_gather(gq_ctx* ctx, gq_buf x, uint64_t x_off, uint64_t m, uint64_t k, gq_buf q, gq_buf scale, gq_buf zero, gq_buf bias,
+                              uint64_t b_off, uint64_t n_shard, uint64_t group, int32_t rank, int32_t nranks, const gq_buf* peer_y,
+                              const gq_buf* peer_flag);
 
 #if defined(GQ_BUILD) && defined(__GNUC__)
 #pragma GCC visibility pop

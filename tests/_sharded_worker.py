@@ -71,6 +71,21 @@ def main() -> None:
             assert np.array_equal(got2, got), "peer gather differs from the nccl gather"
             dist.barrier()
         peers.close()
+        # the linear and the gather in one kernel (the ring kernel's shapes), against the oracle on the whole weight
+        k2, per = 4096, 80  # 80 features per rank: five 16-row blocks
+        w2 = (rng.standard_normal((per * world, k2)) * 0.015).astype(np.float32)
+        b2 = rng.standard_normal(per * world).astype(np.float32)
+        x2 = rng.standard_normal((3, k2)).astype(np.float32)
+        q2, s2, z2 = oracle.quantize_q4(w2, group)
+        layer2 = ShardedLinear.from_full(w2, b2, world, rank, bits=4, group_size=group)
+        peers2 = PeerGather(world, rank, 3, per * world, exchange)
+        for step in range(4):
+            xs = (x2 * (step + 1)).astype(np.float32)
+            ref = oracle.linear_q4(xs, q2, s2, z2, b2, k2, group)
+            got = peers2.linear_gather(layer2.q, _C.Tensor.from_numpy(xs), layer2.bias).numpy()
+            assert np.abs(got - ref).max() / np.abs(ref).max() <= 1e-5, f"fused linear + gather, step {step}"
+            dist.barrier()
+        peers2.close()
         comm.close()
     dist.barrier()
     print(f"OK {rank}", flush=True)
