@@ -598,7 +598,7 @@ def main() -> None:
         "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic", "config": workload_config(world),
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": None, "peak_kind": peak_kind, "kernel": "gemv_q4_ring_kernel<1 row of x, 2 groups per warp>",
+                     "traffic": 33071872, "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of one launch, ncu capture summarised in profiles/gemv_q4_ring_int4_m1_decode_c2.md", "peak_kind": peak_kind, "kernel": "gemv_q4_ring_kernel<1 row of x, 2 groups per warp>",
                      "algorithmic_bytes_per_launch": bytes_launch, "us_per_launch": per_launch_us},
         "cpu_baseline": cpu,
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": K_IN * 4, "d2h_bytes_per_step": REPLICAS * y_bytes,

@@ -583,11 +583,23 @@ int32_t gq_int4_linear(gq_ctx* ctx, gq_buf x, uint64_t x_off, uint64_t m, uint64
             // Straight after another kernel of this library whose outputs are known, the launch may begin while that one
             // drains (its weight copies only; it waits for it to finish before it reads x or writes y), provided its
             // weights are not what that kernel wrote.
+            // More rows of x than one launch takes (4 for in_features 4096, 2 for 8192) go in passes of that many, up to 16
+            // rows: the packed weight (a few tens of MB) stays in L2 between the passes.
             const bool overlap = weights_settled(ctx, {q, scale, zero});
-            done = launch_gemv_q4_ring(ctx->stream, ctx->prop.multiProcessorCount, ctx->status_dev, xp, m, k, qp, sp, zp, bp, n, group, yp, overlap,
-                                       weights_settled(ctx, {x}));
+            const uint64_t per_pass = k == 4096 ? 4 : 2;
+            if (m <= 16) {
+                for (uint64_t r = 0; r < m; r += per_pass) {
+                    const uint64_t rows = m - r < per_pass ? m - r : per_pass;
+                    const bool first = r == 0;
+                    done = launch_gemv_q4_ring(ctx->stream, ctx->prop.multiProcessorCount, ctx->status_dev, xp + r * k, rows, k, qp, sp, zp, bp, n, group,
+                                               yp + r * n, first ? overlap : (y != q && y != scale && y != zero),
+                                               first ? weights_settled(ctx, {x}) : x != y);
+                    if (!done) break;  // refused on the first pass: nothing was launched
+                    if (!first) ctx->stats.launches++;
+                }
+            }
             if (done) name = "gemv_q4_ring";
-            if (!done && kernel == GQ_KERNEL_RING) fail("gq_int4_linear: the ring kernel takes one or two rows of x, group_size 128 and in_features 4096 or 8192 (m = %llu, k = %llu, group_size = %llu)", (unsigned long long)m, (unsigned long long)k, (unsigned long long)group);
+            if (!done && kernel == GQ_KERNEL_RING) fail("gq_int4_linear: the ring kernel takes up to 16 rows of x, group_size 128 and in_features 4096 or 8192 (m = %llu, k = %llu, group_size = %llu)", (unsigned long long)m, (unsigned long long)k, (unsigned long long)group);
         }
         if (!done && (kernel == GQ_KERNEL_AUTO || kernel == GQ_KERNEL_IMMA)) {
             done = launch_gemv_q4_imma(ctx->stream, ctx->prop.multiProcessorCount, ctx->status_dev, xp, m, k, qp, sp, zp, bp, n, group, yp, weights_settled(ctx, {q, scale, zero}));

@@ -62,7 +62,8 @@ def test_int8_linear(g, m, n, k, with_bias):
 INT4_SHAPES = [(1, 1, 32, 32), (2, 300, 384, 128), (1, 2500, 128, 128), (2, 151, 4864, 256), (1, 777, 1000, 128),
                (1, 5, 128, 128), (3, 4, 130, 128), (8, 7, 256, 64), (2, 64, 896, 128),
                (9, 6, 4864, 128), (4, 33, 4096, 128), (16, 40, 1024, 32), (1, 300, 8192, 128), (5, 7, 70, 32),
-               (1, 2500, 512, 128), (1, 333, 4096, 128), (1, 97, 14336, 128), (2, 1500, 1024, 128), (2, 40, 12288, 128), (2, 700, 4096, 128), (3, 100, 4096, 128), (4, 333, 4096, 128),
+               (1, 2500, 512, 128), (1, 333, 4096, 128), (1, 97, 14336, 128), (2, 1500, 1024, 128), (2, 40, 12288, 128), (2, 700, 4096, 128), (3, 100, 4096, 128), (4, 333, 4096, 128), (16, 200, 4096, 128), (9, 50, 4096, 128), (8, 90, 8192, 128),
+               (5, 33, 8192, 128),
                (1, 3000, 16384, 128)]
 
 
@@ -84,7 +85,7 @@ def test_int4_linear(g, m, n, k, group, with_bias):
     np.testing.assert_array_equal(y, ref)
     assert (np.abs(y - want) <= bound).all()
     kernels = [_lib.KERNEL_DP4A, _lib.KERNEL_AUTO] + ([_lib.KERNEL_IMMA] if m <= 2 and group % 128 == 0 else [])
-    kernels += [_lib.KERNEL_RING] if group == 128 and ((m <= 2 and k in (4096, 8192)) or (m <= 4 and k == 4096)) else []
+    kernels += [_lib.KERNEL_RING] if group == 128 and m <= 16 and k in (4096, 8192) else []
     for kernel in kernels:
         y = t._q.linear(xt, bt, kernel).numpy()
         assert rel(y, ref) <= TOL
