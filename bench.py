@@ -578,6 +578,26 @@ def main() -> None:
         extras["m1_reference_order_float_kernel_us_per_launch"] = t
         extras["weight_only_GBps"] = base.nbytes / (per_launch_us * 1e-6) / 1e9  # the reference's own convention
         extras["frac_of_nominal_8TBps"] = achieved / 8000.0
+        # config 1: int8 per-row x[1,896] . W[4864,896]^T, 64 weight copies per graph (280 MB > L2) and one copy (L2-hot)
+        rng1 = np.random.default_rng(SEED + 1)
+        w1 = _C.Int8Weight.quantize(_C.Tensor.from_numpy((rng1.standard_normal((4864, 896)) * SIGMA).astype(np.float32)))
+        x1c = _C.Tensor.from_numpy(rng1.standard_normal((1, 896)).astype(np.float32))
+
+        def copy8():
+            q8 = _C.Tensor.empty(w1.packed().shape, "int32", persistent=True)
+            s8 = _C.Tensor.empty(w1.scale().shape, "float32", persistent=True)
+            q8.copy_(w1.packed()), s8.copy_(w1.scale())
+            return _C.Int8Weight(q8, s8, w1.shape)
+
+        c1_bytes = w1.nbytes + 4 * 896 + 4 * 4864
+        for label, ws8 in (("c1_int8_4864x896_m1", [copy8() for _ in range(64)]), ("c1_int8_4864x896_m1_l2_hot", [w1] * 64)):
+            _C.begin_capture()
+            keep = [wt.linear(x1c) for wt in ws8]
+            g8 = _C.end_capture()
+            t = timed(g8, max(steps2 // 4, 5), 3) * 1e3 / (max(steps2 // 4, 5) * 64)
+            extras[label + "_us_per_launch"] = t
+            extras[label + "_GBps"] = c1_bytes / (t * 1e-6) / 1e9
+            del g8, keep
 
     if world > 1 and not args.no_extras:
         extras["sharded_c3"] = sharded_c3(world, rank, dist, timed_fn=timed, capture_mod=_C, lib=_lib)

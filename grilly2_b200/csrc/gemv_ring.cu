@@ -191,16 +191,19 @@ __global__ void __launch_bounds__(kThreads, 1)
     uint32_t* scratch = scratch_all + warp * (kScratchWords * NT);
     uint32_t bf[GPW][NT][8];
     float coef[GPW][NT], zcoef[GPW][NT];
-    float xv[GPW][MR][4];  // every load of x is requested before the first conversion waits for one
+    constexpr bool kHoist = GPW * MR <= 8;  // registers permitting, every load of x is requested before the first conversion waits for one
+    float xv[kHoist ? GPW : 1][MR][4];
     // x may be the previous launch's output: wait for that launch to finish, unless the caller knows that it is not
     // (x_settled); y is only written after a wait in either case. The producer warp did not wait: the weights it fetches
     // are not written by that launch.
     if (!x_settled) asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (kHoist) {
 #pragma unroll
-    for (int gi = 0; gi < GPW; ++gi)
+        for (int gi = 0; gi < GPW; ++gi)
 #pragma unroll
-        for (int r = 0; r < MR; ++r)
-            if (warp + gi * kWarps < groups) load_group(x + (size_t)r * k, k, warp + gi * kWarps, lane, xv[gi][r]);
+            for (int r = 0; r < MR; ++r)
+                if (warp + gi * kWarps < groups) load_group(x + (size_t)r * k, k, warp + gi * kWarps, lane, xv[kHoist ? gi : 0][r]);
+    }
 #pragma unroll
     for (int gi = 0; gi < GPW; ++gi) {
         const uint32_t G = warp + gi * kWarps;
@@ -212,8 +215,12 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
         if (G >= groups) continue;  // uniform over the warp
         float inv[MR], xs[MR];
+        if (!kHoist) {
 #pragma unroll
-        for (int r = 0; r < MR; ++r) convert_group(xv[gi][r], lane, 4 * r, scratch, inv[r], xs[r]);
+            for (int r = 0; r < MR; ++r) load_group(x + (size_t)r * k, k, G, lane, xv[0][r]);
+        }
+#pragma unroll
+        for (int r = 0; r < MR; ++r) convert_group(xv[kHoist ? gi : 0][r], lane, 4 * r, scratch, inv[r], xs[r]);
         __syncwarp();
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
@@ -375,7 +382,7 @@ void launch(cudaStream_t s, uint32_t grid, uint64_t smem, const uint32_t* q, con
 
 }  // namespace
 
-// Up to four rows of x (three or four: K = 4096 only), group_size 128, K a multiple of 4096 (so that a row of scales is whole 128-byte tile rows) of which two
+// Up to four rows of x, group_size 128, K a multiple of 4096 (so that a row of scales is whole 128-byte tile rows) of which two
 // 16-row blocks fit shared memory (K <= 8192).
 // Returns false when the shape is not this kernel's.
 bool launch_gemv_q4_ring(cudaStream_t s, int sm_count, uint32_t* status, const float* x, uint64_t m, uint64_t k, const uint32_t* q,
@@ -390,7 +397,7 @@ bool launch_gemv_q4_ring(cudaStream_t s, int sm_count, uint32_t* status, const f
     const uint64_t blocks = (blocks_total + grid - 1) / grid;  // the most 16-row blocks a CTA gets
     const uint64_t stage_stride = ((kBlockRows / 2) * (2 * row_bytes + kRowPad) + 1023) / 1024 * 1024 + 2 * (groups / 32) * 2048;
     const uint64_t tiles = (m + 1) / 2;
-    if (m > 2 && gpw > 2) return false;  // the B fragments of three or four rows of x fit the registers for K = 4096 only
+    if (m > 2 && gpw > 4) return false;  // the B fragments of three or four rows of x must fit the registers
     const uint64_t per_stage = stage_stride + kWarps * 32 * 4 * tiles;
     const uint64_t fixed = 1024 + kWarps * kScratchWords * 4 * tiles + kMaxStages * 4 + 2 * kMaxStages * 8 + 64;
     const uint64_t budget = 226 * 1024;
@@ -417,9 +424,11 @@ bool launch_gemv_q4_ring(cudaStream_t s, int sm_count, uint32_t* status, const f
         else if (gpw <= 4) GQ_RING(2, 4);
         else GQ_RING(2, 8);
     } else if (m == 3) {
-        GQ_RING(3, 2);
+        if (gpw <= 2) GQ_RING(3, 2);
+        else GQ_RING(3, 4);
     } else {
-        GQ_RING(4, 2);
+        if (gpw <= 2) GQ_RING(4, 2);
+        else GQ_RING(4, 4);
     }
 #undef GQ_RING
     return true;

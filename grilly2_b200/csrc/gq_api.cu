@@ -583,10 +583,10 @@ int32_t gq_int4_linear(gq_ctx* ctx, gq_buf x, uint64_t x_off, uint64_t m, uint64
             // Straight after another kernel of this library whose outputs are known, the launch may begin while that one
             // drains (its weight copies only; it waits for it to finish before it reads x or writes y), provided its
             // weights are not what that kernel wrote.
-            // More rows of x than one launch takes (4 for in_features 4096, 2 for 8192) go in passes of that many, up to 16
+            // More rows of x than one launch takes (4) go in passes of that many, up to 16
             // rows: the packed weight (a few tens of MB) stays in L2 between the passes.
             const bool overlap = weights_settled(ctx, {q, scale, zero});
-            const uint64_t per_pass = k == 4096 ? 4 : 2;
+            const uint64_t per_pass = 4;
             if (m <= 16) {
                 for (uint64_t r = 0; r < m; r += per_pass) {
                     const uint64_t rows = m - r < per_pass ? m - r : per_pass;
