@@ -75,8 +75,8 @@ typedef uint64_t gq_buf; /* 0 is never a valid handle */
 #define GQ_KERNEL_IMMA 4   /* the same arithmetic on the warp-level int8 tensor instruction: the fast path for
                               one or two rows of x (int4: group_size a multiple of 128) */
 #define GQ_KERNEL_RING 6   /* int4 group-128 decode on the warp-level int8 tensor instruction with K split by group over the
-                              warps (digits of x in registers, weights through a deep ring of bulk copies): one or two
-                              rows of x, in_features 4096 or 8192: what AUTO picks there */
+                              warps (digits of x in registers, weights through a deep ring of bulk copies): in_features 4096
+                              or 8192, up to four rows of x per launch and up to 16 in passes: what AUTO picks there */
 
 typedef struct gq_caps { /* replaces gc_caps, gc_shim.h:43-50 */
     char device_name[256];
