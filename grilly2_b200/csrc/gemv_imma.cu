@@ -136,7 +136,7 @@ __device__ __forceinline__ void prepare_x(const float* __restrict__ xr, uint32_t
         } else if (PRO == 2) {  // x'[j] = silu(x[j]) * x[k + j]
             float4 g4 = make_float4(0.f, 0.f, 0.f, 0.f), u4 = g4;
             if (live && k0 < k) g4 = __ldg(reinterpret_cast<const float4*>(xr + k0)), u4 = __ldg(reinterpret_cast<const float4*>(xr + k + k0));
-            xv[0] = silu_mul(g4.x, u4.x), xv[1] = silu_mul(g4.y, u4.y), xv[2] = silu_mul(g4.z, u4.z), xv[3] = silu_mul(g4.w, u4.w);
+            xv[0] = silu_mul_fast(g4.x, u4.x), xv[1] = silu_mul_fast(g4.y, u4.y), xv[2] = silu_mul_fast(g4.z, u4.z), xv[3] = silu_mul_fast(g4.w, u4.w);
         } else if (XVEC) {
 #pragma unroll
             for (int h = 0; h < E / 4; ++h) {

@@ -240,7 +240,8 @@ int32_t gq_attn_decode_rope(gq_ctx* ctx, gq_buf qkv, gq_buf cos, gq_buf sin, gq_
  * saving a launch and a round trip of the row. No counterpart in the reference, which launches them one by one.
  * gq_int8_linear_norm:   h = x + residual (residual 0: h = x); h_out = h (if not 0); y = W . (h / sqrt(mean(h^2) + eps) * w) + bias
  *                        — gq_add_rms_norm then gq_int8_linear.
- * gq_int8_linear_swiglu: y = W . (silu(gate_up[0:k]) * gate_up[k:2k]) + bias — gq_swiglu then gq_int8_linear.
+ * gq_int8_linear_swiglu: y = W . (silu(gate_up[0:k]) * gate_up[k:2k]) + bias — gq_swiglu then gq_int8_linear, with the
+ *                        hardware's exp2 and reciprocal (about 1e-6 relative to the separate operators).
  * k = in_features of the layer, a multiple of 4; x, residual, w, h_out and gate_up at offset 0. */
 int32_t gq_int8_linear_norm(gq_ctx* ctx, gq_buf x, gq_buf residual, gq_buf norm_weight, float eps, gq_buf h_out, uint64_t k, gq_buf q,
                             gq_buf scale, gq_buf bias, uint64_t b_off, uint64_t n, gq_buf y);

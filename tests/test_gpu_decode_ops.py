@@ -70,7 +70,7 @@ def test_attention_refuses_other_head_sizes():
 
 @pytest.mark.parametrize("k,n", [(896, 1152), (4864, 896), (896, 151936), (64, 5)])
 def test_fused_norm_and_swiglu_linears_equal_the_separate_operators(k, n):
-    """gq_int8_linear_norm == gq_add_rms_norm then gq_int8_linear; gq_int8_linear_swiglu == gq_swiglu then gq_int8_linear."""
+    """gq_int8_linear_norm == gq_add_rms_norm then gq_int8_linear; gq_int8_linear_swiglu == gq_swiglu then gq_int8_linear (to 2e-6)."""
     _C, _lib, lib, ctx = _env()
     rng = np.random.default_rng(k + n)
     w = _C.Int8Weight.quantize(_C.Tensor.from_numpy((rng.standard_normal((n, k)) * 0.05).astype(np.float32)))
@@ -92,7 +92,7 @@ def test_fused_norm_and_swiglu_linears_equal_the_separate_operators(k, n):
     act = _C.Tensor.empty((1, k), "float32")
     _lib.check(lib.gq_swiglu(ctx, gu.storage.handle, 1, k, act.storage.handle))
     want = w.linear(act, None, _lib.KERNEL_IMMA).numpy()
-    np.testing.assert_array_equal(w.linear_swiglu(gu).numpy(), want)
+    assert np.abs(w.linear_swiglu(gu).numpy() - want).max() <= 2e-6 * np.abs(want).max()  # hardware exp2 and reciprocal in the prologue
 
 
 def test_fused_linears_refuse_row_lengths_that_are_not_multiples_of_four():
