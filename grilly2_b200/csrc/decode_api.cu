@@ -124,7 +124,7 @@ int32_t gq_attn_decode_rope(gq_ctx* ctx, gq_buf qkv, gq_buf cos, gq_buf sin, gq_
         auto op = (float*)view(ctx, out, 0, heads * dim, 4, "gq_attn_decode_rope output");
         if (((uintptr_t)qp | (uintptr_t)cp | (uintptr_t)sp | (uintptr_t)kp | (uintptr_t)vp) & 15) fail("gq_attn_decode_rope: buffers and cache offsets must be 16-byte aligned");
         launch_attn_decode(ctx->stream, qp, kp, vp, lp, (uint32_t)layer, (uint32_t)heads, (uint32_t)kv_heads, (uint32_t)dim,
-                           (uint32_t)max_len, scale, splits, scp, op, cp, sp);
+                           (uint32_t)max_len, scale, splits, scp, op, cp, sp, weights_settled(ctx, {kcache, vcache, lens, cos, sin, scratch}));
         after_launch(ctx, "attn_decode_rope", {qkv, cos, sin, kcache, vcache, lens, scratch, out}, {kcache, vcache, scratch, out});
     });
 }

@@ -206,8 +206,13 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const float* 
                                                                   const uint32_t* __restrict__ lens, uint32_t layer, uint32_t heads,
                                                                   uint32_t kv_heads, uint32_t max_len, float scale, uint32_t chunk,
                                                                   float* scratch, float* __restrict__ out, const float* __restrict__ cosv,
-                                                                  const float* __restrict__ sinv) {
-    GQ_GRID_DEP_SYNC();
+                                                                  const float* __restrict__ sinv, bool early) {
+    // `early`: the kernel ahead in the stream wrote none of the cache, the cursor and the rotary tables, so they are read while
+    // it still runs; the query row (and every write) waits for it.
+    if (!early) {
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    }
     constexpr uint32_t dim = 4 * L, KP = kAttnThreads / L;
     __shared__ float s_sc[kAttnMaxChunk];
     __shared__ float s_red[kAttnThreads / 32];
@@ -226,7 +231,6 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const float* 
     // The first passes' keys AND values are requested at once, before the cursor is known (rows past it are valid
     // memory and are masked below): q, the cursor, K and V then cost one memory latency instead of four in a row.
     constexpr int kPre = 4;
-    float4 q4 = reinterpret_cast<const float4*>(q + (size_t)h * dim)[sub];
     float4 kpre[kPre], vpre[kPre];
 #pragma unroll
     for (int p = 0; p < kPre; ++p) {
@@ -239,11 +243,20 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const float* 
     const uint32_t len = min(pos + 1, max_len);
     const uint32_t j1 = min(len, j0 + chunk);
     float4 knew = make_float4(0.0f, 0.0f, 0.0f, 0.0f), vnew = knew;
+    float4 c4 = knew, s4 = knew;
+    if (ROPE) {
+        const uint32_t p = min(pos, max_len - 1);
+        c4 = reinterpret_cast<const float4*>(cosv + (size_t)p * dim)[sub], s4 = reinterpret_cast<const float4*>(sinv + (size_t)p * dim)[sub];
+    }
+    if (early) {
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    }
+    float4 q4 = reinterpret_cast<const float4*>(q + (size_t)h * dim)[sub];
     if (ROPE) {
         // y = x cos + rotate_half(x) sin; rotate_half(x)[d] = -x[d + dim/2] below dim/2, x[d - dim/2] above
-        const uint32_t p = min(pos, max_len - 1), partner = (sub + L / 2) % L;
+        const uint32_t partner = (sub + L / 2) % L;
         const float sign = sub < L / 2 ? -1.0f : 1.0f;
-        const float4 c4 = reinterpret_cast<const float4*>(cosv + (size_t)p * dim)[sub], s4 = reinterpret_cast<const float4*>(sinv + (size_t)p * dim)[sub];
         auto rotate = [&](const float4& xv, const float4& pv) {
             float4 r;
             r.x = __fadd_rn(__fmul_rn(xv.x, c4.x), __fmul_rn(sign * pv.x, s4.x)), r.y = __fadd_rn(__fmul_rn(xv.y, c4.y), __fmul_rn(sign * pv.y, s4.y));
@@ -405,7 +418,7 @@ uint64_t attn_scratch_floats(uint32_t heads, uint32_t dim, uint32_t splits) { re
 // q | k | v row, rotated and appended here.
 void launch_attn_decode(cudaStream_t s, const float* q, float* kc, float* vc, const uint32_t* lens, uint32_t layer, uint32_t heads,
                         uint32_t kv_heads, uint32_t dim, uint32_t max_len, float scale, uint32_t splits, float* scratch, float* out,
-                        const float* cosv, const float* sinv) {
+                        const float* cosv, const float* sinv, bool early) {
     const uint32_t chunk = (max_len + splits - 1) / splits;
     if (splits > kAttnMaxChunk || chunk > kAttnMaxChunk)
         fail("attention: a cache of %u positions is beyond this kernel (%u splits of %u keys)", max_len, splits, chunk);
@@ -414,10 +427,10 @@ void launch_attn_decode(cudaStream_t s, const float* q, float* kc, float* vc, co
     do {                                                                                                                              \
         if (cosv)                                                                                                                     \
             launch_after(attn_decode_kernel<LV, true>, grid, dim3(kAttnThreads), 0, s, q, kc, vc, lens, layer, heads, kv_heads, max_len, \
-                         scale, chunk, scratch, out, cosv, sinv);                                                                     \
+                         scale, chunk, scratch, out, cosv, sinv, early);                                                              \
         else                                                                                                                          \
             launch_after(attn_decode_kernel<LV, false>, grid, dim3(kAttnThreads), 0, s, q, kc, vc, lens, layer, heads, kv_heads, max_len, \
-                         scale, chunk, scratch, out, cosv, sinv);                                                                     \
+                         scale, chunk, scratch, out, cosv, sinv, early);                                                              \
     } while (0)
     if (dim == 32)
         GQ_ATTN(8);

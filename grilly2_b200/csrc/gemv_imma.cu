@@ -225,7 +225,6 @@ __global__ void __launch_bounds__(kThreads, 1)
                      uint32_t nstages, uint32_t* status, Prologue pro, bool early) {
     // Launched so that it may start before the kernel ahead of it has finished: nothing below touches global memory
     // before a griddepcontrol.wait, except the producer's weight copies when `early` says that kernel did not write them.
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     constexpr int R = IS4 ? 8 : 4;
     extern __shared__ __align__(128) uint8_t smem_raw[];
     uint8_t* stages = smem_raw;                                                  // nstages * kStageBytes
@@ -277,6 +276,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 
     // ── consumers ──
     asm volatile("griddepcontrol.wait;" ::: "memory");  // x may be the output of the kernel ahead
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // only now: see launch_after
     const uint32_t g = lane >> 2, t = lane & 3;
     __shared__ double s_red[kWarps];
     float rinv = 0.0f;

@@ -139,8 +139,6 @@ __global__ void __launch_bounds__(kThreads, 1)
     volatile uint32_t* failed = reinterpret_cast<volatile uint32_t*>(empty + kMaxStages);
 
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    // A following launch that asked for it may start its CTAs as ours exit; it still waits (below) before touching x or y.
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     // Output features are dealt out in whole 16-row blocks (a CTA gets floor or ceil of blocks / CTAs of them), so no CTA
     // pays a block's latency for a few rows.
     const uint32_t blocks_total = (n + kBlockRows - 1) / kBlockRows;
@@ -196,7 +194,10 @@ __global__ void __launch_bounds__(kThreads, 1)
     // x may be the previous launch's output: wait for that launch to finish, unless the caller knows that it is not
     // (x_settled); y is only written after a wait in either case. The producer warp did not wait: the weights it fetches
     // are not written by that launch.
-    if (!x_settled) asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (!x_settled) {
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // the launch behind may start now (see launch_after)
+    }
     if (kHoist) {
 #pragma unroll
         for (int gi = 0; gi < GPW; ++gi)
@@ -252,6 +253,10 @@ __global__ void __launch_bounds__(kThreads, 1)
         so0[gi] = sz_off + gb + r0 * 128u + ((gc ^ (r0 & 7u)) << 4), so1[gi] = sz_off + gb + r1 * 128u + ((gc ^ (r1 & 7u)) << 4);
     }
     const uint32_t zr_delta = zr_off - sz_off;
+    if (x_settled && warp == 0) {  // nothing waited yet: one warp does, after its conversion, and lets the launch behind start
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    }
     const uint32_t smem_base = smem_u32(smem);
     for (uint32_t rb = 0; rb < blocks; ++rb) {
         const uint32_t s = rb % nstages, round = rb / nstages;

@@ -116,12 +116,14 @@ void check_dims(const char* op, uint64_t a, uint64_t b, uint64_t c = 1);
 // A kernel whose FIRST statement is GQ_GRID_DEP_SYNC() may be launched with launch_after(): its CTAs are scheduled
 // as soon as the kernel before it in the stream lets them (programmatic stream serialization) and then wait, in
 // hardware, until that kernel has finished and its writes are visible. Stream-order semantics are unchanged (nothing
-// is read or written before the wait); what is saved is the launch gap. Inside a capture the edge is recorded as such.
+// is read or written before the wait); what is saved is the launch gap. A kernel lets the one behind it start only AFTER its
+// own wait has returned, so whatever runs early in that next kernel knows that everything up to the kernel before this one is
+// complete: the only writes in doubt are this kernel's own. Inside a capture the edge is recorded as such.
 #ifdef __CUDACC__
 #define GQ_GRID_DEP_SYNC()                                                  \
     do {                                                                    \
-        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");     \
         asm volatile("griddepcontrol.wait;" ::: "memory");                  \
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");     \
     } while (0)
 
 template <typename... KArgs, typename... Args>
@@ -209,7 +211,7 @@ uint32_t attn_splits(uint32_t heads, uint32_t max_len, int sm_count);
 uint64_t attn_scratch_floats(uint32_t heads, uint32_t dim, uint32_t splits);
 void launch_attn_decode(cudaStream_t s, const float* q, float* kc, float* vc, const uint32_t* lens, uint32_t layer, uint32_t heads,
                         uint32_t kv_heads, uint32_t dim, uint32_t max_len, float scale, uint32_t splits, float* scratch, float* out,
-                        const float* cosv = nullptr, const float* sinv = nullptr);
+                        const float* cosv = nullptr, const float* sinv = nullptr, bool early = false);
 void launch_swiglu(cudaStream_t s, const float* gate_up, uint64_t rows, uint64_t width, float* out);
 uint64_t argmax_state_bytes();
 void launch_argmax_rows(cudaStream_t s, const float* v, uint64_t rows, uint64_t n, int32_t* out, void* state);
