@@ -63,7 +63,7 @@ INT4_SHAPES = [(1, 1, 32, 32), (2, 300, 384, 128), (1, 2500, 128, 128), (2, 151,
                (1, 5, 128, 128), (3, 4, 130, 128), (8, 7, 256, 64), (2, 64, 896, 128),
                (9, 6, 4864, 128), (4, 33, 4096, 128), (16, 40, 1024, 32), (1, 300, 8192, 128), (5, 7, 70, 32),
                (1, 2500, 512, 128), (1, 333, 4096, 128), (1, 97, 14336, 128), (2, 1500, 1024, 128), (2, 40, 12288, 128), (2, 700, 4096, 128), (3, 100, 4096, 128), (4, 333, 4096, 128), (16, 200, 4096, 128), (9, 50, 4096, 128), (8, 90, 8192, 128),
-               (5, 33, 8192, 128),
+               (5, 33, 8192, 128), (1, 7, 4096, 128), (4, 1, 4096, 128), (1, 16, 8192, 128), (13, 17, 4096, 128),
                (1, 3000, 16384, 128)]
 
 

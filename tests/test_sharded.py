@@ -46,7 +46,7 @@ def test_sharded_linear_over_two_gpus():
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("m,n,k", [(1, 80, 4096), (3, 333, 4096), (2, 48, 8192)])
+@pytest.mark.parametrize("m,n,k", [(1, 80, 4096), (3, 333, 4096), (2, 48, 8192), (4, 5, 4096)])
 def test_fused_linear_gather_with_a_single_rank_equals_the_linear(m, n, k):
     """World size 1 (the only peer is the rank itself): gq_int4_linear_gather must equal gq_int4_linear, step after step."""
     import numpy as np
