@@ -147,37 +147,52 @@ __global__ void __launch_bounds__(kThreads, 1)
     const uint32_t nrows = row_end - row_begin;
     const uint32_t blocks = b1 - b0;
 
-    if (tid < nstages) {
-        mbar_init(full + tid, 1);
-        mbar_init(empty + tid, kWarps);
-        counts[tid] = 0;
+    // The producer warp initialises the barriers itself and requests the first round of blocks at once; the barrier that
+    // publishes them to the consumers comes after the consumers' conversion of x, so neither costs the other anything.
+    auto request = [&](uint32_t rb) {  // lanes 0-7 bulk-copy a block's weight rows two at a time, lanes 16.. and 24.. fetch its scale and
+                                       // zero-point tiles
+        const uint32_t s = rb % nstages;
+        const uint32_t rows_here = min(kBlockRows, nrows - rb * kBlockRows);
+        if (lane == 0) mbar_arrive_expect_tx(full + s, rows_here * row_bytes + 2 * nbox * 2048u);
+        __syncwarp();
+        uint8_t* dst = smem + (size_t)s * stage_stride;
+        const size_t row0 = (size_t)row_begin + (size_t)rb * kBlockRows;
+        if (2 * lane < rows_here)  // features 2 lane and 2 lane + 1 (the last pair of the CTA may be a single row)
+            bulk_load(dst + lane * pitch, reinterpret_cast<const uint8_t*>(q) + (row0 + 2 * lane) * row_bytes,
+                      min(2u, rows_here - 2 * lane) * row_bytes, full + s);
+        else if (lane >= 16 && lane < 16 + nbox)
+            tma_load_2d(dst + sz_off + (lane - 16) * 2048u, &smap, (int32_t)((lane - 16) * 32), (int32_t)row0, full + s);
+        else if (lane >= 24 && lane < 24 + nbox)
+            tma_load_2d(dst + zr_off + (lane - 24) * 2048u, &zmap, (int32_t)((lane - 24) * 32), (int32_t)row0, full + s);
+    };
+    // Two blocks are requested before anything else happens in the CTA, the rest of the first round right after the arrival below
+    // (requesting the whole ring here made the 14336 x 4096 layer slower: the flood delays the few CTAs of the launch ahead that
+    // still wait for a seventh block, and with them that launch's end, which this launch's writes wait for).
+    const uint32_t first_round = min(min(blocks, nstages), 2u);
+    if (warp == kWarps) {
+        if (lane < nstages) {
+            mbar_init(full + lane, 1);
+            mbar_init(empty + lane, kWarps);
+            counts[lane] = 0;
+        }
+        if (lane == 0) *failed = 0;
+        __syncwarp();
+        if (lane == 0) mbar_fence_init();
+        __syncwarp();
+        for (uint32_t rb = 0; rb < first_round; ++rb) request(rb);
+        // the consumers meet this arrival after their conversion of x (named barrier 4): neither side waits for the other before
+        asm volatile("bar.arrive 4, %0;" ::"n"(kThreads) : "memory");
     }
-    if (tid == 0) {
-        *failed = 0;
-        mbar_fence_init();
-    }
-    __syncthreads();
 
     if (warp == kWarps) {
-        // ── producer: lanes 0-7 bulk-copy a block's weight rows two at a time, lanes 16.. and 24.. fetch its scale and zero-point tiles ──
-        for (uint32_t rb = 0; rb < blocks; ++rb) {
+        // ── producer: refills a stage as soon as every consumer warp has let go of it ──
+        for (uint32_t rb = first_round; rb < blocks; ++rb) {
             const uint32_t s = rb % nstages, round = rb / nstages;
             bool ok = true;
             if (round && lane == 0) ok = mbar_wait(empty + s, (round - 1) & 1, failed, status, kStatusEmptyWaitTimedOut);
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) break;
-            const uint32_t rows_here = min(kBlockRows, nrows - rb * kBlockRows);
-            if (lane == 0) mbar_arrive_expect_tx(full + s, rows_here * row_bytes + 2 * nbox * 2048u);
-            __syncwarp();
-            uint8_t* dst = smem + (size_t)s * stage_stride;
-            const size_t row0 = (size_t)row_begin + (size_t)rb * kBlockRows;
-            if (2 * lane < rows_here)  // lanes 0-7: features 2 lane and 2 lane + 1 (the last pair of the CTA may be a single row)
-                bulk_load(dst + lane * pitch, reinterpret_cast<const uint8_t*>(q) + (row0 + 2 * lane) * row_bytes,
-                          min(2u, rows_here - 2 * lane) * row_bytes, full + s);
-            else if (lane >= 16 && lane < 16 + nbox)
-                tma_load_2d(dst + sz_off + (lane - 16) * 2048u, &smap, (int32_t)((lane - 16) * 32), (int32_t)row0, full + s);
-            else if (lane >= 24 && lane < 24 + nbox)
-                tma_load_2d(dst + zr_off + (lane - 24) * 2048u, &zmap, (int32_t)((lane - 24) * 32), (int32_t)row0, full + s);
+            request(rb);
         }
         return;
     }
@@ -253,6 +268,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         so0[gi] = sz_off + gb + r0 * 128u + ((gc ^ (r0 & 7u)) << 4), so1[gi] = sz_off + gb + r1 * 128u + ((gc ^ (r1 & 7u)) << 4);
     }
     const uint32_t zr_delta = zr_off - sz_off;
+    asm volatile("bar.sync 4, %0;" ::"n"(kThreads) : "memory");  // the producer's barriers and counters are ready
     if (x_settled && warp == 0) {  // nothing waited yet: one warp does, after its conversion, and lets the launch behind start
         asm volatile("griddepcontrol.wait;" ::: "memory");
         asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
