@@ -244,18 +244,19 @@ __global__ void __launch_bounds__(kThreads, 1)
     const uint32_t parts = (rowbytes + kPartBytes - 1) / kPartBytes;  // stages per tile
     const uint32_t tiles = (ce - cb + 15) / 16;
 
-    if (threadIdx.x == 0) {
-        for (uint32_t s = 0; s < nstages; ++s) {
-            mbar_init(full + s, 1);        // the producer's arrive.expect_tx
-            mbar_init(empty + s, kWarps);  // one arrival per consumer warp
-        }
-        *failed = 0;
-        mbar_fence_init();
-    }
-    __syncthreads();
-
     if (warp == kWarps) {
-        // ── producer ──
+        // ── producer: sets the barriers up itself; the consumers meet it on named barrier 4 after converting x, so neither waits
+        // for the other at the start ──
+        if (lane == 0) {
+            for (uint32_t s = 0; s < nstages; ++s) {
+                mbar_init(full + s, 1);        // the producer's arrive.expect_tx
+                mbar_init(empty + s, kWarps);  // one arrival per consumer warp
+            }
+            *failed = 0;
+            mbar_fence_init();
+        }
+        __syncwarp();
+        asm volatile("bar.arrive 4, %0;" ::"n"(kThreads) : "memory");
         if (!early) asm volatile("griddepcontrol.wait;" ::: "memory");
         uint32_t s = 0, round = 0;
         for (uint32_t tile = 0; tile < tiles; ++tile) {
@@ -285,6 +286,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     for (int r = 0; r < MR; ++r)
         prepare_x<IS4, XVEC, PRO>(x + (size_t)r * k, r, k, nblocks, xb, xinv + r * nblocks, xsum + r * nblocks, pro, rinv);
     named_barrier_sync(1, kWarps * 32);
+    asm volatile("bar.sync 4, %0;" ::"n"(kThreads) : "memory");  // the producer's barriers are ready
 
     // this thread finishes feature row g (even t) or g + 8 (odd t) of each tile, for row t / 2 of x
     const uint32_t rowoff = g + 8 * (t & 1), xrow = t >> 1;
