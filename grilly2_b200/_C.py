@@ -46,12 +46,26 @@ def _l():
 class _Storage:
     """One gq_buf handle, released when the last tensor naming it dies."""
 
-    __slots__ = ("handle", "bytes", "__weakref__")
+    __slots__ = ("handle", "bytes", "parent", "__weakref__")
 
     def __init__(self, nbytes: int, mem: int) -> None:
         out = ctypes.c_uint64()
         check(_l().gq_buffer_create(context(), int(nbytes), mem, ctypes.byref(out)))
-        self.handle, self.bytes = out.value, int(nbytes)
+        self.handle, self.bytes, self.parent = out.value, int(nbytes), None
+
+    @classmethod
+    def window(cls, parent: "_Storage", byte_offset: int, nbytes: int) -> "_Storage":
+        """A handle of its own onto ``nbytes`` of ``parent`` from ``byte_offset`` on (gq_buffer_wrap of the parent's
+        address): for operators that write their output at the start of the buffer they are given, so that several
+        outputs can land side by side in one allocation. The parent stays alive as long as the window does."""
+        if byte_offset < 0 or nbytes < 0 or byte_offset + nbytes > parent.bytes or byte_offset % 16:
+            raise IndexError("window out of range (or not 16-byte aligned)")
+        ptr, out = ctypes.c_void_p(), ctypes.c_uint64()
+        check(_l().gq_buffer_ptr(context(), parent.handle, ctypes.byref(ptr)))
+        check(_l().gq_buffer_wrap(context(), ctypes.c_void_p(ptr.value + byte_offset), int(nbytes), ctypes.byref(out)))
+        self = object.__new__(cls)
+        self.handle, self.bytes, self.parent = out.value, int(nbytes), parent
+        return self
 
     def __del__(self) -> None:
         try:
@@ -115,6 +129,14 @@ class Tensor:
             raise IndexError("index out of range in self")
         return Tensor(self.storage, (length,) + self.shape[1:], self.dtype, self.offset + start * inner)
 
+    def window_rows(self, start: int, length: int) -> "Tensor":
+        """Rows [start, start + length) as a tensor at offset 0 of a buffer handle of its own (see _Storage.window)."""
+        inner = self.numel() // self.shape[0] if self.shape[0] else 0
+        if start < 0 or length < 0 or start + length > self.shape[0]:
+            raise IndexError("index out of range in self")
+        st = _Storage.window(self.storage, (self.offset + start * inner) * 4, length * inner * 4)
+        return Tensor(st, (length,) + self.shape[1:], self.dtype, 0)
+
     def clone_data(self) -> "Tensor":
         out = Tensor.empty(self.shape, self.dtype)
         out.copy_(self)
@@ -157,6 +179,16 @@ def _check_linear(kind, input, bias, n, k):
     out_shape = input.shape[:-1] + (n,)
     m = input.numel() // max(k, 1)
     return out_shape, m
+
+
+def _output(out, shape):
+    """A fresh output, or the caller's: float32, the right size, at the start of its buffer (the operators write there)."""
+    if out is None:
+        return Tensor.empty(shape, F32)
+    _require(out, F32, "linear output")
+    if out.numel() != int(np.prod(shape, dtype=np.int64)) or out.offset:
+        raise RuntimeError(f"linear: the output must hold {list(shape)} at offset 0 of its buffer, got {list(out.shape)} at {out.offset}")
+    return out
 
 
 class Int8Weight:
@@ -231,10 +263,10 @@ class Int8Weight:
                                       w.storage.handle))
         return w
 
-    def linear(self, input: Tensor, bias: Tensor | None = None, kernel: int = KERNEL_AUTO) -> Tensor:
+    def linear(self, input: Tensor, bias: Tensor | None = None, kernel: int = KERNEL_AUTO, out: Tensor | None = None) -> Tensor:
         n, k = self._shape
         out_shape, m = _check_linear("int8", input, bias, n, k)
-        y = Tensor.empty(out_shape, F32)
+        y = _output(out, out_shape)
         check(_l().gq_int8_linear(context(), input.storage.handle, input.offset, m, k, self._qt.storage.handle,
                                   self._scale.storage.handle, bias.storage.handle if bias is not None else 0,
                                   bias.offset if bias is not None else 0, n, y.storage.handle, kernel))
@@ -380,10 +412,10 @@ class Int4Weight:
                                       self._zero.storage.handle, n, k, self._group, w.storage.handle))
         return w
 
-    def linear(self, input: Tensor, bias: Tensor | None = None, kernel: int = KERNEL_AUTO) -> Tensor:
+    def linear(self, input: Tensor, bias: Tensor | None = None, kernel: int = KERNEL_AUTO, out: Tensor | None = None) -> Tensor:
         n, k = self._shape
         out_shape, m = _check_linear("int4", input, bias, n, k)
-        y = Tensor.empty(out_shape, F32)
+        y = _output(out, out_shape)
         check(_l().gq_int4_linear(context(), input.storage.handle, input.offset, m, k, self._qt.storage.handle,
                                   self._scale.storage.handle, self._zero.storage.handle,
                                   bias.storage.handle if bias is not None else 0,

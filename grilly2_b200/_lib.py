@@ -82,8 +82,9 @@ PROTOTYPES = {
     "gq_all_gather_columns": [vp, vp, u64, u64, u64, u64],
     "gq_buffer_ipc_export": [vp, u64, vp, u64],
     "gq_buffer_ipc_open": [vp, vp, u64, P(u64)],
-    "gq_peer_gather": [vp, u64, u64, u64, i32, i32, P(u64), P(u64)],
-    "gq_int4_linear_gather": [vp, u64, u64, u64, u64, u64, u64, u64, u64, u64, u64, u64, i32, i32, P(u64), P(u64)],
+    "gq_peer_gather": [vp, u64, u64, u64, i32, i32, P(u64), u64, u64],
+    "gq_int4_linear_gather": [vp, u64, u64, u64, u64, u64, u64, u64, u64, u64, u64, u64, i32, i32, P(u64), u64, u64],
+    "gq_set_wait_limit_us": [vp, u64],
 }
 VOID_FUNCTIONS = {"gq_destroy": [vp], "gq_graph_destroy": [vp, vp], "gq_comm_destroy": [vp, vp]}
 

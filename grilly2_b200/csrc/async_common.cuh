@@ -14,6 +14,7 @@ enum : uint32_t {
     kStatusFullWaitTimedOut = 1,   // a consumer gave up waiting for a bulk copy
     kStatusEmptyWaitTimedOut = 2,  // a producer gave up waiting for a free stage
     kStatusMmaWaitTimedOut = 3,    // a wait on tensor-core completion gave up
+    kStatusPeerWaitTimedOut = 16,  // + r: a gather gave up waiting for rank r's block of y
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }

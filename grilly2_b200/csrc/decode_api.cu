@@ -170,6 +170,13 @@ int32_t gq_int8_linear_norm(gq_ctx* ctx, gq_buf x, gq_buf residual, gq_buf norm_
         auto sp = (const float*)view(ctx, scale, 0, n, 4, "gq_int8_linear_norm scale");
         auto bp = bias ? (const float*)view(ctx, bias, b_off, n, 4, "gq_int8_linear_norm bias") : nullptr;
         auto yp = (float*)view(ctx, y, 0, n, 4, "gq_int8_linear_norm output");
+        // Every CTA re-reads x and residual for the row's norm while CTA 0 already stores h_out: in place would be a race.
+        if (ranges_overlap(pro.h_out, k * 4, xp, k * 4) || ranges_overlap(pro.h_out, k * 4, pro.res, k * 4))
+            fail("gq_int8_linear_norm: h_out must not overlap x or residual (every CTA reads them while one writes h_out); "
+                 "use gq_add_rms_norm, which is safe in place, or a separate buffer");
+        if (ranges_overlap(yp, n * 4, xp, k * 4) || ranges_overlap(yp, n * 4, pro.res, k * 4) || ranges_overlap(yp, n * 4, pro.h_out, k * 4) ||
+            ranges_overlap(yp, n * 4, pro.w, k * 4))
+            fail("gq_int8_linear_norm: the output must not overlap x, residual, the norm weight or h_out");
         if (!launch_gemv_q8_imma_fused(ctx->stream, ctx->prop.multiProcessorCount, ctx->status_dev, xp, k, qp, sp, bp, n, yp, 1, pro,
                                        weights_settled(ctx, {q, scale})))
             fail("gq_int8_linear_norm: in_features = %llu must be a multiple of 4 that fits shared memory, and the buffers 16-byte aligned", (unsigned long long)k);
@@ -188,6 +195,7 @@ int32_t gq_int8_linear_swiglu(gq_ctx* ctx, gq_buf gate_up, uint64_t k, gq_buf q,
         auto sp = (const float*)view(ctx, scale, 0, n, 4, "gq_int8_linear_swiglu scale");
         auto bp = bias ? (const float*)view(ctx, bias, b_off, n, 4, "gq_int8_linear_swiglu bias") : nullptr;
         auto yp = (float*)view(ctx, y, 0, n, 4, "gq_int8_linear_swiglu output");
+        if (ranges_overlap(yp, n * 4, xp, 2 * k * 4)) fail("gq_int8_linear_swiglu: the output must not overlap gate_up");
         if (!launch_gemv_q8_imma_fused(ctx->stream, ctx->prop.multiProcessorCount, ctx->status_dev, xp, k, qp, sp, bp, n, yp, 2, Prologue(),
                                        weights_settled(ctx, {q, scale})))
             fail("gq_int8_linear_swiglu: in_features = %llu must be a multiple of 4 that fits shared memory, and the input 16-byte aligned", (unsigned long long)k);

@@ -64,6 +64,15 @@ __device__ __forceinline__ uint4 lds128(uint32_t addr) {
     return v;
 }
 
+__device__ __forceinline__ void st_sys_u64(unsigned long long* p, unsigned long long v) {
+    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long ld_sys_u64(const unsigned long long* p) {
+    unsigned long long v;
+    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+
 // One group of one row of x -> digit words in the warp's scratch, plus 2^(e-30) and the group's sum of x.
 // Lane L converts x[128 G + 32 tt + 8 i + 2 b + par], b = 0..3, with tt = L / 8, i = (L / 2) % 4, par = L % 2:
 // the four values one packed weight word's even (par = 0) or odd (par = 1) nibbles of chunk tt meet in MMA i.
@@ -139,24 +148,28 @@ __global__ void __launch_bounds__(kThreads, 1)
     volatile uint32_t* failed = reinterpret_cast<volatile uint32_t*>(empty + kMaxStages);
 
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    // Output features are dealt out in whole 16-row blocks (a CTA gets floor or ceil of blocks / CTAs of them), so no CTA
-    // pays a block's latency for a few rows.
-    const uint32_t blocks_total = (n + kBlockRows - 1) / kBlockRows;
-    const uint32_t b0 = (uint32_t)((uint64_t)blocks_total * blockIdx.x / gridDim.x), b1 = (uint32_t)((uint64_t)blocks_total * (blockIdx.x + 1) / gridDim.x);
-    const uint32_t row_begin = b0 * kBlockRows, row_end = min(b1 * kBlockRows, n);
+    // Output features are dealt out in PAIRS of rows (the unit of a weight copy), the same number to every CTA to within one
+    // pair, and a CTA's pairs are spread evenly over its blocks of at most 16 rows: every CTA streams the same bytes in the
+    // same number of blocks, so none is left with a block more than the others at the end of the launch.
+    const uint32_t pairs_total = (n + 1) >> 1;
+    const uint32_t p0 = (uint32_t)((uint64_t)pairs_total * blockIdx.x / gridDim.x), p1 = (uint32_t)((uint64_t)pairs_total * (blockIdx.x + 1) / gridDim.x);
+    const uint32_t row_begin = 2 * p0, row_end = min(2 * p1, n);
     const uint32_t nrows = row_end - row_begin;
-    const uint32_t blocks = b1 - b0;
+    const uint32_t npairs = p1 - p0;
+    const uint32_t blocks = (npairs + kBlockRows / 2 - 1) / (kBlockRows / 2);
+    auto block_first = [&](uint32_t rb) { return 2 * (uint32_t)((uint64_t)npairs * rb / blocks); };                 // first row of block rb within the CTA
+    auto block_rows = [&](uint32_t rb) { return min(2 * (uint32_t)((uint64_t)npairs * (rb + 1) / blocks), nrows) - block_first(rb); };
 
     // The producer warp initialises the barriers itself and requests the first round of blocks at once; the barrier that
     // publishes them to the consumers comes after the consumers' conversion of x, so neither costs the other anything.
     auto request = [&](uint32_t rb) {  // lanes 0-7 bulk-copy a block's weight rows two at a time, lanes 16.. and 24.. fetch its scale and
                                        // zero-point tiles
         const uint32_t s = rb % nstages;
-        const uint32_t rows_here = min(kBlockRows, nrows - rb * kBlockRows);
+        const uint32_t rows_here = block_rows(rb);
         if (lane == 0) mbar_arrive_expect_tx(full + s, rows_here * row_bytes + 2 * nbox * 2048u);
         __syncwarp();
         uint8_t* dst = smem + (size_t)s * stage_stride;
-        const size_t row0 = (size_t)row_begin + (size_t)rb * kBlockRows;
+        const size_t row0 = (size_t)row_begin + block_first(rb);
         if (2 * lane < rows_here)  // features 2 lane and 2 lane + 1 (the last pair of the CTA may be a single row)
             bulk_load(dst + lane * pitch, reinterpret_cast<const uint8_t*>(q) + (row0 + 2 * lane) * row_bytes,
                       min(2u, rows_here - 2 * lane) * row_bytes, full + s);
@@ -274,6 +287,8 @@ __global__ void __launch_bounds__(kThreads, 1)
         asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     }
     const uint32_t smem_base = smem_u32(smem);
+    uint32_t step = 0;  // PEER: this call's number, read from the device once the launch ahead is known to be done
+    bool have_step = false;
     for (uint32_t rb = 0; rb < blocks; ++rb) {
         const uint32_t s = rb % nstages, round = rb / nstages;
         if (!mbar_wait(full + s, round & 1, failed, status, kStatusFullWaitTimedOut)) break;
@@ -325,7 +340,8 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (last) {
             __threadfence_block();
             asm volatile("griddepcontrol.wait;" ::: "memory");  // y (and bias) may be buffers the launch ahead still uses
-            const uint32_t f = lane & 15u, j = rb * kBlockRows + f;
+            const uint32_t f = lane & 15u, j = block_first(rb) + f;
+            const bool row_valid = f < block_rows(rb);
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
                 const uint32_t xr = 2 * nt + (lane >> 4);
@@ -333,10 +349,13 @@ __global__ void __launch_bounds__(kThreads, 1)
                 float tot = p[0];
 #pragma unroll
                 for (int w = 1; w < kWarps; ++w) tot = __fadd_rn(tot, p[w * 32 * NT]);
-                if (xr < MR && j < nrows) {
+                if (xr < MR && row_valid) {
                     const float val = bias ? __fadd_rn(tot, bias[row_begin + j]) : tot;
-                    if (PEER) {  // this rank's block of columns, stored straight into every rank's y_full
-                        for (uint32_t pr = 0; pr < peer.nranks; ++pr) peer.y[pr][(size_t)xr * peer.n_full + (size_t)peer.rank * n + row_begin + j] = val;
+                    if (PEER) {  // this rank's block of columns, sent to every rank's receive buffer: value and step in one word
+                        if (!have_step) step = *reinterpret_cast<const volatile uint32_t*>(peer.state) + 1u, have_step = true;
+                        const unsigned long long word = ((unsigned long long)step << 32) | __float_as_uint(val);
+                        const size_t at = ((size_t)(step & 1u) * peer.m_total + peer.row0 + xr) * peer.n_full + (size_t)peer.rank * n + row_begin + j;
+                        for (uint32_t pr = 0; pr < peer.nranks; ++pr) st_sys_u64(peer.ll[pr] + at, word);
                     } else {
                         y[(size_t)xr * n + row_begin + j] = val;
                     }
@@ -349,35 +368,36 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (lane == 0) mbar_arrive(empty + s);  // everything this warp does with the block is done
     }
     if (PEER) {
-        // Put-and-signal: when the last CTA of the grid has seen every CTA's stores fenced, it bumps this rank's counter
-        // in every rank's flag words, then waits (bounded) until every rank's counter here has reached this step, so that
-        // y_full is complete on this GPU when the kernel ends. The step word makes a captured launch count on by itself.
-        __threadfence_system();
-        __syncwarp();
-        __shared__ uint32_t s_warps_done;
-        if (tid == 0) s_warps_done = 0;
-        named_barrier_sync(3, kWarps * 32);
-        bool finisher = false;
-        if (lane == 0) finisher = atomicAdd(&s_warps_done, 1u) == kWarps - 1;
-        if (finisher) {
-            uint32_t* mine = peer.flag[peer.rank];
-            if (atomicAdd(mine + peer.nranks + 1, 1u) == gridDim.x - 1) {
-                mine[peer.nranks + 1] = 0;
-                __threadfence_system();
-                for (uint32_t pr = 0; pr < peer.nranks; ++pr) atomicAdd_system(peer.flag[pr] + peer.rank, 1u);
-                const uint32_t step = mine[peer.nranks] + 1;
-                const long long start = clock64();
-                for (uint32_t src = 0; src < peer.nranks; ++src) {
-                    volatile uint32_t* f = mine + src;
-                    while ((int32_t)(*f - step) < 0) {
-                        if (clock64() - start > 4000000000ll) {  // ~2 s: give up, tell the host
-                            atomicCAS(status, 0u, 16u + src);
-                            break;
-                        }
-                    }
+        // Receive: every value arrives as one 64-bit word (step << 32 | float bits) in this rank's receive buffer, written by
+        // its owner's epilogue above with a single store, so a word whose upper half is this step IS the value: no fence, no
+        // counter, no signal. The CTAs share the buffer out, wait (bounded) for their words and write the plain y_full. Two
+        // halves of the buffer alternate by step parity: a rank can be at most one step ahead of the slowest (it cannot
+        // finish step s + 1 without that rank's step s + 1 words), so the words of step s are never overwritten before
+        // they were read. The step word lives on the device, so a captured launch counts on by itself at every replay.
+        asm volatile("griddepcontrol.wait;" ::: "memory");  // y_full and the step word belong to the launch ahead until it is done
+        if (!have_step) step = *reinterpret_cast<const volatile uint32_t*>(peer.state) + 1u;
+        const uint32_t ctid = tid, total = MR * peer.n_full;
+        const uint32_t e0 = (uint32_t)((uint64_t)total * blockIdx.x / gridDim.x), e1 = (uint32_t)((uint64_t)total * (blockIdx.x + 1) / gridDim.x);
+        const unsigned long long* mine = peer.ll[peer.rank] + ((size_t)(step & 1u) * peer.m_total + peer.row0) * peer.n_full;
+        const long long start = clock64();
+        for (uint32_t i = e0 + ctid; i < e1; i += kWarps * 32) {
+            unsigned long long v;
+            for (;;) {
+                v = ld_sys_u64(mine + i);
+                if ((uint32_t)(v >> 32) == step) break;
+                if (clock64() - start > peer.wait_cycles) {  // give up, tell the host which rank's words never came
+                    atomicCAS(status, 0u, kStatusPeerWaitTimedOut + (i % peer.n_full) / n);
+                    break;
                 }
-                __threadfence_system();
-                mine[peer.nranks] = step;
+            }
+            peer.y_full[(size_t)peer.row0 * peer.n_full + i] = __uint_as_float((uint32_t)v);
+        }
+        named_barrier_sync(3, kWarps * 32);
+        if (ctid == 0) {
+            __threadfence();
+            if (atomicAdd(peer.state + 1, 1u) == gridDim.x - 1) {  // the grid's last CTA: the call is finished
+                peer.state[1] = 0;
+                peer.state[0] = step;
             }
         }
     }
@@ -413,9 +433,9 @@ bool launch_gemv_q4_ring(cudaStream_t s, int sm_count, uint32_t* status, const f
     if (((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(scale) | reinterpret_cast<uintptr_t>(zero)) & 15) != 0) return false;
     const uint64_t groups = k / 128, row_bytes = k / 2;
     const uint64_t gpw = (groups + kWarps - 1) / kWarps;
-    const uint64_t blocks_total = (n + kBlockRows - 1) / kBlockRows;
+    const uint64_t pairs_total = (n + 1) / 2, blocks_total = (pairs_total + kBlockRows / 2 - 1) / (kBlockRows / 2);
     const uint32_t grid = (uint32_t)(blocks_total < (uint64_t)sm_count ? blocks_total : (uint64_t)sm_count);
-    const uint64_t blocks = (blocks_total + grid - 1) / grid;  // the most 16-row blocks a CTA gets
+    const uint64_t blocks = ((pairs_total + grid - 1) / grid + kBlockRows / 2 - 1) / (kBlockRows / 2);  // the most blocks a CTA gets
     const uint64_t stage_stride = ((kBlockRows / 2) * (2 * row_bytes + kRowPad) + 1023) / 1024 * 1024 + 2 * (groups / 32) * 2048;
     const uint64_t tiles = (m + 1) / 2;
     if (m > 2 && gpw > 4) return false;  // the B fragments of three or four rows of x must fit the registers

@@ -12,6 +12,7 @@
 #include <cstring>
 
 #include "gq_internal.h"
+#include "async_common.cuh"
 
 namespace gq {
 
@@ -108,22 +109,6 @@ bool weights_settled(const gq_ctx* ctx, std::initializer_list<gq_buf> weights) {
     return true;
 }
 
-void* ensure_scratch(gq_ctx* ctx, uint64_t bytes) {
-    if (ctx->scratch_bytes >= bytes) return ctx->scratch;
-    if (ctx->capturing) fail("the context's scratch would have to grow to %llu bytes inside a capture: run the step once eagerly first", (unsigned long long)bytes);
-    if (ctx->scratch) {
-        GQ_CUDA(cudaStreamSynchronize(ctx->stream));
-        cudaFree(ctx->scratch);
-        ctx->scratch = nullptr;
-        ctx->scratch_bytes = 0;
-    }
-    uint64_t cap = bucket_of(bytes);
-    GQ_CUDA(cudaMalloc(&ctx->scratch, cap));
-    ctx->scratch_bytes = cap;
-    ctx->stats.buffer_allocations++;
-    return ctx->scratch;
-}
-
 static void host_wait(gq_ctx* ctx) {
     auto t0 = std::chrono::steady_clock::now();
     cudaError_t e = cudaStreamSynchronize(ctx->stream);
@@ -135,8 +120,11 @@ static void host_wait(gq_ctx* ctx) {
     if (ctx->status_host && *ctx->status_host) {
         const uint32_t code = *ctx->status_host;
         *ctx->status_host = 0;
+        if (code >= kStatusPeerWaitTimedOut)
+            fail("a gather gave up waiting for rank %u's block of the output (code %u = 16 + the rank; the limit is set by "
+                 "gq_set_wait_limit_us); its results are not valid", code - kStatusPeerWaitTimedOut, code);
         fail("a kernel gave up a bounded wait (code %u: 1 = a bulk copy never landed, 2 = a pipeline stage was never freed, "
-             "3 = the tensor cores never signalled completion); its results are not valid", code);
+             "3 = the tensor cores never signalled completion, 4 = a grid-wide barrier was never completed); its results are not valid", code);
     }
 }
 
@@ -197,10 +185,11 @@ void gq_destroy(gq_ctx* ctx) {
             std::lock_guard<std::mutex> lock(ctx->mutex);
             cudaSetDevice(ctx->device);
             cudaStreamSynchronize(ctx->stream);
-            for (auto& kv : ctx->buffers)
+            for (auto& kv : ctx->buffers) {
+                if (kv.second.ipc && kv.second.ptr) cudaIpcCloseMemHandle(kv.second.ptr);
                 if (kv.second.owned && kv.second.ptr) cudaFree(kv.second.ptr);
+            }
             for (auto& kv : ctx->pool) cudaFree(kv.second);
-            if (ctx->scratch) cudaFree(ctx->scratch);
             if (ctx->argmax_state) cudaFree(ctx->argmax_state);
             if (ctx->status_host) cudaFreeHost(ctx->status_host);
             cudaStreamDestroy(ctx->stream);
@@ -340,8 +329,7 @@ int32_t gq_download(gq_ctx* ctx, gq_buf src, uint64_t offset, void* dst, uint64_
         if (bytes) {
             if (!dst) fail("gq_download: null destination");
             ctx->prev_known = false;
-            ctx->prev_known = false;
-        GQ_CUDA(cudaMemcpyAsync(dst, s, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+            GQ_CUDA(cudaMemcpyAsync(dst, s, bytes, cudaMemcpyDeviceToHost, ctx->stream));
         }
         host_wait(ctx);
         ctx->stats.downloads++;
@@ -430,6 +418,16 @@ int32_t gq_synchronize(gq_ctx* ctx) {
     });
 }
 
+int32_t gq_set_wait_limit_us(gq_ctx* ctx, uint64_t microseconds) {
+    return guarded([&] {
+        Locked l(ctx);
+        // prop.clockRate is the SM clock in kHz: cycles = us * kHz / 1000
+        const uint64_t us = microseconds ? microseconds : 2000000ull;
+        if (us > 3600ull * 1000000ull) fail("gq_set_wait_limit_us: at most one hour");
+        ctx->peer_wait_cycles = (long long)(us * (uint64_t)(ctx->prop.clockRate > 0 ? ctx->prop.clockRate : 1965000) / 1000ull);
+    });
+}
+
 int32_t gq_stats_get(gq_ctx* ctx, gq_stats* out) {
     return guarded([&] {
         Locked l(ctx);
@@ -495,6 +493,7 @@ int32_t gq_int8_linear(gq_ctx* ctx, gq_buf x, uint64_t x_off, uint64_t m, uint64
         auto sp = (const float*)view(ctx, scale, 0, n, 4, "gq_int8_linear scale");
         auto bp = bias ? (const float*)view(ctx, bias, b_off, n, 4, "gq_int8_linear bias") : nullptr;
         auto yp = (float*)view(ctx, y, 0, m * n, 4, "gq_int8_linear output");
+        if (ranges_overlap(yp, m * n * 4, xp, m * k * 4)) fail("gq_int8_linear: the output must not overlap the input (CTAs read x while others write y)");
         if (m == 0 || n == 0) return;  // quant.rs:267-269
         bool done = false;
         const char* name = "gemv_q8";
@@ -574,6 +573,7 @@ int32_t gq_int4_linear(gq_ctx* ctx, gq_buf x, uint64_t x_off, uint64_t m, uint64
         auto zp = (const float*)view(ctx, zero, 0, n * groups, 4, "gq_int4_linear zero");
         auto bp = bias ? (const float*)view(ctx, bias, b_off, n, 4, "gq_int4_linear bias") : nullptr;
         auto yp = (float*)view(ctx, y, 0, m * n, 4, "gq_int4_linear output");
+        if (ranges_overlap(yp, m * n * 4, xp, m * k * 4)) fail("gq_int4_linear: the output must not overlap the input (CTAs read x while others write y)");
         if (m == 0 || n == 0) return;
         if (kernel == GQ_KERNEL_UMMA) fail("gq_int4_linear: the tcgen05 decode kernel is built for int8 weights only");
         if (kernel == GQ_KERNEL_TENSOR) fail("gq_int4_linear: there is no tensor-core int4 kernel (the reference has none either, crates/grilly-infer/src/quant4.rs:412-413)");
@@ -804,53 +804,63 @@ int32_t gq_buffer_ipc_open(gq_ctx* ctx, const void* handle, uint64_t buffer_byte
     });
 }
 
-int32_t gq_peer_gather(gq_ctx* ctx, gq_buf src, uint64_t m, uint64_t n_shard, int32_t rank, int32_t nranks,
-                       const gq_buf* peer_y, const gq_buf* peer_flag) {
+static PeerOut peer_views(gq_ctx* ctx, const char* op, uint64_t m, uint64_t n_shard, int32_t rank, int32_t nranks, const gq_buf* peer_recv,
+                           gq_buf state, gq_buf y_full) {
+    if (nranks < 1 || nranks > 8 || rank < 0 || rank >= nranks) fail("%s: rank %d of %d is out of range (at most 8 ranks)", op, rank, nranks);
+    if (!peer_recv) fail("%s: null handle array", op);
+    PeerOut peer;
+    peer.nranks = (uint32_t)nranks, peer.rank = (uint32_t)rank, peer.n_full = (uint32_t)(n_shard * nranks), peer.m_total = (uint32_t)m;
+    peer.wait_cycles = ctx->peer_wait_cycles;
+    for (int i = 0; i < nranks; ++i) peer.ll[i] = (unsigned long long*)view(ctx, peer_recv[i], 0, 2 * m * n_shard * nranks, 8, "gather receive buffer");
+    peer.state = (uint32_t*)view(ctx, state, 0, 2, 4, "gather state words");
+    peer.y_full = (float*)view(ctx, y_full, 0, m * n_shard * nranks, 4, "gather y_full");
+    return peer;
+}
+
+int32_t gq_peer_gather(gq_ctx* ctx, gq_buf src, uint64_t m, uint64_t n_shard, int32_t rank, int32_t nranks, const gq_buf* peer_recv,
+                       gq_buf state, gq_buf y_full) {
     return guarded([&] {
         Locked l(ctx);
-        if (nranks < 1 || nranks > 8 || rank < 0 || rank >= nranks) fail("gq_peer_gather: rank %d of %d is out of range (at most 8 ranks)", rank, nranks);
-        if (!peer_y || !peer_flag) fail("gq_peer_gather: null handle arrays");
-        check_dims("gq_peer_gather", m, n_shard * nranks);
+        check_dims("gq_peer_gather", m, n_shard * (nranks > 0 ? nranks : 1));
+        if (m * n_shard * (uint64_t)(nranks > 0 ? nranks : 1) > 0x7fffffffull) fail("gq_peer_gather: more than 2^31 - 1 values");
         auto sp = (const float*)view(ctx, src, 0, m * n_shard, 4, "gq_peer_gather source");
-        float* ys[8];
-        uint32_t* fl[8];
-        for (int i = 0; i < nranks; ++i) {
-            ys[i] = (float*)view(ctx, peer_y[i], 0, m * n_shard * nranks, 4, "gq_peer_gather y_full");
-            fl[i] = (uint32_t*)view(ctx, peer_flag[i], 0, nranks + 1, 4, "gq_peer_gather flags");
-        }
+        PeerOut peer = peer_views(ctx, "gq_peer_gather", m, n_shard, rank, nranks, peer_recv, state, y_full);
+        if (src == y_full) fail("gq_peer_gather: the source block and y_full must be different buffers");
         if (m == 0 || n_shard == 0) return;
-        launch_peer_gather(ctx->stream, ys, fl, sp, m, n_shard, rank, nranks, ctx->status_dev);
-        after_launch(ctx, "peer_gather", {src, peer_y[rank], peer_flag[rank]});
+        launch_peer_gather(ctx->stream, ctx->prop.multiProcessorCount, peer, sp, m, n_shard, ctx->status_dev);
+        after_launch(ctx, "peer_gather", {src, peer_recv[rank], state, y_full}, {peer_recv[rank], state, y_full});
     });
 }
 
 int32_t gq_int4_linear_gather(gq_ctx* ctx, gq_buf x, uint64_t x_off, uint64_t m, uint64_t k, gq_buf q, gq_buf scale, gq_buf zero, gq_buf bias,
-                              uint64_t b_off, uint64_t n_shard, uint64_t group, int32_t rank, int32_t nranks, const gq_buf* peer_y,
-                              const gq_buf* peer_flag) {
+                              uint64_t b_off, uint64_t n_shard, uint64_t group, int32_t rank, int32_t nranks, const gq_buf* peer_recv,
+                              gq_buf state, gq_buf y_full) {
     return guarded([&] {
         Locked l(ctx);
-        if (nranks < 1 || nranks > 8 || rank < 0 || rank >= nranks) fail("gq_int4_linear_gather: rank %d of %d is out of range (at most 8 ranks)", rank, nranks);
-        if (!peer_y || !peer_flag) fail("gq_int4_linear_gather: null handle arrays");
-        check_dims("gq_int4_linear_gather", m, k, n_shard * nranks);
+        check_dims("gq_int4_linear_gather", m, k, n_shard * (nranks > 0 ? nranks : 1));
         check_group(group);
         if (m == 0 || n_shard == 0) fail("gq_int4_linear_gather: an empty layer");
+        if (m > 16) fail("gq_int4_linear_gather: at most 16 rows of x (m = %llu)", (unsigned long long)m);
         const uint64_t groups = (k + group - 1) / group;
         auto xp = (const float*)view(ctx, x, x_off, m * k, 4, "gq_int4_linear_gather input");
         auto qp = (const uint32_t*)view(ctx, q, 0, n_shard * words4(k), 4, "gq_int4_linear_gather q");
         auto sp = (const float*)view(ctx, scale, 0, n_shard * groups, 4, "gq_int4_linear_gather scale");
         auto zp = (const float*)view(ctx, zero, 0, n_shard * groups, 4, "gq_int4_linear_gather zero");
         auto bp = bias ? (const float*)view(ctx, bias, b_off, n_shard, 4, "gq_int4_linear_gather bias") : nullptr;
-        PeerOut peer;
-        peer.nranks = (uint32_t)nranks, peer.rank = (uint32_t)rank, peer.n_full = (uint32_t)(n_shard * nranks);
-        for (int i = 0; i < nranks; ++i) {
-            peer.y[i] = (float*)view(ctx, peer_y[i], 0, m * n_shard * nranks, 4, "gq_int4_linear_gather y_full");
-            peer.flag[i] = (uint32_t*)view(ctx, peer_flag[i], 0, nranks + 2, 4, "gq_int4_linear_gather flags");
+        PeerOut peer = peer_views(ctx, "gq_int4_linear_gather", m, n_shard, rank, nranks, peer_recv, state, y_full);
+        if (y_full == x) fail("gq_int4_linear_gather: y_full must not be the input buffer");
+        // more rows of x than one launch takes go in passes, each a gather of its own rows (and a step of its own)
+        const uint64_t per_pass = 4;
+        for (uint64_t r = 0; r < m; r += per_pass) {
+            const uint64_t rows = m - r < per_pass ? m - r : per_pass;
+            peer.row0 = (uint32_t)r;
+            if (!launch_gemv_q4_ring(ctx->stream, ctx->prop.multiProcessorCount, ctx->status_dev, xp + r * k, rows, k, qp, sp, zp, bp, n_shard, group, nullptr,
+                                     r == 0 ? weights_settled(ctx, {q, scale, zero}) : true, false, &peer))
+                fail("gq_int4_linear_gather: the fused kernel takes group_size 128 and in_features 4096 or 8192 (m = %llu, k = %llu, group_size = %llu)",
+                     (unsigned long long)m, (unsigned long long)k, (unsigned long long)group);
+            if (r) ctx->stats.launches++;
         }
-        if (!launch_gemv_q4_ring(ctx->stream, ctx->prop.multiProcessorCount, ctx->status_dev, xp, m, k, qp, sp, zp, bp, n_shard, group, nullptr,
-                                 weights_settled(ctx, {q, scale, zero}), false, &peer))
-            fail("gq_int4_linear_gather: the fused kernel takes up to four rows of x, group_size 128 and in_features 4096 or 8192 (m = %llu, k = %llu, group_size = %llu)",
-                 (unsigned long long)m, (unsigned long long)k, (unsigned long long)group);
-        after_launch(ctx, "gemv_q4_ring_gather", {x, q, scale, zero, bias, peer_y[rank], peer_flag[rank]}, {peer_y[rank], peer_flag[rank]});
+        after_launch(ctx, "gemv_q4_ring_gather", {x, q, scale, zero, bias, peer_recv[rank], state, y_full}, {peer_recv[rank], state, y_full});
     });
 }
 

@@ -73,15 +73,15 @@ struct gq_ctx {
     // host checks it whenever it waits for the stream.
     uint32_t* status_host = nullptr;
     uint32_t* status_dev = nullptr;
-    // lazily created device scratch owned by the context (tensor-core paths)
-    void* scratch = nullptr;
     // What the last operation put on the stream wrote, when that operation was one of this library's kernels whose
     // outputs are known (prev_known): a GEMV that follows may then fetch its weights before that kernel has finished,
     // provided they are none of these buffers.
     bool prev_known = false;
     gq_buf prev_written[4] = {0, 0, 0, 0};
     void* argmax_state = nullptr;  // keys and counters of gq_argmax_rows, zero between calls
-    uint64_t scratch_bytes = 0;
+    // How long a kernel waits for another GPU's data before it gives up and reports through the status word, in SM
+    // clock cycles (gq_set_wait_limit_us).
+    long long peer_wait_cycles = 4000000000ll;
 };
 
 namespace gq {
@@ -140,11 +140,18 @@ void launch_after(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, 
 
 // A checked view of `count` elements of `elem` bytes at element offset `off`.
 void* view(gq_ctx* ctx, gq_buf buf, uint64_t off, uint64_t count, uint64_t elem, const char* what);
+// True when two device ranges share a byte. The linears read x from many CTAs while others already write y (and, in the
+// fused forms, h_out), so an output that overlaps an input would be read half-updated: the entry points refuse it.
+inline bool ranges_overlap(const void* a, uint64_t a_bytes, const void* b, uint64_t b_bytes) {
+    if (!a || !b || !a_bytes || !b_bytes) return false;
+    const char* pa = static_cast<const char*>(a);
+    const char* pb = static_cast<const char*>(b);
+    return pa < pb + b_bytes && pb < pa + a_bytes;
+}
 // Counts a launch, notes buffers for an open capture, honours launch_blocking.
 void after_launch(gq_ctx* ctx, const char* kernel, std::initializer_list<gq_buf> used, std::initializer_list<gq_buf> written = {});
 // True when none of `weights` was written by the operation before this one on the stream (and that operation is known).
 bool weights_settled(const gq_ctx* ctx, std::initializer_list<gq_buf> weights);
-void* ensure_scratch(gq_ctx* ctx, uint64_t bytes);
 
 // ── kernels (each file states which reference shader it replaces) ─────────
 void launch_quantize_q8(cudaStream_t s, const float* w, uint64_t rows, uint64_t k, uint32_t* q, float* scale);
@@ -167,12 +174,16 @@ bool launch_gemv_q4_dp4a(cudaStream_t s, int sm_count, const float* x, uint64_t 
 bool launch_gemv_q8_imma(cudaStream_t s, int sm_count, uint32_t* status, const float* x, uint64_t m, uint64_t k, const uint32_t* q,
                          const float* scale, const float* bias, uint64_t n, float* y, bool weights_settled);
 struct Prologue;
-// Where a column-sharded layer's outputs go when the gather is fused into the GEMV: every rank's y_full (peer-mapped,
-// this rank's own included) and every rank's flag words (one counter per source rank, a step word, a CTA counter).
+// A column-sharded layer's gather: every rank's receive buffer (peer-mapped, this rank's own included) of
+// 2 x m_total x n_full 64-bit words (step << 32 | float bits; the halves alternate by step parity), this rank's plain
+// y_full [m_total][n_full], and this rank's two state words (the step of the last finished call, the CTAs done).
+// A call covers rows [row0, row0 + rows) of y.
 struct PeerOut {
-    float* y[8] = {};
-    uint32_t* flag[8] = {};
-    uint32_t nranks = 0, rank = 0, n_full = 0;
+    unsigned long long* ll[8] = {};
+    float* y_full = nullptr;
+    uint32_t* state = nullptr;
+    uint32_t nranks = 0, rank = 0, n_full = 0, m_total = 0, row0 = 0;
+    long long wait_cycles = 0;
 };
 bool launch_gemv_q8_imma_fused(cudaStream_t s, int sm_count, uint32_t* status, const float* x, uint64_t k, const uint32_t* q,
                                const float* scale, const float* bias, uint64_t n, float* y, int kind, const Prologue& pro, bool weights_settled);
@@ -197,8 +208,7 @@ gq_comm* comm_create(int nranks, int rank, const void* id128);
 void comm_destroy(gq_comm* c);
 void comm_info(gq_comm* c, int* nranks, int* rank);
 void all_gather_columns(cudaStream_t s, gq_comm* c, const float* src, float* dst, uint64_t m, uint64_t n_shard);
-void launch_peer_gather(cudaStream_t s, float* const* y, uint32_t* const* flag, const float* src, uint64_t m, uint64_t n_shard,
-                        int rank, int nranks, uint32_t* status);
+void launch_peer_gather(cudaStream_t s, int sm_count, const PeerOut& peer, const float* src, uint64_t m, uint64_t n_shard, uint32_t* status);
 
 // decode-step operators (decode_ops.cu)
 void launch_embedding(cudaStream_t s, const float* table, const int32_t* ids, uint64_t rows, uint64_t width, uint64_t vocab, float* out);

@@ -9,14 +9,18 @@
 //    row of y inside a group: a rank's receive buffer for row r is row r of
 //    y_full itself, so no transpose is needed. NCCL is loaded with dlopen the
 //    first time a communicator is made; a single-GPU process never needs it.
-//  * gq_peer_gather — this library's own put-and-signal collective over
-//    peer-mapped memory (CUDA IPC): each rank stores its block straight into
-//    every peer's y_full with ordinary peer stores, fences, and bumps a
-//    counter in the peer's flag buffer; then waits — with a bound, reporting
-//    through the context's status word — until every peer's counter has
-//    reached this step. For the <= 230 KB this path moves it is latency, not
-//    bandwidth, that matters, and a store + flag is one NVLink traversal.
-//    No TMA and no multicast is involved: plain st.global to a peer pointer.
+//  * gq_peer_gather — this library's own collective over peer-mapped memory
+//    (CUDA IPC). Each value of y travels as ONE 64-bit word, step << 32 | the
+//    float's bits, stored with a single plain store into every rank's receive
+//    buffer; a receiver knows a word has arrived when its upper half is the
+//    step it is waiting for. There is no fence, no counter and no signal: one
+//    NVLink traversal per value, which for the <= 230 KB this path moves is
+//    what matters. The receiver's wait is bounded and reports through the
+//    context's status word. The buffer has two halves that alternate by step
+//    parity (a rank can be at most one step ahead of the slowest). No TMA and
+//    no multicast is involved. gq_int4_linear_gather speaks the same protocol
+//    from the GEMV's own epilogue (gemv_ring.cu), so the two may be mixed on
+//    one set of buffers.
 #include <dlfcn.h>
 #include <nccl.h>
 
@@ -71,46 +75,49 @@ void nccl_check(ncclResult_t r, const char* what) {
 }
 
 constexpr int kMaxRanks = 8;
-constexpr uint32_t kPeerBlocks = 8;  // CTAs that copy (and signal) per destination rank
-struct PeerArgs {
-    float* y[kMaxRanks];         // every rank's y_full (own included), peer-mapped
-    uint32_t* flag[kMaxRanks];   // every rank's counters, one per source rank
-};
 
-// grid = (blocks_per_peer, nranks): CTA (b, p) copies this rank's block into rank p's y_full, then
-// signals. CTA (0, rank) afterwards waits for the peers' signals.
-__global__ void __launch_bounds__(256) peer_gather_kernel(PeerArgs args, const float* __restrict__ src, uint32_t m, uint32_t n_shard,
-                                                         uint32_t n_full, uint32_t rank, uint32_t nranks, uint32_t* status) {
-    const uint32_t p = blockIdx.y;
-    float* dst = args.y[p] + (size_t)rank * n_shard;
-    const uint32_t total = m * n_shard;
-    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+__device__ __forceinline__ void st_sys_u64(unsigned long long* p, unsigned long long v) {
+    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long ld_sys_u64(const unsigned long long* p) {
+    unsigned long long v;
+    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// Every CTA sends a slice of this rank's block to every rank, then receives a slice of the whole y.
+__global__ void __launch_bounds__(256) peer_gather_kernel(PeerOut peer, const float* __restrict__ src, uint32_t m, uint32_t n_shard,
+                                                         uint32_t* status) {
+    const uint32_t step = *reinterpret_cast<const volatile uint32_t*>(peer.state) + 1u;  // the last CTA to finish writes it: every CTA has read it by then
+    const size_t half = ((size_t)(step & 1u) * peer.m_total + peer.row0) * peer.n_full;
+    const uint32_t tid = blockIdx.x * blockDim.x + threadIdx.x, nthreads = gridDim.x * blockDim.x;
+    for (uint32_t i = tid; i < m * n_shard; i += nthreads) {
         const uint32_t r = i / n_shard, c = i - r * n_shard;
-        dst[(size_t)r * n_full + c] = src[i];
+        const unsigned long long word = ((unsigned long long)step << 32) | __float_as_uint(src[i]);
+        const size_t at = half + (size_t)r * peer.n_full + (size_t)peer.rank * n_shard + c;
+        for (uint32_t pr = 0; pr < peer.nranks; ++pr) st_sys_u64(peer.ll[pr] + at, word);
     }
-    __threadfence_system();  // the stores above are visible system-wide before the signal below
-    __syncthreads();
-    if (threadIdx.x == 0) atomicAdd_system(args.flag[p] + rank, 1u);
-    if (p == rank && blockIdx.x == 0) {
-        // The step number lives in the flag buffer (word nranks), so a captured launch counts on by
-        // itself at every replay. Every source rank signals gridDim.x times per step.
-        uint32_t* step_word = args.flag[rank] + nranks;
-        const uint32_t step = *step_word + 1;
-        __syncthreads();
-        if (threadIdx.x < nranks) {
-            const uint32_t want = step * gridDim.x;
-            volatile uint32_t* f = args.flag[rank] + threadIdx.x;
-            const long long start = clock64();
-            while ((int32_t)(*f - want) < 0) {
-                if (clock64() - start > 4000000000ll) {  // ~2 s: give up, tell the host
-                    atomicCAS(status, 0u, 16u + threadIdx.x);
-                    break;
-                }
+    const unsigned long long* mine = peer.ll[peer.rank] + half;
+    const long long start = clock64();
+    for (uint32_t i = tid; i < m * peer.n_full; i += nthreads) {
+        unsigned long long v;
+        for (;;) {
+            v = ld_sys_u64(mine + i);
+            if ((uint32_t)(v >> 32) == step) break;
+            if (clock64() - start > peer.wait_cycles) {  // give up, tell the host which rank's words never came
+                atomicCAS(status, 0u, kStatusPeerWaitTimedOut + (i % peer.n_full) / n_shard);
+                break;
             }
-            __threadfence_system();
         }
-        __syncthreads();
-        if (threadIdx.x == 0) *step_word = step;
+        peer.y_full[(size_t)peer.row0 * peer.n_full + i] = __uint_as_float((uint32_t)v);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        if (atomicAdd(peer.state + 1, 1u) == gridDim.x - 1) {
+            peer.state[1] = 0;
+            peer.state[0] = step;
+        }
     }
 }
 
@@ -153,13 +160,13 @@ void all_gather_columns(cudaStream_t s, gq_comm* c, const float* src, float* dst
     nccl_check(nccl().GroupEnd(), "ncclGroupEnd");
 }
 
-void launch_peer_gather(cudaStream_t s, float* const* y, uint32_t* const* flag, const float* src, uint64_t m, uint64_t n_shard,
-                        int rank, int nranks, uint32_t* status) {
-    PeerArgs args{};
-    for (int i = 0; i < nranks; ++i) args.y[i] = y[i], args.flag[i] = flag[i];
-    // a fixed CTA count per destination, so that the signals expected per step never depend on the size
-    peer_gather_kernel<<<dim3(kPeerBlocks, nranks), 256, 0, s>>>(args, src, (uint32_t)m, (uint32_t)n_shard, (uint32_t)(n_shard * nranks),
-                                                          (uint32_t)rank, (uint32_t)nranks, status);
+void launch_peer_gather(cudaStream_t s, int sm_count, const PeerOut& peer, const float* src, uint64_t m, uint64_t n_shard, uint32_t* status) {
+    // all CTAs must be resident at once (a CTA waits for words other CTAs of this very launch send): at most one per SM
+    const uint64_t work = m * n_shard * peer.nranks;
+    uint64_t grid = (work + 1023) / 1024;
+    if (grid > (uint64_t)sm_count) grid = sm_count;
+    if (grid < 1) grid = 1;
+    peer_gather_kernel<<<(uint32_t)grid, 256, 0, s>>>(peer, src, (uint32_t)m, (uint32_t)n_shard, status);
 }
 
 }  // namespace gq

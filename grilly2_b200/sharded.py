@@ -6,7 +6,8 @@ parameters are per row / per (row, group)), and the blocks of ``y`` are
 gathered so that every rank holds ``y[m][n]``.
 
 Two gathers are offered: NCCL (``Comm`` + ``all_gather``) and this library's
-own put-and-signal collective over peer-mapped memory (``PeerGather``).
+own collective over peer-mapped memory (``PeerGather``: one 64-bit
+value-and-step word per output, no fence or signal).
 Rendezvous data (the NCCL id, the IPC handles) travels through whatever the
 caller has; ``from_torch_distributed`` helpers use ``torch.distributed``'s
 object collectives, which work on gloo and nccl alike.
@@ -73,69 +74,62 @@ class Comm:
 
 
 class PeerGather:
-    """Put-and-signal gather over CUDA IPC. Holds two ``y_full`` buffers that
-    alternate between steps (a fast rank may already be storing step s + 1
-    while a slow one still reads step s) and one flag buffer."""
+    """This library's own gather over CUDA IPC for a fixed (m, n_full). Holds this rank's receive buffer (two halves that
+    the DEVICE alternates by step parity, so a captured call alternates by itself at every replay), its two state words,
+    and handles to every other rank's receive buffer. ``gather`` and ``linear_gather`` speak the same protocol and may be
+    mixed; every rank must make the same sequence of calls."""
 
     def __init__(self, world: int, rank: int, m: int, n_full: int, exchange) -> None:
         """``exchange(obj) -> list`` returns every rank's ``obj`` in rank order
         (e.g. ``torch.distributed.all_gather_object``)."""
         lib, ctx = _lib.load(), _C.context()
-        self.world, self.rank, self.m, self.n_full, self.step = world, rank, m, n_full, 0
-        self.y = [_C.Tensor.empty((m, n_full), "float32", persistent=True) for _ in range(2)]
-        self.flags = _C.Tensor.from_numpy(np.zeros(world + 1, dtype=np.int32), persistent=True)
-        # the fused linear + gather signals once per rank and step and keeps a CTA counter: flag words of its own
-        self.fused_flags = _C.Tensor.from_numpy(np.zeros(world + 2, dtype=np.int32), persistent=True)
+        self.world, self.rank, self.m, self.n_full = world, rank, m, n_full
+        self.recv = _C.Tensor.from_numpy(np.zeros(2 * m * n_full * 2, dtype=np.int32), persistent=True)  # 64-bit words
+        self.state = _C.Tensor.from_numpy(np.zeros(2, dtype=np.int32), persistent=True)
         _C.synchronize()
-
-        def export(t):
-            buf = ctypes.create_string_buffer(64)
-            check(lib.gq_buffer_ipc_export(ctx, t.storage.handle, buf, 64))
-            return buf.raw
-
-        mine = {"y": [export(t) for t in self.y], "flags": export(self.flags), "fused_flags": export(self.fused_flags)}
-        everyone = exchange(mine)
+        buf = ctypes.create_string_buffer(64)
+        check(lib.gq_buffer_ipc_export(ctx, self.recv.storage.handle, buf, 64))
+        everyone = exchange(buf.raw)
         self._opened = []
 
-        def open_(raw, nbytes):
+        def open_(raw):
             out = ctypes.c_uint64()
-            check(lib.gq_buffer_ipc_open(ctx, ctypes.create_string_buffer(raw, 64), nbytes, ctypes.byref(out)))
+            check(lib.gq_buffer_ipc_open(ctx, ctypes.create_string_buffer(raw, 64), 2 * m * n_full * 8, ctypes.byref(out)))
             self._opened.append(out.value)
             return out.value
 
-        self._y_handles = [[self.y[b].storage.handle if r == rank else open_(everyone[r]["y"][b], m * n_full * 4)
-                            for r in range(world)] for b in range(2)]
-        self._flag_handles = [self.flags.storage.handle if r == rank else open_(everyone[r]["flags"], (world + 1) * 4)
-                              for r in range(world)]
-        self._fused_flag_handles = [self.fused_flags.storage.handle if r == rank else open_(everyone[r]["fused_flags"], (world + 2) * 4)
-                                    for r in range(world)]
+        self._recv_handles = [self.recv.storage.handle if r == rank else open_(everyone[r]) for r in range(world)]
 
-    def gather(self, y_shard: "_C.Tensor") -> "_C.Tensor":
+    def _out(self, out):
+        return out if out is not None else _C.Tensor.empty((self.m, self.n_full), "float32")
+
+    def gather(self, y_shard: "_C.Tensor", out: "_C.Tensor | None" = None) -> "_C.Tensor":
         lib, ctx = _lib.load(), _C.context()
-        self.step += 1
-        b = self.step & 1
         arr = ctypes.c_uint64 * self.world
         m = y_shard.numel() // y_shard.shape[-1]
-        check(lib.gq_peer_gather(ctx, y_shard.storage.handle, m, y_shard.shape[-1], self.rank, self.world,
-                                 arr(*self._y_handles[b]), arr(*self._flag_handles)))
-        return self.y[b]
+        if m != self.m or y_shard.shape[-1] * self.world != self.n_full:
+            raise RuntimeError(f"gather: a block of {m} x {y_shard.shape[-1]} over {self.world} ranks does not fill y_full {self.m} x {self.n_full}")
+        out = self._out(out)
+        check(lib.gq_peer_gather(ctx, y_shard.storage.handle, m, y_shard.shape[-1], self.rank, self.world, arr(*self._recv_handles),
+                                 self.state.storage.handle, out.storage.handle))
+        return out
 
-    def linear_gather(self, weight: "_C.Int4Weight", x: "_C.Tensor", bias: "_C.Tensor | None" = None) -> "_C.Tensor":
-        """This rank's int4 block times x, stored from the GEMV's epilogue into every rank's y_full: one kernel for the
-        linear and the gather (group size 128, in_features 4096 or 8192, up to four rows of x)."""
+    def linear_gather(self, weight: "_C.Int4Weight", x: "_C.Tensor", bias: "_C.Tensor | None" = None,
+                      out: "_C.Tensor | None" = None) -> "_C.Tensor":
+        """This rank's int4 block times x, sent from the GEMV's epilogue to every rank: one kernel for the linear and the
+        gather (group size 128, in_features 4096 or 8192, up to 16 rows of x)."""
         lib, ctx = _lib.load(), _C.context()
-        self.step += 1
-        b = self.step & 1
         arr = ctypes.c_uint64 * self.world
         n_shard, k = weight.shape
         m = x.numel() // k
         if m != self.m or n_shard * self.world != self.n_full:
             raise RuntimeError(f"linear_gather: {m} x {n_shard} x {self.world} ranks does not fill y_full {self.m} x {self.n_full}")
+        out = self._out(out)
         check(lib.gq_int4_linear_gather(ctx, x.storage.handle, x.offset, m, k, weight._qt.storage.handle, weight._scale.storage.handle,
                                         weight._zero.storage.handle, bias.storage.handle if bias is not None else 0,
                                         bias.offset if bias is not None else 0, n_shard, weight._group, self.rank, self.world,
-                                        arr(*self._y_handles[b]), arr(*self._fused_flag_handles)))
-        return self.y[b]
+                                        arr(*self._recv_handles), self.state.storage.handle, out.storage.handle))
+        return out
 
     def close(self) -> None:
         lib, ctx = _lib.load(), _C.context()

@@ -162,7 +162,7 @@ int32_t gq_int8_quantize(gq_ctx* ctx, gq_buf w, uint64_t w_off, uint64_t rows, u
  * y[m][n] = (sum_k x[m][k] * q[n][k]) * scale[n] (+ bias[n]); bias == 0 means none.
  * AUTO: IMMA for one or two rows, the dp4a GEMV for a few more; the
  * tensor-core GEMM for many, when the shape meets its alignment rules
- * (k % 4 == 0, x_off % 4 == 0). */
+ * (k % 4 == 0, x_off % 4 == 0). y must not overlap x (refused). */
 int32_t gq_int8_linear(gq_ctx* ctx, gq_buf x, uint64_t x_off, uint64_t m, uint64_t k, gq_buf q, gq_buf scale,
                        gq_buf bias, uint64_t b_off, uint64_t n, gq_buf y, int32_t kernel);
 
@@ -242,7 +242,9 @@ int32_t gq_attn_decode_rope(gq_ctx* ctx, gq_buf qkv, gq_buf cos, gq_buf sin, gq_
  *                        — gq_add_rms_norm then gq_int8_linear.
  * gq_int8_linear_swiglu: y = W . (silu(gate_up[0:k]) * gate_up[k:2k]) + bias — gq_swiglu then gq_int8_linear, with the
  *                        hardware's exp2 and reciprocal (about 1e-6 relative to the separate operators).
- * k = in_features of the layer, a multiple of 4; x, residual, w, h_out and gate_up at offset 0. */
+ * k = in_features of the layer, a multiple of 4; x, residual, w, h_out and gate_up at offset 0. Outputs must not overlap
+ * inputs: h_out may not be x or residual (every CTA reads them for the row's norm while one stores h_out; gq_add_rms_norm is
+ * the in-place form), y may not overlap any input. Refused with GQ_ERR. */
 int32_t gq_int8_linear_norm(gq_ctx* ctx, gq_buf x, gq_buf residual, gq_buf norm_weight, float eps, gq_buf h_out, uint64_t k, gq_buf q,
                             gq_buf scale, gq_buf bias, uint64_t b_off, uint64_t n, gq_buf y);
 int32_t gq_int8_linear_swiglu(gq_ctx* ctx, gq_buf gate_up, uint64_t k, gq_buf q, gq_buf scale, gq_buf bias, uint64_t b_off, uint64_t n,
@@ -285,24 +287,32 @@ int32_t gq_all_gather_columns(gq_ctx* ctx, gq_comm* comm, gq_buf src, gq_buf dst
 int32_t gq_buffer_ipc_export(gq_ctx* ctx, gq_buf buf, void* out, uint64_t bytes);
 int32_t gq_buffer_ipc_open(gq_ctx* ctx, const void* handle, uint64_t buffer_bytes, gq_buf* out);
 
-/* This library's own gather over NVLink: every rank stores its block into each rank's y_full
- * (peer_y[i] = a handle to rank i's y_full: its own buffer for i == rank, an ipc-opened one otherwise),
- * then signals a counter in peer_flag[i] (nranks + 1 uint32 each — one counter per source rank and this
- * rank's step number — zeroed once before the first call) and waits, at most ~2 s, for every peer's
- * signal of this step. Every rank must make the same sequence of calls; the step number is kept on the
- * device, so a captured call keeps counting when replayed. The caller alternates two y_full buffers
- * between calls (a fast rank may store the next step while a slow one still reads this one). A wait
- * that gives up is reported by the next host wait (GQ_ERR). */
+/* This library's own gather over NVLink. Every value of y travels as ONE 64-bit word, step << 32 | the
+ * float's bits, written with a single plain store into every rank's RECEIVE buffer (peer_recv[i] = a handle to
+ * rank i's receive buffer: its own for i == rank, an ipc-opened one otherwise; GQ_PEER_RECV_BYTES(m, n_full)
+ * bytes, zeroed once before the first call). A word whose upper half is the current step has arrived: no
+ * fence, counter or signal is involved. The kernel then waits, at most the context's wait limit
+ * (gq_set_wait_limit_us, default ~2 s), for all words of this step and writes this rank's plain
+ * y_full[m][n_full] (a local buffer). `state` is two uint32 words of this rank, zeroed once: the step number
+ * lives on the device, so a captured call keeps counting when replayed. The receive buffer has two halves that
+ * the device alternates by step parity, which is all the protection needed: a rank can be at most one step
+ * ahead of the slowest. Every rank must make the same sequence of calls on one set of buffers. A wait that
+ * gives up is reported by the next host wait (GQ_ERR naming the rank whose words never came); the context
+ * stays usable. */
+#define GQ_PEER_RECV_BYTES(m, n_full) (2ull * (uint64_t)(m) * (uint64_t)(n_full) * 8ull)
 int32_t gq_peer_gather(gq_ctx* ctx, gq_buf src, uint64_t m, uint64_t n_shard, int32_t rank, int32_t nranks,
-                       const gq_buf* peer_y, const gq_buf* peer_flag);
-/* gq_int4_linear and the gather in ONE kernel: this rank's block of columns is stored from the GEMV's epilogue straight into every
- * rank's y_full (plain peer stores), the grid's last CTA then signals every rank and waits (bounded, ~2 s, reported through the
- * context's status) until every rank has signalled this step. peer_y / peer_flag as for gq_peer_gather, except that the flag
- * buffers hold nranks + 2 words and one signal per rank and step, so a flag buffer serves one of the two collectives only.
- * Shapes: the ring kernel's (group_size 128, in_features 4096 or 8192, up to four rows of x). */
+                       const gq_buf* peer_recv, gq_buf state, gq_buf y_full);
+/* gq_int4_linear and the gather in ONE kernel: the GEMV's epilogue sends this rank's block of columns straight to every
+ * rank's receive buffer (plain peer stores of value-and-step words, as above) and the CTAs then share out the receiving of the
+ * whole y into y_full. Same buffers and protocol as gq_peer_gather, so calls of both kinds may be mixed on one set.
+ * Shapes: the ring kernel's (group_size 128, in_features 4096 or 8192); up to 16 rows of x, four per pass. */
 int32_t gq_int4_linear_gather(gq_ctx* ctx, gq_buf x, uint64_t x_off, uint64_t m, uint64_t k, gq_buf q, gq_buf scale, gq_buf zero, gq_buf bias,
-                              uint64_t b_off, uint64_t n_shard, uint64_t group, int32_t rank, int32_t nranks, const gq_buf* peer_y,
-                              const gq_buf* peer_flag);
+                              uint64_t b_off, uint64_t n_shard, uint64_t group, int32_t rank, int32_t nranks, const gq_buf* peer_recv,
+                              gq_buf state, gq_buf y_full);
+/* How long a kernel waits for another GPU's data before it gives up (0 restores the default, ~2 s). Failure
+ * detection in the reference's convention: misuse and failure are reported, never thrown
+ * (crates/grilly-sys/tests/gpu.rs:272-329); the reference itself has no multi-GPU wait. */
+int32_t gq_set_wait_limit_us(gq_ctx* ctx, uint64_t microseconds);
 
 #if defined(GQ_BUILD) && defined(__GNUC__)
 #pragma GCC visibility pop

@@ -61,7 +61,7 @@ def main() -> None:
             return out
 
         peers = PeerGather(world, rank, 3, n, exchange)
-        for step in range(3):  # several steps: the flag counters and the two buffers must keep working
+        for step in range(3):  # several steps: the step word and the two halves of the receive buffer must keep working
             xs = (x * (step + 1)).astype(np.float32)
             ref = oracle.linear_q4(xs, qf, sf, zf, b, k, group)
             y_shard = layer.local(_C.Tensor.from_numpy(xs))
@@ -71,21 +71,53 @@ def main() -> None:
             assert np.array_equal(got2, got), "peer gather differs from the nccl gather"
             dist.barrier()
         peers.close()
-        # the linear and the gather in one kernel (the ring kernel's shapes), against the oracle on the whole weight
-        k2, per = 4096, 80  # 80 features per rank: five 16-row blocks
+        # the linear and the gather in one kernel (the ring kernel's shapes), against the oracle on the whole weight;
+        # m = 3 is one pass, m = 8 and m = 16 are passes of four rows
+        k2, per = 4096, 80  # 80 features per rank: five blocks of 16 rows
         w2 = (rng.standard_normal((per * world, k2)) * 0.015).astype(np.float32)
         b2 = rng.standard_normal(per * world).astype(np.float32)
-        x2 = rng.standard_normal((3, k2)).astype(np.float32)
         q2, s2, z2 = oracle.quantize_q4(w2, group)
         layer2 = ShardedLinear.from_full(w2, b2, world, rank, bits=4, group_size=group)
-        peers2 = PeerGather(world, rank, 3, per * world, exchange)
-        for step in range(4):
-            xs = (x2 * (step + 1)).astype(np.float32)
-            ref = oracle.linear_q4(xs, q2, s2, z2, b2, k2, group)
-            got = peers2.linear_gather(layer2.q, _C.Tensor.from_numpy(xs), layer2.bias).numpy()
-            assert np.abs(got - ref).max() / np.abs(ref).max() <= 1e-5, f"fused linear + gather, step {step}"
-            dist.barrier()
-        peers2.close()
+        for m2 in (3, 8, 16):
+            x2 = rng.standard_normal((m2, k2)).astype(np.float32)
+            peers2 = PeerGather(world, rank, m2, per * world, exchange)
+            for step in range(4):
+                xs = (x2 * (step + 1)).astype(np.float32)
+                ref = oracle.linear_q4(xs, q2, s2, z2, b2, k2, group)
+                got = peers2.linear_gather(layer2.q, _C.Tensor.from_numpy(xs), layer2.bias).numpy()
+                assert np.abs(got - ref).max() / np.abs(ref).max() <= 1e-5, f"fused linear + gather, m = {m2}, step {step}"
+                if step == 1:  # the separate gather on the same buffers, in between: one protocol
+                    sep = peers2.gather(layer2.q.linear(_C.Tensor.from_numpy(xs), layer2.bias)).numpy()
+                    assert np.array_equal(sep, got), "separate gather differs from the fused one"
+                dist.barrier()
+            peers2.close()
+        # A captured graph holding ONE gather, replayed many times with a different x each time and no host wait in
+        # between: the device alternates the halves of the receive buffer by itself, so a rank that runs ahead never
+        # overwrites what a slower one still has to read. Every step's result is kept and checked at the end.
+        steps, m3 = 24, 2
+        xs_all = rng.standard_normal((steps, m3, k2)).astype(np.float32)
+        xs_dev = _C.Tensor.from_numpy(xs_all)
+        x_in = _C.Tensor.empty((m3, k2), "float32", persistent=True)
+        hist = _C.Tensor.empty((steps, m3, per * world), "float32", persistent=True)
+        peers3 = PeerGather(world, rank, m3, per * world, exchange)
+        x_in.copy_(xs_dev.narrow_rows(0, 1).reshape((m3, k2)))
+        peers3.linear_gather(layer2.q, x_in, layer2.bias)  # eager once
+        _C.begin_capture()
+        y_cap = peers3.linear_gather(layer2.q, x_in, layer2.bias)
+        graph = _C.end_capture()
+        _C.synchronize()
+        dist.barrier()
+        for i in range(steps):
+            x_in.copy_(xs_dev.narrow_rows(i, 1).reshape((m3, k2)))
+            graph.replay()
+            hist.narrow_rows(i, 1).reshape((m3, per * world)).copy_(y_cap)
+        got_all = hist.numpy()
+        for i in range(steps):
+            ref = oracle.linear_q4(xs_all[i], q2, s2, z2, b2, k2, group)
+            assert np.abs(got_all[i] - ref).max() / np.abs(ref).max() <= 1e-5, f"replayed gather, step {i}"
+        del graph
+        dist.barrier()
+        peers3.close()
         comm.close()
     dist.barrier()
     print(f"OK {rank}", flush=True)

@@ -13,7 +13,11 @@ What it pins, and with what:
   tests use as their oracle (tests/python/test_quantization.py:38-43 and
   :172-190), evaluated by torch here, on the shape list and edge cases of
   crates/grilly-infer/tests/quant.rs:62-83 (an all-zero row; a row whose
-  extremes land on +-127.5 and a tie at 0.5).
+  extremes land on +-127.5 and a tie at 0.5), with the inputs drawn by that
+  test's own seeded xorshift generator and seeds (quant.rs:27-37, seed
+  n * 1000 + k, range [-3, 3]): the vectors the reference's test holds. The
+  reference's host `reference()` (quant.rs:40-53), restated in numpy float32,
+  is evaluated beside the torch formula and must agree bit for bit.
 
 The arrays are stored with their inputs, so the tests need neither the
 reference nor torch.
@@ -61,8 +65,21 @@ def int4_formula(w, group):
     return levels.reshape(rows, -1)[:, :k].to(torch.uint8).numpy(), scale.numpy(), zero.numpy()
 
 
+def int8_host_reference(w):
+    """The reference's own host check, crates/grilly-infer/tests/quant.rs:40-53 (`reference`), statement for statement in
+    numpy float32: amax by fold of |v|, scale = max(amax / 127.5, eps), inv = 1 / scale, q = clamp(round_ties_even(v * inv))."""
+    f32 = np.float32
+    amax = np.abs(w).max(axis=1).astype(f32)
+    scale = np.maximum(amax / f32(127.5), np.finfo(f32).eps).astype(f32)
+    inv = (f32(1.0) / scale).astype(f32)
+    q = np.clip(np.rint((w * inv[:, None]).astype(f32)), -128.0, 127.0).astype(np.int8)
+    return q, scale
+
+
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) != 2:
+        sys.exit("usage: python tests/golden/make_golden.py /path/to/the/reference/checkout")
+    ref = sys.argv[1]
     gptq = load_gptq(ref)
 
     out = {}
@@ -91,6 +108,8 @@ def main():
             if k > 2:
                 w[2, 2] = 0.01
         q, scale, deq = int8_formula(w)
+        q_host, scale_host = int8_host_reference(w)  # two independent statements of the reference's check must agree
+        assert np.array_equal(q, q_host) and np.array_equal(scale.view(np.uint32), scale_host.view(np.uint32)), (n, k)
         out.update({f"w{i}": w, f"q{i}": q, f"scale{i}": scale, f"deq{i}": deq})
     out["count"] = np.int64(len(shapes))
     np.savez_compressed(os.path.join(HERE, "int8_formula.npz"), **out)

@@ -2,15 +2,27 @@
 the float64 numpy model (oracle/llama_ref.py), mirroring
 tests/python/test_generation.py:46-70 and test_fused_ops.py of the reference.
 
-Tolerance: |logits - ref| <= 1e-4 * max|ref| (float32 accumulation through 24
-layers against float64; the reference holds its own float32 model to 1e-5 *
-max|logit| against another float32 implementation), greedy tokens identical,
-and a graph replay equal to the eager step bit for bit.
+Tolerance: |logits - ref| <= TOL * max|ref| against float64, with TOL the
+reference's own 1e-5 (tests/python/test_generation.py:53,58 holds its float32
+model to that against another float32 implementation) on the path made of the
+separate operators, and TOL_FUSED on the path whose SwiGLU runs inside the
+GEMV's prologue with the hardware exp2 / reciprocal. Each test prints the worst
+ratio it saw, so the margin is on record. Greedy tokens identical, and a graph
+replay equal to the eager step bit for bit.
 """
 import numpy as np
 import pytest
 
 pytestmark = pytest.mark.gpu
+
+TOL = 1e-5        # the separate operators: the reference's own bound
+TOL_FUSED = 1e-5  # norm, SwiGLU and rotary fused into their neighbours
+
+
+def worst(got, want, what):
+    ratio = float(np.abs(got - want).max() / np.abs(want).max())
+    print(f"[decode parity] {what}: max|logit - ref| / max|ref| = {ratio:.3e}")
+    return ratio
 
 
 def small_config():
@@ -48,7 +60,7 @@ def test_decode_steps_match_the_float64_model(prefill, fused):
         logits, nxt = model.step(_C.Tensor.from_numpy(np.array([token], dtype=np.int32)))
         want = ref.step(token)
         got = logits.numpy()[0]
-        assert np.abs(got - want).max() <= 1e-4 * np.abs(want).max(), f"step {step}"
+        assert worst(got, want, f"small model, prefill {prefill}, fused {fused}, step {step}") <= (TOL_FUSED if fused else TOL), f"step {step}"
         assert int(nxt.numpy()[0]) == int(np.argmax(want))
         assert (model.cache.lengths() == prefill + step + 1).all()
         token = int(nxt.numpy()[0])
@@ -85,15 +97,16 @@ def test_captured_step_replays_like_the_eager_one():
     assert (fast_model.cache.lengths() == 10 + len(tokens)).all()
 
 
-def test_full_size_config5_step():
+@pytest.mark.parametrize("fused", [True, False], ids=["fused", "separate"])
+def test_full_size_config5_step(fused):
     """Qwen2.5-0.5B architecture, cache pre-filled to 1023 positions, one step at position 1023."""
     from grilly2_b200 import _C
     from grilly2_b200.infer import llama
     cfg = llama.qwen25_05b(1024)
-    model, ref = build(cfg, 4, 1023)
+    model, ref = build(cfg, 4, 1023, fused)
     logits, nxt = model.step(_C.Tensor.from_numpy(np.array([12345], dtype=np.int32)))
     want = ref.step(12345)
     got = logits.numpy()[0]
-    assert np.abs(got - want).max() <= 1e-4 * np.abs(want).max()
+    assert worst(got, want, f"config 5, fused {fused}") <= (TOL_FUSED if fused else TOL)
     assert int(nxt.numpy()[0]) == int(np.argmax(want))
     assert (model.cache.lengths() == 1024).all()

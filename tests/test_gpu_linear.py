@@ -175,7 +175,7 @@ def test_benchmark_configs_full_size(g, config):
         ref = oracle.linear_q8(x, q, scale, None, 896)
         ms = [1]
     else:
-        n, k, sigma, seed, ms = (14336, 4096, 0.02, 1, [1, 4, 16]) if config == "c2" else (28672, 8192, 0.015, 2, [1, 8])
+        n, k, sigma, seed, ms = (14336, 4096, 0.02, 1, [1, 4, 16]) if config == "c2" else (28672, 8192, 0.015, 2, [1, 8, 16])
         rng = np.random.default_rng(seed)
         x = rng.standard_normal((max(ms), k)).astype(np.float32)
         w = (rng.standard_normal((n, k)) * sigma).astype(np.float32)
@@ -230,3 +230,33 @@ def test_dp4a_digit_planes_on_hard_inputs(g):
     for bad in (np.inf, np.nan):
         xbad[0, 5] = bad
         assert np.isnan(w4.linear(_C.Tensor.from_numpy(xbad), None, _lib.KERNEL_RING).numpy()).all()
+
+
+def test_outputs_that_overlap_inputs_are_refused(g):
+    """Many CTAs read x while others already write y (and, in the fused norm, h_out): an output that shares memory with
+    an input is reported, not computed."""
+    import ctypes
+    from grilly2_b200 import _C, _lib
+    lib, ctx = _lib.load(), _C.context()
+    rng = np.random.default_rng(2)
+    k = n = 64
+    w = rng.standard_normal((n, k)).astype(np.float32)
+    w8 = _C.Int8Weight.quantize(_C.Tensor.from_numpy(w))
+    w4 = _C.Int4Weight.quantize(_C.Tensor.from_numpy(w), 32)
+    x = _C.Tensor.from_numpy(rng.standard_normal((1, k)).astype(np.float32))
+    res = _C.Tensor.from_numpy(rng.standard_normal((1, k)).astype(np.float32))
+    nw = _C.Tensor.from_numpy(np.ones(k, dtype=np.float32))
+    y = _C.Tensor.empty((1, n), "float32")
+    hx, hq, hs = x.storage.handle, w8._qt.storage.handle, w8._scale.storage.handle
+    assert lib.gq_int8_linear(ctx, hx, 0, 1, k, hq, hs, 0, 0, n, hx, 0) == _lib.GQ_ERR and "overlap" in _lib.last_error()
+    assert lib.gq_int4_linear(ctx, hx, 0, 1, k, w4._qt.storage.handle, w4._scale.storage.handle, w4._zero.storage.handle, 0, 0, n, 32, hx, 0) == _lib.GQ_ERR
+    assert "overlap" in _lib.last_error()
+    for h_out in (hx, res.storage.handle):  # the residual stream updated in place
+        rc = lib.gq_int8_linear_norm(ctx, hx, res.storage.handle, nw.storage.handle, 1e-6, h_out, k, hq, hs, 0, 0, n, y.storage.handle)
+        assert rc == _lib.GQ_ERR and "h_out must not overlap" in _lib.last_error()
+    rc = lib.gq_int8_linear_norm(ctx, hx, res.storage.handle, nw.storage.handle, 1e-6, 0, k, hq, hs, 0, 0, n, hx)
+    assert rc == _lib.GQ_ERR and "output must not overlap" in _lib.last_error()
+    # a separate h_out is fine
+    h = _C.Tensor.empty((1, k), "float32")
+    _lib.check(lib.gq_int8_linear_norm(ctx, hx, res.storage.handle, nw.storage.handle, 1e-6, h.storage.handle, k, hq, hs, 0, 0, n, y.storage.handle))
+    np.testing.assert_array_equal(h.numpy(), x.numpy() + res.numpy())

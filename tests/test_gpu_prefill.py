@@ -58,10 +58,10 @@ def test_prefill_refuses_shapes_it_cannot_map(g):
     assert t._q.linear(x._t, None).numpy().shape == ref.shape
 
 
-@pytest.mark.parametrize("m", [256, 2048])
+@pytest.mark.parametrize("m", [256, 2048, 8192])
 def test_prefill_benchmark_shape(g, m):
     """Config 4: x [m, 4096], W [14336, 4096]. m = 256 is compared outright; at
-    m = 2048 a sample of rows is (rows of x are independent), plus the
+    m = 2048 and m = 8192 a sample of rows is (rows of x are independent), plus the
     replay-equals-eager property."""
     from grilly2_b200.infer.quantization import Int8Tensor
     rng = np.random.default_rng(3)

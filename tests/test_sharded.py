@@ -46,7 +46,7 @@ def test_sharded_linear_over_two_gpus():
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("m,n,k", [(1, 80, 4096), (3, 333, 4096), (2, 48, 8192), (4, 5, 4096)])
+@pytest.mark.parametrize("m,n,k", [(1, 80, 4096), (3, 333, 4096), (2, 48, 8192), (4, 5, 4096), (9, 100, 4096), (16, 37, 8192)])
 def test_fused_linear_gather_with_a_single_rank_equals_the_linear(m, n, k):
     """World size 1 (the only peer is the rank itself): gq_int4_linear_gather must equal gq_int4_linear, step after step."""
     import numpy as np
@@ -62,3 +62,49 @@ def test_fused_linear_gather_with_a_single_rank_equals_the_linear(m, n, k):
         got = peers.linear_gather(w, x, bias).numpy()
         np.testing.assert_array_equal(got, want)
     peers.close()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("fused", [False, True], ids=["gather", "linear_gather"])
+def test_a_gather_whose_peer_never_sends_gives_up_and_reports_the_rank(fused):
+    """Failure detection without a fault: two "ranks" whose receive buffers both live in this process, and nobody
+    plays rank 1. With the wait limit at 20 ms the kernel returns, the next host wait is GQ_ERR naming rank 1, the
+    status clears, and an ordinary linear on the same context then answers correctly."""
+    import ctypes
+
+    import numpy as np
+
+    import oracle
+    from grilly2_b200 import _C, _lib
+    lib, ctx = _lib.load(), _C.context()
+    rng = np.random.default_rng(5)
+    m, n_shard, k = 2, 48, 4096
+    w = (rng.standard_normal((n_shard, k)) * 0.02).astype(np.float32)
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    wt = _C.Int4Weight.quantize(_C.Tensor.from_numpy(w), 128)
+    xt = _C.Tensor.from_numpy(x)
+    recv = [_C.Tensor.from_numpy(np.zeros(2 * m * 2 * n_shard * 2, dtype=np.int32), persistent=True) for _ in range(2)]
+    state = _C.Tensor.from_numpy(np.zeros(2, dtype=np.int32), persistent=True)
+    y_full = _C.Tensor.empty((m, 2 * n_shard), "float32")
+    handles = (ctypes.c_uint64 * 2)(recv[0].storage.handle, recv[1].storage.handle)
+    _C.synchronize()
+    _lib.check(lib.gq_set_wait_limit_us(ctx, 20000))
+    try:
+        if fused:
+            _lib.check(lib.gq_int4_linear_gather(ctx, xt.storage.handle, 0, m, k, wt._qt.storage.handle, wt._scale.storage.handle,
+                                                 wt._zero.storage.handle, 0, 0, n_shard, 128, 0, 2, handles, state.storage.handle,
+                                                 y_full.storage.handle))
+        else:
+            y = wt.linear(xt)
+            _lib.check(lib.gq_peer_gather(ctx, y.storage.handle, m, n_shard, 0, 2, handles, state.storage.handle, y_full.storage.handle))
+        assert lib.gq_synchronize(ctx) == _lib.GQ_ERR
+        assert "rank 1" in _lib.last_error() and "17" in _lib.last_error()
+        assert lib.gq_synchronize(ctx) == _lib.GQ_OK  # reported once; the context stays usable
+    finally:
+        _lib.check(lib.gq_set_wait_limit_us(ctx, 0))
+    # this rank's own half did arrive
+    q, sc, z = oracle.quantize_q4(w, 128)
+    ref = oracle.linear_q4(x, q, sc, z, None, k, 128)
+    got = y_full.numpy()[:, :n_shard]
+    assert np.abs(got - ref).max() / np.abs(ref).max() <= 1e-5
+    assert np.abs(wt.linear(xt).numpy() - ref).max() / np.abs(ref).max() <= 1e-5
