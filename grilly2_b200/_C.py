@@ -215,6 +215,30 @@ class Int8Weight:
         return Int8Weight(q, scale, (n, k))
 
     @staticmethod
+    def quantize_fused(weights) -> "Int8Weight":
+        """The float32 parts of a fused projection (same in_features), quantized straight into ONE weight at their row
+        offsets: equal bit for bit to ``cat`` of the parts quantized apart, without ever holding the parts twice."""
+        weights = list(weights)
+        if not weights:
+            raise RuntimeError("Int8Weight::quantize_fused: no weights")
+        for w in weights:
+            _require(w, F32, "int8 weight-only quantization")
+            if len(w.shape) != 2:
+                raise RuntimeError(f"expected a 2-D weight (out_features, in_features), got {list(w.shape)}")
+        k = weights[0].shape[1]
+        if k == 0 or any(w.shape[1] != k for w in weights):
+            raise RuntimeError(f"Int8Weight::quantize_fused: in_features differ or are zero ({[w.shape[1] for w in weights]})")
+        n = sum(w.shape[0] for w in weights)
+        q = Tensor.empty((n, _words8(k)), I32, persistent=True)
+        scale = Tensor.empty((n,), F32, persistent=True)
+        row = 0
+        for w in weights:
+            check(_l().gq_int8_quantize_rows(context(), w.storage.handle, w.offset, w.shape[0], k, q.storage.handle, scale.storage.handle,
+                                             row, n))
+            row += w.shape[0]
+        return Int8Weight(q, scale, (n, k))
+
+    @staticmethod
     def cat(parts) -> "Int8Weight":
         parts = list(parts)
         if not parts:
@@ -353,6 +377,31 @@ class Int4Weight:
             return out
 
         return Int4Weight(held(q, I32), held(scale, F32), held(zero, F32), (n, in_features), group_size)
+
+    @staticmethod
+    def quantize_fused(weights, group_size: int) -> "Int4Weight":
+        """As Int8Weight.quantize_fused: the parts quantized straight into one weight at their row offsets."""
+        weights = list(weights)
+        if not weights:
+            raise RuntimeError("Int4Weight::quantize_fused: no weights")
+        Int4Weight._check_group(group_size)
+        for w in weights:
+            _require(w, F32, "int4 weight-only quantization")
+            if len(w.shape) != 2:
+                raise RuntimeError(f"expected a 2-D weight (out_features, in_features), got {list(w.shape)}")
+        k = weights[0].shape[1]
+        if k == 0 or any(w.shape[1] != k for w in weights):
+            raise RuntimeError(f"Int4Weight::quantize_fused: in_features differ or are zero ({[w.shape[1] for w in weights]})")
+        n, groups = sum(w.shape[0] for w in weights), -(-k // group_size)
+        q = Tensor.empty((n, _words4(k)), I32, persistent=True)
+        scale = Tensor.empty((n, groups), F32, persistent=True)
+        zero = Tensor.empty((n, groups), F32, persistent=True)
+        row = 0
+        for w in weights:
+            check(_l().gq_int4_quantize_rows(context(), w.storage.handle, w.offset, w.shape[0], k, group_size, q.storage.handle,
+                                             scale.storage.handle, zero.storage.handle, row, n))
+            row += w.shape[0]
+        return Int4Weight(q, scale, zero, (n, k), group_size)
 
     @staticmethod
     def cat(parts) -> "Int4Weight":

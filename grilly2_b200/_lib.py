@@ -55,6 +55,8 @@ PROTOTYPES = {
     "gq_stats_get": [vp, P(Stats)],
     "gq_persistent_peak_reset": [vp],
     "gq_int8_quantize": [vp, u64, u64, u64, u64, u64, u64],
+    "gq_int8_quantize_rows": [vp, u64, u64, u64, u64, u64, u64, u64, u64],
+    "gq_int4_quantize_rows": [vp, u64, u64, u64, u64, u64, u64, u64, u64, u64, u64],
     "gq_int8_linear": [vp, u64, u64, u64, u64, u64, u64, u64, u64, u64, u64, i32],
     "gq_int8_dequantize": [vp, u64, u64, u64, u64, u64],
     "gq_int4_quantize": [vp, u64, u64, u64, u64, u64, u64, u64, u64],
@@ -77,6 +79,7 @@ PROTOTYPES = {
     "gq_int8_linear_swiglu": [vp, u64, u64, u64, u64, u64, u64, u64, u64],
     "gq_swiglu": [vp, u64, u64, u64, u64],
     "gq_argmax_rows": [vp, u64, u64, u64, u64],
+    "gq_sample": [vp, u64, u64, u64, u64, u64, u64, u32, u32, ctypes.c_double, u64, ctypes.c_double, ctypes.c_double, u64, u64, u64, u64, u64, u64],
     "gq_comm_unique_id": [vp, u64],
     "gq_comm_create": [vp, i32, i32, vp, P(vp)],
     "gq_all_gather_columns": [vp, vp, u64, u64, u64, u64],

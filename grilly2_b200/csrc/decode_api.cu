@@ -154,6 +154,37 @@ int32_t gq_argmax_rows(gq_ctx* ctx, gq_buf v, uint64_t rows, uint64_t n, gq_buf 
     });
 }
 
+int32_t gq_sample(gq_ctx* ctx, gq_buf logits, uint64_t rows, uint64_t vocab, gq_buf history, uint64_t hist_cap, gq_buf hist_len, uint32_t append,
+                  uint32_t do_sample, double temperature, uint64_t top_k, double top_p, double repetition_penalty, gq_buf uniforms,
+                  uint64_t uniform_rows, gq_buf draws, gq_buf scratch, gq_buf tokens, gq_buf probs) {
+    return guarded([&] {
+        Locked l(ctx);
+        check_dims("gq_sample", rows, vocab, hist_cap);
+        if (vocab == 0) fail("gq_sample: expected (batch, vocab) with vocab > 0");
+        // Hugging Face's checks, with its messages (crates/grilly-infer/src/sampling.rs:70-96)
+        if (!(repetition_penalty > 0.0)) fail("`penalty` has to be a strictly positive float, but is %g", repetition_penalty);
+        if (do_sample) {
+            if (!(temperature > 0.0))
+                fail("`temperature` (=%g) has to be a strictly positive float, otherwise your next token scores will be invalid. If you're "
+                     "looking for greedy decoding strategies, set `do_sample=False`.", temperature);
+            if (!(top_p >= 0.0 && top_p <= 1.0)) fail("`top_p` has to be a float > 0 and < 1, but is %g", top_p);
+        }
+        auto lp = (const float*)view(ctx, logits, 0, rows * vocab, 4, "gq_sample logits");
+        auto hp = history ? (int32_t*)view(ctx, history, 0, rows * hist_cap, 4, "gq_sample history") : nullptr;
+        auto hl = history ? (uint32_t*)view(ctx, hist_len, 0, 1, 4, "gq_sample history length") : nullptr;
+        auto up = do_sample ? (const float*)view(ctx, uniforms, 0, uniform_rows * rows, 4, "gq_sample uniforms") : nullptr;
+        if (do_sample && uniform_rows == 0) fail("gq_sample: sampling needs at least one row of uniform numbers");
+        auto dp = (uint32_t*)view(ctx, draws, 0, 1, 4, "gq_sample draw counter");
+        auto sp = (float*)view(ctx, scratch, 0, 2 * rows * vocab, 4, "gq_sample scratch");
+        auto tp = (int32_t*)view(ctx, tokens, 0, rows, 4, "gq_sample tokens");
+        auto pp = probs ? (float*)view(ctx, probs, 0, rows * vocab, 4, "gq_sample probabilities") : nullptr;
+        if (rows == 0) return;
+        launch_sample(ctx->stream, lp, rows, vocab, hp, hist_cap, hl, do_sample != 0, (float)temperature, top_k, (float)(1.0 - top_p),
+                      (float)repetition_penalty, up, uniform_rows, dp, sp, sp + rows * vocab, tp, pp, append != 0, ctx->sample_state);
+        after_launch(ctx, "sample", {logits, history, hist_len, uniforms, draws, scratch, tokens, probs}, {});
+    });
+}
+
 int32_t gq_int8_linear_norm(gq_ctx* ctx, gq_buf x, gq_buf residual, gq_buf norm_weight, float eps, gq_buf h_out, uint64_t k, gq_buf q,
                             gq_buf scale, gq_buf bias, uint64_t b_off, uint64_t n, gq_buf y) {
     return guarded([&] {

@@ -109,6 +109,24 @@ bool weights_settled(const gq_ctx* ctx, std::initializer_list<gq_buf> weights) {
     return true;
 }
 
+void* context_scratch(gq_ctx* ctx, uint64_t bytes) {
+    if (ctx->scratch_bytes >= bytes) return ctx->scratch;
+    if (ctx->capturing)
+        fail("the context's scratch would have to grow to %llu bytes inside a capture: run the step once eagerly first "
+             "(the reference records on the second sighting of a shape for the same reason, python/grilly/_graph.py:100-163)",
+             (unsigned long long)bytes);
+    uint64_t cap = 1ull << 20;
+    while (cap < bytes) cap <<= 1;
+    void* p = nullptr;
+    GQ_CUDA(cudaMalloc(&p, cap));
+    GQ_CUDA(cudaMemsetAsync(p, 0, cap, ctx->stream));
+    if (ctx->scratch) ctx->retired_scratch.push_back(ctx->scratch);  // launches already on the stream, and graphs, may still name it
+    ctx->scratch = p, ctx->scratch_bytes = cap;
+    ctx->stats.buffer_allocations++;
+    ctx->prev_known = false;
+    return p;
+}
+
 static void host_wait(gq_ctx* ctx) {
     auto t0 = std::chrono::steady_clock::now();
     cudaError_t e = cudaStreamSynchronize(ctx->stream);
@@ -168,6 +186,8 @@ int32_t gq_create(int32_t device, gq_ctx** out) {
             GQ_CUDA(cudaHostGetDevicePointer((void**)&ctx->status_dev, ctx->status_host, 0));
             GQ_CUDA(cudaMalloc(&ctx->argmax_state, argmax_state_bytes()));
             GQ_CUDA(cudaMemset(ctx->argmax_state, 0, argmax_state_bytes()));
+            GQ_CUDA(cudaMalloc(&ctx->sample_state, sample_state_bytes()));
+            GQ_CUDA(cudaMemset(ctx->sample_state, 0, sample_state_bytes()));
             const char* lb = getenv("GQ_LAUNCH_BLOCKING");
             ctx->launch_blocking = lb && lb[0] == '1';
         } catch (...) {
@@ -191,6 +211,9 @@ void gq_destroy(gq_ctx* ctx) {
             }
             for (auto& kv : ctx->pool) cudaFree(kv.second);
             if (ctx->argmax_state) cudaFree(ctx->argmax_state);
+            if (ctx->sample_state) cudaFree(ctx->sample_state);
+            if (ctx->scratch) cudaFree(ctx->scratch);
+            for (void* p : ctx->retired_scratch) cudaFree(p);
             if (ctx->status_host) cudaFreeHost(ctx->status_host);
             cudaStreamDestroy(ctx->stream);
         }
@@ -469,6 +492,45 @@ int32_t gq_int8_quantize(gq_ctx* ctx, gq_buf w, uint64_t w_off, uint64_t rows, u
     });
 }
 
+int32_t gq_int8_quantize_rows(gq_ctx* ctx, gq_buf w, uint64_t w_off, uint64_t rows, uint64_t k, gq_buf q, gq_buf scale, uint64_t row0,
+                              uint64_t total_rows) {
+    return guarded([&] {
+        Locked l(ctx);
+        check_dims("gq_int8_quantize_rows", rows, k, total_rows);
+        if (k == 0) fail("cannot quantize a weight with no input features");
+        if (row0 > total_rows || rows > total_rows - row0)
+            fail("gq_int8_quantize_rows: rows %llu..%llu do not fit a weight of %llu rows", (unsigned long long)row0,
+                 (unsigned long long)(row0 + rows), (unsigned long long)total_rows);
+        auto wp = (const float*)view(ctx, w, w_off, rows * k, 4, "gq_int8_quantize_rows weight");
+        auto qp = (uint32_t*)view(ctx, q, 0, total_rows * words8(k), 4, "gq_int8_quantize_rows q");
+        auto sp = (float*)view(ctx, scale, 0, total_rows, 4, "gq_int8_quantize_rows scale");
+        if (rows == 0) return;
+        launch_quantize_q8(ctx->stream, wp, rows, k, qp + row0 * words8(k), sp + row0);
+        after_launch(ctx, "quantize_q8", {w, q, scale});
+    });
+}
+
+int32_t gq_int4_quantize_rows(gq_ctx* ctx, gq_buf w, uint64_t w_off, uint64_t rows, uint64_t k, uint64_t group, gq_buf q, gq_buf scale, gq_buf zero,
+                              uint64_t row0, uint64_t total_rows) {
+    return guarded([&] {
+        Locked l(ctx);
+        check_dims("gq_int4_quantize_rows", rows, k, total_rows);
+        if (k == 0) fail("cannot quantize a weight with no input features");
+        check_group(group);
+        if (row0 > total_rows || rows > total_rows - row0)
+            fail("gq_int4_quantize_rows: rows %llu..%llu do not fit a weight of %llu rows", (unsigned long long)row0,
+                 (unsigned long long)(row0 + rows), (unsigned long long)total_rows);
+        const uint64_t groups = (k + group - 1) / group;
+        auto wp = (const float*)view(ctx, w, w_off, rows * k, 4, "gq_int4_quantize_rows weight");
+        auto qp = (uint32_t*)view(ctx, q, 0, total_rows * words4(k), 4, "gq_int4_quantize_rows q");
+        auto sp = (float*)view(ctx, scale, 0, total_rows * groups, 4, "gq_int4_quantize_rows scale");
+        auto zp = (float*)view(ctx, zero, 0, total_rows * groups, 4, "gq_int4_quantize_rows zero");
+        if (rows == 0) return;
+        launch_quantize_q4(ctx->stream, wp, rows, k, group, qp + row0 * words4(k), sp + row0 * groups, zp + row0 * groups);
+        after_launch(ctx, "quantize_q4", {w, q, scale, zero});
+    });
+}
+
 int32_t gq_int8_dequantize(gq_ctx* ctx, gq_buf q, gq_buf scale, uint64_t rows, uint64_t k, gq_buf w) {
     return guarded([&] {
         Locked l(ctx);
@@ -575,7 +637,16 @@ int32_t gq_int4_linear(gq_ctx* ctx, gq_buf x, uint64_t x_off, uint64_t m, uint64
         auto yp = (float*)view(ctx, y, 0, m * n, 4, "gq_int4_linear output");
         if (ranges_overlap(yp, m * n * 4, xp, m * k * 4)) fail("gq_int4_linear: the output must not overlap the input (CTAs read x while others write y)");
         if (m == 0 || n == 0) return;
-        if (kernel == GQ_KERNEL_UMMA) fail("gq_int4_linear: the tcgen05 decode kernel is built for int8 weights only");
+        if (kernel == GQ_KERNEL_UMMA) {
+            const uint64_t need = gemv_q4_umma_scratch_bytes(m, k, n, ctx->prop.multiProcessorCount);
+            if (!need || !launch_gemv_q4_umma(ctx->stream, ctx->prop.multiProcessorCount, ctx->status_dev, xp, m, k, qp, sp, zp, bp, n, group, yp,
+                                              context_scratch(ctx, need)))
+                fail("gq_int4_linear: the tcgen05 decode kernel takes group_size 128, in_features a multiple of 128, 1 to 16 rows of x and "
+                     "16-byte aligned x (m = %llu, k = %llu, group_size = %llu, x_off = %llu)",
+                     (unsigned long long)m, (unsigned long long)k, (unsigned long long)group, (unsigned long long)x_off);
+            after_launch(ctx, "gemv_q4_umma", {x, q, scale, zero, bias, y}, {y});
+            return;
+        }
         if (kernel == GQ_KERNEL_TENSOR) fail("gq_int4_linear: there is no tensor-core int4 kernel (the reference has none either, crates/grilly-infer/src/quant4.rs:412-413)");
         bool done = false;
         const char* name = "gemv_q4";

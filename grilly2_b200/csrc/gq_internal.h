@@ -79,9 +79,15 @@ struct gq_ctx {
     bool prev_known = false;
     gq_buf prev_written[4] = {0, 0, 0, 0};
     void* argmax_state = nullptr;  // keys and counters of gq_argmax_rows, zero between calls
+    void* sample_state = nullptr;  // gq_sample's arrival ticket, zero between calls
     // How long a kernel waits for another GPU's data before it gives up and reports through the status word, in SM
     // clock cycles (gq_set_wait_limit_us).
     long long peer_wait_cycles = 4000000000ll;
+    // Scratch of kernels that split K over CTAs (partial sums, arrival counters). Grow-only: a block that a captured
+    // graph may name is kept until the context is destroyed.
+    void* scratch = nullptr;
+    uint64_t scratch_bytes = 0;
+    std::vector<void*> retired_scratch;
 };
 
 namespace gq {
@@ -194,6 +200,14 @@ bool launch_gemv_q4_imma(cudaStream_t s, int sm_count, uint32_t* status, const f
                          const float* scale, const float* zero, const float* bias, uint64_t n, uint64_t group, float* y,
                          bool weights_settled);
 
+// int4 group-128 decode on tcgen05 for 1 to 16 rows of x in one pass (gemv_umma4.cu). The scratch holds the K slices'
+// partial sums and the per-tile arrival counters (zero between launches).
+uint64_t gemv_q4_umma_scratch_bytes(uint64_t m, uint64_t k, uint64_t n, int sm_count);
+bool launch_gemv_q4_umma(cudaStream_t s, int sm_count, uint32_t* status, const float* x, uint64_t m, uint64_t k, const uint32_t* q,
+                         const float* scale, const float* zero, const float* bias, uint64_t n, uint64_t group, float* y, void* scratch);
+// Zeroed device memory owned by the context, grown (never shrunk or moved while graphs may name it) on demand.
+void* context_scratch(gq_ctx* ctx, uint64_t bytes);
+
 bool launch_gemv_q8_tc(cudaStream_t s, int sm_count, uint32_t* status, const float* x, uint64_t m, uint64_t k, const uint32_t* q,
                        const float* scale, const float* bias, uint64_t n, float* y);
 
@@ -223,6 +237,10 @@ void launch_attn_decode(cudaStream_t s, const float* q, float* kc, float* vc, co
                         uint32_t kv_heads, uint32_t dim, uint32_t max_len, float scale, uint32_t splits, float* scratch, float* out,
                         const float* cosv = nullptr, const float* sinv = nullptr, bool early = false);
 void launch_swiglu(cudaStream_t s, const float* gate_up, uint64_t rows, uint64_t width, float* out);
+uint64_t sample_state_bytes();
+void launch_sample(cudaStream_t s, const float* logits, uint64_t rows, uint64_t v, int32_t* history, uint64_t hist_cap, uint32_t* hist_len,
+                   bool do_sample, float temperature, uint64_t top_k, float one_minus_p, float penalty, const float* uniforms,
+                   uint64_t uniform_rows, uint32_t* draws, float* scores, float* ex, int32_t* tokens, float* probs, bool append, void* state);
 uint64_t argmax_state_bytes();
 void launch_argmax_rows(cudaStream_t s, const float* v, uint64_t rows, uint64_t n, int32_t* out, void* state);
 

@@ -122,6 +122,9 @@ class LlamaDecoder:
         def q8(a):
             return _C.Int8Weight.quantize(T(np.ascontiguousarray(a, dtype=np.float32)))
 
+        def q8_fused(parts):  # q | k | v and gate | up are quantized straight into the fused weight: no second copy of the parts
+            return _C.Int8Weight.quantize_fused([T(np.ascontiguousarray(a, dtype=np.float32)) for a in parts])
+
         self.embed = T(weights["embed"], persistent=True)
         self.lm_head = q8(weights["embed"])  # tied; the table itself stays float32
         self.norm = T(weights["norm"], persistent=True)
@@ -129,10 +132,10 @@ class LlamaDecoder:
         for lw in weights["layers"]:
             self.layers.append({
                 "input_norm": T(lw["input_norm"], persistent=True), "post_norm": T(lw["post_norm"], persistent=True),
-                "qkv": _C.Int8Weight.cat([q8(lw["q"]), q8(lw["k"]), q8(lw["v"])]),
+                "qkv": q8_fused([lw["q"], lw["k"], lw["v"]]),
                 "qkv_bias": T(np.concatenate([lw["q_bias"], lw["k_bias"], lw["v_bias"]]), persistent=True) if cfg.attention_bias else None,
                 "o": q8(lw["o"]),
-                "gate_up": _C.Int8Weight.cat([q8(lw["gate"]), q8(lw["up"])]),
+                "gate_up": q8_fused([lw["gate"], lw["up"]]),
                 "down": q8(lw["down"]),
             })
         cos, sin = rotary_tables(cfg)
@@ -149,8 +152,9 @@ class LlamaDecoder:
                                           h.storage.handle if h is not None else 0))
         return y, h
 
-    def step(self, token: "_C.Tensor"):
-        """token: int32 [1]. Returns (logits [1, vocab], next_token int32 [1]); advances the cache."""
+    def step(self, token: "_C.Tensor", want_argmax: bool = True):
+        """token: int32 [1]. Returns (logits [1, vocab], next_token int32 [1]); advances the cache. With want_argmax
+        False the greedy token is not computed (a sampler follows) and None is returned in its place."""
         c, lib, ctx = self.cfg, _lib.load(), _C.context()
         L, Hq, Hkv, D = c.num_hidden_layers, c.num_attention_heads, c.num_key_value_heads, c.head_dim
         hidden = _C.Tensor.empty((1, c.hidden_size), "float32")
@@ -195,8 +199,10 @@ class LlamaDecoder:
         else:
             x, _ = self._norm(hidden, delta, self.norm, False)
             logits = self.lm_head.linear(x)
-        nxt = _C.Tensor.empty((1,), "int32")
-        check(lib.gq_argmax_rows(ctx, logits.storage.handle, 1, c.vocab_size, nxt.storage.handle))
+        nxt = None
+        if want_argmax:
+            nxt = _C.Tensor.empty((1,), "int32")
+            check(lib.gq_argmax_rows(ctx, logits.storage.handle, 1, c.vocab_size, nxt.storage.handle))
         check(lib.gq_kv_advance(ctx, self.cache.lens.storage.handle, L, c.max_cache_len))
         return logits, nxt
 

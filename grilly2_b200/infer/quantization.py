@@ -26,7 +26,7 @@ from .. import Size, Tensor, _C, _DEVICE, _not_yet, _require_tensor, _resolve_de
 from ..nn.modules import Linear, Parameter
 
 __all__ = ["Int4Tensor", "Int4WeightOnlyConfig", "Int8Tensor", "Int8WeightOnlyConfig", "PerRow", "QuantizedTensor",
-           "load_quantized_", "quantize_"]
+           "load_packed_", "load_quantized_", "quantize_", "save_packed"]
 
 
 @dataclass(frozen=True)
@@ -272,3 +272,100 @@ def load_quantized_(model, filename, config, filter_fn=_is_linear, strict: bool 
         return _quantized(value, config) if key in wanted else None
 
     return stream_into(model, filename, strict=strict, convert=convert)
+
+
+# ── pre-packed checkpoints ────────────────────────────────────────────────
+# The reference quantizes at load time from a float checkpoint (load_quantized_ above) and names a checkpoint that
+# already holds the packed weights as its next step (docs/inference.md:900-904). This is that step: a safetensors file
+# whose quantized weights are stored as they lie on the device — `<name>.__q` (int32 words), `<name>.__scale` and, for
+# int4, `<name>.__zero` — with the packing described in the metadata. Loading uploads each packed tensor straight into
+# persistent device memory: no float32 copy of a quantized weight exists at any point, on the host or the device.
+
+_PACKED = "grilly_packed"
+
+
+def save_packed(model, filename) -> set[str]:
+    """Write ``model``'s parameters to ``filename`` (safetensors): quantized weights packed, the rest float32 / int32 as
+    they are. Returns the tensor names written."""
+    import json
+    import struct
+
+    import numpy as np
+    entries, blobs, meta, at = {}, [], {_PACKED: "1"}, 0
+
+    def add(name, arr):
+        nonlocal at
+        arr = np.ascontiguousarray(arr)
+        dtype = {"float32": "F32", "int32": "I32"}[str(arr.dtype)]
+        entries[name] = {"dtype": dtype, "shape": list(arr.shape), "data_offsets": [at, at + arr.nbytes]}
+        blobs.append(arr.tobytes())
+        at += arr.nbytes
+
+    for name, p in model.state_dict(keep_vars=True).items():
+        if isinstance(p, Int8Tensor):
+            add(name + ".__q", p._q.packed().numpy())
+            add(name + ".__scale", p._q.scale().numpy())
+            meta[name] = json.dumps({"bits": 8, "shape": list(p.shape)})
+        elif isinstance(p, Int4Tensor):
+            add(name + ".__q", p._q.packed().numpy())
+            add(name + ".__scale", p._q.scale().numpy())
+            add(name + ".__zero", p._q.zero().numpy())
+            meta[name] = json.dumps({"bits": 4, "shape": list(p.shape), "group_size": p.group_size})
+        else:
+            add(name, p.numpy())
+    header = json.dumps({"__metadata__": meta, **entries}, separators=(",", ":")).encode("utf-8")
+    header += b" " * (-len(header) % 8)
+    with open(filename, "wb") as f:
+        f.write(struct.pack("<Q", len(header)))
+        f.write(header)
+        for b in blobs:
+            f.write(b)
+    return set(entries)
+
+
+def load_packed_(model, filename, strict: bool = True) -> set[str]:
+    """Load a ``save_packed`` file into ``model``, tensor by tensor. A packed weight replaces the module's float weight
+    with the quantized tensor the file describes (whatever the module held before); nothing is quantized or dequantized.
+    Returns the parameter names the file held."""
+    import json
+
+    from .. import _C
+    from .safetensors import safe_open
+    own = set(model.state_dict(keep_vars=True))
+    seen: set[str] = set()
+    with safe_open(filename) as f:
+        meta = f.metadata() or {}
+        if meta.get(_PACKED) != "1":
+            raise RuntimeError(f"{filename} is not a pre-packed checkpoint (no {_PACKED} marker): load it with load_quantized_")
+        packed = {k: json.loads(v) for k, v in meta.items() if k != _PACKED}
+        names = f.offset_keys()
+        plain = [k for k in names if ".__" not in k]
+        unexpected = [k for k in list(packed) + plain if k not in own]
+        if strict and unexpected:
+            raise RuntimeError("Unexpected key(s) in state_dict: " + ", ".join(f'"{k}"' for k in unexpected))
+        for key in plain:
+            if key in own:
+                model.load_state_dict({key: f.get_tensor(key)}, assign=True, strict=False)
+                seen.add(key)
+        for key, info in packed.items():
+            if key not in own:
+                continue
+            n, k = info["shape"]
+            q = f.get_tensor(key + ".__q")._t        # int32 words, uploaded as they are into persistent memory
+            scale = f.get_tensor(key + ".__scale")._t
+            if info["bits"] == 8:
+                if tuple(q.shape) != (n, -(-k // 16) * 4) or tuple(scale.shape) != (n,):
+                    raise RuntimeError(f"{key}: packed int8 tensors {list(q.shape)} / {list(scale.shape)} do not describe a ({n}, {k}) weight")
+                value = Int8Tensor._holding(_C.Int8Weight(q, scale, (n, k)))
+            else:
+                zero = f.get_tensor(key + ".__zero")._t
+                value = Int4Tensor._holding(_C.Int4Weight.from_parts(q, scale, zero, k, int(info["group_size"])))
+            owner, _, attr = key.rpartition(".")
+            setattr(model.get_submodule(owner), attr, value)
+            seen.add(key)
+            del q, scale, value
+    if strict:
+        missing = [k for k in own if k not in seen]
+        if missing:
+            raise RuntimeError("Missing key(s) in state_dict: " + ", ".join(f'"{k}"' for k in missing))
+    return seen

@@ -70,8 +70,9 @@ typedef uint64_t gq_buf; /* 0 is never a valid handle */
 #define GQ_KERNEL_TENSOR 2 /* tcgen05 tensor-core GEMM (tf32), dequantised in shared memory */
 #define GQ_KERNEL_DP4A 3   /* GEMV on integer dot products (dp4a) against exact fixed-point digit planes of x,
                               within float32 rounding of GQ_KERNEL_GEMV; any group size, up to 16 rows */
-#define GQ_KERNEL_UMMA 5   /* decode GEMV on tcgen05 (kind::i8, accumulators in tensor memory), weights fed to the
-                              tensor core by TMA exactly as they lie in HBM: one or two rows of x */
+#define GQ_KERNEL_UMMA 5   /* decode linear on tcgen05 (kind::i8, accumulators in tensor memory), weights fed to the
+                              tensor core by TMA exactly as they lie in HBM. int8: one or two rows of x. int4 (group_size
+                              128, in_features a multiple of 128): 1 to 16 rows of x in ONE pass over the weight */
 #define GQ_KERNEL_IMMA 4   /* the same arithmetic on the warp-level int8 tensor instruction: the fast path for
                               one or two rows of x (int4: group_size a multiple of 128) */
 #define GQ_KERNEL_RING 6   /* int4 group-128 decode on the warp-level int8 tensor instruction with K split by group over the
@@ -157,6 +158,15 @@ int32_t gq_persistent_peak_reset(gq_ctx* ctx);
  * q must hold rows*words8 words, scale rows floats. */
 int32_t gq_int8_quantize(gq_ctx* ctx, gq_buf w, uint64_t w_off, uint64_t rows, uint64_t k, gq_buf q, gq_buf scale);
 
+/* The same packer writing rows [row0, row0 + rows) of a LARGER weight of total_rows rows (q: total_rows * words8 words,
+ * scale: total_rows floats): the parts of a fused projection (q | k | v, gate | up) are quantized straight into the fused
+ * weight, one call per part, instead of being quantized apart and copied together, so the parts never exist twice on the
+ * device. No counterpart in the reference, which names this as its next step (docs/inference.md:900-904;
+ * python/grilly/infer/models/llama.py:108-131 builds the fused weight with Int8Weight::cat). Bit for bit what quantizing
+ * the parts and gq_copy-ing them together gives, because the parameters are per row. */
+int32_t gq_int8_quantize_rows(gq_ctx* ctx, gq_buf w, uint64_t w_off, uint64_t rows, uint64_t k, gq_buf q, gq_buf scale, uint64_t row0,
+                              uint64_t total_rows);
+
 /* LINEAR / LINEAR_TILED{x,q,scale,bias,y; m,k,n,vecs,x_off,b_off,has_bias,x_vec4}
  * — quant.rs:25-39,233-304, g2-linear-q8.glsl:33-95, g2-linear-q8-tiled.glsl:41-100.
  * y[m][n] = (sum_k x[m][k] * q[n][k]) * scale[n] (+ bias[n]); bias == 0 means none.
@@ -175,6 +185,10 @@ int32_t gq_int8_dequantize(gq_ctx* ctx, gq_buf q, gq_buf scale, uint64_t rows, u
  * g2-quantize-q4.glsl:30-70. group must be a positive multiple of 32. */
 int32_t gq_int4_quantize(gq_ctx* ctx, gq_buf w, uint64_t w_off, uint64_t rows, uint64_t k, uint64_t group, gq_buf q,
                          gq_buf scale, gq_buf zero);
+
+/* As gq_int8_quantize_rows, for int4: rows [row0, row0 + rows) of a weight of total_rows rows. */
+int32_t gq_int4_quantize_rows(gq_ctx* ctx, gq_buf w, uint64_t w_off, uint64_t rows, uint64_t k, uint64_t group, gq_buf q, gq_buf scale,
+                              gq_buf zero, uint64_t row0, uint64_t total_rows);
 
 /* LINEAR{x,q,scale,zero,bias,y; m,k,n,vecs,group,groups,x_off,b_off,has_bias,x_vec4}
  * — quant4.rs:33-39,371-442, g2-linear-q4.glsl:43-111. */
@@ -260,6 +274,20 @@ int32_t gq_attn_decode_static(gq_ctx* ctx, gq_buf q, gq_buf kcache, uint64_t k_o
                               float scale, gq_buf out);
 /* out[r][j] = silu(gate_up[r][j]) * gate_up[r][width + j] — ops.rs:148-212, g2-swiglu.glsl:21-29. */
 int32_t gq_swiglu(gq_ctx* ctx, gq_buf gate_up, uint64_t rows, uint64_t width, gq_buf out);
+/* The next token of every row, chosen on the device — crates/grilly-infer/src/sampling.rs:1-60,
+ * shaders/g2-sample.glsl: Hugging Face's processors in generate()'s order (repetition penalty over `history`,
+ * then with do_sample temperature, top_k (0 = off), top_p (1 = off)) and a draw from what is left by the inverse
+ * CDF in token order; without do_sample the first index of the largest penalized score. tokens: int32 per row,
+ * -1 where nothing can be drawn (every score -inf). probs (0 = none) receives the filtered distribution.
+ * Where the reference passes each row's uniform number and the history length from the host, here they are read
+ * from device memory so that a captured step replays: `uniforms` holds uniform_rows x rows floats in [0, 1) and the
+ * launch uses row (*draws % uniform_rows), adding one to the uint32 word `draws` when do_sample; `history`
+ * (0 = none) is int32 [rows][hist_cap] of which the uint32 word `hist_len` says how many are set, and with
+ * `append` the chosen token is written at that place and the word advanced (a full history takes nothing more).
+ * scratch: 2 * rows * vocab floats. */
+int32_t gq_sample(gq_ctx* ctx, gq_buf logits, uint64_t rows, uint64_t vocab, gq_buf history, uint64_t hist_cap, gq_buf hist_len, uint32_t append,
+                  uint32_t do_sample, double temperature, uint64_t top_k, double top_p, double repetition_penalty, gq_buf uniforms,
+                  uint64_t uniform_rows, gq_buf draws, gq_buf scratch, gq_buf tokens, gq_buf probs);
 /* out[r] = index of the maximum of row r (int32; the first on ties) — g2-argreduce-rows.glsl:42-77. */
 int32_t gq_argmax_rows(gq_ctx* ctx, gq_buf v, uint64_t rows, uint64_t n, gq_buf out);
 
