@@ -77,6 +77,8 @@ PROTOTYPES = {
     "gq_attn_decode_rope": [vp, u64, u64, u64, u64, u64, u64, u64, u64, u64, u64, u64, u64, u64, u64, ctypes.c_float, u64, u64],
     "gq_int8_linear_norm": [vp, u64, u64, u64, ctypes.c_float, u64, u64, u64, u64, u64, u64, u64, u64],
     "gq_int8_linear_swiglu": [vp, u64, u64, u64, u64, u64, u64, u64, u64],
+    "gq_attn_prefill": [vp, u64, u64, u64, u64, u64, u64, u64, u64, u64, u64, u64, u64, u64, u64, u64, u64, u64, ctypes.c_float, u64, u64],
+    "gq_kv_advance_by": [vp, u64, u64, u64, u64],
     "gq_swiglu": [vp, u64, u64, u64, u64],
     "gq_argmax_rows": [vp, u64, u64, u64, u64],
     "gq_sample": [vp, u64, u64, u64, u64, u64, u64, u32, u32, ctypes.c_double, u64, ctypes.c_double, ctypes.c_double, u64, u64, u64, u64, u64, u64],

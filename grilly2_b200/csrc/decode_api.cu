@@ -129,6 +129,54 @@ int32_t gq_attn_decode_rope(gq_ctx* ctx, gq_buf qkv, gq_buf cos, gq_buf sin, gq_
     });
 }
 
+int32_t gq_attn_prefill(gq_ctx* ctx, gq_buf qkv, uint64_t rows, gq_buf cos, gq_buf sin, gq_buf kcache, uint64_t k_off, gq_buf vcache, uint64_t v_off,
+                        gq_buf kscale, gq_buf vscale, gq_buf lens, uint64_t layer, uint64_t layers, uint64_t heads, uint64_t kv_heads, uint64_t dim,
+                        uint64_t max_len, float scale, gq_buf q_scratch, gq_buf out) {
+    return guarded([&] {
+        Locked l(ctx);
+        check_dims("gq_attn_prefill", rows, heads * dim, max_len);
+        check_dims("gq_attn_prefill", kv_heads, layers);
+        if (heads == 0 || kv_heads == 0 || heads % kv_heads)
+            fail("gq_attn_prefill: %llu heads do not group over %llu kv heads", (unsigned long long)heads, (unsigned long long)kv_heads);
+        if (dim != 32 && dim != 64 && dim != 128) fail("gq_attn_prefill: head_dim must be 32, 64 or 128, got %llu", (unsigned long long)dim);
+        if (max_len == 0) fail("gq_attn_prefill: a cache of no positions");
+        if (layer >= layers) fail("gq_attn_prefill: layer %llu of %llu", (unsigned long long)layer, (unsigned long long)layers);
+        if ((kscale == 0) != (vscale == 0)) fail("gq_attn_prefill: an int8 cache needs both scale buffers");
+        const bool q8 = kscale != 0;
+        if (k_off % dim || v_off % dim) fail("gq_attn_prefill: cache offsets must be whole rows (multiples of head_dim)");
+        const uint64_t qsz = heads * dim, kvsz = kv_heads * dim, cache = kv_heads * max_len * dim;
+        auto qp = (const float*)view(ctx, qkv, 0, rows * (qsz + 2 * kvsz), 4, "gq_attn_prefill qkv");
+        auto cp = (const float*)view(ctx, cos, 0, max_len * dim, 4, "gq_attn_prefill cos");
+        auto sp = (const float*)view(ctx, sin, 0, max_len * dim, 4, "gq_attn_prefill sin");
+        void* kp = view(ctx, kcache, k_off, cache, q8 ? 1 : 4, "gq_attn_prefill key cache");
+        void* vp = view(ctx, vcache, v_off, cache, q8 ? 1 : 4, "gq_attn_prefill value cache");
+        auto ksp = q8 ? (float*)view(ctx, kscale, k_off / dim, kv_heads * max_len, 4, "gq_attn_prefill key scales") : nullptr;
+        auto vsp = q8 ? (float*)view(ctx, vscale, v_off / dim, kv_heads * max_len, 4, "gq_attn_prefill value scales") : nullptr;
+        auto lp = (const uint32_t*)view(ctx, lens, 0, layers, 4, "gq_attn_prefill cursor");
+        auto qs = (float*)view(ctx, q_scratch, 0, rows * qsz, 4, "gq_attn_prefill rotated queries");
+        auto op = (float*)view(ctx, out, 0, rows * qsz, 4, "gq_attn_prefill output");
+        if (ranges_overlap(op, rows * qsz * 4, qs, rows * qsz * 4)) fail("gq_attn_prefill: the output must not be the rotated-query scratch");
+        if (rows == 0) return;
+        launch_rope_append_rows(ctx->stream, qp, cp, sp, lp, (uint32_t)layer, (uint32_t)rows, (uint32_t)heads, (uint32_t)kv_heads, (uint32_t)dim,
+                                (uint32_t)max_len, qs, kp, vp, ksp, vsp, q8);
+        launch_attn_prefill(ctx->stream, qs, kp, vp, ksp, vsp, lp, (uint32_t)layer, (uint32_t)rows, (uint32_t)heads, (uint32_t)kv_heads, (uint32_t)dim,
+                            (uint32_t)max_len, scale, op, q8);
+        ctx->stats.launches++;
+        after_launch(ctx, "attn_prefill", {qkv, cos, sin, kcache, vcache, kscale, vscale, lens, q_scratch, out}, {});
+    });
+}
+
+int32_t gq_kv_advance_by(gq_ctx* ctx, gq_buf lens, uint64_t layers, uint64_t max_len, uint64_t count) {
+    return guarded([&] {
+        Locked l(ctx);
+        check_dims("gq_kv_advance_by", layers, max_len, count);
+        auto lp = (uint32_t*)view(ctx, lens, 0, layers, 4, "gq_kv_advance_by cursor");
+        if (layers == 0 || count == 0) return;
+        launch_kv_advance_by(ctx->stream, lp, (uint32_t)layers, (uint32_t)max_len, (uint32_t)count);
+        after_launch(ctx, "kv_advance_by", {lens}, {});
+    });
+}
+
 int32_t gq_swiglu(gq_ctx* ctx, gq_buf gate_up, uint64_t rows, uint64_t width, gq_buf out) {
     return guarded([&] {
         Locked l(ctx);

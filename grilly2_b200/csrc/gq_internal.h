@@ -236,6 +236,13 @@ uint64_t attn_scratch_floats(uint32_t heads, uint32_t dim, uint32_t splits);
 void launch_attn_decode(cudaStream_t s, const float* q, float* kc, float* vc, const uint32_t* lens, uint32_t layer, uint32_t heads,
                         uint32_t kv_heads, uint32_t dim, uint32_t max_len, float scale, uint32_t splits, float* scratch, float* out,
                         const float* cosv = nullptr, const float* sinv = nullptr, bool early = false);
+void launch_rope_append_rows(cudaStream_t s, const float* qkv, const float* cosv, const float* sinv, const uint32_t* lens, uint32_t layer,
+                             uint32_t rows, uint32_t heads, uint32_t kv_heads, uint32_t dim, uint32_t max_len, float* q_out, void* kc, void* vc,
+                             float* kscale, float* vscale, bool int8_cache);
+void launch_attn_prefill(cudaStream_t s, const float* q, const void* kc, const void* vc, const float* kscale, const float* vscale,
+                         const uint32_t* lens, uint32_t layer, uint32_t rows, uint32_t heads, uint32_t kv_heads, uint32_t dim, uint32_t max_len,
+                         float scale, float* out, bool int8_cache);
+void launch_kv_advance_by(cudaStream_t s, uint32_t* lens, uint32_t layers, uint32_t max_len, uint32_t count);
 void launch_swiglu(cudaStream_t s, const float* gate_up, uint64_t rows, uint64_t width, float* out);
 uint64_t sample_state_bytes();
 void launch_sample(cudaStream_t s, const float* logits, uint64_t rows, uint64_t v, int32_t* history, uint64_t hist_cap, uint32_t* hist_len,

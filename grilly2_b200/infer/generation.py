@@ -9,9 +9,9 @@ the sampler — and the sampler writes its token where the next step's embedding
 reads it and appends it to a device history. The host only replays; it reads
 back a token per step when there is an end-of-sequence id to stop at (as the
 reference reads back only the sampled ids, generation.py:173), and nothing at
-all until the end otherwise. The prompt is fed through the same step one token
-at a time (there is no prefill attention here; greedy and sampled continuations
-are unaffected by how the cache was filled).
+all until the end otherwise. The prompt but for its last token goes through
+``LlamaDecoder.prefill`` (all rows at once, causal attention over the cache);
+the last token is the first step's input.
 """
 from __future__ import annotations
 
@@ -88,12 +88,11 @@ def generate(model, inputs=None, generation_config: GenerationConfig | None = No
         logits, _ = model.step(token, want_argmax=False)
         sampler.sample(logits, out=token)  # chooses, writes the next input, appends to the device history
 
-    # the prompt: every token but the last goes through the step with its successor forced (the draw is discarded)
     import grilly2_b200 as g
     run = g.graphed(step) if graphed else step
-    for t in range(1, prompt):
-        model.step(token, want_argmax=False)
-        token.copy_(_C.Tensor.from_numpy(ids[0, t:t + 1].astype(np.int32)))
+    if prompt > 1:  # the prompt but for its last token: one pass over all its rows
+        model.prefill(_C.Tensor.from_numpy(ids[0, :-1].astype(np.int32)))
+        token.copy_(_C.Tensor.from_numpy(ids[0, -1:].astype(np.int32)))
     sampler.set_history(ids)
     done = 0
     for _ in range(steps):

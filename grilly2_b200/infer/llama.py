@@ -82,22 +82,34 @@ def random_weights(cfg: LlamaConfig, seed: int = 4, sigma: float = 0.02) -> dict
 
 
 class KvCache:
-    """float32 K and V for every layer, [layers][kv_heads][max_len][head_dim], with the per-layer cursor on
-    the device (crates/grilly-infer/src/kv_cache.rs:21-33)."""
+    """K and V for every layer, [layers][kv_heads][max_len][head_dim], with the per-layer cursor on the device
+    (crates/grilly-infer/src/kv_cache.rs:21-33): float32 as the reference's, or with ``int8=True`` int8 codes and one
+    float32 scale per cached row (a quarter of the bytes a decoded token reads; no counterpart in the reference)."""
 
-    def __init__(self, cfg: LlamaConfig) -> None:
-        self.cfg = cfg
+    def __init__(self, cfg: LlamaConfig, int8: bool = False) -> None:
+        self.cfg, self.int8 = cfg, bool(int8)
         self.layer_elems = cfg.num_key_value_heads * cfg.max_cache_len * cfg.head_dim
+        self.layer_rows = cfg.num_key_value_heads * cfg.max_cache_len
         n = cfg.num_hidden_layers * self.layer_elems
-        self.k = _C.Tensor.empty((n,), "float32", persistent=True)
-        self.v = _C.Tensor.empty((n,), "float32", persistent=True)
+        if self.int8:
+            self.k = _C.Tensor.from_numpy(np.zeros(n // 4, dtype=np.int32), persistent=True)  # n bytes of int8 codes
+            self.v = _C.Tensor.from_numpy(np.zeros(n // 4, dtype=np.int32), persistent=True)
+            rows = cfg.num_hidden_layers * self.layer_rows
+            self.kscale = _C.Tensor.from_numpy(np.ones(rows, dtype=np.float32), persistent=True)
+            self.vscale = _C.Tensor.from_numpy(np.ones(rows, dtype=np.float32), persistent=True)
+        else:
+            self.k = _C.Tensor.empty((n,), "float32", persistent=True)
+            self.v = _C.Tensor.empty((n,), "float32", persistent=True)
+            self.kscale = self.vscale = None
         self.lens = _C.Tensor.from_numpy(np.zeros(cfg.num_hidden_layers, dtype=np.int32), persistent=True)
         out = ctypes.c_uint64()
         check(_lib.load().gq_attn_scratch_bytes(_C.context(), cfg.num_attention_heads, cfg.head_dim, cfg.max_cache_len, ctypes.byref(out)))
         self.scratch = _C.Tensor.from_numpy(np.zeros(out.value // 4, dtype=np.float32), persistent=True)
 
     def fill(self, k: np.ndarray, v: np.ndarray, length: int) -> None:
-        """Install `length` cached positions: k, v are [layers][kv_heads][length][head_dim]."""
+        """Install `length` cached positions: k, v are [layers][kv_heads][length][head_dim] (float32 cache only)."""
+        if self.int8:
+            raise NotImplementedError("grilly: installing float rows into an int8 cache is not implemented yet (prefill instead)")
         c = self.cfg
         full_k = np.zeros((c.num_hidden_layers, c.num_key_value_heads, c.max_cache_len, c.head_dim), dtype=np.float32)
         full_v = np.zeros_like(full_k)
@@ -106,6 +118,10 @@ class KvCache:
         self.v = _C.Tensor.from_numpy(full_v.reshape(-1), persistent=True)
         self.lens = _C.Tensor.from_numpy(np.full(c.num_hidden_layers, length, dtype=np.int32), persistent=True)
 
+    def nbytes(self) -> int:
+        per = self.cfg.num_hidden_layers * self.layer_elems
+        return 2 * (per + 4 * self.cfg.num_hidden_layers * self.layer_rows) if self.int8 else 2 * 4 * per
+
     def lengths(self) -> np.ndarray:
         return self.lens.numpy()
 
@@ -113,10 +129,11 @@ class KvCache:
 class LlamaDecoder:
     """The quantized model and its cache; ``step(token)`` decodes one token."""
 
-    def __init__(self, cfg: LlamaConfig, weights: dict, fused: bool = True) -> None:
+    def __init__(self, cfg: LlamaConfig, weights: dict, fused: bool = True, int8_kv: bool = False) -> None:
         self.cfg = cfg
         # fused: norms and SwiGLU run inside the following projection (one launch each); needs row lengths that are multiples of 4
         self.fused = fused and cfg.hidden_size % 4 == 0 and cfg.intermediate_size % 4 == 0
+        self.int8_kv = bool(int8_kv)
         T = _C.Tensor.from_numpy
 
         def q8(a):
@@ -140,17 +157,59 @@ class LlamaDecoder:
             })
         cos, sin = rotary_tables(cfg)
         self.cos, self.sin = T(cos, persistent=True), T(sin, persistent=True)
-        self.cache = KvCache(cfg)
+        self.cache = KvCache(cfg, int8=self.int8_kv)
 
     # the operators, as thin calls into the C ABI
-    def _norm(self, x, residual, weight, want_sum: bool):
+    def _norm(self, x, residual, weight, want_sum: bool, rows: int = 1):
         H = self.cfg.hidden_size
-        y = _C.Tensor.empty((1, H), "float32")
-        h = _C.Tensor.empty((1, H), "float32") if want_sum else None
+        y = _C.Tensor.empty((rows, H), "float32")
+        h = _C.Tensor.empty((rows, H), "float32") if want_sum else None
         check(_lib.load().gq_add_rms_norm(_C.context(), x.storage.handle, residual.storage.handle if residual is not None else 0,
-                                          weight.storage.handle, 1, H, self.cfg.rms_norm_eps, y.storage.handle,
+                                          weight.storage.handle, rows, H, self.cfg.rms_norm_eps, y.storage.handle,
                                           h.storage.handle if h is not None else 0))
         return y, h
+
+    def _attend_rows(self, qkv, rows: int, li: int):
+        """Rotary + cache append + causal attention for `rows` new tokens of layer li (gq_attn_prefill)."""
+        c, cache = self.cfg, self.cache
+        off = li * cache.layer_elems
+        attn = _C.Tensor.empty((rows, c.q_size), "float32")
+        q_rot = _C.Tensor.empty((rows, c.q_size), "float32")
+        check(_lib.load().gq_attn_prefill(
+            _C.context(), qkv.storage.handle, rows, self.cos.storage.handle, self.sin.storage.handle, cache.k.storage.handle, off,
+            cache.v.storage.handle, off, cache.kscale.storage.handle if cache.int8 else 0, cache.vscale.storage.handle if cache.int8 else 0,
+            cache.lens.storage.handle, li, c.num_hidden_layers, c.num_attention_heads, c.num_key_value_heads, c.head_dim, c.max_cache_len,
+            float(c.head_dim) ** -0.5, q_rot.storage.handle, attn.storage.handle))
+        return attn
+
+    def prefill(self, tokens: "_C.Tensor"):
+        """tokens: int32 [T], continuing the cache from its cursor. Every layer runs on all T rows at once — the linears
+        take the kernel their row count selects (decode kernels up to 16 rows, the tensor-core GEMM from 64) — with causal
+        attention over the cache (python/grilly/infer/models/llama.py:340-366 with logits_to_keep=1). Returns the LAST
+        position's logits [1, vocab] and advances the cursor by T."""
+        c, lib, ctx = self.cfg, _lib.load(), _C.context()
+        T = tokens.numel()
+        if T == 0:
+            raise RuntimeError("prefill needs at least one token")
+        hidden = _C.Tensor.empty((T, c.hidden_size), "float32")
+        check(lib.gq_embedding(ctx, self.embed.storage.handle, tokens.storage.handle, T, c.hidden_size, c.vocab_size, hidden.storage.handle))
+        delta = None
+        for li, lw in enumerate(self.layers):
+            x, summed = self._norm(hidden, delta, lw["input_norm"], delta is not None, T)
+            if summed is not None:
+                hidden = summed
+            qkv = lw["qkv"].linear(x, lw["qkv_bias"])
+            o = lw["o"].linear(self._attend_rows(qkv, T, li))
+            x, hidden = self._norm(hidden, o, lw["post_norm"], True, T)
+            gu = lw["gate_up"].linear(x)
+            act = _C.Tensor.empty((T, c.intermediate_size), "float32")
+            check(lib.gq_swiglu(ctx, gu.storage.handle, T, c.intermediate_size, act.storage.handle))
+            delta = lw["down"].linear(act)
+        last_h, last_d = hidden.window_rows(T - 1, 1), delta.window_rows(T - 1, 1)
+        x, _ = self._norm(last_h, last_d, self.norm, False)
+        logits = self.lm_head.linear(x)
+        check(lib.gq_kv_advance_by(ctx, self.cache.lens.storage.handle, c.num_hidden_layers, c.max_cache_len, T))
+        return logits
 
     def step(self, token: "_C.Tensor", want_argmax: bool = True):
         """token: int32 [1]. Returns (logits [1, vocab], next_token int32 [1]); advances the cache. With want_argmax
@@ -171,7 +230,9 @@ class LlamaDecoder:
                 hidden = summed
             off = li * self.cache.layer_elems
             attn = _C.Tensor.empty((1, c.q_size), "float32")
-            if fused:  # rotary, the cache append and attention in one launch
+            if self.int8_kv:  # the int8 cache: rotary, quantized append and attention through the prompt kernels, one row
+                attn = self._attend_rows(qkv, 1, li)
+            elif fused:  # rotary, the cache append and attention in one launch
                 check(lib.gq_attn_decode_rope(ctx, qkv.storage.handle, self.cos.storage.handle, self.sin.storage.handle,
                                               self.cache.k.storage.handle, off, self.cache.v.storage.handle, off,
                                               self.cache.lens.storage.handle, li, L, Hq, Hkv, D, c.max_cache_len, float(D) ** -0.5,

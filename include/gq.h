@@ -272,6 +272,21 @@ int32_t gq_int8_linear_swiglu(gq_ctx* ctx, gq_buf gate_up, uint64_t k, gq_buf q,
 int32_t gq_attn_decode_static(gq_ctx* ctx, gq_buf q, gq_buf kcache, uint64_t k_off, gq_buf vcache, uint64_t v_off, gq_buf lens,
                               uint64_t layer, uint64_t layers, uint64_t heads, uint64_t kv_heads, uint64_t dim, uint64_t max_len,
                               float scale, gq_buf out);
+/* Prompt processing for `rows` new tokens at once — the prefill branch of python/grilly/infer/models/llama.py:168-179
+ * (rope on q and k, causal scaled_dot_product_attention with grouped queries, cache.append) in two launches: the rows'
+ * q are rotated into q_scratch, their k (rotated) and v are appended at cache positions lens[layer] + t, and every
+ * query attends causally over positions 0 .. lens[layer] + t. The positions come from the DEVICE cursor, so the rows
+ * may continue a non-empty cache (chunked prefill) and the call may be captured; rows == 1 is a decode step's
+ * attention. The cursor is not advanced: gq_kv_advance_by does that once per step, after the last layer.
+ * With kscale / vscale (float32 [layers * kv_heads * max_len], one per cached row) the cache buffers hold int8
+ * codes [kv_heads][max_len][dim] (k_off / v_off in bytes then): every appended row is stored as rint(v / s),
+ * s = max|v| / 127, and dequantized as it is read — a quarter of the bytes per decoded token. The reference's cache
+ * is exact float32 (crates/grilly-infer/src/kv_cache.rs:1-19): the int8 form has no counterpart there. */
+int32_t gq_attn_prefill(gq_ctx* ctx, gq_buf qkv, uint64_t rows, gq_buf cos, gq_buf sin, gq_buf kcache, uint64_t k_off, gq_buf vcache, uint64_t v_off,
+                        gq_buf kscale, gq_buf vscale, gq_buf lens, uint64_t layer, uint64_t layers, uint64_t heads, uint64_t kv_heads, uint64_t dim,
+                        uint64_t max_len, float scale, gq_buf q_scratch, gq_buf out);
+/* lens[l] = min(lens[l] + count, max_len) for all layers — g2-kv-advance.glsl:18-21 for a whole prompt chunk. */
+int32_t gq_kv_advance_by(gq_ctx* ctx, gq_buf lens, uint64_t layers, uint64_t max_len, uint64_t count);
 /* out[r][j] = silu(gate_up[r][j]) * gate_up[r][width + j] — ops.rs:148-212, g2-swiglu.glsl:21-29. */
 int32_t gq_swiglu(gq_ctx* ctx, gq_buf gate_up, uint64_t rows, uint64_t width, gq_buf out);
 /* The next token of every row, chosen on the device — crates/grilly-infer/src/sampling.rs:1-60,

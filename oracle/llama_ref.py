@@ -24,8 +24,9 @@ def _deq(w: np.ndarray) -> np.ndarray:
 
 
 class DecoderRef:
-    def __init__(self, cfg, weights: dict, cos: np.ndarray, sin: np.ndarray) -> None:
+    def __init__(self, cfg, weights: dict, cos: np.ndarray, sin: np.ndarray, int8_kv: bool = False) -> None:
         self.cfg = cfg
+        self.int8_kv = int8_kv  # cached rows stored as rint(v / s) * s, s = float32(max|v|) / 127, as the int8 cache does
         self.embed = weights["embed"].astype(np.float64)
         self.head = _deq(weights["embed"])
         self.norm = weights["norm"].astype(np.float64)
@@ -50,6 +51,17 @@ class DecoderRef:
         rot = np.concatenate([-x[:, d // 2:], x[:, :d // 2]], axis=1)
         return x * self.cos[pos] + rot * self.sin[pos]
 
+    def _stored(self, rows):
+        """What the cache holds for these rows: themselves, or their int8 codes times the row's scale (the rows reach
+        the cache as float32, so the scale and the codes are formed from the float32 values)."""
+        if not self.int8_kv:
+            return rows
+        r32 = rows.astype(np.float32)
+        amax = np.abs(r32).max(axis=-1, keepdims=True)
+        scale = np.where(amax > 0, (amax / np.float32(127.0)).astype(np.float32), np.float32(1.0)).astype(np.float32)
+        codes = np.clip(np.rint((r32 / scale).astype(np.float32)), -127, 127)
+        return codes.astype(np.float64) * scale.astype(np.float64)
+
     def step(self, token: int) -> np.ndarray:
         c = self.cfg
         pos = self.length
@@ -61,7 +73,7 @@ class DecoderRef:
             v = lw["v"] @ x + lw["v_bias"]
             q, k = self._rope(q, pos), self._rope(k, pos)
             if pos < c.max_cache_len:
-                self.k[li, :, pos], self.v[li, :, pos] = k, v.reshape(-1, c.head_dim)
+                self.k[li, :, pos], self.v[li, :, pos] = self._stored(k), self._stored(v.reshape(-1, c.head_dim))
             n = min(pos + 1, c.max_cache_len)
             out = np.zeros((c.num_attention_heads, c.head_dim))
             rep = c.num_attention_heads // c.num_key_value_heads
