@@ -62,6 +62,8 @@ PROTOTYPES = {
     "gq_int4_quantize": [vp, u64, u64, u64, u64, u64, u64, u64, u64],
     "gq_int4_linear": [vp, u64, u64, u64, u64, u64, u64, u64, u64, u64, u64, u64, u64, i32],
     "gq_int4_dequantize": [vp, u64, u64, u64, u64, u64, u64, u64],
+    "gq_gptq_hessian_add": [vp, u64, u64, u64, u64, u64],
+    "gq_gptq_quantize": [vp, u64, u64, u64, u64, u64, u64, u64, u64, u64],
     "gq_begin_capture": [vp],
     "gq_end_capture": [vp, P(vp)],
     "gq_capturing": [vp, P(u32)],

@@ -686,6 +686,45 @@ int32_t gq_int4_linear(gq_ctx* ctx, gq_buf x, uint64_t x_off, uint64_t m, uint64
     });
 }
 
+// ── GPTQ ─────────────────────────────────────────────────────────────────
+
+int32_t gq_gptq_hessian_add(gq_ctx* ctx, gq_buf x, uint64_t x_off, uint64_t rows, uint64_t k, gq_buf hessian) {
+    return guarded([&] {
+        Locked l(ctx);
+        check_dims("gq_gptq_hessian_add", rows, k);
+        if (k == 0) fail("gq_gptq_hessian_add: no input features");
+        auto xp = (const float*)view(ctx, x, x_off, rows * k, 4, "gq_gptq_hessian_add inputs");
+        auto hp = (float*)view(ctx, hessian, 0, k * k, 4, "gq_gptq_hessian_add hessian");
+        if (rows == 0) return;
+        launch_hessian_add(ctx->stream, xp, rows, k, hp);
+        after_launch(ctx, "gptq_hessian_add", {x, hessian});
+    });
+}
+
+int32_t gq_gptq_quantize(gq_ctx* ctx, gq_buf work, uint64_t rows, uint64_t k, uint64_t group, gq_buf upper, gq_buf errors, gq_buf q, gq_buf scale,
+                         gq_buf zero) {
+    return guarded([&] {
+        Locked l(ctx);
+        check_dims("gq_gptq_quantize", rows, k);
+        check_group(group);
+        // python/grilly/infer/gptq.py:128-129
+        if (k == 0 || k % group) fail("in_features %llu must be a whole number of groups of %llu", (unsigned long long)k, (unsigned long long)group);
+        if (128 % group) fail("gq_gptq_quantize: group_size %llu is not implemented yet (32, 64 or 128: a group must lie inside a block of 128 columns)", (unsigned long long)group);
+        const uint64_t groups = k / group;
+        auto wp = (float*)view(ctx, work, 0, rows * k, 4, "gq_gptq_quantize working weight");
+        auto up = (const float*)view(ctx, upper, 0, k * k, 4, "gq_gptq_quantize inverse Cholesky factor");
+        auto ep = (float*)view(ctx, errors, 0, gptq_error_floats(rows), 4, "gq_gptq_quantize errors");
+        auto qp = (uint32_t*)view(ctx, q, 0, rows * words4(k), 4, "gq_gptq_quantize q");
+        auto sp = (float*)view(ctx, scale, 0, rows * groups, 4, "gq_gptq_quantize scale");
+        auto zp = (float*)view(ctx, zero, 0, rows * groups, 4, "gq_gptq_quantize zero");
+        if (rows == 0) return;
+        GQ_CUDA(cudaMemsetAsync(qp, 0, rows * words4(k) * 4, ctx->stream));  // padding words stay zero
+        launch_gptq(ctx->stream, wp, up, rows, k, group, ep, qp, sp, zp);
+        ctx->stats.launches += 2 * ((k + 127) / 128) - 1;
+        after_launch(ctx, "gptq", {work, upper, errors, q, scale, zero});
+    });
+}
+
 // ── capture / replay ─────────────────────────────────────────────────────
 
 int32_t gq_begin_capture(gq_ctx* ctx) {

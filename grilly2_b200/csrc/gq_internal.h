@@ -224,6 +224,11 @@ void comm_info(gq_comm* c, int* nranks, int* rank);
 void all_gather_columns(cudaStream_t s, gq_comm* c, const float* src, float* dst, uint64_t m, uint64_t n_shard);
 void launch_peer_gather(cudaStream_t s, int sm_count, const PeerOut& peer, const float* src, uint64_t m, uint64_t n_shard, uint32_t* status);
 
+// GPTQ (gptq.cu)
+void launch_hessian_add(cudaStream_t s, const float* x, uint64_t rows, uint64_t k, float* h);
+uint64_t gptq_error_floats(uint64_t n);
+void launch_gptq(cudaStream_t s, float* w, const float* u, uint64_t n, uint64_t k, uint64_t group, float* err, uint32_t* q, float* scale, float* zero);
+
 // decode-step operators (decode_ops.cu)
 void launch_embedding(cudaStream_t s, const float* table, const int32_t* ids, uint64_t rows, uint64_t width, uint64_t vocab, float* out);
 void launch_add_rms_norm(cudaStream_t s, const float* x, const float* res, const float* w, uint64_t rows, uint64_t n, float eps,

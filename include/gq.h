@@ -201,6 +201,23 @@ int32_t gq_int4_linear(gq_ctx* ctx, gq_buf x, uint64_t x_off, uint64_t m, uint64
 int32_t gq_int4_dequantize(gq_ctx* ctx, gq_buf q, gq_buf scale, gq_buf zero, uint64_t rows, uint64_t k,
                            uint64_t group, gq_buf w);
 
+/* ── GPTQ on the device ──────────────────────────────────────────────────
+ * The reference runs both in numpy on the host (python/grilly/infer/gptq.py:87-181, the column loop;
+ * python/grilly/infer/calibration.py:97-123, the Hessian capture): 263 s per model, docs/inference.md:357-359. */
+
+/* hessian[k][k] += 2 X^T X for the calibration rows X (rows, k) at x_off: GPTQ's H. float32, symmetric. */
+int32_t gq_gptq_hessian_add(gq_ctx* ctx, gq_buf x, uint64_t x_off, uint64_t rows, uint64_t k, gq_buf hessian);
+/* The column loop of gptq.py:150-178 on `work`, a float32 COPY of the weight (rows, k) that the call consumes:
+ * column by column each value is rounded to its int4 level with the group's parameters taken from the weights as
+ * they stand when the loop reaches the group, and the rounding error, divided by upper[j][j], is pushed into the
+ * columns not yet quantized along row j of `upper` — the (k, k) upper factor U, U^T U = H^-1 after damping, which
+ * the caller computes once per layer (gptq.py:68-84). Writes the packed levels, scales and zero points in the
+ * int4 layout (an Int4Weight). errors: scratch of rows * 128 floats. group_size 32, 64 or 128 (a group must lie
+ * inside a block of 128 columns); act_order / static_groups are not implemented. With a diagonal `upper` the
+ * result is gq_int4_quantize's, bit for bit. */
+int32_t gq_gptq_quantize(gq_ctx* ctx, gq_buf work, uint64_t rows, uint64_t k, uint64_t group, gq_buf upper, gq_buf errors, gq_buf q, gq_buf scale,
+                         gq_buf zero);
+
 /* ── capture / replay — crates/grilly-core/src/graph.rs:43-164,
  * device.rs:365-416, as CUDA graphs. Capture is context-wide: capture from
  * the thread that replays, with nothing else running on the context
