@@ -33,6 +33,18 @@ class Stats(ctypes.Structure):
         "persistent_peak", "uploads", "downloads")]
 
 
+class DecodeLayer(ctypes.Structure):
+    _fields_ = [(n, u64) for n in ("input_norm", "qkv_q", "qkv_scale", "qkv_bias", "o_q", "o_scale", "post_norm", "gate_up_q",
+                                   "gate_up_scale", "down_q", "down_scale")]
+
+
+class DecodeDesc(ctypes.Structure):
+    _fields_ = ([(n, u64) for n in ("hidden", "heads", "kv_heads", "dim", "inter", "vocab", "layers", "max_len")] +
+                [("eps", ctypes.c_float), ("attn_scale", ctypes.c_float)] +
+                [(n, u64) for n in ("embed", "final_norm", "head_q", "head_scale", "cos", "sin", "kcache", "vcache", "lens")] +
+                [("layer", P(DecodeLayer))])
+
+
 # name -> argument types; every function but the three noted returns int32 status
 PROTOTYPES = {
     "gq_create": [i32, P(vp)],
@@ -83,6 +95,8 @@ PROTOTYPES = {
     "gq_kv_advance_by": [vp, u64, u64, u64, u64],
     "gq_swiglu": [vp, u64, u64, u64, u64],
     "gq_argmax_rows": [vp, u64, u64, u64, u64],
+    "gq_decode_plan_create": [vp, P(DecodeDesc), P(vp)],
+    "gq_decode_plan_step": [vp, vp, u64, u64, u64],
     "gq_sample": [vp, u64, u64, u64, u64, u64, u64, u32, u32, ctypes.c_double, u64, ctypes.c_double, ctypes.c_double, u64, u64, u64, u64, u64, u64],
     "gq_comm_unique_id": [vp, u64],
     "gq_comm_create": [vp, i32, i32, vp, P(vp)],
@@ -93,7 +107,7 @@ PROTOTYPES = {
     "gq_int4_linear_gather": [vp, u64, u64, u64, u64, u64, u64, u64, u64, u64, u64, u64, i32, i32, P(u64), u64, u64],
     "gq_set_wait_limit_us": [vp, u64],
 }
-VOID_FUNCTIONS = {"gq_destroy": [vp], "gq_graph_destroy": [vp, vp], "gq_comm_destroy": [vp, vp]}
+VOID_FUNCTIONS = {"gq_destroy": [vp], "gq_graph_destroy": [vp, vp], "gq_comm_destroy": [vp, vp], "gq_decode_plan_destroy": [vp, vp]}
 
 _lib = None
 

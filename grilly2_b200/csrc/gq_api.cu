@@ -57,7 +57,7 @@ static uint64_t bucket_of(uint64_t bytes) {
     return cap;
 }
 
-static void drop_ref(gq_ctx* ctx, gq_buf h) {
+void drop_ref(gq_ctx* ctx, gq_buf h) {
     auto it = ctx->buffers.find(h);
     if (it == ctx->buffers.end()) return;
     Buffer& b = it->second;

@@ -115,6 +115,8 @@ struct Locked {  // serialises calls on a context and makes its device current
     }
 };
 Buffer& lookup(gq_ctx* ctx, gq_buf h, const char* what);
+// Gives back one reference to a buffer (a released handle's memory is freed with its last reference).
+void drop_ref(gq_ctx* ctx, gq_buf h);
 void check_dims(const char* op, uint64_t a, uint64_t b, uint64_t c = 1);
 
 

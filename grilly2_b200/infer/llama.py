@@ -129,8 +129,11 @@ class KvCache:
 class LlamaDecoder:
     """The quantized model and its cache; ``step(token)`` decodes one token."""
 
-    def __init__(self, cfg: LlamaConfig, weights: dict, fused: bool = True, int8_kv: bool = False) -> None:
+    def __init__(self, cfg: LlamaConfig, weights: dict, fused: bool = True, int8_kv: bool = False, persistent: bool = False) -> None:
         self.cfg = cfg
+        # persistent: the whole step as one cooperative kernel (gq_decode_plan_*) instead of a launch per operator
+        self.persistent = bool(persistent) and not int8_kv
+        self._plan = None
         # fused: norms and SwiGLU run inside the following projection (one launch each); needs row lengths that are multiples of 4
         self.fused = fused and cfg.hidden_size % 4 == 0 and cfg.intermediate_size % 4 == 0
         self.int8_kv = bool(int8_kv)
@@ -211,10 +214,48 @@ class LlamaDecoder:
         check(lib.gq_kv_advance_by(ctx, self.cache.lens.storage.handle, c.num_hidden_layers, c.max_cache_len, T))
         return logits
 
+    def _make_plan(self):
+        c, lib = self.cfg, _lib.load()
+        layers = (_lib.DecodeLayer * c.num_hidden_layers)()
+        for i, lw in enumerate(self.layers):
+            d = layers[i]
+            d.input_norm, d.post_norm = lw["input_norm"].storage.handle, lw["post_norm"].storage.handle
+            d.qkv_q, d.qkv_scale = lw["qkv"]._qt.storage.handle, lw["qkv"]._scale.storage.handle
+            d.qkv_bias = lw["qkv_bias"].storage.handle if lw["qkv_bias"] is not None else 0
+            d.o_q, d.o_scale = lw["o"]._qt.storage.handle, lw["o"]._scale.storage.handle
+            d.gate_up_q, d.gate_up_scale = lw["gate_up"]._qt.storage.handle, lw["gate_up"]._scale.storage.handle
+            d.down_q, d.down_scale = lw["down"]._qt.storage.handle, lw["down"]._scale.storage.handle
+        desc = _lib.DecodeDesc(hidden=c.hidden_size, heads=c.num_attention_heads, kv_heads=c.num_key_value_heads, dim=c.head_dim,
+                               inter=c.intermediate_size, vocab=c.vocab_size, layers=c.num_hidden_layers, max_len=c.max_cache_len,
+                               eps=c.rms_norm_eps, attn_scale=float(c.head_dim) ** -0.5, embed=self.embed.storage.handle,
+                               final_norm=self.norm.storage.handle, head_q=self.lm_head._qt.storage.handle,
+                               head_scale=self.lm_head._scale.storage.handle, cos=self.cos.storage.handle, sin=self.sin.storage.handle,
+                               kcache=self.cache.k.storage.handle, vcache=self.cache.v.storage.handle, lens=self.cache.lens.storage.handle,
+                               layer=layers)
+        out = ctypes.c_void_p()
+        check(lib.gq_decode_plan_create(_C.context(), ctypes.byref(desc), ctypes.byref(out)))
+        self._plan, self._plan_cache = out, (self.cache.k, self.cache.v, self.cache.lens)
+
+    def __del__(self):
+        try:
+            if self._plan is not None:
+                _lib.load().gq_decode_plan_destroy(_C.context(), self._plan)
+        except Exception:
+            pass
+
     def step(self, token: "_C.Tensor", want_argmax: bool = True):
         """token: int32 [1]. Returns (logits [1, vocab], next_token int32 [1]); advances the cache. With want_argmax
         False the greedy token is not computed (a sampler follows) and None is returned in its place."""
         c, lib, ctx = self.cfg, _lib.load(), _C.context()
+        if self.persistent:
+            if self._plan is None or self._plan_cache[0] is not self.cache.k or self._plan_cache[2] is not self.cache.lens:
+                if self._plan is not None:
+                    lib.gq_decode_plan_destroy(ctx, self._plan)
+                self._make_plan()  # names the cache's buffers: made anew when fill() replaced them
+            logits = _C.Tensor.empty((1, c.vocab_size), "float32")
+            nxt = _C.Tensor.empty((1,), "int32")
+            check(lib.gq_decode_plan_step(ctx, self._plan, token.storage.handle, logits.storage.handle, nxt.storage.handle))
+            return logits, nxt
         L, Hq, Hkv, D = c.num_hidden_layers, c.num_attention_heads, c.num_key_value_heads, c.head_dim
         hidden = _C.Tensor.empty((1, c.hidden_size), "float32")
         check(lib.gq_embedding(ctx, self.embed.storage.handle, token.storage.handle, 1, c.hidden_size, c.vocab_size, hidden.storage.handle))

@@ -320,6 +320,35 @@ int32_t gq_swiglu(gq_ctx* ctx, gq_buf gate_up, uint64_t rows, uint64_t width, gq
 int32_t gq_sample(gq_ctx* ctx, gq_buf logits, uint64_t rows, uint64_t vocab, gq_buf history, uint64_t hist_cap, gq_buf hist_len, uint32_t append,
                   uint32_t do_sample, double temperature, uint64_t top_k, double top_p, double repetition_penalty, gq_buf uniforms,
                   uint64_t uniform_rows, gq_buf draws, gq_buf scratch, gq_buf tokens, gq_buf probs);
+/* The whole decode step (one token, batch 1, int8 weights, float32 cache) as ONE persistent kernel: what
+ * python/grilly/infer/models/llama.py:353-366 issues as ~270 dispatches, and gq_embedding ... gq_argmax_rows above as
+ * ~125 launches, runs as phases of a single cooperative launch separated by grid-wide barriers, each CTA's share of
+ * every weight prefetched into shared memory phases ahead. Same results as the operator-by-operator step to float32
+ * rounding (the linears use the fixed-point arithmetic of the fast GEMV). The plan names the model's buffers (it
+ * retains them until it is destroyed) and owns its activations; a step reads the token from device memory, writes the
+ * logits and the greedy next token, appends to the cache at the device cursor and advances it: capture it and replay.
+ * Shapes: hidden, heads * dim and inter multiples of 16; hidden <= 4096, the other two <= 8192; dim 32, 64 or 128;
+ * kv_heads * 16 <= the SM count. Every wait inside is bounded by the context's wait limit (gq_set_wait_limit_us). */
+typedef struct gq_decode_layer {
+    gq_buf input_norm;                    /* float32 [hidden] */
+    gq_buf qkv_q, qkv_scale, qkv_bias;    /* int8 codes [(heads + 2 kv_heads) dim][hidden], scales, bias (0 = none) */
+    gq_buf o_q, o_scale;                  /* [hidden][heads dim] */
+    gq_buf post_norm;                     /* float32 [hidden] */
+    gq_buf gate_up_q, gate_up_scale;      /* gate rows then up rows: [2 inter][hidden] */
+    gq_buf down_q, down_scale;            /* [hidden][inter] */
+} gq_decode_layer;
+typedef struct gq_decode_desc {
+    uint64_t hidden, heads, kv_heads, dim, inter, vocab, layers, max_len;
+    float eps, attn_scale;
+    gq_buf embed, final_norm, head_q, head_scale; /* float32 table [vocab][hidden]; the (tied) head's int8 codes and scales */
+    gq_buf cos, sin;                              /* [max_len][dim] */
+    gq_buf kcache, vcache, lens;                  /* float32 [layers][kv_heads][max_len][dim]; uint32 [layers] */
+    const gq_decode_layer* layer;                 /* [layers] */
+} gq_decode_desc;
+typedef struct gq_decode_plan gq_decode_plan;
+int32_t gq_decode_plan_create(gq_ctx* ctx, const gq_decode_desc* desc, gq_decode_plan** out);
+int32_t gq_decode_plan_step(gq_ctx* ctx, gq_decode_plan* plan, gq_buf token, gq_buf logits, gq_buf next_token);
+void gq_decode_plan_destroy(gq_ctx* ctx, gq_decode_plan* plan);
 /* out[r] = index of the maximum of row r (int32; the first on ties) — g2-argreduce-rows.glsl:42-77. */
 int32_t gq_argmax_rows(gq_ctx* ctx, gq_buf v, uint64_t rows, uint64_t n, gq_buf out);
 

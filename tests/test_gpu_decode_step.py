@@ -31,13 +31,13 @@ def small_config():
                        head_dim=32, intermediate_size=256, max_cache_len=48)
 
 
-def build(cfg, seed, prefill, fused=True):
+def build(cfg, seed, prefill, fused=True, persistent=False):
     from grilly2_b200.infer import llama
     from oracle.llama_ref import DecoderRef
     w = llama.random_weights(cfg, seed=seed, sigma=0.05)
     for i, lw in enumerate(w["layers"]):  # non-trivial norm weights
         lw["input_norm"] = (1 + 0.1 * np.random.default_rng(100 + i).standard_normal(cfg.hidden_size)).astype(np.float32)
-    model = llama.LlamaDecoder(cfg, w, fused=fused)
+    model = llama.LlamaDecoder(cfg, w, fused=fused, persistent=persistent)
     cos, sin = llama.rotary_tables(cfg)
     ref = DecoderRef(cfg, w, cos, sin)
     if prefill:
@@ -108,5 +108,59 @@ def test_full_size_config5_step(fused):
     want = ref.step(12345)
     got = logits.numpy()[0]
     assert worst(got, want, f"config 5, fused {fused}") <= (TOL_FUSED if fused else TOL)
+    assert int(nxt.numpy()[0]) == int(np.argmax(want))
+    assert (model.cache.lengths() == 1024).all()
+
+
+@pytest.mark.parametrize("prefill", [0, 20, 47])
+def test_the_persistent_step_matches_the_float64_model_and_the_operator_by_operator_step(prefill):
+    """One cooperative kernel for the whole step: same tolerance against float64 as the launch-per-operator step, the
+    same greedy tokens, the same cache contents, and (captured) the same results when replayed."""
+    import grilly2_b200 as g
+    from grilly2_b200 import _C
+    cfg = small_config()
+    model, ref = build(cfg, 4, prefill, persistent=True)
+    twin, _ = build(cfg, 4, prefill)
+    token = 7
+    for step in range(min(4, cfg.max_cache_len - prefill)):  # up to the cache's last position (a full cache is the next test's)
+        t = _C.Tensor.from_numpy(np.array([token], dtype=np.int32))
+        logits, nxt = model.step(t)
+        lt, nt = twin.step(t)
+        want = ref.step(token)
+        got = logits.numpy()[0]
+        assert worst(got, want, f"persistent step, prefill {prefill}, step {step}") <= TOL
+        assert np.abs(got - lt.numpy()[0]).max() <= 2e-6 * np.abs(want).max()
+        assert int(nxt.numpy()[0]) == int(np.argmax(want)) == int(nt.numpy()[0])
+        np.testing.assert_array_equal(model.cache.lengths(), twin.cache.lengths())
+        token = int(nxt.numpy()[0])
+    np.testing.assert_allclose(model.cache.k.numpy(), twin.cache.k.numpy(), rtol=0, atol=2e-6)
+    np.testing.assert_allclose(model.cache.v.numpy(), twin.cache.v.numpy(), rtol=0, atol=2e-6)
+
+
+def test_the_persistent_step_replays_in_a_graph_and_saturates_a_full_cache():
+    import grilly2_b200 as g
+    from grilly2_b200 import _C
+    cfg = small_config()
+    eager, _ = build(cfg, 6, 40, persistent=True)
+    fast_model, _ = build(cfg, 6, 40, persistent=True)
+    fast = g.graphed(fast_model.step)
+    for tk in [5, 9, 11, 2, 40, 41, 3, 8, 1, 2]:  # ten steps from 40: the cache (48) fills up on the way
+        t = np.array([tk], dtype=np.int32)
+        le, ne = eager.step(_C.Tensor.from_numpy(t))
+        lf, nf = fast(_C.Tensor.from_numpy(t))
+        np.testing.assert_array_equal(lf.numpy(), le.numpy())
+        assert int(nf.numpy()[0]) == int(ne.numpy()[0])
+    assert (fast.misses, fast.captures, fast.replays) == (1, 1, 8)
+    assert (fast_model.cache.lengths() == cfg.max_cache_len).all()
+
+
+def test_full_size_config5_persistent_step():
+    from grilly2_b200 import _C
+    from grilly2_b200.infer import llama
+    cfg = llama.qwen25_05b(1024)
+    model, ref = build(cfg, 4, 1023, persistent=True)
+    logits, nxt = model.step(_C.Tensor.from_numpy(np.array([12345], dtype=np.int32)))
+    want = ref.step(12345)
+    assert worst(logits.numpy()[0], want, "config 5, persistent") <= TOL
     assert int(nxt.numpy()[0]) == int(np.argmax(want))
     assert (model.cache.lengths() == 1024).all()
