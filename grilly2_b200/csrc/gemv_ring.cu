@@ -374,10 +374,12 @@ __global__ void __launch_bounds__(kThreads, 1)
         // halves of the buffer alternate by step parity: a rank can be at most one step ahead of the slowest (it cannot
         // finish step s + 1 without that rank's step s + 1 words), so the words of step s are never overwritten before
         // they were read. The step word lives on the device, so a captured launch counts on by itself at every replay.
+        // (Letting only a few CTAs receive, so that the launch behind gets the other SMs early, measured no faster.)
+        const uint32_t receivers = gridDim.x;
         asm volatile("griddepcontrol.wait;" ::: "memory");  // y_full and the step word belong to the launch ahead until it is done
         if (!have_step) step = *reinterpret_cast<const volatile uint32_t*>(peer.state) + 1u;
         const uint32_t ctid = tid, total = MR * peer.n_full;
-        const uint32_t e0 = (uint32_t)((uint64_t)total * blockIdx.x / gridDim.x), e1 = (uint32_t)((uint64_t)total * (blockIdx.x + 1) / gridDim.x);
+        const uint32_t e0 = (uint32_t)((uint64_t)total * blockIdx.x / receivers), e1 = (uint32_t)((uint64_t)total * (blockIdx.x + 1) / receivers);
         const unsigned long long* mine = peer.ll[peer.rank] + ((size_t)(step & 1u) * peer.m_total + peer.row0) * peer.n_full;
         const long long start = clock64();
         for (uint32_t i = e0 + ctid; i < e1; i += kWarps * 32) {
@@ -395,7 +397,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         named_barrier_sync(3, kWarps * 32);
         if (ctid == 0) {
             __threadfence();
-            if (atomicAdd(peer.state + 1, 1u) == gridDim.x - 1) {  // the grid's last CTA: the call is finished
+            if (atomicAdd(peer.state + 1, 1u) == receivers - 1) {  // the last receiver: the call is finished
                 peer.state[1] = 0;
                 peer.state[0] = step;
             }

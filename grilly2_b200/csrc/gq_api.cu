@@ -965,7 +965,7 @@ int32_t gq_int4_linear_gather(gq_ctx* ctx, gq_buf x, uint64_t x_off, uint64_t m,
             const uint64_t rows = m - r < per_pass ? m - r : per_pass;
             peer.row0 = (uint32_t)r;
             if (!launch_gemv_q4_ring(ctx->stream, ctx->prop.multiProcessorCount, ctx->status_dev, xp + r * k, rows, k, qp, sp, zp, bp, n_shard, group, nullptr,
-                                     r == 0 ? weights_settled(ctx, {q, scale, zero}) : true, false, &peer))
+                                     r == 0 ? weights_settled(ctx, {q, scale, zero}) : true, r == 0 ? weights_settled(ctx, {x}) : x != y_full, &peer))
                 fail("gq_int4_linear_gather: the fused kernel takes group_size 128 and in_features 4096 or 8192 (m = %llu, k = %llu, group_size = %llu)",
                      (unsigned long long)m, (unsigned long long)k, (unsigned long long)group);
             if (r) ctx->stats.launches++;
