@@ -551,6 +551,8 @@ def main() -> None:
         tensor whose rows receive the outputs (one contiguous buffer)."""
         x = _C.Tensor.from_numpy(c3_x(m))
         outs = [None if out_all is None else out_all.window_rows(i, 1).reshape((m, out_all.shape[-1])) for i in range(len(ws))]
+        if variant != "fused":
+            ws[0].linear(x)  # first sighting of the shape runs eagerly (the context's scratch may grow), the second is recorded
         _C.begin_capture()
         ys = []
         for wt, o in zip(ws, outs):
@@ -660,6 +662,14 @@ def main() -> None:
             extras[f"c3_m{m}_us"] = us
             extras[f"c3_m{m}_GBps"] = algorithmic_bytes(m, n, k) / (us * 1e-6) / 1e9
             extras[f"c3_m{m}_frac_of_measured_hbm"] = extras[f"c3_m{m}_GBps"] / peak
+            # the same through the warp-level ring kernel alone (passes of four rows): what AUTO ran before the tcgen05 kernel
+            xr = _C.Tensor.from_numpy(c3_x(m))
+            weights[0].linear(xr, None, _lib.KERNEL_RING)
+            _C.begin_capture()
+            keep = [wt.linear(xr, None, _lib.KERNEL_RING) for wt in weights]
+            gr = _C.end_capture()
+            extras[f"c3_m{m}_ring_passes_us"] = timed(gr, steps2, 3) * 1e3 / (steps2 * len(weights))
+            del gr, keep
         us, _ = time_variant(1, "linear", [weights[0]] * reps)
         extras["c3_m1_l2_hot_us"] = us
         del weights[1:]
@@ -671,6 +681,7 @@ def main() -> None:
 
         def c2_graph(m, ws, kernel=_lib.KERNEL_AUTO):
             xx = _C.Tensor.from_numpy(x2[:m])
+            ws[0].linear(xx, None, kernel)  # first sighting eagerly, as above
             _C.begin_capture()
             keep = [w.linear(xx, None, kernel) for w in ws]
             return keep, _C.end_capture()
@@ -683,6 +694,9 @@ def main() -> None:
             del gm, keep
         keep, gm = c2_graph(1, [ws2[0]] * 16)
         extras["c2_m1_l2_hot_us"] = timed(gm, steps2, 3) * 1e3 / (steps2 * 16)
+        del gm, keep
+        keep, gm = c2_graph(16, ws2, _lib.KERNEL_RING)
+        extras["c2_m16_ring_passes_us"] = timed(gm, max(steps2 // 4, 5), 3) * 1e3 / (max(steps2 // 4, 5) * 16)
         del gm, keep
         for label, kern in (("imma_streaming", _lib.KERNEL_IMMA), ("dp4a", _lib.KERNEL_DP4A), ("reference_order_float", _lib.KERNEL_GEMV)):
             keep, gm = c2_graph(1, ws2, kern)

@@ -181,6 +181,13 @@ def _check_linear(kind, input, bias, n, k):
     return out_shape, m
 
 
+def _check_grad(kind, grad, n):
+    _require(grad, F32, "linear backward")
+    if not grad.shape or grad.shape[-1] != n:
+        raise RuntimeError(f"linear backward: grad {list(grad.shape)} does not end in out_features = {n}")
+    return grad.numel() // max(n, 1)
+
+
 def _output(out, shape):
     """A fresh output, or the caller's: float32, the right size, at the start of its buffer (the operators write there)."""
     if out is None:
@@ -295,6 +302,18 @@ class Int8Weight:
                                   self._scale.storage.handle, bias.storage.handle if bias is not None else 0,
                                   bias.offset if bias is not None else 0, n, y.storage.handle, kernel))
         return y
+
+    def linear_backward(self, grad: Tensor, need_input: bool = True, need_bias: bool = False):
+        """(grad_input, grad_bias) of ``linear`` with the weight frozen: grad @ dequantize(W) and grad summed over the
+        leading dimensions (crates/grilly-infer/src/quant.rs:326-349). The weight itself gets no gradient."""
+        n, k = self._shape
+        m = _check_grad("int8", grad, n)
+        gx = Tensor.empty(tuple(grad.shape[:-1]) + (k,), F32) if need_input else None
+        gb = Tensor.empty((n,), F32) if need_bias else None
+        check(_l().gq_int8_linear_backward(context(), grad.storage.handle, grad.offset, m, self._qt.storage.handle,
+                                           self._scale.storage.handle, n, k, gx.storage.handle if gx is not None else 0,
+                                           gb.storage.handle if gb is not None else 0))
+        return gx, gb
 
     def linear_norm(self, x: Tensor, residual: Tensor | None, norm_weight: Tensor, eps: float, bias: Tensor | None = None,
                     want_sum: bool = False):
@@ -470,6 +489,18 @@ class Int4Weight:
                                   bias.storage.handle if bias is not None else 0,
                                   bias.offset if bias is not None else 0, n, self._group, y.storage.handle, kernel))
         return y
+
+
+    def linear_backward(self, grad: Tensor, need_input: bool = True, need_bias: bool = False):
+        """(grad_input, grad_bias) of ``linear`` with the weight frozen (crates/grilly-infer/src/quant4.rs:447-480)."""
+        n, k = self._shape
+        m = _check_grad("int4", grad, n)
+        gx = Tensor.empty(tuple(grad.shape[:-1]) + (k,), F32) if need_input else None
+        gb = Tensor.empty((n,), F32) if need_bias else None
+        check(_l().gq_int4_linear_backward(context(), grad.storage.handle, grad.offset, m, self._qt.storage.handle,
+                                           self._scale.storage.handle, self._zero.storage.handle, n, k, self._group,
+                                           gx.storage.handle if gx is not None else 0, gb.storage.handle if gb is not None else 0))
+        return gx, gb
 
 
 # ── capture, statistics (crates/grilly-py/src/ops.rs:484,584,611-657) ─────

@@ -106,6 +106,8 @@ PROTOTYPES = {
     "gq_peer_gather": [vp, u64, u64, u64, i32, i32, P(u64), u64, u64],
     "gq_int4_linear_gather": [vp, u64, u64, u64, u64, u64, u64, u64, u64, u64, u64, u64, i32, i32, P(u64), u64, u64],
     "gq_set_wait_limit_us": [vp, u64],
+    "gq_int8_linear_backward": [vp, u64, u64, u64, u64, u64, u64, u64, u64, u64],
+    "gq_int4_linear_backward": [vp, u64, u64, u64, u64, u64, u64, u64, u64, u64, u64, u64],
 }
 VOID_FUNCTIONS = {"gq_destroy": [vp], "gq_graph_destroy": [vp, vp], "gq_comm_destroy": [vp, vp], "gq_decode_plan_destroy": [vp, vp]}
 

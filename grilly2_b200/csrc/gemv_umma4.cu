@@ -2,22 +2,18 @@
 // fifth-generation tensor cores (tcgen05.mma kind::i8, accumulators in tensor
 // memory), ONE pass over the weight whatever the number of rows.
 //
-// Why it is shaped like this (measured on B200 with a loop of back-to-back
-// instructions at full clock): a kind::i8 tcgen05.mma takes ~83 ns (~163
-// cycles at 1965 MHz; ~175 when a fresh A tile streams from shared memory)
-// whatever M (64 / 128) and N (<= 128) are. Time therefore goes with the
-// NUMBER of instructions, so the operand that is streamed — the weight — is
-// the 128-row A operand, each instruction eats 128 features x 32 bytes of it,
-// and every row of x rides along for free as more columns of B (N = 16, 32 or
-// 64). The same figure is this formulation's ceiling: two instructions per 4 KB
-// of packed weight and SM is 3.6 TB/s over 148 SMs, 0.56 of the measured HBM
-// rate, at ANY number of rows up to 16 — above what the warp-level kernel
-// reaches in passes of four rows, below what it reaches at one to four rows,
-// which is why AUTO keeps that kernel and this one is chosen with
-// GQ_KERNEL_UMMA. Today it runs at about half its ceiling (14336 x 4096: ~26 us
-// at 1 row, ~51 us at 16): stores to tensor memory do not overlap the
-// multiplications they feed, and the drain warps' per-group work is latency
-// bound.
+// Why it is shaped like this (measured on B200 with loops of back-to-back
+// instructions): a kind::i8 tcgen05.mma takes ~83 ns for any N up to 64, ~92 ns
+// at N = 128 and ~133 ns at N = 256 (M = 64; K = 32 bytes). Time goes with the
+// NUMBER of instructions far more than with their width, so the operand that is
+// streamed — the weight — is the WIDE one: it is the B operand, up to 256
+// features x 32 bytes per instruction, read by the tensor core straight from the
+// shared memory the TMA wrote it to, and the rows of x are the 64-row A operand
+// (16 rows x 4 digit planes). Two instructions per 8 KB of packed weight and SM
+// = 4.5 TB/s over 148 SMs, 0.69 of the measured HBM rate, at ANY number of rows
+// up to 16. (A first version streamed the weight as the 128-row A operand out
+// of tensor memory: half the bytes per instruction, and the stores to tensor
+// memory did not overlap the multiplications they fed.)
 //
 // Arithmetic. The packed weight is never unpacked to one byte per level. Byte
 // j of a group of 128 k holds levels 2j (low nibble) and 2j + 1 (high nibble):
@@ -25,40 +21,41 @@
 // the group, and U_j = X[2j], V_j = X[2j+1] - 16 X[2j] (|V| < 2^31):
 //     sum_k level_k X_k = sum_j b_j U_j + sum_j hi_j V_j .
 // The first sum multiplies the RAW bytes exactly as they lie in HBM (u8); the
-// second needs only the high nibbles, (w >> 4) & 0x0f0f0f0f. Four warps copy
-// both to TENSOR MEMORY (tcgen05.st), the A operand of all four instructions. U and V are split in four signed base-256
-// digits, the columns of B (column 4 r + d = digit d of row r of x); all four
-// MMAs of a group (two 32-byte K slices, raw and high) accumulate into one
-// int32 tile D[128 features][N] — exact. Eight warps drain D group by group
-// (a thread owns a feature, i.e. a TMEM lane), recombine the digits in float32,
-// and apply the group's scale and zero point as the reference does:
+// second needs only the high nibbles, (w >> 4) & 0x0f0f0f0f, which four warps
+// write to a second shared-memory buffer (a thread = two feature rows; the same
+// threads bring the stage's scales and zero points). U and V are split in four
+// signed base-256 digits, the rows of A (one row per row of x and digit); all
+// four MMAs of a group (two 32-byte K slices, raw and high) accumulate into one
+// int32 tile D[64][features] — exact. An M = 64 accumulator occupies lanes 0-15
+// of each 32-lane quarter of tensor memory, so the two groups of a stage sit in
+// the lower and upper half-lanes of the same columns, and sixteen warps drain
+// both with 16-lane loads (every thread busy). The rows are ordered so that a
+// thread receives digits 2 p and 2 p + 1 of one row of x: it joins them as
+// integers (D + 256 D'), converts once, and applies the group's scale and zero
+// point as the reference does:
 //     y[r][f] = sum_g  s[f][g] (sum_k level x) + (zero[f][g] - 8 s[f][g]) (sum_k x).
 // The only approximation is X (2^-27 of the group's max |x|). A non-finite x
 // gives NaN outputs.
 //
 // Work split. The digits of x for all of K do not fit shared memory beside the
 // weight ring when there are many rows (16 rows x 4096 k = 256 KB), so K is cut
-// in slices: CTA c works on slice c % slices for the feature tiles
-// c / slices, + lanes, ... and keeps only its slice's digits (<= 64 KB). With
-// more than one slice the partial sums go to a scratch buffer and the last CTA
-// to finish a tile (a counter per tile, left at zero again) adds them in slice
-// order — deterministic — and writes y. The host picks (slices, tile height) to
-// minimise instructions per CTA (gemv_umma4_plan).
+// in slices: CTA c works on slice c % slices for the feature tiles c / slices,
+// + lanes, ... and converts and keeps only its slice of x. With more than one
+// slice the partial sums go to a scratch buffer and a second, small kernel adds
+// them in slice order (deterministic) and adds the bias. The host picks
+// (slices, tile width) to minimise the busiest CTA's time (make_plan).
 //
-// Pipeline per CTA: warp 0 = TMA producer (one box of tile_rows x 128 bytes =
-// two groups per stage, 128-byte swizzle, 4 to 8 stages); warp 1 = MMA issuer
-// and TMEM owner; warps 4-7 move a stage's raw bytes and high nibbles to tensor
-// memory (both A operands are read from there); warps 8-15 = drain. x is
-// converted to digit tiles once per call by a small kernel of its own
-// (x_digits_kernel), and each CTA bulk-copies its slice's tiles. Every wait is
-// bounded (status word -> GQ_ERR).
+// Pipeline per CTA (704 threads): warp 0 = TMA producer (one box of tile_rows x
+// 128 bytes = two groups per stage, 128-byte swizzle); warp 1 = MMA issuer and
+// TMEM owner; warps 2-5 = high nibbles + scales, a stage at a time; warps
+// 6-21 = drain. Every wait is bounded (status word -> GQ_ERR).
 //
 // Replaces, for these shapes, the decode branch of Int4Weight::linear
 // (crates/grilly-infer/src/quant4.rs:371-442, g2-linear-q4.glsl:43-111), which
 // reads W twice at 16 rows; this reads it once.
 // Algorithmic bytes per launch: packed weights + scales + zeros + x + y
 // (+ bias). Bound: HBM bandwidth, with the tensor-core instruction count
-// (K / 64 per 128 features) about level with it.
+// (K / 64 per 256 features) just above it.
 #include <type_traits>
 
 #include "gq_internal.h"
@@ -68,27 +65,28 @@ namespace gq {
 
 namespace {
 
-constexpr int kThreads = 512;
-constexpr uint32_t kStageBytes = 128 * 128;  // 128 feature rows x 128 raw bytes (two groups)
-constexpr int kMaxStages = 8;
-constexpr int kMinStages = 4;
-constexpr uint32_t kMaxTilesPerCta = 64;     // tiles whose partial sums a CTA may have outstanding when K is split
-constexpr uint32_t kDBufs = 4;               // accumulator tiles in flight
-constexpr uint32_t kACol0 = 256;             // TMEM columns 0-255: D ring; 256-447: three A tiles of 64 columns (32 raw, 32 high nibbles)
-constexpr uint32_t kABufs = 3;
-constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kSmemBudget = 224 * 1024;
-constexpr uint64_t kCounterBytes = 256 * 1024;  // the scratch begins with the tiles' arrival counters (always at the same place, so
-                                                // that they are zero between launches whatever shapes share the scratch), then the partial sums
+constexpr int kThreads = 704;  // 88 registers per thread
+constexpr uint32_t kFirstNibbleWarp = 2, kNibbleWarps = 4, kFirstDrainWarp = 6, kDrainWarps = 16;
+constexpr uint32_t kTileMax = 256;   // features per tile = N of the instruction
+constexpr uint32_t kSzSlots = 4;     // stages whose scales are in shared memory at a time
+constexpr int kMaxStages = 4;
+constexpr int kMinStages = 2;
+constexpr uint32_t kTmemCols = 512;  // two accumulators of 256 columns
+constexpr uint32_t kSmemBudget = 227 * 1024;
+constexpr uint32_t kMaxTileStages = 16;  // stages of a tile (pairs of groups of a K slice)
+constexpr uint32_t kBarrierBytes = (2 * kMaxStages + 2 + 4 + kMaxTileStages) * 8 + 16;
 
 struct Plan {
     uint32_t slices, gps, tile_rows, tiles, lanes, grid;
-    uint32_t nstages;      // ring depth: what the digits leave of shared memory
-    uint32_t digit_bytes;  // bytes of one group's digit tile: NC rows of 128 bytes, or 8 rows when x has one or two rows (the
-                           // descriptor then reads the same eight rows for every 8-column block of B: columns 8.. repeat 0..7)
+    uint32_t nstages;   // ring depth: what the digits leave of shared memory
+    uint32_t rows_pad;  // digit rows kept per group: 16, 32 or 64 (4 per row of x); the instruction reads 64, the rest is whatever follows
 };
 
-// digits of one group's tile: row n (column of D) of 128 bytes — bytes 0-63 the digits of U, 64-127 of V — in 8-row
+// Row of A (and of the accumulator) that holds digit d of row r of x: rows 16 s .. 16 s + 15 go to quarter s of tensor
+// memory, and a 16-lane load hands a thread rows j and j + 8 of it, so digit pairs (0, 1) and (2, 3) sit 8 rows apart.
+__device__ __forceinline__ uint32_t digit_row(uint32_t r, uint32_t d) { return 16u * (r >> 2) + 2u * (r & 3u) + (d >> 1) + 8u * (d & 1u); }
+
+// digits of one group's tile: row n of 128 bytes — bytes 0-63 the digits of U, 64-127 of V — in 8-row
 // 128-byte-swizzled atoms, as the tensor core's K-major descriptors read them.
 __device__ __forceinline__ uint32_t digit_offset(uint32_t n, uint32_t o) {
     return (n >> 3) * 1024u + (n & 7u) * 128u + ((((o >> 4) ^ n) & 7u) << 4) + (o & 15u);
@@ -105,152 +103,203 @@ __device__ __forceinline__ void split_digits(int X, uint32_t (&word)[4], int shi
     word[2] |= ((uint32_t)d2 & 0xFFu) << shift, word[3] |= ((uint32_t)d3 & 0xFFu) << shift;
 }
 
-// x -> digit tiles, once per call: CTA = eight half-warps, a half-warp converts one (group, row) of 128 values, lane l the
-// 8 values 8 l .. 8 l + 7. Output: groups tiles of `dbytes` in the layout above, then per group 16 (sum of x, 2^(e-26)) pairs.
-__global__ void __launch_bounds__(128) x_digits_kernel(const float* __restrict__ x, uint32_t m, uint32_t k, uint32_t groups, uint32_t dbytes,
-                                                       uint8_t* __restrict__ out) {
-    GQ_GRID_DEP_SYNC();
-    const uint32_t lane = threadIdx.x & 31, l = lane & 15u;
-    const uint32_t item = (blockIdx.x * 128 + threadIdx.x) >> 4;
-    if (item >= groups * m) return;  // uniform per half-warp; the shuffles below stay inside the half
-    const uint32_t hmask = 0xFFFFu << (lane & 16u);
-    uint8_t* digits = out;
-    float2* xsinv = reinterpret_cast<float2*>(out + (size_t)groups * dbytes);
-    {
-          {
-            const uint32_t gl = item / m, r = item - gl * m;
-            const float* xr = x + (size_t)r * k + (size_t)gl * 128u + 8u * l;
-            const float4 a = __ldg(reinterpret_cast<const float4*>(xr)), b = __ldg(reinterpret_cast<const float4*>(xr) + 1);
-            const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-            float amax = 0.0f;
-            bool bad = false;
+// One (group, row) of x = 128 values -> its rows of the group's digit tile and its (sum of x, 2^(e-26)) pair; a half-warp
+// does it, lane l the 8 values 8 l .. 8 l + 7 (already loaded: a, b).
+__device__ __forceinline__ void convert_item(const float4 a, const float4 b, uint32_t l, uint32_t hmask, uint8_t* tile, uint32_t r, float2* xs_out) {
+    const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    float amax = 0.0f;
+    bool bad = false;
 #pragma unroll
-            for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i])), bad |= !(fabsf(v[i]) <= 3.402823466e+38f);
-            if (bad) amax = __uint_as_float(0x7f800000u);
+    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i])), bad |= !(fabsf(v[i]) <= 3.402823466e+38f);
+    if (bad) amax = __uint_as_float(0x7f800000u);
 #pragma unroll
-            for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(hmask, amax, o));
-            uint32_t e = __float_as_uint(amax) >> 23;
-            float mult, inv;
-            if (e == 255) {
-                mult = 0.0f, inv = __uint_as_float(0x7fc00000u);
-            } else if (amax == 0.0f) {
-                mult = inv = 0.0f;
-            } else {
-                e = max(e, 32u);
-                mult = __uint_as_float((279u - e) << 23);  // 2^(26 - e'), 2^e' > amax
-                inv = __uint_as_float((e - 25u) << 23);    // 2^(e' - 26)
-            }
-            uint32_t uw[4] = {0u, 0u, 0u, 0u}, vw[4] = {0u, 0u, 0u, 0u};
-            int sum_lo = 0, sum_hi = 0;  // X = lo + 65536 hi, lo a signed 16-bit number: both sums stay inside int32
-#pragma unroll
-            for (int p = 0; p < 4; ++p) {
-                const int X0 = __float2int_rn(v[2 * p] * mult), X1 = __float2int_rn(v[2 * p + 1] * mult);
-                const int l0 = (int)(int16_t)X0, l1 = (int)(int16_t)X1;
-                sum_lo += l0 + l1, sum_hi += ((X0 - l0) >> 16) + ((X1 - l1) >> 16);
-                split_digits(X0, uw, 8 * p);
-                split_digits(X1 - 16 * X0, vw, 8 * p);
-            }
-#pragma unroll
-            for (int o = 8; o > 0; o >>= 1) {
-                sum_lo += __shfl_xor_sync(hmask, sum_lo, o);
-                sum_hi += __shfl_xor_sync(hmask, sum_hi, o);
-            }
-            uint8_t* tile = digits + (size_t)gl * dbytes;
-#pragma unroll
-            for (int d = 0; d < 4; ++d) {
-                *reinterpret_cast<uint32_t*>(tile + digit_offset(4 * r + d, 4 * l)) = uw[d];
-                *reinterpret_cast<uint32_t*>(tile + digit_offset(4 * r + d, 64 + 4 * l)) = vw[d];
-            }
-            if (l == 0) xsinv[gl * 16 + r] = make_float2(__fmaf_rn((float)sum_hi, 65536.0f, (float)sum_lo) * inv, inv);
-          }
+    for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(hmask, amax, o));
+    uint32_t e = __float_as_uint(amax) >> 23;
+    float mult, inv;
+    if (e == 255) {
+        mult = 0.0f, inv = __uint_as_float(0x7fc00000u);
+    } else if (amax == 0.0f) {
+        mult = inv = 0.0f;
+    } else {
+        e = max(e, 32u);
+        mult = __uint_as_float((279u - e) << 23);  // 2^(26 - e'), 2^e' > amax
+        inv = __uint_as_float((e - 25u) << 23);    // 2^(e' - 26)
     }
+    uint32_t uw[4] = {0u, 0u, 0u, 0u}, vw[4] = {0u, 0u, 0u, 0u};
+    int sum_lo = 0, sum_hi = 0;  // X = lo + 65536 hi, lo a signed 16-bit number: both sums stay inside int32
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+        const int X0 = __float2int_rn(v[2 * p] * mult), X1 = __float2int_rn(v[2 * p + 1] * mult);
+        const int l0 = (int)(int16_t)X0, l1 = (int)(int16_t)X1;
+        sum_lo += l0 + l1, sum_hi += ((X0 - l0) >> 16) + ((X1 - l1) >> 16);
+        split_digits(X0, uw, 8 * p);
+        split_digits(X1 - 16 * X0, vw, 8 * p);
+    }
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) {
+        sum_lo += __shfl_xor_sync(hmask, sum_lo, o);
+        sum_hi += __shfl_xor_sync(hmask, sum_hi, o);
+    }
+#pragma unroll
+    for (int d = 0; d < 4; ++d) {
+        *reinterpret_cast<uint32_t*>(tile + digit_offset(digit_row(r, d), 4 * l)) = uw[d];
+        *reinterpret_cast<uint32_t*>(tile + digit_offset(digit_row(r, d), 64 + 4 * l)) = vw[d];
+    }
+    if (l == 0) *xs_out = make_float2(__fmaf_rn((float)sum_hi, 65536.0f, (float)sum_lo) * inv, inv);
 }
 
-template <int NC>
+// x -> digit tiles, once per call: CTA = eight half-warps, a half-warp converts one (group, row) of 128 values. Output:
+// `groups` tiles of rows_pad x 128 bytes in the layout above (the rows of x the call does not have are zero), then per
+// group 16 (sum of x, 2^(e-26)) pairs (zero for rows m .. 15).
+__global__ void __launch_bounds__(128) x_digits_kernel(const float* __restrict__ x, uint32_t m, uint32_t k, uint32_t groups, uint32_t rows_pad,
+                                                       uint8_t* __restrict__ out) {
+    GQ_GRID_DEP_SYNC();
+    const uint32_t lane = threadIdx.x & 31, l = lane & 15u, hmask = 0xFFFFu << (lane & 16u);
+    const uint32_t item = (blockIdx.x * 128 + threadIdx.x) >> 4, rows = rows_pad >> 2;
+    if (item >= groups * rows) return;  // uniform per half-warp
+    const uint32_t gl = item / rows, r = item - gl * rows;
+    uint8_t* tile = out + (size_t)gl * rows_pad * 128u;
+    float2* xsinv = reinterpret_cast<float2*>(out + (size_t)groups * rows_pad * 128u) + gl * 16;
+    if (r >= m) {
+#pragma unroll
+        for (uint32_t d = 0; d < 4; ++d) {
+            *reinterpret_cast<uint32_t*>(tile + digit_offset(digit_row(r, d), 4 * l)) = 0u;
+            *reinterpret_cast<uint32_t*>(tile + digit_offset(digit_row(r, d), 64 + 4 * l)) = 0u;
+        }
+        if (l == 0) xsinv[r] = make_float2(0.0f, 0.0f);
+        if (r == rows - 1 && l < 16 - rows) xsinv[rows + l] = make_float2(0.0f, 0.0f);  // the pairs of rows beyond rows_pad / 4
+        return;
+    }
+    const float4* p = reinterpret_cast<const float4*>(x + (size_t)r * k + (size_t)gl * 128u + 8u * l);
+    convert_item(__ldg(p), __ldg(p + 1), l, hmask, tile, r, xsinv + r);
+    if (r == rows - 1 && l < 16 - rows) xsinv[rows + l] = make_float2(0.0f, 0.0f);
+}
+
+// Shared-memory matrix descriptor for a K-major operand of 32 bytes of K in unswizzled core-matrix order: a core matrix is
+// 8 rows x 16 bytes stored contiguously (128 bytes); the two core matrices of a row block lie `lbo` bytes apart, row
+// blocks `sbo` bytes apart.
+__device__ __forceinline__ uint64_t umma_desc_plain(uint32_t smem_addr, uint32_t lbo, uint32_t sbo) {
+    return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo >> 4) << 16) | ((uint64_t)(sbo >> 4) << 32) | ((uint64_t)1 << 46);
+}
+
+// 16 lanes x 256 bits, eight times along the columns: register 4 i + {0, 1} = lane (t / 4), columns 8 i + 2 (t % 4) + {0, 1};
+// register 4 i + {2, 3} = lane (t / 4) + 8, same columns (t = the thread's index in the warp). No memory clobber: the compiler
+// may move shared-memory loads across it; what orders the registers' uses is tmem_wait_ld_of.
+__device__ __forceinline__ void tmem_ld_16x256b_x8(uint32_t addr, uint32_t (&r)[32]) {
+    asm volatile("tcgen05.ld.sync.aligned.16x256b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(addr));
+}
+// Waits for the thread's loads from tensor memory; the registers pass through it, so nothing reads them earlier.
+__device__ __forceinline__ void tmem_wait_ld_of(uint32_t (&r)[32]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31]));
+}
+
+// two float32 lanes in one 64-bit register: d = a * b + c on both
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ float2 unpack2(uint64_t v) {
+    float2 r;
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(r.x), "=f"(r.y) : "l"(v));
+    return r;
+}
+__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+
 __global__ void __launch_bounds__(kThreads, 1)
     gemv_q4_umma_kernel(const __grid_constant__ CUtensorMap wmap, const uint8_t* __restrict__ xdigits, const float* __restrict__ scale,
                         const float* __restrict__ zero, const float* __restrict__ bias, float* __restrict__ y, float* __restrict__ partials,
-                        uint32_t* __restrict__ counters, uint32_t m, uint32_t k, uint32_t n, uint32_t groups, Plan plan, uint32_t* status) {
+                        uint32_t m, uint32_t k, uint32_t n, uint32_t groups, Plan plan, uint32_t* status) {
     extern __shared__ uint8_t smem_unaligned[];
     uint8_t* smem = smem_unaligned + ((1024u - (smem_u32(smem_unaligned) & 1023u)) & 1023u);
-    const uint32_t nstages = plan.nstages, dbytes = plan.digit_bytes;
-    const uint32_t b_sbo = dbytes == 1024u ? 0u : 1024u;  // stride between 8-column blocks of B (0: all blocks read the same eight rows)
-    uint8_t* ring = smem;                                          // nstages x 16 KB
-    uint8_t* digits = ring + (size_t)nstages * kStageBytes;        // gps tiles of dbytes
-    float2* xsinv = reinterpret_cast<float2*>(digits + (size_t)plan.gps * dbytes);  // [gps][16]: (sum of x, 2^(e-26)) per group and row
-    uint64_t* full = reinterpret_cast<uint64_t*>(xsinv + (size_t)plan.gps * 16);
+    const uint32_t nstages = plan.nstages, gps = plan.gps, tile_rows = plan.tile_rows;
+    const uint32_t stage_bytes = tile_rows * 128u, dstride = plan.rows_pad * 128u, slot_bytes = tile_rows * 16u;
+    uint8_t* ring = smem;                                    // nstages x (tile_rows x 128 raw bytes, as the TMA leaves them)
+    uint8_t* digits = ring + (size_t)nstages * stage_bytes;  // gps tiles of dstride bytes (the instruction reads 8 KB from each: the tail is whatever follows)
+    uint8_t* hibuf = digits + (size_t)gps * dstride;         // the high nibbles of a stage: four K slices of tile_rows x 32 bytes
+    uint8_t* szring = hibuf + stage_bytes;                   // kSzSlots x [2 groups][tile_rows / 2] float4 (s, s', z - 8 s, z' - 8 s') of two features
+    float2* xsinv = reinterpret_cast<float2*>(szring + kSzSlots * slot_bytes);  // [gps][16]: (sum of x, 2^(e-26)) per group and row
+    uint64_t* full = reinterpret_cast<uint64_t*>(xsinv + (size_t)gps * 16);
     uint64_t* empty = full + kMaxStages;
-    uint64_t* afull = empty + kMaxStages;   // [4] an A tile is in tensor memory
-    uint64_t* aempty = afull + 4;        // [4] ... and has been multiplied
-    uint64_t* dfull = aempty + 4;        // [kDBufs] an accumulator is complete
-    uint64_t* dempty = dfull + kDBufs;   // [kDBufs] ... and has been read out
-    uint64_t* dgfull = dempty + kDBufs;  // the slice's digit tiles have landed
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dgfull + 1);
+    uint64_t* hfull = empty + kMaxStages;  // the stage's high nibbles and scales are in shared memory
+    uint64_t* hempty = hfull + 1;          // ... and the nibbles have been multiplied
+    uint64_t* dfull = hempty + 1;          // [2] an accumulator (two groups) is complete
+    uint64_t* dempty = dfull + 2;          // [2] ... and has been read out
+    uint64_t* dgfull = dempty + 2;         // [kMaxTileStages] the digit tiles of the slice's stage i are in shared memory
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dgfull + kMaxTileStages);
     volatile uint32_t* failed = tmem_slot + 1;
-    uint32_t* last_flags = tmem_slot + 2;  // [kMaxTilesPerCta] K split: was this CTA the last to finish the tile
 
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t slice = blockIdx.x % plan.slices, tlane = blockIdx.x / plan.slices;
-    const uint32_t g_begin = slice * plan.gps, g_end = min(groups, g_begin + plan.gps);
+    const uint32_t g_begin = slice * gps, g_end = min(groups, g_begin + gps);
     const uint32_t ngroups = g_end > g_begin ? g_end - g_begin : 0u;
     const uint32_t nstage_tile = (ngroups + 1) >> 1;
-    constexpr uint32_t kDrainWarps = NC == 64 ? 8 : 4;
+    const uint32_t my_tiles = (ngroups && tlane < plan.tiles) ? (plan.tiles - tlane + plan.lanes - 1) / plan.lanes : 0u;
 
-    GQ_GRID_DEP_SYNC();
+    // The kernel ahead in the stream is always this call's x_digits_kernel, which itself began by waiting for everything
+    // before it: the weights, scales and zero points are settled, and only the digit tiles are still being written. So the
+    // set-up and the first weight stages run while that kernel does; the digit copies alone wait for it (below).
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (tid == 0) {
         for (uint32_t s = 0; s < nstages; ++s) {
             mbar_init(full + s, 1);
-            mbar_init(empty + s, 4);  // the four warps that read a stage out
+            mbar_init(empty + s, 1 + kNibbleWarps);  // the raw multiplications (one commit) and the warps that read the stage
         }
-        for (uint32_t a = 0; a < kABufs; ++a) {
-            mbar_init(afull + a, 4);
-            mbar_init(aempty + a, 1);
-        }
-        for (uint32_t d = 0; d < kDBufs; ++d) {
+        mbar_init(hfull, kNibbleWarps);
+        mbar_init(hempty, 1);
+        for (uint32_t d = 0; d < 2; ++d) {
             mbar_init(dfull + d, 1);
             mbar_init(dempty + d, kDrainWarps);
         }
-        mbar_init(dgfull, 1);
+        for (uint32_t i = 0; i < kMaxTileStages; ++i) mbar_init(dgfull + i, 1);
         *failed = 0;
         mbar_fence_init();
         tma_prefetch_map(&wmap);
     }
     if (warp == 1) tmem_alloc(tmem_slot, kTmemCols);
+    // a slice that ends in half a stage: the missing group's (sum of x, 2^(e-26)) pairs are zero (its weights are the zeros
+    // the TMA fills in beyond K; the copies below bring the pairs of the groups that exist)
+    for (uint32_t i = ngroups * 16 + tid; i < gps * 16; i += kThreads) xsinv[i] = make_float2(0.0f, 0.0f);
     __syncthreads();
 
-    // ── the producer fills the ring once before anything else happens (the weights do not depend on x) ──
+    // ── the producer fills the ring before anything else happens (the weights do not depend on x) ──
     uint32_t ps = 0, pround = 0, ptile = tlane, pi = 0;  // producer position (warp 0, lane 0)
     auto produce_one = [&]() -> bool {  // requests the next stage; false when nothing is left or a wait gave up
-        if (!ngroups || ptile >= plan.tiles) return false;
+        if (!my_tiles || ptile >= plan.tiles) return false;
         if (pround && !mbar_wait(empty + ps, (pround - 1) & 1, failed, status, kStatusEmptyWaitTimedOut)) return false;
-        if (pi == 0) {
-            // The tile's scales and zero points (contiguous: tile_rows x groups floats each) are asked into L2 a ring's depth
-            // before the drain warps read them: under a full weight stream a miss costs them ~2.7 us.
-            const size_t first = (size_t)ptile * plan.tile_rows * groups * 4, last = min((size_t)(ptile + 1) * plan.tile_rows, (size_t)n) * groups * 4;
-            const size_t lo = first & ~(size_t)15, bytes = (last - lo) & ~(size_t)15;
-            if (bytes) {
-                asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(reinterpret_cast<const uint8_t*>(scale) + lo), "r"((uint32_t)bytes) : "memory");
-                asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(reinterpret_cast<const uint8_t*>(zero) + lo), "r"((uint32_t)bytes) : "memory");
-            }
-        }
-        mbar_arrive_expect_tx(full + ps, plan.tile_rows * 128u);
-        tma_load_2d(ring + (size_t)ps * kStageBytes, &wmap, (int32_t)((g_begin + 2 * pi) * 64u), (int32_t)(ptile * plan.tile_rows), full + ps);
+        mbar_arrive_expect_tx(full + ps, stage_bytes);
+        tma_load_2d(ring + (size_t)ps * stage_bytes, &wmap, (int32_t)((g_begin + 2 * pi) * 64u), (int32_t)(ptile * tile_rows), full + ps);
         if (++pi == nstage_tile) pi = 0, ptile += plan.lanes;
         if (++ps == nstages) ps = 0, ++pround;
         return true;
     };
-    if (warp == 0) {
-        if (lane == 0)
-            for (uint32_t i = 0; i < nstages; ++i)
-                if (!produce_one()) break;
-    }
-    if (warp == 0 && lane == 0 && ngroups) {
-        // the slice's digit tiles and (sum, 2^(e-26)) pairs, as the conversion kernel left them in global memory: bulk copies
-        const uint32_t dig_bytes = ngroups * dbytes, xs_bytes = ngroups * 128u;
-        mbar_arrive_expect_tx(dgfull, dig_bytes + xs_bytes);
-        for (uint32_t off = 0; off < dig_bytes; off += 32768u)
-            bulk_load(digits + off, xdigits + (size_t)g_begin * dbytes + off, min(32768u, dig_bytes - off), dgfull);
-        bulk_load(xsinv, xdigits + (size_t)groups * dbytes + (size_t)g_begin * 128u, xs_bytes, dgfull);
+    if (warp == 0 && lane == 0 && my_tiles) {
+        // stage by stage: the weights of ring stage i, then the digit tiles of the slice's stage i (bulk copies of what the
+        // conversion kernel left in global memory; they stay for all the CTA's tiles)
+        const uint8_t* dsrc = xdigits + (size_t)g_begin * dstride;
+        for (uint32_t i = 0; i < nstages; ++i) produce_one();
+        asm volatile("griddepcontrol.wait;" ::: "memory");  // the digit tiles are complete and visible from here on
+        for (uint32_t i = 0; i < nstage_tile; ++i) {
+            {
+                const uint32_t ng = min(2u, ngroups - 2 * i), bytes = ng * dstride;
+                mbar_arrive_expect_tx(dgfull + i, bytes + (i == 0 ? ngroups * 128u : 0u));
+                for (uint32_t off = 0; off < bytes; off += 8192u)
+                    bulk_load(digits + (size_t)2 * i * dstride + off, dsrc + (size_t)2 * i * dstride + off, min(8192u, bytes - off), dgfull + i);
+                if (i == 0) bulk_load(xsinv, xdigits + (size_t)groups * dstride + (size_t)g_begin * 128u, ngroups * 128u, dgfull);
+            }
+        }
     }
     tc_fence_before_sync();
     __syncthreads();
@@ -262,232 +311,219 @@ __global__ void __launch_bounds__(kThreads, 1)
             while (produce_one()) {
             }
     } else if (warp == 1) {
-        if (lane == 0 && ngroups) {
-            // Both A operands come from tensor memory (the raw bytes and the high nibbles, written there by warps 4-7): a
-            // kind::i8 instruction whose A streams from shared memory took ~175 cycles in a loop of fresh tiles, ~97 with A
-            // in tensor memory.
-            constexpr uint32_t idesc = umma_idesc(2, 0, 1, 128, NC);  // s32 accumulate, u8 weights x s8 digits
-            uint32_t it = 0, dcount = 0;
-            bool ok = mbar_wait(dgfull, 0, failed, status, kStatusFullWaitTimedOut);
-            for (uint32_t tile = tlane; tile < plan.tiles && ok; tile += plan.lanes) {
-                for (uint32_t i = 0; i < nstage_tile && ok; ++i, ++it) {
-                    const uint32_t ng = min(2u, ngroups - 2 * i), abuf = it % kABufs;
-                    ok = mbar_wait(afull + abuf, (it / kABufs) & 1, failed, status, kStatusMmaWaitTimedOut);
-                    if (!ok) break;
-                    tc_fence_after_sync();
-                    const uint32_t a_raw = tmem + kACol0 + abuf * 64, a_hi = a_raw + 32;
-                    for (uint32_t gi = 0; gi < ng && ok; ++gi) {
-                        const uint32_t dc = dcount + gi, db = dc % kDBufs;
-                        if (dc >= kDBufs) ok = mbar_wait(dempty + db, (dc / kDBufs - 1) & 1, failed, status, kStatusMmaWaitTimedOut);
-                        if (!ok) break;
+        if (lane == 0 && my_tiles) {
+            const uint32_t idesc = umma_idesc(2, 1, 0, 64, tile_rows);  // s32 accumulate, s8 digits x u8 weights
+            const uint32_t hi_addr = smem_u32(hibuf);
+            const uint32_t total = my_tiles * nstage_tile;
+            // Two queues, each in stage order: raw bytes x digits of U (needs the stage's weights, its digits, and its
+            // accumulator drained) and high nibbles x digits of V (needs the eight warps' buffer). Whichever is ready is
+            // issued; the raw multiplications may run one stage ahead, so that the warps have a stage's time.
+            auto ready = [](uint64_t* bar, uint32_t parity) {
+                uint32_t done;
+                asm volatile(
+                    "{\n\t.reg .pred p;\n\t"
+                    "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                    "selp.u32 %0, 1, 0, p;\n\t}"
+                    : "=r"(done)
+                    : "r"(smem_u32(bar)), "r"(parity)
+                    : "memory");
+                return done != 0;
+            };
+            uint32_t raw_next = 0, hi_next = 0;
+            long long idle_since = 0;
+            while (hi_next < total) {
+                bool progressed = false;
+                if (raw_next < total && raw_next <= hi_next + 1) {
+                    const uint32_t it = raw_next, s = it % nstages, buf = it & 1u, i = it % nstage_tile;
+                    if (ready(full + s, (it / nstages) & 1) && (it >= nstage_tile || ready(dgfull + i, 0)) &&
+                        (it < 2 || ready(dempty + buf, ((it >> 1) - 1) & 1))) {
                         tc_fence_after_sync();
-                        const uint32_t x_addr = smem_u32(digits + (size_t)(2 * i + gi) * dbytes);
+                        const uint32_t raw_addr = smem_u32(ring + (size_t)s * stage_bytes);
+                        // group 2 i in the lower half-lanes of the accumulator, group 2 i + 1 in the upper
 #pragma unroll
-                        for (uint32_t h = 0; h < 2; ++h) {  // raw bytes x digits of U, high nibbles x digits of V
-                            umma_i8_ts(tmem + db * NC, a_raw + (2 * gi + h) * 8, umma_desc_k128(x_addr + 32 * h, b_sbo), idesc, h != 0);
-                            umma_i8_ts(tmem + db * NC, a_hi + (2 * gi + h) * 8, umma_desc_k128(x_addr + 64 + 32 * h, b_sbo), idesc, true);
+                        for (uint32_t j = 0; j < 4; ++j) {
+                            const uint32_t gi = j >> 1, h = j & 1u;
+                            const uint32_t x_addr = smem_u32(digits + (size_t)(2 * i + gi) * dstride);
+                            umma_i8_ss(tmem_addr(tmem, 16 * gi, buf * kTileMax), umma_desc_k128(x_addr + 32 * h), umma_desc_k128(raw_addr + 32 * j), idesc, h != 0);
                         }
-                        umma_commit(dfull + db);
+                        umma_commit(empty + s);
+                        ++raw_next, progressed = true;
                     }
-                    if (!ok) break;
-                    umma_commit(aempty + abuf);
-                    dcount += ng;
+                }
+                if (hi_next < raw_next && ready(hfull, hi_next & 1)) {
+                    const uint32_t it = hi_next, buf = it & 1u, i = it % nstage_tile;
+                    tc_fence_after_sync();
+#pragma unroll
+                    for (uint32_t j = 0; j < 4; ++j) {
+                        const uint32_t gi = j >> 1, h = j & 1u;
+                        const uint32_t x_addr = smem_u32(digits + (size_t)(2 * i + gi) * dstride);
+                        umma_i8_ss(tmem_addr(tmem, 16 * gi, buf * kTileMax), umma_desc_k128(x_addr + 64 + 32 * h),
+                                   umma_desc_plain(hi_addr + j * tile_rows * 32u, 128, 256), idesc, true);
+                    }
+                    umma_commit(hempty);
+                    umma_commit(dfull + buf);
+                    ++hi_next, progressed = true;
+                }
+                if (progressed) {
+                    idle_since = 0;
+                } else if (*failed) {
+                    break;
+                } else if (idle_since == 0) {
+                    idle_since = clock64();
+                    __nanosleep(40);
+                } else if (clock64() - idle_since > 4000000000ll) {  // ~2 s with nothing to issue: give up as mbar_wait does
+                    *failed = kStatusMmaWaitTimedOut;
+                    atomicCAS(status, 0u, (uint32_t)kStatusMmaWaitTimedOut);
+                    break;
+                } else {
+                    __nanosleep(40);  // nothing to issue: leave the issue slots to the warps that share this scheduler
                 }
             }
         }
-    } else if (warp >= 4 && warp < 8) {
-        // ── the stage's raw bytes and high nibbles -> tensor memory: thread = one feature row = one TMEM lane ──
-        const uint32_t sub = warp & 3u, row = 32 * sub + lane;
+    } else if (warp >= kFirstNibbleWarp && warp < kFirstDrainWarp) {
+        // ── per stage: the high nibbles of the thread's two feature rows (row and row + 128), and the rows' scales and zero
+        // points ──
+        const uint32_t row = tid - kFirstNibbleWarp * 32;  // 0 .. 127
         uint32_t s = 0, round = 0, it = 0;
-        bool ok = ngroups != 0;
-        for (uint32_t tile = tlane; tile < plan.tiles && ok; tile += plan.lanes) {
+        bool ok = true;
+        for (uint32_t tl = 0; tl < my_tiles && ok; ++tl) {
+            const uint32_t f0 = (tlane + tl * plan.lanes) * tile_rows;
             for (uint32_t i = 0; i < nstage_tile && ok; ++i, ++it) {
-                const uint32_t abuf = it % kABufs;
-                if (lane == 0) {
-                    ok = mbar_wait(full + s, round & 1, failed, status, kStatusFullWaitTimedOut);
-                    if (ok && it >= kABufs) ok = mbar_wait(aempty + abuf, (it / kABufs - 1) & 1, failed, status, kStatusMmaWaitTimedOut);
+                // the scales first: their latency runs under the wait for the stage
+                float sv[2][2], zv[2][2];
+#pragma unroll
+                for (uint32_t rr = 0; rr < 2; ++rr) {
+                    const uint32_t rw = row + 128 * rr;
+                    const bool fvalid = rw < tile_rows && f0 + rw < n;
+                    const size_t at = (size_t)(fvalid ? f0 + rw : 0) * groups + g_begin + 2 * i;
+#pragma unroll
+                    for (uint32_t g = 0; g < 2; ++g) {
+                        const bool have = fvalid && 2 * i + g < ngroups;
+                        sv[rr][g] = have ? __ldg(scale + at + g) : 0.0f;
+                        zv[rr][g] = have ? __ldg(zero + at + g) : 0.0f;
+                    }
                 }
+                if (lane == 0) ok = mbar_wait(full + s, round & 1, failed, status, kStatusFullWaitTimedOut);
                 ok = __shfl_sync(0xffffffffu, ok, 0);
                 if (!ok) break;
-                const uint8_t* src = ring + (size_t)s * kStageBytes + row * 128u;
-                uint32_t raw[32], hi[32];  // a store to tensor memory reads its registers until tcgen05.wait::st: two arrays
+                // row by row (eight 16-byte pieces in registers at a time): the first row is read before the wait for the
+                // nibble buffer, the second after it
+                uint4 w[8];
+                auto read_row = [&](uint32_t rw) {
+                    if (rw >= tile_rows) return;
+                    const uint8_t* src = ring + (size_t)s * stage_bytes + rw * 128u;
 #pragma unroll
-                for (uint32_t c = 0; c < 8; ++c) {
-                    const uint4 w = *reinterpret_cast<const uint4*>(src + ((c ^ (row & 7u)) << 4));
-                    raw[4 * c] = w.x, raw[4 * c + 1] = w.y, raw[4 * c + 2] = w.z, raw[4 * c + 3] = w.w;
+                    for (uint32_t c = 0; c < 8; ++c) {
+                        w[c] = *reinterpret_cast<const uint4*>(src + ((c ^ (rw & 7u)) << 4));
+                        w[c].x = (w[c].x >> 4) & 0x0f0f0f0fu, w[c].y = (w[c].y >> 4) & 0x0f0f0f0fu;
+                        w[c].z = (w[c].z >> 4) & 0x0f0f0f0fu, w[c].w = (w[c].w >> 4) & 0x0f0f0f0fu;
+                    }
+                };
+                auto write_row = [&](uint32_t rw, uint32_t rr) {
+                    if (rw >= tile_rows) return;
+                    uint8_t* dst = hibuf + (rw >> 3) * 256u + (rw & 7u) * 16u;
+#pragma unroll
+                    for (uint32_t c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(dst + (c >> 1) * tile_rows * 32u + (c & 1u) * 128u) = w[c];
+                    float* slot = reinterpret_cast<float*>(szring + (it % kSzSlots) * slot_bytes) + (rw >> 1) * 4 + (rw & 1u);
+                    slot[0] = sv[rr][0], slot[2] = __fmaf_rn(-8.0f, sv[rr][0], zv[rr][0]);
+                    slot[tile_rows * 2] = sv[rr][1], slot[tile_rows * 2 + 2] = __fmaf_rn(-8.0f, sv[rr][1], zv[rr][1]);
+                };
+                read_row(row);
+                if (it >= 1) {
+                    if (lane == 0) ok = mbar_wait(hempty, (it - 1) & 1, failed, status, kStatusMmaWaitTimedOut);
+                    ok = __shfl_sync(0xffffffffu, ok, 0);
+                    if (!ok) break;
                 }
-#pragma unroll
-                for (uint32_t c = 0; c < 32; ++c) hi[c] = (raw[c] >> 4) & 0x0f0f0f0fu;
-                tc_fence_after_sync();
-                tmem_st32(tmem_addr(tmem, 32 * sub, kACol0 + abuf * 64), raw);
-                tmem_st32(tmem_addr(tmem, 32 * sub, kACol0 + abuf * 64 + 32), hi);
-                tmem_wait_st();
-                tc_fence_before_sync();
+                write_row(row, 0);
+                read_row(row + 128);
                 __syncwarp();
-                if (lane == 0) {
-                    mbar_arrive(afull + abuf);
-                    mbar_arrive(empty + s);  // the stage has been read: the producer may refill it
-                }
+                if (lane == 0) mbar_arrive(empty + s);  // the stage has been read: with the raw multiplications done the producer may refill it
+                write_row(row + 128, 1);
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(hfull);
                 if (++s == nstages) s = 0, ++round;
             }
         }
-    } else if (warp >= 8 && warp < 8 + kDrainWarps) {
-        // ── drain: thread = one feature; per group read the int32 digit sums, recombine, scale, accumulate ──
-        constexpr uint32_t CW = NC < 32 ? NC : 32;  // columns this warp reads: rows r0 .. r0 + CW / 4 - 1 of x
-        constexpr uint32_t RW = CW / 4;
-        const uint32_t sub = warp & 3u, half = (warp - 8) >> 2, r0 = half * 8, f = 32 * sub + lane;
-        bool ok = ngroups != 0;
-        if (ok && lane == 0) ok = mbar_wait(dgfull, 0, failed, status, kStatusFullWaitTimedOut);
-        ok = __shfl_sync(0xffffffffu, ok, 0);
-        const uint32_t my_tiles_d = tlane < plan.tiles ? (plan.tiles - tlane + plan.lanes - 1) / plan.lanes : 0u;
-        const uint32_t total = my_tiles_d * ngroups;  // the CTA's groups, tile after tile: one accumulator tile each
-        const bool frow = f < plan.tile_rows;
-        // scale and zero point of flat group g for this thread's feature
-        auto sz_ptr = [&](uint32_t g, const float* base) {
-            const uint32_t tl = g / ngroups, gl = g - tl * ngroups, feature = (tlane + tl * plan.lanes) * plan.tile_rows + f;
-            return base + (size_t)((frow && feature < n) ? feature : 0) * groups + g_begin + gl;
-        };
-        // The accumulator is read 16 columns (four rows of x) at a time: step q = group q / kParts, columns 16 (q % kParts).
-        constexpr uint32_t kParts = CW / 16;
-        const uint32_t steps = total * kParts;
-        // waits for the step's accumulator (at its first part) and requests the columns (the registers are valid after finish_load)
-        auto wait_and_load = [&](uint32_t q, uint32_t (&d)[16]) {
-            const uint32_t g = q / kParts, part = q % kParts, db = g % kDBufs;
-            if (part == 0) {
-                if (lane == 0 && ok) ok = mbar_wait(dfull + db, (g / kDBufs) & 1, failed, status, kStatusMmaWaitTimedOut);
-                ok = __shfl_sync(0xffffffffu, ok, 0);
-            }
-            if (!ok) return;
-            tc_fence_after_sync();
-            tmem_ld16(tmem_addr(tmem, 32 * sub, db * NC + half * 32 + part * 16), d);
-        };
-        auto finish_load = [&](uint32_t q, uint32_t (&d)[16]) {
-            if (!ok) return;
-            tmem_wait_ld();
+    } else if (warp >= kFirstDrainWarp) {
+        // ── drain: warp = (quarter of tensor memory = four rows of x, 64 columns); thread t holds, for column block i of
+        // eight, columns 8 i + 2 (t % 4) + {0, 1} of accumulator rows t / 4 and t / 4 + 8: digits 2 p and 2 p + 1
+        // (p = (t / 4) % 2) of row 4 sub + t / 8 of x ──
+        const uint32_t dw = warp - kFirstDrainWarp, sub = warp & 3u, cq = dw >> 2, q = lane & 3u, dp = (lane >> 2) & 1u;
+        const uint32_t r = 4 * sub + (lane >> 3);
+        const float dscale = dp ? 65536.0f : 1.0f;  // 256^(2 p)
+        const bool live = 64 * cq < tile_rows;       // a narrow tile leaves the last quarters without columns
+        bool ok = my_tiles != 0;
+        if (ok) {  // the (sum of x, 2^(e-26)) pairs arrive with the first stage's digits
+            if (lane == 0) ok = mbar_wait(dgfull, 0, failed, status, kStatusFullWaitTimedOut);
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+        }
+        uint32_t it = 0;
+        for (uint32_t tl = 0; tl < my_tiles && ok; ++tl) {
+            const uint32_t tile = tlane + tl * plan.lanes;
+            uint64_t acc[8];
 #pragma unroll
-            for (uint32_t i = 0; i < 16; ++i) asm volatile("" : "+r"(d[i]));  // nothing reads the registers before the wait above
-            if (q % kParts == kParts - 1) {  // the whole accumulator has been read: the tensor core may overwrite it
+            for (uint32_t i = 0; i < 8; ++i) acc[i] = 0ull;
+            for (uint32_t i = 0; i < nstage_tile && ok; ++i, ++it) {
+                const uint32_t buf = it & 1u;
+                if (lane == 0) ok = mbar_wait(dfull + buf, (it >> 1) & 1, failed, status, kStatusMmaWaitTimedOut);
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) break;
+                tc_fence_after_sync();
+                if (live) {
+                    const float4* slot = reinterpret_cast<const float4*>(szring + (it % kSzSlots) * slot_bytes) + 32 * cq + q;
+                    // one load of the warp's 64 columns per group: few, large loads, because each waits its turn behind the
+                    // multiplication that is accumulating into tensor memory at that moment
+                    uint32_t d[32];
+#pragma unroll
+                    for (uint32_t p = 0; p < 2; ++p) {
+                        tmem_ld_16x256b_x8(tmem_addr(tmem, 32 * sub + 16 * p, buf * kTileMax + 64 * cq), d);
+                        // 2^(e-26) of the group and row (0 for what the call does not have) times 256^(2 p); the sum of x goes
+                        // with the zero point in the thread of digits 0 and 1
+                        const float2 xs = xsinv[(2 * i + p) * 16 + r];
+                        const float c = xs.y * dscale, z = dp == 0 ? xs.x : 0.0f;
+                        const uint64_t c2 = pack2(c, c), z2 = pack2(z, z);
+                        const float4* srow = slot + p * (tile_rows >> 1);
+                        tmem_wait_ld_of(d);
+#pragma unroll
+                        for (uint32_t i8 = 0; i8 < 8; ++i8) {
+                            if (64 * cq + 8 * i8 >= tile_rows) continue;  // uniform: the tile ends inside this warp's columns
+                            const float4 sz = srow[4 * i8];
+                            // |digit sum| < 2^22: D + 256 D' is exact in int32; its conversion rounds to 24 bits like every
+                            // float32 operation after it
+                            const int v0 = (int)d[4 * i8] + 256 * (int)d[4 * i8 + 2], v1 = (int)d[4 * i8 + 1] + 256 * (int)d[4 * i8 + 3];
+                            const uint64_t f = pack2(__int2float_rn(v0), __int2float_rn(v1));
+                            acc[i8] = fma2(pack2(sz.z, sz.w), z2, fma2(pack2(sz.x, sz.y), mul2(f, c2), acc[i8]));
+                        }
+                    }
+                }
                 tc_fence_before_sync();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(dempty + (q / kParts) % kDBufs);
+                if (lane == 0) mbar_arrive(dempty + buf);
             }
-        };
-        float acc[RW];
-        float s_cur[4], z_cur[4], s_nxt[4], z_nxt[4];
-        auto ldg_pinned = [](const float* p) {  // a load the compiler cannot sink to its use: it is requested HERE
-            float v;
-            asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(v) : "l"(p));
-            return v;
-        };
-        auto fetch_sz = [&](uint32_t g0, float (&sv)[4], float (&zv)[4]) {
+            if (!ok) break;
+            // The two halves of a row of x sit in threads t and t ^ 4: add them, each keeping half of the column blocks
+            // (blocks 2 kk + p), in a fixed order.
+            float2 out[4];
 #pragma unroll
-            for (uint32_t j = 0; j < 4; ++j) {
-                const bool have = g0 + j < total;
-                sv[j] = have ? ldg_pinned(sz_ptr(g0 + j, scale)) : 0.0f;
-                zv[j] = have ? ldg_pinned(sz_ptr(g0 + j, zero)) : 0.0f;
-            }
-        };
-        auto math = [&](uint32_t q, const uint32_t (&d)[16], float s, float z, auto part_c) {
-            constexpr uint32_t PART = decltype(part_c)::value;
-            const uint32_t g = q / kParts, tl = g / ngroups, gl = g - tl * ngroups;
-            if (gl == 0) {
-#pragma unroll
-                for (uint32_t r = 0; r < 4; ++r) acc[PART * 4 + r] = 0.0f;
-            }
-            const float zm = __fmaf_rn(-8.0f, s, z);
-            const float2* xi = xsinv + gl * 16 + r0 + PART * 4;
-#pragma unroll
-            for (uint32_t r = 0; r < 4; ++r) {
-                if (r0 + PART * 4 + r < m) {
-                    // |digit sum| < 2^22: 12582912 + c is exact in float32, so two full-rate instructions convert it
-                    const float f0 = __int_as_float((int)d[4 * r] + 0x4B400000) - 12582912.0f;
-                    const float f1 = __int_as_float((int)d[4 * r + 1] + 0x4B400000) - 12582912.0f;
-                    const float f2 = __int_as_float((int)d[4 * r + 2] + 0x4B400000) - 12582912.0f;
-                    const float f3 = __int_as_float((int)d[4 * r + 3] + 0x4B400000) - 12582912.0f;
-                    const float t = __fmaf_rn(__fmaf_rn(__fmaf_rn(f3, 256.0f, f2), 256.0f, f1), 256.0f, f0);
-                    const float2 c = xi[r];  // (sum of x over the group, 2^(e-26))
-                    acc[PART * 4 + r] = __fmaf_rn(zm, c.x, __fmaf_rn(s, t * c.y, acc[PART * 4 + r]));
-                }
-            }
-            if (gl == ngroups - 1 && PART == kParts - 1) {  // the tile's results
-                const uint32_t feature = (tlane + tl * plan.lanes) * plan.tile_rows + f;
-                if (frow && feature < n && ok) {
-                    if (plan.slices == 1) {
-                        const float bs = bias ? bias[feature] : 0.0f;
-#pragma unroll
-                        for (uint32_t r = 0; r < RW; ++r)
-                            if (r0 + r < m) y[(size_t)(r0 + r) * n + feature] = bias ? __fadd_rn(acc[r], bs) : acc[r];
-                    } else {  // K is split: this slice's partial sums; they are added up once the CTA has done all its tiles
-#pragma unroll
-                        for (uint32_t r = 0; r < RW; ++r)
-                            if (r0 + r < m) __stcg(partials + ((size_t)slice * m + r0 + r) * n + feature, acc[r]);
-                    }
-                }
-            }
-        };
-        // Two register sets of 16: while one is worked on, the next columns are already on their way out of tensor memory;
-        // and the scales of the next four groups are requested while the current four are in use.
-        uint32_t da[16], dbuf[16];
-        using P0 = std::integral_constant<uint32_t, 0>;
-        using P1 = std::integral_constant<uint32_t, kParts - 1>;  // odd steps: part 1 when a group has two parts, else part 0
-        if (steps) {
-            fetch_sz(0, s_cur, z_cur);
-            wait_and_load(0, da);
-            finish_load(0, da);
-        }
-        constexpr uint32_t kStepsPerChunk = 4 * kParts;  // four groups
-        for (uint32_t q = 0; q < steps && ok; q += kStepsPerChunk) {
-            fetch_sz(q / kParts + 4, s_nxt, z_nxt);
-#pragma unroll
-            for (uint32_t j = 0; j < kStepsPerChunk; j += 2) {
-                const uint32_t q0 = q + j;
-                if (q0 >= steps || !ok) break;
-                if (q0 + 1 < steps) wait_and_load(q0 + 1, dbuf);
-                math(q0, da, s_cur[j / kParts], z_cur[j / kParts], P0{});
-                if (q0 + 1 < steps) finish_load(q0 + 1, dbuf);
-                if (q0 + 2 < steps) wait_and_load(q0 + 2, da);
-                if (q0 + 1 < steps && ok) math(q0 + 1, dbuf, s_cur[(j + 1) / kParts], z_cur[(j + 1) / kParts], P1{});
-                if (q0 + 2 < steps) finish_load(q0 + 2, da);
+            for (uint32_t kk = 0; kk < 4; ++kk) {
+                const float2 a0 = unpack2(acc[2 * kk]), a1 = unpack2(acc[2 * kk + 1]);
+                const float2 keep = dp ? a1 : a0, send = dp ? a0 : a1;
+                const float ox = __shfl_xor_sync(0xffffffffu, send.x, 4), oy = __shfl_xor_sync(0xffffffffu, send.y, 4);
+                // low digits + high digits, whichever thread does the sum
+                out[kk].x = dp ? __fadd_rn(ox, keep.x) : __fadd_rn(keep.x, ox);
+                out[kk].y = dp ? __fadd_rn(oy, keep.y) : __fadd_rn(keep.y, oy);
             }
 #pragma unroll
-            for (uint32_t j = 0; j < 4; ++j) s_cur[j] = s_nxt[j], z_cur[j] = z_nxt[j];
-        }
-        if (plan.slices > 1) {
-            // One fence and one round of counters for all the CTA's tiles (a round per tile cost ~4 us each). The last CTA to
-            // arrive at a tile adds the slices' partial sums in slice order (deterministic), writes y and leaves the counter at
-            // zero for the next launch.
-            __threadfence();
-            named_barrier_sync(5, kDrainWarps * 32);
-            const uint32_t dt = tid - 8 * 32, my_tiles = tlane < plan.tiles ? (plan.tiles - tlane + plan.lanes - 1) / plan.lanes : 0u;
-            if (dt < my_tiles) {
-                const uint32_t tile = tlane + dt * plan.lanes;
-                const uint32_t old = atomicAdd(counters + tile, 1u);
-                last_flags[dt] = old == plan.slices - 1;
-                if (old == plan.slices - 1) counters[tile] = 0;
-            }
-            named_barrier_sync(5, kDrainWarps * 32);
-            __threadfence();
-            for (uint32_t j = 0; j < my_tiles; ++j) {
-                if (!last_flags[j]) continue;
-                const uint32_t feature = (tlane + j * plan.lanes) * plan.tile_rows + f;
-                if (!(f < plan.tile_rows && feature < n && ok)) continue;
-                const float bs = bias ? bias[feature] : 0.0f;
+            for (uint32_t kk = 0; kk < 4; ++kk) {
+                const uint32_t col = 64 * cq + 8 * (2 * kk + dp) + 2 * q;  // and col + 1
+                const uint32_t feature = tile * tile_rows + col;
 #pragma unroll
-                for (uint32_t r = 0; r < RW; ++r) {
-                    if (r0 + r < m) {
-                        float tot = 0.0f;  // eight slices' values are requested before the first is used
-#pragma unroll
-                        for (uint32_t s0 = 0; s0 < 16; s0 += 8) {
-                            if (s0 >= plan.slices) break;
-                            float part[8];
-#pragma unroll
-                            for (uint32_t sl = 0; sl < 8; ++sl) part[sl] = s0 + sl < plan.slices ? __ldcg(partials + ((size_t)(s0 + sl) * m + r0 + r) * n + feature) : 0.0f;
-#pragma unroll
-                            for (uint32_t sl = 0; sl < 8; ++sl)
-                                if (s0 + sl < plan.slices) tot = s0 + sl == 0 ? part[0] : __fadd_rn(tot, part[sl]);
-                        }
-                        y[(size_t)(r0 + r) * n + feature] = bias ? __fadd_rn(tot, bs) : tot;
-                    }
+                for (uint32_t e = 0; e < 2; ++e) {
+                    if (col + e >= tile_rows || feature + e >= n || r >= m) continue;
+                    const float v = e ? out[kk].y : out[kk].x;
+                    if (plan.slices == 1) y[(size_t)r * n + feature + e] = bias ? __fadd_rn(v, bias[feature + e]) : v;
+                    else partials[((size_t)slice * m + r) * n + feature + e] = v;  // K is split: added up by slice_sum_kernel
                 }
             }
         }
@@ -497,34 +533,59 @@ __global__ void __launch_bounds__(kThreads, 1)
     if (warp == 1) tmem_dealloc(tmem, kTmemCols);
 }
 
-// (slices, tile height) that minimise the time of the busiest CTA: its tensor-core instructions, plus what splitting K
-// costs (one round of fences and counters at the end, and the partial sums' traffic).
-Plan make_plan(uint64_t m, uint64_t n, uint64_t groups, uint32_t nc, int sm_count) {
-    const uint32_t digit_bytes = m <= 2 ? 1024u : nc * 128u;
-    const uint32_t fixed = 1024 + (2 * kMaxStages + 9 + 2 * kDBufs) * 8 + 16 + kMaxTilesPerCta * 4 + 64;
+// y = the slices' partial sums added in slice order (+ bias): thread = one output
+__global__ void __launch_bounds__(256) slice_sum_kernel(const float* __restrict__ partials, uint32_t slices, uint32_t total, uint32_t n,
+                                                        const float* __restrict__ bias, float* __restrict__ y) {
+    GQ_GRID_DEP_SYNC();
+    const uint32_t idx = blockIdx.x * 256 + threadIdx.x;
+    if (idx >= total) return;
+    float part[16];
+#pragma unroll
+    for (uint32_t s = 0; s < 16; ++s) part[s] = s < slices ? __ldcg(partials + (size_t)s * total + idx) : 0.0f;
+    float tot = part[0];
+#pragma unroll
+    for (uint32_t s = 1; s < 16; ++s)
+        if (s < slices) tot = __fadd_rn(tot, part[s]);
+    y[idx] = bias ? __fadd_rn(tot, bias[idx % n]) : tot;
+}
+
+// nanoseconds of one instruction at N columns (M = 64, K = 32 bytes)
+double mma_ns(uint32_t ncols) {
+    if (ncols <= 64) return 83.0;
+    if (ncols <= 128) return 83.0 + (ncols - 64) * (9.0 / 64.0);
+    return 92.0 + (ncols - 128) * (41.0 / 128.0);
+}
+
+size_t smem_bytes(uint32_t gps, uint32_t tile_rows, uint32_t rows_pad, uint32_t nstages) {
+    return 1024 + (size_t)(nstages + 1) * tile_rows * 128 + (size_t)gps * rows_pad * 128 + (size_t)kSzSlots * tile_rows * 16 + (size_t)gps * 128 + kBarrierBytes + 64 +
+           8192;  // the instruction reads 8 KB from the last group's digits whatever rows_pad is: keep that inside the allocation
+}
+
+// (slices, tile width) that minimise the time of the busiest CTA: per stage eight instructions, or the drain of its 2 x 64
+// accumulator rows if that is longer (~4 ns per column); ~0.4 us per tile of results; when K is split, the second kernel.
+Plan make_plan(uint64_t m, uint64_t n, uint64_t groups, int sm_count) {
+    const uint32_t rows_pad = m <= 4 ? 16u : m <= 8 ? 32u : 64u;
     Plan best{};
     double best_cost = 1e30;
-    const uint32_t tiles_min = (uint32_t)((n + 127) / 128);
-    for (uint32_t ks = 1; ks <= 16 && ks <= groups; ++ks) {
-        const uint32_t gps = (uint32_t)((groups + ks - 1) / ks);
-        const uint64_t resident = (uint64_t)gps * (digit_bytes + 128) + fixed;
-        if (resident + (uint64_t)kMinStages * kStageBytes > kSmemBudget) continue;
-        uint32_t nstages = (uint32_t)((kSmemBudget - resident) / kStageBytes);
-        if (nstages > (uint32_t)kMaxStages) nstages = kMaxStages;
+    for (uint32_t ks = 1; ks <= 16 && ks <= (uint32_t)sm_count; ++ks) {
+        uint32_t gps = (uint32_t)((groups + ks - 1) / ks);
+        gps += gps & 1u;  // whole stages: only the last slice may end in half a stage (the TMA fills what lies beyond K with zeros)
         const uint32_t slices = (uint32_t)((groups + gps - 1) / gps);
-        if (slices > (uint32_t)sm_count || slices > 16) continue;
+        if (slices != ks) continue;  // the same cut as a smaller ks
         const uint32_t lanes_max = (uint32_t)sm_count / slices;
-        for (uint32_t t = tiles_min; t <= tiles_min + 2 * (uint32_t)sm_count && t <= n; ++t) {
-            const uint32_t tile_rows = (uint32_t)((n + t - 1) / t);
+        const uint32_t stages_per_tile = gps / 2;
+        if (stages_per_tile > kMaxTileStages) continue;
+        for (uint32_t tile_rows = 16; tile_rows <= kTileMax; tile_rows += 16) {
+            if (smem_bytes(gps, tile_rows, rows_pad, kMinStages) > kSmemBudget) continue;
+            uint32_t nstages = kMinStages;
+            while (nstages < (uint32_t)kMaxStages && smem_bytes(gps, tile_rows, rows_pad, nstages + 1) <= kSmemBudget) ++nstages;
             const uint32_t tiles = (uint32_t)((n + tile_rows - 1) / tile_rows);
             const uint32_t lanes = tiles < lanes_max ? tiles : lanes_max;
             const uint32_t rounds = (tiles + lanes - 1) / lanes;
-            if (slices > 1 && rounds > kMaxTilesPerCta) continue;
-            // cycles: 4 instructions of ~96 cycles per group and tile (a stage holds two groups); when K is split, ~4 us for the
-            // closing round and the partial sums' traffic at ~22 bytes per cycle per SM
-            double cost = (double)rounds * ((gps + 1) / 2 * 2) * 4.0 * 96.0 + (nstages < 6 ? 300.0 * (6 - nstages) : 0.0);
-            if (slices > 1) cost += 8000.0 + (double)slices * m * n * 8.0 / (sm_count * 22.0);
-            if (cost < best_cost) best_cost = cost, best = Plan{slices, gps, tile_rows, tiles, lanes, lanes * slices, nstages, digit_bytes};
+            const double stage_ns = fmax(8.0 * mma_ns(tile_rows), 4.0 * tile_rows);
+            double cost = (double)rounds * (stages_per_tile * stage_ns + 400.0) + (nstages < 3 ? 1500.0 : 0.0);
+            if (slices > 1) cost += 3000.0 + (double)slices * m * n * 8.0 / 4000.0;
+            if (cost < best_cost) best_cost = cost, best = Plan{slices, gps, tile_rows, tiles, lanes, lanes * slices, nstages, rows_pad};
         }
     }
     return best;
@@ -532,43 +593,38 @@ Plan make_plan(uint64_t m, uint64_t n, uint64_t groups, uint32_t nc, int sm_coun
 
 }  // namespace
 
-static uint64_t digits_region_bytes(uint64_t groups, uint32_t digit_bytes) { return (groups * (digit_bytes + 128ull) + 1023) / 1024 * 1024; }
+static uint64_t digits_region_bytes(uint64_t groups, uint32_t rows_pad) { return (groups * (rows_pad * 128ull + 128ull) + 1023) / 1024 * 1024; }
 
+// The scratch holds the digit tiles of x and, when K is split, the slices' partial sums.
 uint64_t gemv_q4_umma_scratch_bytes(uint64_t m, uint64_t k, uint64_t n, int sm_count) {
     if (m < 1 || m > 16 || k == 0 || k % 128 || n == 0) return 0;
-    const uint32_t nc = m <= 4 ? 16 : m <= 8 ? 32 : 64;
-    const Plan p = make_plan(m, n, k / 128, nc, sm_count);
+    const Plan p = make_plan(m, n, k / 128, sm_count);
     if (p.grid == 0) return 0;
-    if ((uint64_t)p.tiles * 4 > kCounterBytes) return 0;
-    return kCounterBytes + digits_region_bytes(k / 128, p.digit_bytes) + (p.slices > 1 ? (uint64_t)p.slices * m * n * 4 : 0);
+    return digits_region_bytes(k / 128, p.rows_pad) + (p.slices > 1 ? (uint64_t)p.slices * m * n * 4 : 0);
 }
 
 // Returns false when the shape is not this kernel's: group_size 128, in_features a multiple of 128, 1 to 16 rows of x,
-// 16-byte aligned x and weights. `scratch` holds gemv_q4_umma_scratch_bytes bytes whose first 256 KB (the counters) are zero
-// between launches. Two launches: x -> digit tiles (tiny), then the linear, which starts streaming weights while the first runs.
+// 16-byte aligned x and weights. `scratch` holds gemv_q4_umma_scratch_bytes bytes. Up to three launches: x -> digit tiles
+// (tiny), the linear, and the sum over the K slices.
 bool launch_gemv_q4_umma(cudaStream_t s, int sm_count, uint32_t* status, const float* x, uint64_t m, uint64_t k, const uint32_t* q,
                          const float* scale, const float* zero, const float* bias, uint64_t n, uint64_t group, float* y, void* scratch) {
-    if (m < 1 || m > 16 || group != 128 || k == 0 || k % 128 || n == 0 || n > 0x7fffffffull || k > (1ull << 24)) return false;
+    if (m < 1 || m > 16 || group != 128 || k == 0 || k % 128 || n == 0 || m * n > 0x7fffffffull || k > (1ull << 24)) return false;
     if (((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(x)) & 15) != 0) return false;
-    const uint32_t nc = m <= 4 ? 16 : m <= 8 ? 32 : 64;
     const uint64_t groups = k / 128, row_bytes = k / 2;
-    const Plan p = make_plan(m, n, groups, nc, sm_count);
-    if (p.grid == 0 || (uint64_t)p.tiles * 4 > kCounterBytes) return false;
-    uint32_t* counters = reinterpret_cast<uint32_t*>(scratch);
-    uint8_t* xdigits = reinterpret_cast<uint8_t*>(scratch) + kCounterBytes;
-    float* partials = reinterpret_cast<float*>(xdigits + digits_region_bytes(groups, p.digit_bytes));
+    const Plan p = make_plan(m, n, groups, sm_count);
+    if (p.grid == 0) return false;
+    uint8_t* xdigits = reinterpret_cast<uint8_t*>(scratch);
+    float* partials = reinterpret_cast<float*>(xdigits + digits_region_bytes(groups, p.rows_pad));
     const CUtensorMap wmap = make_tensor_map_2d(q, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, row_bytes, n, row_bytes, 128, p.tile_rows, Swizzle::B128);
-    const size_t smem = 1024 + (size_t)p.nstages * kStageBytes + (size_t)p.gps * (p.digit_bytes + 128) + (2 * kMaxStages + 9 + 2 * kDBufs) * 8 + 16 +
-                        kMaxTilesPerCta * 4 + 64;
-    launch_after(x_digits_kernel, dim3((uint32_t)((groups * m + 7) / 8)), dim3(128), 0, s, x, (uint32_t)m, (uint32_t)k, (uint32_t)groups, p.digit_bytes, xdigits);
-    auto go = [&](auto kernel) {
-        GQ_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        launch_after(kernel, dim3(p.grid), dim3(kThreads), smem, s, wmap, (const uint8_t*)xdigits, scale, zero, bias, y, partials, counters, (uint32_t)m,
-                     (uint32_t)k, (uint32_t)n, (uint32_t)groups, p, status);
-    };
-    if (nc == 16) go(gemv_q4_umma_kernel<16>);
-    else if (nc == 32) go(gemv_q4_umma_kernel<32>);
-    else go(gemv_q4_umma_kernel<64>);
+    const size_t smem = smem_bytes(p.gps, p.tile_rows, p.rows_pad, p.nstages);
+    launch_after(x_digits_kernel, dim3((uint32_t)((groups * (p.rows_pad / 4) + 7) / 8)), dim3(128), 0, s, x, (uint32_t)m, (uint32_t)k, (uint32_t)groups, p.rows_pad,
+                 xdigits);
+    GQ_CUDA(cudaFuncSetAttribute(gemv_q4_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    launch_after(gemv_q4_umma_kernel, dim3(p.grid), dim3(kThreads), smem, s, wmap, (const uint8_t*)xdigits, scale, zero, p.slices > 1 ? nullptr : bias, y,
+                 partials, (uint32_t)m, (uint32_t)k, (uint32_t)n, (uint32_t)groups, p, status);
+    if (p.slices > 1)
+        launch_after(slice_sum_kernel, dim3((uint32_t)((m * n + 255) / 256)), dim3(256), 0, s, (const float*)partials, p.slices, (uint32_t)(m * n), (uint32_t)n,
+                     bias, y);
     return true;
 }
 

@@ -544,6 +544,45 @@ int32_t gq_int8_dequantize(gq_ctx* ctx, gq_buf q, gq_buf scale, uint64_t rows, u
     });
 }
 
+int32_t gq_int8_linear_backward(gq_ctx* ctx, gq_buf grad, uint64_t g_off, uint64_t m, gq_buf q, gq_buf scale, uint64_t n, uint64_t k, gq_buf grad_x,
+                                gq_buf grad_bias) {
+    return guarded([&] {
+        Locked l(ctx);
+        check_dims("gq_int8_linear_backward", m, k, n);
+        auto gp = (const float*)view(ctx, grad, g_off, m * n, 4, "gq_int8_linear_backward grad");
+        auto qp = (const uint32_t*)view(ctx, q, 0, n * words8(k), 4, "gq_int8_linear_backward q");
+        auto sp = (const float*)view(ctx, scale, 0, n, 4, "gq_int8_linear_backward scale");
+        auto xp = grad_x ? (float*)view(ctx, grad_x, 0, m * k, 4, "gq_int8_linear_backward grad_x") : nullptr;
+        auto bp = grad_bias ? (float*)view(ctx, grad_bias, 0, n, 4, "gq_int8_linear_backward grad_bias") : nullptr;
+        if ((xp && ranges_overlap(xp, m * k * 4, gp, m * n * 4)) || (bp && ranges_overlap(bp, n * 4, gp, m * n * 4)))
+            fail("gq_int8_linear_backward: the outputs must not overlap grad");
+        if (xp && m && k) launch_linear_backward_q8(ctx->stream, gp, m, qp, sp, n, k, xp);
+        if (bp && n) launch_column_sum(ctx->stream, gp, m, n, bp);
+        after_launch(ctx, "linear_backward_q8", {grad, q, scale, grad_x, grad_bias});
+    });
+}
+
+int32_t gq_int4_linear_backward(gq_ctx* ctx, gq_buf grad, uint64_t g_off, uint64_t m, gq_buf q, gq_buf scale, gq_buf zero, uint64_t n, uint64_t k,
+                                uint64_t group, gq_buf grad_x, gq_buf grad_bias) {
+    return guarded([&] {
+        Locked l(ctx);
+        check_dims("gq_int4_linear_backward", m, k, n);
+        check_group(group);
+        const uint64_t groups = (k + group - 1) / group;
+        auto gp = (const float*)view(ctx, grad, g_off, m * n, 4, "gq_int4_linear_backward grad");
+        auto qp = (const uint32_t*)view(ctx, q, 0, n * words4(k), 4, "gq_int4_linear_backward q");
+        auto sp = (const float*)view(ctx, scale, 0, n * groups, 4, "gq_int4_linear_backward scale");
+        auto zp = (const float*)view(ctx, zero, 0, n * groups, 4, "gq_int4_linear_backward zero");
+        auto xp = grad_x ? (float*)view(ctx, grad_x, 0, m * k, 4, "gq_int4_linear_backward grad_x") : nullptr;
+        auto bp = grad_bias ? (float*)view(ctx, grad_bias, 0, n, 4, "gq_int4_linear_backward grad_bias") : nullptr;
+        if ((xp && ranges_overlap(xp, m * k * 4, gp, m * n * 4)) || (bp && ranges_overlap(bp, n * 4, gp, m * n * 4)))
+            fail("gq_int4_linear_backward: the outputs must not overlap grad");
+        if (xp && m && k) launch_linear_backward_q4(ctx->stream, gp, m, qp, sp, zp, n, k, group, xp);
+        if (bp && n) launch_column_sum(ctx->stream, gp, m, n, bp);
+        after_launch(ctx, "linear_backward_q4", {grad, q, scale, zero, grad_x, grad_bias});
+    });
+}
+
 int32_t gq_int8_linear(gq_ctx* ctx, gq_buf x, uint64_t x_off, uint64_t m, uint64_t k, gq_buf q, gq_buf scale,
                        gq_buf bias, uint64_t b_off, uint64_t n, gq_buf y, int32_t kernel) {
     return guarded([&] {
@@ -637,6 +676,24 @@ int32_t gq_int4_linear(gq_ctx* ctx, gq_buf x, uint64_t x_off, uint64_t m, uint64
         auto yp = (float*)view(ctx, y, 0, m * n, 4, "gq_int4_linear output");
         if (ranges_overlap(yp, m * n * 4, xp, m * k * 4)) fail("gq_int4_linear: the output must not overlap the input (CTAs read x while others write y)");
         if (m == 0 || n == 0) return;
+        if (kernel == GQ_KERNEL_AUTO && m >= 3 && m <= 16 && group == 128 && k % 128 == 0) {
+            // The tensor-core kernel reads the weight once whatever m is, at about 2.2 bytes per ns after ~9 us of launches and
+            // start-up; the warp-level ring kernel (K = 4096 or 8192) takes a pass at ~4.5 bytes per ns per four rows of x, the
+            // dp4a kernel elsewhere grows with every row. Measured on B200 (14336 x 4096, 28672 x 8192, 3584 x 8192); weights
+            // under 4 MB stay with the single-launch kernels.
+            const double mb = (double)n * (double)k / 2e6;
+            const double umma_us = 9.0 + mb / 2.2;
+            const bool ring_shape = k == 4096 || k == 8192;
+            const double other_us = ring_shape ? (double)((m + 3) / 4) * (2.5 + mb / 4.5) : mb * (0.26 * (double)m + 0.27);
+            const uint64_t need = gemv_q4_umma_scratch_bytes(m, k, n, ctx->prop.multiProcessorCount);
+            // (a scratch that would have to grow inside a capture leaves the choice to the kernels that need none)
+            if (mb >= 4.0 && umma_us < other_us && need && !(ctx->capturing && ctx->scratch_bytes < need) &&
+                launch_gemv_q4_umma(ctx->stream, ctx->prop.multiProcessorCount, ctx->status_dev, xp, m, k, qp, sp, zp, bp, n, group, yp, context_scratch(ctx, need))) {
+                after_launch(ctx, "gemv_q4_umma", {x, q, scale, zero, bias, y}, {y});
+                ctx->stats.launches += 2;  // the digit conversion ahead of it and the sum over the K slices behind it
+                return;
+            }
+        }
         if (kernel == GQ_KERNEL_UMMA) {
             const uint64_t need = gemv_q4_umma_scratch_bytes(m, k, n, ctx->prop.multiProcessorCount);
             if (!need || !launch_gemv_q4_umma(ctx->stream, ctx->prop.multiProcessorCount, ctx->status_dev, xp, m, k, qp, sp, zp, bp, n, group, yp,

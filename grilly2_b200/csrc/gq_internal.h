@@ -166,6 +166,12 @@ void launch_quantize_q8(cudaStream_t s, const float* w, uint64_t rows, uint64_t 
 void launch_dequantize_q8(cudaStream_t s, const uint32_t* q, const float* scale, uint64_t rows, uint64_t k, float* w);
 void launch_quantize_q4(cudaStream_t s, const float* w, uint64_t rows, uint64_t k, uint64_t group, uint32_t* q,
                         float* scale, float* zero);
+// The frozen-weight backward (backward.cu): grad_x = grad . dequantize(W) with the weight dequantized on the fly in shared
+// memory, and the column sums of grad for the bias.
+void launch_linear_backward_q8(cudaStream_t s, const float* g, uint64_t m, const uint32_t* q, const float* scale, uint64_t n, uint64_t k, float* gx);
+void launch_linear_backward_q4(cudaStream_t s, const float* g, uint64_t m, const uint32_t* q, const float* scale, const float* zero, uint64_t n,
+                               uint64_t k, uint64_t group, float* gx);
+void launch_column_sum(cudaStream_t s, const float* g, uint64_t m, uint64_t n, float* out);
 void launch_dequantize_q4(cudaStream_t s, const uint32_t* q, const float* scale, const float* zero, uint64_t rows,
                           uint64_t k, uint64_t group, float* w);
 void launch_fill_u32(cudaStream_t s, uint32_t* dst, uint64_t n, uint32_t word);

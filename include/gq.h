@@ -176,6 +176,14 @@ int32_t gq_int8_quantize_rows(gq_ctx* ctx, gq_buf w, uint64_t w_off, uint64_t ro
 int32_t gq_int8_linear(gq_ctx* ctx, gq_buf x, uint64_t x_off, uint64_t m, uint64_t k, gq_buf q, gq_buf scale,
                        gq_buf bias, uint64_t b_off, uint64_t n, gq_buf y, int32_t kernel);
 
+/* The backward of the linear with its weight frozen — LinearInt8Backward, quant.rs:326-349:
+ * grad_x[m][k] = sum_n grad[m][n] * (q[n][k] * scale[n]); grad_bias[n] = sum_m grad[m][n].
+ * grad at element offset g_off; grad_x / grad_bias == 0 means "not needed". The dequantized weight is never written
+ * to memory (the reference materialises it for the duration of the call). float32 products accumulated in float32:
+ * within the reference's bound for this operator, (n + 2) 2^-24 sum|grad w| of float64. Outputs must not overlap grad. */
+int32_t gq_int8_linear_backward(gq_ctx* ctx, gq_buf grad, uint64_t g_off, uint64_t m, gq_buf q, gq_buf scale, uint64_t n, uint64_t k,
+                                gq_buf grad_x, gq_buf grad_bias);
+
 /* DEQUANTIZE{q,scale,w; rows,k,words} — quant.rs:40-46,307-322, g2-dequantize-q8.glsl:15-21 */
 int32_t gq_int8_dequantize(gq_ctx* ctx, gq_buf q, gq_buf scale, uint64_t rows, uint64_t k, gq_buf w);
 
@@ -191,7 +199,11 @@ int32_t gq_int4_quantize_rows(gq_ctx* ctx, gq_buf w, uint64_t w_off, uint64_t ro
                               gq_buf zero, uint64_t row0, uint64_t total_rows);
 
 /* LINEAR{x,q,scale,zero,bias,y; m,k,n,vecs,group,groups,x_off,b_off,has_bias,x_vec4}
- * — quant4.rs:33-39,371-442, g2-linear-q4.glsl:43-111. */
+ * — quant4.rs:33-39,371-442, g2-linear-q4.glsl:43-111.
+ * AUTO (group_size 128): one to four rows of x on the warp-level ring kernel where it applies (in_features 4096 or
+ * 8192), more rows — and three or more rows of other in_features that are multiples of 128 — on the tcgen05 kernel,
+ * which reads the weight once for up to 16 rows, when the weight is large enough to pay for its start-up; the IMMA
+ * and dp4a kernels elsewhere. y must not overlap x (refused). */
 int32_t gq_int4_linear(gq_ctx* ctx, gq_buf x, uint64_t x_off, uint64_t m, uint64_t k, gq_buf q, gq_buf scale,
                        gq_buf zero, gq_buf bias, uint64_t b_off, uint64_t n, uint64_t group, gq_buf y,
                        int32_t kernel);
@@ -200,6 +212,11 @@ int32_t gq_int4_linear(gq_ctx* ctx, gq_buf x, uint64_t x_off, uint64_t m, uint64
  * g2-dequantize-q4.glsl:16-24 */
 int32_t gq_int4_dequantize(gq_ctx* ctx, gq_buf q, gq_buf scale, gq_buf zero, uint64_t rows, uint64_t k,
                            uint64_t group, gq_buf w);
+
+/* As gq_int8_linear_backward for an int4 weight — LinearInt4Backward, quant4.rs:447-480:
+ * grad_x[m][k] = sum_n grad[m][n] * (level[n][k] * scale[n][g] + (zero[n][g] - 8 scale[n][g])), g = k / group. */
+int32_t gq_int4_linear_backward(gq_ctx* ctx, gq_buf grad, uint64_t g_off, uint64_t m, gq_buf q, gq_buf scale, gq_buf zero, uint64_t n,
+                                uint64_t k, uint64_t group, gq_buf grad_x, gq_buf grad_bias);
 
 /* ── GPTQ on the device ──────────────────────────────────────────────────
  * The reference runs both in numpy on the host (python/grilly/infer/gptq.py:87-181, the column loop;

@@ -49,7 +49,7 @@ def main() -> None:
         dist.all_gather_object(blocks, mine)
         assert np.array_equal(assemble_columns(blocks), whole)
     else:
-        from grilly2_b200 import _C
+        from grilly2_b200 import _C, _lib
         from grilly2_b200.sharded import Comm, PeerGather, ShardedLinear
         layer = ShardedLinear.from_full(w, b, world, rank, bits=4, group_size=group)
         assert np.array_equal(layer.q.packed().numpy().view(np.uint32), qf[lo:hi])
@@ -87,7 +87,7 @@ def main() -> None:
                 got = peers2.linear_gather(layer2.q, _C.Tensor.from_numpy(xs), layer2.bias).numpy()
                 assert np.abs(got - ref).max() / np.abs(ref).max() <= 1e-5, f"fused linear + gather, m = {m2}, step {step}"
                 if step == 1:  # the separate gather on the same buffers, in between: one protocol
-                    sep = peers2.gather(layer2.q.linear(_C.Tensor.from_numpy(xs), layer2.bias)).numpy()
+                    sep = peers2.gather(layer2.q.linear(_C.Tensor.from_numpy(xs), layer2.bias, _lib.KERNEL_RING)).numpy()
                     assert np.array_equal(sep, got), "separate gather differs from the fused one"
                 dist.barrier()
             peers2.close()

@@ -48,9 +48,10 @@ def test_sharded_linear_over_two_gpus():
 @pytest.mark.gpu
 @pytest.mark.parametrize("m,n,k", [(1, 80, 4096), (3, 333, 4096), (2, 48, 8192), (4, 5, 4096), (9, 100, 4096), (16, 37, 8192)])
 def test_fused_linear_gather_with_a_single_rank_equals_the_linear(m, n, k):
-    """World size 1 (the only peer is the rank itself): gq_int4_linear_gather must equal gq_int4_linear, step after step."""
+    """World size 1 (the only peer is the rank itself): gq_int4_linear_gather must equal gq_int4_linear on the same (ring)
+    kernel, step after step."""
     import numpy as np
-    from grilly2_b200 import _C
+    from grilly2_b200 import _C, _lib
     from grilly2_b200.sharded import PeerGather
     rng = np.random.default_rng(n + k)
     w = _C.Int4Weight.quantize(_C.Tensor.from_numpy((rng.standard_normal((n, k)) * 0.02).astype(np.float32)), 128)
@@ -58,7 +59,7 @@ def test_fused_linear_gather_with_a_single_rank_equals_the_linear(m, n, k):
     peers = PeerGather(1, 0, m, n, lambda obj: [obj])
     for step in range(3):
         x = _C.Tensor.from_numpy(rng.standard_normal((m, k)).astype(np.float32))
-        want = w.linear(x, bias).numpy()
+        want = w.linear(x, bias, _lib.KERNEL_RING).numpy()
         got = peers.linear_gather(w, x, bias).numpy()
         np.testing.assert_array_equal(got, want)
     peers.close()
