@@ -678,13 +678,17 @@ int32_t gq_int4_linear(gq_ctx* ctx, gq_buf x, uint64_t x_off, uint64_t m, uint64
         if (m == 0 || n == 0) return;
         if (kernel == GQ_KERNEL_AUTO && m >= 3 && m <= 16 && group == 128 && k % 128 == 0) {
             // The tensor-core kernel reads the weight once whatever m is, at about 2.2 bytes per ns after ~9 us of launches and
-            // start-up; the warp-level ring kernel (K = 4096 or 8192) takes a pass at ~4.5 bytes per ns per four rows of x, the
+            // start-up; the warp-level ring kernel (K = 4096 or 8192) takes a pass at ~4.5 bytes per ns (one row) per four rows of x, the
             // dp4a kernel elsewhere grows with every row. Measured on B200 (14336 x 4096, 28672 x 8192, 3584 x 8192); weights
             // under 4 MB stay with the single-launch kernels.
             const double mb = (double)n * (double)k / 2e6;
             const double umma_us = 9.0 + mb / 2.2;
             const bool ring_shape = k == 4096 || k == 8192;
-            const double other_us = ring_shape ? (double)((m + 3) / 4) * (2.5 + mb / 4.5) : mb * (0.26 * (double)m + 0.27);
+            double other_us = mb * (0.26 * (double)m + 0.27);
+            if (ring_shape) {  // a pass with three or four rows runs ~1.7 times as long as a one-row pass (its IMMA issue rate)
+                other_us = 0.0;
+                for (uint64_t r = 0; r < m; r += 4) other_us += (2.5 + mb / 4.5) * (m - r >= 3 ? 1.7 : m - r == 2 ? 1.1 : 1.0);
+            }
             const uint64_t need = gemv_q4_umma_scratch_bytes(m, k, n, ctx->prop.multiProcessorCount);
             // (a scratch that would have to grow inside a capture leaves the choice to the kernels that need none)
             if (mb >= 4.0 && umma_us < other_us && need && !(ctx->capturing && ctx->scratch_bytes < need) &&
