@@ -283,6 +283,52 @@ def measure_prefill(rows: int, steps: int, warmup: int, with_cublas: bool) -> di
             "cublas_tf32_same_shape_fp32_weights": cublas, "launches": 5 * per_batch}
 
 
+def run_decode_rows(args) -> None:
+    """Config 2 (int4 g128, 14336 x 4096) at `--rows` rows of x (1 to 16) through GQ_KERNEL_AUTO: 8 weight copies
+    (264 MB > 2 x L2) in one CUDA graph per step. The workload of the tcgen05 decode kernel's ncu summary."""
+    import torch
+    from grilly2_b200 import _C, _lib
+    m, n, k = max(1, min(args.rows, 16)), C2["n"], C2["k"]
+    rng = np.random.default_rng(C2["seed"])
+    base = _C.Int4Weight.quantize(_C.Tensor.from_numpy((rng.standard_normal((n, k)) * C2["sigma"]).astype(np.float32)), GROUP)
+    ws = []
+    for _ in range(8):
+        q = _C.Tensor.empty(base.packed().shape, "int32", persistent=True)
+        sc = _C.Tensor.empty(base.scale().shape, "float32", persistent=True)
+        z = _C.Tensor.empty(base.zero().shape, "float32", persistent=True)
+        q.copy_(base.packed()), sc.copy_(base.scale()), z.copy_(base.zero())
+        ws.append(_C.Int4Weight(q, sc, z, base.shape, GROUP))
+    x = _C.Tensor.from_numpy(rng.standard_normal((m, k)).astype(np.float32))
+    lib, ctx = _lib.load(), _C.context()
+    stream = _stream_of(lib, ctx)
+    ws[0].linear(x)  # first sighting eagerly (the context's scratch may grow), the second is recorded
+    _C.begin_capture()
+    keep = [w.linear(x) for w in ws]
+    graph = _C.end_capture()
+    steps, warm = min(args.steps, 500), max(args.warmup, 3)
+    for _ in range(warm):
+        graph.replay()
+    _C.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(steps):
+        graph.replay()
+    e1.record(stream)
+    _C.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / (steps * len(ws))
+    peak, kind = measured_peak()
+    b = algorithmic_bytes(m, n, k)
+    print(json.dumps({
+        "metric": METRIC, "value": b / (us * 1e-6) / 1e9, "unit": UNIT, "n_gpus": 1, "steps": steps, "warmup": warm,
+        "ms_per_step": us * len(ws) / 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"C2: int4 group-128 decode linear, x[{m},{k}] . W[{n},{k}]^T, 8 weight copies per step (inputs larger than L2)",
+                   "m": m, "n": n, "k": k, "group_size": GROUP},
+        "roofline": {"bound": "hbm", "achieved": b / (us * 1e-6) / 1e9, "peak": peak, "unit": "GB/s", "frac": b / (us * 1e-6) / 1e9 / peak, "traffic": None,
+                     "peak_kind": kind, "algorithmic_bytes_per_launch": b, "us_per_launch": us},
+        "gpu_launches": steps * len(keep),
+    }))
+
+
 def run_prefill(args) -> None:
     r = measure_prefill(args.rows, min(args.steps, 200), args.warmup, not args.no_extras)
     m, n, k = r["m"], r["n"], r["k"]
@@ -448,9 +494,10 @@ def main() -> None:
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
     ap.add_argument("--no-extras", action="store_true")
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "decode_step"],
-                    help="decode: the headline int4 layer; prefill: the int8 tf32 tensor-core GEMM of config 4; decode_step: config 5")
-    ap.add_argument("--rows", type=int, default=2048, help="rows of x for --workload prefill")
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "decode_step", "decode_rows"],
+                    help="decode: the headline int4 layer; prefill: the int8 tf32 tensor-core GEMM of config 4; decode_step: config 5; "
+                         "decode_rows: config 2 at --rows rows of x (1 to 16)")
+    ap.add_argument("--rows", type=int, default=2048, help="rows of x for --workload prefill (default 2048) and decode_rows (1 to 16)")
     args = ap.parse_args()
     global print
     _real = _quiet_stdout()
@@ -466,6 +513,10 @@ def main() -> None:
         return
     if args.workload == "prefill":
         run_prefill(args)
+        return
+    if args.workload == "decode_rows":
+        if int(os.environ.get("RANK", "0")) == 0:
+            run_decode_rows(args)
         return
     if args.workload == "decode_step":
         if int(os.environ.get("RANK", "0")) == 0:

@@ -52,6 +52,34 @@ def test_static_scratch_attention_equals_the_buffer_one_twice_in_a_row():
     assert _C.submit_stats()["launches"] == before["launches"] + 4
 
 
+def test_static_scratch_attention_replays_inside_a_graph():
+    """Captured after one eager call (the first call on a device looks the array up): every replay equals the buffer form."""
+    from grilly2_b200 import _C, _lib
+    lib, ctx = _lib.load(), _C.context()
+    heads, kv_heads, dim, max_len = 14, 2, 64, 256
+    nbytes = ctypes.c_uint64()
+    _lib.check(lib.gq_attn_scratch_bytes(ctx, heads, dim, max_len, ctypes.byref(nbytes)))
+    scratch = _C.Tensor.from_numpy(np.zeros(nbytes.value // 4, dtype=np.float32))
+    q, k, v, lens = _case(77, heads, kv_heads, dim, max_len, 200)
+    got, want = _C.Tensor.empty((heads, dim), "float32"), _C.Tensor.empty((heads, dim), "float32")
+
+    def static_call():
+        _lib.check(lib.gq_attn_decode_static(ctx, q.storage.handle, k.storage.handle, 0, v.storage.handle, 0, lens.storage.handle, 0, 2,
+                                             heads, kv_heads, dim, max_len, dim ** -0.5, got.storage.handle))
+
+    static_call()
+    _C.begin_capture()
+    static_call()
+    graph = _C.end_capture()
+    for length in (200, 31, 256):
+        lens.copy_(_C.Tensor.from_numpy(np.array([length, 3], dtype=np.int32)))
+        q.copy_(_C.Tensor.from_numpy(np.random.default_rng(length).standard_normal((heads, dim)).astype(np.float32)))
+        graph.replay()
+        _lib.check(lib.gq_attn_decode(ctx, q.storage.handle, k.storage.handle, 0, v.storage.handle, 0, lens.storage.handle, 0, 2,
+                                      heads, kv_heads, dim, max_len, dim ** -0.5, scratch.storage.handle, want.storage.handle))
+        np.testing.assert_array_equal(got.numpy(), want.numpy())
+
+
 def test_static_scratch_attention_refuses_what_does_not_fit():
     from grilly2_b200 import _C, _lib
     lib, ctx = _lib.load(), _C.context()
