@@ -724,7 +724,7 @@ def main() -> None:
         us, _ = time_variant(1, "linear", [weights[0]] * reps)
         extras["c3_m1_l2_hot_us"] = us
         del weights[1:]
-        # C2: int4 14336 x 4096, 16 weight copies (528 MB), m = 1, 4, 16; L2-hot; the older kernels
+        # C2: int4 14336 x 4096, 16 weight copies (528 MB), m = 1, 4, 8, 16; L2-hot; the older kernels
         rng2 = np.random.default_rng(C2["seed"])
         x2 = rng2.standard_normal((16, C2["k"])).astype(np.float32)
         base2 = _C.Int4Weight.quantize(_C.Tensor.from_numpy((rng2.standard_normal((C2["n"], C2["k"])) * C2["sigma"]).astype(np.float32)), GROUP)
@@ -737,7 +737,7 @@ def main() -> None:
             keep = [w.linear(xx, None, kernel) for w in ws]
             return keep, _C.end_capture()
 
-        for m in (1, 4, 16):
+        for m in (1, 4, 8, 16):
             keep, gm = c2_graph(m, ws2)
             us = timed(gm, steps2, 3) * 1e3 / (steps2 * 16)
             b = algorithmic_bytes(m, C2["n"], C2["k"])
