@@ -148,15 +148,16 @@ __global__ void __launch_bounds__(kThreads, 1)
     volatile uint32_t* failed = reinterpret_cast<volatile uint32_t*>(empty + kMaxStages);
 
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    // Output features are dealt out in whole 16-row blocks (a CTA gets floor or ceil of blocks / CTAs of them). A block
-    // costs the warp-level tensor instruction the same time whether its 16 rows are all in use or not, and that time, not
-    // the bytes, is what a block costs here: dealing the rows out evenly in smaller blocks (every CTA the same bytes) ran
-    // 12 % slower on 28672 x 8192 than leaving eight CTAs a block more than the others.
-    const uint32_t blocks_total = (n + kBlockRows - 1) / kBlockRows;
-    const uint32_t b0 = (uint32_t)((uint64_t)blocks_total * blockIdx.x / gridDim.x), b1 = (uint32_t)((uint64_t)blocks_total * (blockIdx.x + 1) / gridDim.x);
-    const uint32_t row_begin = b0 * kBlockRows, row_end = min(b1 * kBlockRows, n);
+    // Output features are dealt out in units of eight rows (a CTA gets floor or ceil of units / CTAs of them) and worked on
+    // in 16-row blocks, so that only a CTA's last block can be a short one. A block costs the warp-level tensor instruction
+    // the same time whether its 16 rows are all in use or not: dealing the rows out evenly in pairs (every CTA the same
+    // bytes, every CTA a short last block) ran 12 % slower on 28672 x 8192 than whole blocks, of which a few CTAs get one
+    // more than the others; eight-row units leave those few CTAs half a block more instead of a whole one.
+    const uint32_t units_total = (n + 7) / 8;
+    const uint32_t u0 = (uint32_t)((uint64_t)units_total * blockIdx.x / gridDim.x), u1 = (uint32_t)((uint64_t)units_total * (blockIdx.x + 1) / gridDim.x);
+    const uint32_t row_begin = u0 * 8, row_end = min(u1 * 8, n);
     const uint32_t nrows = row_end - row_begin;
-    const uint32_t blocks = b1 - b0;
+    const uint32_t blocks = (nrows + kBlockRows - 1) / kBlockRows;
     auto block_first = [&](uint32_t rb) { return rb * kBlockRows; };                           // first row of block rb within the CTA
     auto block_rows = [&](uint32_t rb) { return min(kBlockRows, nrows - rb * kBlockRows); };  // its rows
 
@@ -437,7 +438,8 @@ bool launch_gemv_q4_ring(cudaStream_t s, int sm_count, uint32_t* status, const f
     const uint64_t gpw = (groups + kWarps - 1) / kWarps;
     const uint64_t blocks_total = (n + kBlockRows - 1) / kBlockRows;
     const uint32_t grid = (uint32_t)(blocks_total < (uint64_t)sm_count ? blocks_total : (uint64_t)sm_count);
-    const uint64_t blocks = (blocks_total + grid - 1) / grid;  // the most 16-row blocks a CTA gets
+    const uint64_t units_max = ((n + 7) / 8 + grid - 1) / grid;  // the most eight-row units a CTA gets
+    const uint64_t blocks = (units_max * 8 + kBlockRows - 1) / kBlockRows;  // ... and 16-row blocks
     const uint64_t stage_stride = ((kBlockRows / 2) * (2 * row_bytes + kRowPad) + 1023) / 1024 * 1024 + 2 * (groups / 32) * 2048;
     const uint64_t tiles = (m + 1) / 2;
     if (m > 2 && gpw > 4) return false;  // the B fragments of three or four rows of x must fit the registers

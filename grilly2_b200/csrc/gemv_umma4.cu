@@ -541,20 +541,35 @@ __global__ void __launch_bounds__(kThreads, 1)
     if (warp == 1) tmem_dealloc(tmem, kTmemCols);
 }
 
-// y = the slices' partial sums added in slice order (+ bias): thread = one output
+// y = the slices' partial sums added in slice order (+ bias): thread = V consecutive outputs (V = 4 when rows are a multiple
+// of four outputs long, else 1); every slice's values are requested before the first is used
+template <int V>
 __global__ void __launch_bounds__(256) slice_sum_kernel(const float* __restrict__ partials, uint32_t slices, uint32_t total, uint32_t n,
                                                         const float* __restrict__ bias, float* __restrict__ y) {
     GQ_GRID_DEP_SYNC();
-    const uint32_t idx = blockIdx.x * 256 + threadIdx.x;
+    const uint32_t idx = (blockIdx.x * 256 + threadIdx.x) * V;
     if (idx >= total) return;
-    float part[16];
+    float part[16][V];
 #pragma unroll
-    for (uint32_t s = 0; s < 16; ++s) part[s] = s < slices ? __ldcg(partials + (size_t)s * total + idx) : 0.0f;
-    float tot = part[0];
+    for (uint32_t s = 0; s < 16; ++s) {
+        if (V == 4) {
+            const float4 v = s < slices ? __ldcg(reinterpret_cast<const float4*>(partials + (size_t)s * total + idx)) : make_float4(0.f, 0.f, 0.f, 0.f);
+            part[s][0] = v.x, part[s][V > 1 ? 1 : 0] = v.y, part[s][V > 2 ? 2 : 0] = v.z, part[s][V > 3 ? 3 : 0] = v.w;
+        } else {
+            part[s][0] = s < slices ? __ldcg(partials + (size_t)s * total + idx) : 0.0f;
+        }
+    }
+    float out[V];
 #pragma unroll
-    for (uint32_t s = 1; s < 16; ++s)
-        if (s < slices) tot = __fadd_rn(tot, part[s]);
-    y[idx] = bias ? __fadd_rn(tot, bias[idx % n]) : tot;
+    for (int j = 0; j < V; ++j) {
+        float tot = part[0][j];
+#pragma unroll
+        for (uint32_t s = 1; s < 16; ++s)
+            if (s < slices) tot = __fadd_rn(tot, part[s][j]);
+        out[j] = bias ? __fadd_rn(tot, bias[(idx + j) % n]) : tot;
+    }
+    if (V == 4) *reinterpret_cast<float4*>(y + idx) = make_float4(out[0], out[V > 1 ? 1 : 0], out[V > 2 ? 2 : 0], out[V > 3 ? 3 : 0]);
+    else y[idx] = out[0];
 }
 
 // nanoseconds of one instruction at N columns (M = 64, K = 32 bytes)
@@ -630,9 +645,14 @@ bool launch_gemv_q4_umma(cudaStream_t s, int sm_count, uint32_t* status, const f
     GQ_CUDA(cudaFuncSetAttribute(gemv_q4_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     launch_after(gemv_q4_umma_kernel, dim3(p.grid), dim3(kThreads), smem, s, wmap, (const uint8_t*)xdigits, scale, zero, p.slices > 1 ? nullptr : bias, y,
                  partials, (uint32_t)m, (uint32_t)k, (uint32_t)n, (uint32_t)groups, p, status);
-    if (p.slices > 1)
-        launch_after(slice_sum_kernel, dim3((uint32_t)((m * n + 255) / 256)), dim3(256), 0, s, (const float*)partials, p.slices, (uint32_t)(m * n), (uint32_t)n,
-                     bias, y);
+    if (p.slices > 1) {
+        if (n % 4 == 0 && (reinterpret_cast<uintptr_t>(y) & 15) == 0)
+            launch_after(slice_sum_kernel<4>, dim3((uint32_t)((m * n / 4 + 255) / 256)), dim3(256), 0, s, (const float*)partials, p.slices, (uint32_t)(m * n),
+                         (uint32_t)n, bias, y);
+        else
+            launch_after(slice_sum_kernel<1>, dim3((uint32_t)((m * n + 255) / 256)), dim3(256), 0, s, (const float*)partials, p.slices, (uint32_t)(m * n),
+                         (uint32_t)n, bias, y);
+    }
     return true;
 }
 
