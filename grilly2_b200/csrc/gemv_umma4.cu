@@ -623,14 +623,20 @@ uint64_t gemv_q4_umma_scratch_bytes(uint64_t m, uint64_t k, uint64_t n, int sm_c
     if (m < 1 || m > 16 || k == 0 || k % 128 || n == 0) return 0;
     const Plan p = make_plan(m, n, k / 128, sm_count);
     if (p.grid == 0) return 0;
-    return digits_region_bytes(k / 128, p.rows_pad) + (p.slices > 1 ? (uint64_t)p.slices * m * n * 4 : 0);
+    return digits_region_bytes(k / 128, p.rows_pad) + (p.slices > 1 ? (uint64_t)p.slices : 1ull) * m * n * 4;  // (K not split: room for a copy of y)
+}
+
+const float* gemv_q4_umma_partials(const void* scratch, uint64_t m, uint64_t k, uint64_t n, int sm_count) {
+    const Plan p = make_plan(m, n, k / 128, sm_count);
+    return reinterpret_cast<const float*>(reinterpret_cast<const uint8_t*>(scratch) + digits_region_bytes(k / 128, p.rows_pad));
 }
 
 // Returns false when the shape is not this kernel's: group_size 128, in_features a multiple of 128, 1 to 16 rows of x,
 // 16-byte aligned x and weights. `scratch` holds gemv_q4_umma_scratch_bytes bytes. Up to three launches: x -> digit tiles
 // (tiny), the linear, and the sum over the K slices.
 bool launch_gemv_q4_umma(cudaStream_t s, int sm_count, uint32_t* status, const float* x, uint64_t m, uint64_t k, const uint32_t* q,
-                         const float* scale, const float* zero, const float* bias, uint64_t n, uint64_t group, float* y, void* scratch) {
+                         const float* scale, const float* zero, const float* bias, uint64_t n, uint64_t group, float* y, void* scratch,
+                         uint32_t* deferred) {
     if (m < 1 || m > 16 || group != 128 || k == 0 || k % 128 || n == 0 || m * n > 0x7fffffffull || k > (1ull << 24)) return false;
     if (((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(x)) & 15) != 0) return false;
     const uint64_t groups = k / 128, row_bytes = k / 2;
@@ -645,7 +651,8 @@ bool launch_gemv_q4_umma(cudaStream_t s, int sm_count, uint32_t* status, const f
     GQ_CUDA(cudaFuncSetAttribute(gemv_q4_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     launch_after(gemv_q4_umma_kernel, dim3(p.grid), dim3(kThreads), smem, s, wmap, (const uint8_t*)xdigits, scale, zero, p.slices > 1 ? nullptr : bias, y,
                  partials, (uint32_t)m, (uint32_t)k, (uint32_t)n, (uint32_t)groups, p, status);
-    if (p.slices > 1) {
+    if (deferred) *deferred = p.slices > 1 ? p.slices : 0u;
+    if (p.slices > 1 && !deferred) {
         if (n % 4 == 0 && (reinterpret_cast<uintptr_t>(y) & 15) == 0)
             launch_after(slice_sum_kernel<4>, dim3((uint32_t)((m * n / 4 + 255) / 256)), dim3(256), 0, s, (const float*)partials, p.slices, (uint32_t)(m * n),
                          (uint32_t)n, bias, y);

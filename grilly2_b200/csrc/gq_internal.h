@@ -211,8 +211,12 @@ bool launch_gemv_q4_imma(cudaStream_t s, int sm_count, uint32_t* status, const f
 // int4 group-128 decode on tcgen05 for 1 to 16 rows of x in one pass (gemv_umma4.cu). The scratch holds the K slices'
 // partial sums and the per-tile arrival counters (zero between launches).
 uint64_t gemv_q4_umma_scratch_bytes(uint64_t m, uint64_t k, uint64_t n, int sm_count);
+// `deferred`, when given: the sum over the K slices is left to the caller — *deferred receives the number of slices (their
+// partial sums lie at gemv_q4_umma_partials(scratch, ...), bias NOT added), or 0 when K was not split and y (with bias) is complete.
 bool launch_gemv_q4_umma(cudaStream_t s, int sm_count, uint32_t* status, const float* x, uint64_t m, uint64_t k, const uint32_t* q,
-                         const float* scale, const float* zero, const float* bias, uint64_t n, uint64_t group, float* y, void* scratch);
+                         const float* scale, const float* zero, const float* bias, uint64_t n, uint64_t group, float* y, void* scratch,
+                         uint32_t* deferred = nullptr);
+const float* gemv_q4_umma_partials(const void* scratch, uint64_t m, uint64_t k, uint64_t n, int sm_count);
 // Zeroed device memory owned by the context, grown (never shrunk or moved while graphs may name it) on demand.
 void* context_scratch(gq_ctx* ctx, uint64_t bytes);
 
@@ -230,7 +234,8 @@ gq_comm* comm_create(int nranks, int rank, const void* id128);
 void comm_destroy(gq_comm* c);
 void comm_info(gq_comm* c, int* nranks, int* rank);
 void all_gather_columns(cudaStream_t s, gq_comm* c, const float* src, float* dst, uint64_t m, uint64_t n_shard);
-void launch_peer_gather(cudaStream_t s, int sm_count, const PeerOut& peer, const float* src, uint64_t m, uint64_t n_shard, uint32_t* status);
+void launch_peer_gather(cudaStream_t s, int sm_count, const PeerOut& peer, const float* src, uint64_t m, uint64_t n_shard, uint32_t* status,
+                        uint32_t slices = 0, const float* bias = nullptr);
 
 // GPTQ (gptq.cu)
 void launch_hessian_add(cudaStream_t s, const float* x, uint64_t rows, uint64_t k, float* h);

@@ -86,14 +86,29 @@ __device__ __forceinline__ unsigned long long ld_sys_u64(const unsigned long lon
 }
 
 // Every CTA sends a slice of this rank's block to every rank, then receives a slice of the whole y.
+// slices > 0: src holds `slices` partial results of m x n_shard floats each (the tcgen05 decode kernel's K slices); what is
+// sent is their sum in slice order, plus bias.
 __global__ void __launch_bounds__(256) peer_gather_kernel(PeerOut peer, const float* __restrict__ src, uint32_t m, uint32_t n_shard,
-                                                         uint32_t* status) {
+                                                         uint32_t slices, const float* __restrict__ bias, uint32_t* status) {
     const uint32_t step = *reinterpret_cast<const volatile uint32_t*>(peer.state) + 1u;  // the last CTA to finish writes it: every CTA has read it by then
     const size_t half = ((size_t)(step & 1u) * peer.m_total + peer.row0) * peer.n_full;
     const uint32_t tid = blockIdx.x * blockDim.x + threadIdx.x, nthreads = gridDim.x * blockDim.x;
     for (uint32_t i = tid; i < m * n_shard; i += nthreads) {
         const uint32_t r = i / n_shard, c = i - r * n_shard;
-        const unsigned long long word = ((unsigned long long)step << 32) | __float_as_uint(src[i]);
+        float value;
+        if (slices == 0) {
+            value = src[i];
+        } else {
+            float part[16];  // every slice's value is requested before the first is used
+#pragma unroll
+            for (uint32_t sl = 0; sl < 16; ++sl) part[sl] = sl < slices ? __ldcg(src + (size_t)sl * m * n_shard + i) : 0.0f;
+            value = part[0];
+#pragma unroll
+            for (uint32_t sl = 1; sl < 16; ++sl)
+                if (sl < slices) value = __fadd_rn(value, part[sl]);
+            if (bias) value = __fadd_rn(value, bias[c]);
+        }
+        const unsigned long long word = ((unsigned long long)step << 32) | __float_as_uint(value);
         const size_t at = half + (size_t)r * peer.n_full + (size_t)peer.rank * n_shard + c;
         for (uint32_t pr = 0; pr < peer.nranks; ++pr) st_sys_u64(peer.ll[pr] + at, word);
     }
@@ -160,13 +175,14 @@ void all_gather_columns(cudaStream_t s, gq_comm* c, const float* src, float* dst
     nccl_check(nccl().GroupEnd(), "ncclGroupEnd");
 }
 
-void launch_peer_gather(cudaStream_t s, int sm_count, const PeerOut& peer, const float* src, uint64_t m, uint64_t n_shard, uint32_t* status) {
+void launch_peer_gather(cudaStream_t s, int sm_count, const PeerOut& peer, const float* src, uint64_t m, uint64_t n_shard, uint32_t* status,
+                        uint32_t slices, const float* bias) {
     // all CTAs must be resident at once (a CTA waits for words other CTAs of this very launch send): at most one per SM
     const uint64_t work = m * n_shard * peer.nranks;
     uint64_t grid = (work + 1023) / 1024;
     if (grid > (uint64_t)sm_count) grid = sm_count;
     if (grid < 1) grid = 1;
-    peer_gather_kernel<<<(uint32_t)grid, 256, 0, s>>>(peer, src, (uint32_t)m, (uint32_t)n_shard, status);
+    peer_gather_kernel<<<(uint32_t)grid, 256, 0, s>>>(peer, src, (uint32_t)m, (uint32_t)n_shard, slices, bias, status);
 }
 
 }  // namespace gq

@@ -411,7 +411,10 @@ int32_t gq_peer_gather(gq_ctx* ctx, gq_buf src, uint64_t m, uint64_t n_shard, in
 /* gq_int4_linear and the gather in ONE kernel: the GEMV's epilogue sends this rank's block of columns straight to every
  * rank's receive buffer (plain peer stores of value-and-step words, as above) and the CTAs then share out the receiving of the
  * whole y into y_full. Same buffers and protocol as gq_peer_gather, so calls of both kinds may be mixed on one set.
- * Shapes: the ring kernel's (group_size 128, in_features 4096 or 8192); up to 16 rows of x, four per pass. */
+ * Shapes: the ring kernel's (group_size 128, in_features 4096 or 8192); up to 16 rows of x, four per pass. Where
+ * gq_int4_linear's AUTO would pick the tcgen05 decode kernel (five and more rows on a shard of 4 MB and more; any
+ * in_features that is a multiple of 128), that kernel runs instead and the gather adds up its K slices' partial sums
+ * (and the bias) as it sends them: one pass over the weight, one launch less than linear-then-gather. */
 int32_t gq_int4_linear_gather(gq_ctx* ctx, gq_buf x, uint64_t x_off, uint64_t m, uint64_t k, gq_buf q, gq_buf scale, gq_buf zero, gq_buf bias,
                               uint64_t b_off, uint64_t n_shard, uint64_t group, int32_t rank, int32_t nranks, const gq_buf* peer_recv,
                               gq_buf state, gq_buf y_full);

@@ -91,6 +91,22 @@ def main() -> None:
                     assert np.array_equal(sep, got), "separate gather differs from the fused one"
                 dist.barrier()
             peers2.close()
+        # a shard large enough (4 MB and more) for the tcgen05 decode kernel: many rows go through it, the gather adding up its
+        # K slices' partial sums as it sends them
+        k4, per4 = 8192, 1024
+        w4 = (rng.standard_normal((per4 * world, k4)) * 0.015).astype(np.float32)
+        b4 = rng.standard_normal(per4 * world).astype(np.float32)
+        q4, s4, z4 = oracle.quantize_q4(w4, group)
+        layer4 = ShardedLinear.from_full(w4, b4, world, rank, bits=4, group_size=group)
+        for m4 in (16, 6):
+            peers4 = PeerGather(world, rank, m4, per4 * world, exchange)
+            for step in range(3):
+                xs = (rng.standard_normal((m4, k4)) * (step + 1)).astype(np.float32)
+                ref = oracle.linear_q4(xs, q4, s4, z4, b4, k4, group)
+                got = peers4.linear_gather(layer4.q, _C.Tensor.from_numpy(xs), layer4.bias).numpy()
+                assert np.abs(got - ref).max() / np.abs(ref).max() <= 1e-5, f"tensor-core linear + gather, m = {m4}, step {step}"
+                dist.barrier()
+            peers4.close()
         # A captured graph holding ONE gather, replayed many times with a different x each time and no host wait in
         # between: the device alternates the halves of the receive buffer by itself, so a rank that runs ahead never
         # overwrites what a slower one still has to read. Every step's result is kept and checked at the end.

@@ -66,6 +66,34 @@ def test_fused_linear_gather_with_a_single_rank_equals_the_linear(m, n, k):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("m,n,k", [(16, 1024, 8192), (9, 2304, 4096), (5, 1100, 12288)])
+def test_many_rows_on_a_large_shard_take_the_tensor_core_route_and_equal_the_linear(m, n, k):
+    """Five and more rows on a weight of 4 MB and more: gq_int4_linear_gather runs the tcgen05 decode kernel and lets the
+    gather add up its K slices; with one rank that must equal gq_int4_linear (which picks the same kernel and adds the
+    slices in the same order) bit for bit, and the CPU oracle within 1e-5, step after step."""
+    import numpy as np
+    import oracle
+    from grilly2_b200 import _C
+    from grilly2_b200.sharded import PeerGather
+    rng = np.random.default_rng(n + k)
+    wf = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
+    w = _C.Int4Weight.quantize(_C.Tensor.from_numpy(wf), 128)
+    q, s, z = oracle.quantize_q4(wf, 128)
+    b = rng.standard_normal(n).astype(np.float32)
+    bias = _C.Tensor.from_numpy(b)
+    peers = PeerGather(1, 0, m, n, lambda obj: [obj])
+    for step in range(3):
+        xs = rng.standard_normal((m, k)).astype(np.float32)
+        x = _C.Tensor.from_numpy(xs)
+        want = w.linear(x, bias).numpy()
+        got = peers.linear_gather(w, x, bias).numpy()
+        np.testing.assert_array_equal(got, want)
+        ref = oracle.linear_q4(xs, q, s, z, b, k, 128)
+        assert np.abs(got - ref).max() / np.abs(ref).max() <= 1e-5
+    peers.close()
+
+
+@pytest.mark.gpu
 @pytest.mark.parametrize("fused", [False, True], ids=["gather", "linear_gather"])
 def test_a_gather_whose_peer_never_sends_gives_up_and_reports_the_rank(fused):
     """Failure detection without a fault: two "ranks" whose receive buffers both live in this process, and nobody
