@@ -8,7 +8,9 @@
 // The first call on a device looks the array's address up (set-up: one
 // cudaGetSymbolAddress, remembered per device); make that call before any
 // stream capture begins. The array is zero when the module loads and every
-// launch leaves the counters at zero again, which is all the kernel needs.
+// launch leaves the counters at zero again, which is all the kernel needs; the
+// counters lie at the start of the array whatever the shape, so calls of
+// different shapes may follow one another.
 // Every call on a device shares the one array: calls that overlap on the GPU
 // (two contexts, hence two streams, on one device) race on it; calls on one
 // context are ordered by its stream and do not.
@@ -18,7 +20,7 @@
 
 namespace {
 
-// 2 MiB: room for heads * splits * (head_dim + 2) + heads floats, e.g. 32 heads x 64 splits x head_dim 128.
+// 2 MiB: room for 1024 counters + heads * splits * (head_dim + 2) floats, e.g. 32 heads x 64 splits x head_dim 128.
 constexpr uint64_t kStaticScratchFloats = 512ull * 1024ull;
 static __device__ __align__(256) float g_attn_scratch[kStaticScratchFloats];
 

@@ -187,12 +187,16 @@ __global__ void __launch_bounds__(256) argmax_rows_kernel(const float* __restric
 // which it then resets — merges the splits:
 //   out = sum_s acc_s exp(m_s - M) / sum_s z_s exp(m_s - M),  M = max_s m_s.
 // The length is the cache cursor plus the token just appended, read from
-// device memory. scratch: heads * splits * (dim + 2) floats, then `heads`
-// counters that must be zero before the first call.
+// device memory. scratch: kAttnCounterWords counters (one per head) that must be
+// zero before the first call and are left at zero by every call, then heads *
+// splits * (dim + 2) floats. The counters come FIRST, at the same place whatever
+// the shape, so that calls of different shapes may share one scratch: behind the
+// partial results they would land inside what a call of another shape left there.
 constexpr int kAttnThreads = 128;
 constexpr uint32_t kAttnMaxChunk = 512;  // keys per split (scores live in shared memory)
 constexpr uint32_t kAttnChunk = 32;      // keys per split aimed at: short dependent chains, many CTAs
 constexpr uint32_t kAttnMaxSplits = 64;
+constexpr uint32_t kAttnCounterWords = 1024;  // heads at most
 
 // L = dim / 4 lanes share a key (one float4 of the row each), so a CTA takes 128 / L keys per pass with every
 // load of the pass independent of the others.
@@ -225,8 +229,8 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const float* 
     const uint32_t j0 = split * chunk, jcap = min(j0 + chunk, max_len);  // where this split's keys lie, whatever the cursor says
     const float4* kb = reinterpret_cast<const float4*>(kc + (size_t)g * max_len * dim);
     const float4* vb = reinterpret_cast<const float4*>(vc + (size_t)g * max_len * dim);
-    float* part = scratch + ((size_t)h * splits + split) * (dim + 2);
-    uint32_t* counters = reinterpret_cast<uint32_t*>(scratch + (size_t)heads * splits * (dim + 2));
+    float* part = scratch + kAttnCounterWords + ((size_t)h * splits + split) * (dim + 2);
+    uint32_t* counters = reinterpret_cast<uint32_t*>(scratch);
 
     // The first passes' keys AND values are requested at once, before the cursor is known (rows past it are valid
     // memory and are masked below): q, the cursor, K and V then cost one memory latency instead of four in a row.
@@ -358,7 +362,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const float* 
     __syncthreads();
     if (!s_last) return;
     __threadfence();
-    const float* hp = scratch + (size_t)h * splits * (dim + 2);
+    const float* hp = scratch + kAttnCounterWords + (size_t)h * splits * (dim + 2);
     // the weights exp(m_s - M) once, in shared memory (the scores are no longer needed)
     float M = -INFINITY;
     for (uint32_t s = 0; s < splits; ++s) M = fmaxf(M, __ldcg(hp + s * (dim + 2)));
@@ -413,13 +417,14 @@ uint32_t attn_splits(uint32_t heads, uint32_t max_len, int sm_count) {
     if (splits < need) splits = need;
     return splits < 1 ? 1 : splits;
 }
-uint64_t attn_scratch_floats(uint32_t heads, uint32_t dim, uint32_t splits) { return (uint64_t)heads * splits * (dim + 2) + heads; }
+uint64_t attn_scratch_floats(uint32_t heads, uint32_t dim, uint32_t splits) { return (uint64_t)kAttnCounterWords + (uint64_t)heads * splits * (dim + 2); }
 // cosv == nullptr: q is the rotated query and the cache already holds the new token (after rope_kv_append). Otherwise q is the raw
 // q | k | v row, rotated and appended here.
 void launch_attn_decode(cudaStream_t s, const float* q, float* kc, float* vc, const uint32_t* lens, uint32_t layer, uint32_t heads,
                         uint32_t kv_heads, uint32_t dim, uint32_t max_len, float scale, uint32_t splits, float* scratch, float* out,
                         const float* cosv, const float* sinv, bool early) {
     const uint32_t chunk = (max_len + splits - 1) / splits;
+    if (heads > kAttnCounterWords) fail("attention: at most %u heads (got %u)", kAttnCounterWords, heads);
     if (splits > kAttnMaxChunk || chunk > kAttnMaxChunk)
         fail("attention: a cache of %u positions is beyond this kernel (%u splits of %u keys)", max_len, splits, chunk);
     const dim3 grid(splits, heads);

@@ -300,8 +300,9 @@ int32_t gq_int8_linear_swiglu(gq_ctx* ctx, gq_buf gate_up, uint64_t k, gq_buf q,
 /* gq_attn_decode with the scratch in a fixed 2 MiB array of the library's own device memory: takes no scratch
  * buffer and allocates nothing, on the first call or later. No counterpart in the reference (its scratch is
  * a pooled buffer, kv_cache.rs:502-528). The first call on a device does the set-up (an address look-up):
- * make it before a stream capture begins. Refuses shapes whose heads * splits * (dim + 2) + heads floats exceed
- * the array. Every call on a device shares the array, so calls that overlap on the GPU race; calls on one
+ * make it before a stream capture begins. Refuses shapes whose 1024 + heads * splits * (dim + 2) floats exceed
+ * the array (the per-head counters lie in its first 1024 words whatever the shape, so calls of different shapes may
+ * follow one another). Every call on a device shares the array, so calls that overlap on the GPU race; calls on one
  * context are stream-ordered and do not. */
 int32_t gq_attn_decode_static(gq_ctx* ctx, gq_buf q, gq_buf kcache, uint64_t k_off, gq_buf vcache, uint64_t v_off, gq_buf lens,
                               uint64_t layer, uint64_t layers, uint64_t heads, uint64_t kv_heads, uint64_t dim, uint64_t max_len,
