@@ -49,8 +49,17 @@ constexpr int kThreads = (kWarps + 1) * 32;      // plus the producer warp
 constexpr int kPanel = 128;                      // rows a CTA reduces at a time
 constexpr uint32_t kPartBytes = 2048;            // bytes of a weight row per stage: 32 blocks, two per consumer warp
 constexpr int kBlocksPerWarp = kPartBytes / 64 / kWarps;
+constexpr uint32_t kRowStride = kPartBytes + 64;  // 64 mod 128: rows land in different banks
+constexpr uint32_t kStageBytes = 16 * kRowStride;
 constexpr int kMaxStages = 5;
 
+__device__ __forceinline__ uint4 ldg_stream(const uint4* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
 
 // D(16x8, s32) += A(16x32, u8 row-major) * B(32x8, s8 column-major)
 __device__ __forceinline__ void mma_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -179,7 +188,7 @@ __device__ __forceinline__ void prepare_x(const float* __restrict__ xr, uint32_t
 // ── the kernel ───────────────────────────────────────────────────────────
 // Warp 16 is the producer: it streams the CTA's weight rows into a ring of
 // shared-memory stages with bulk (TMA) copies, one copy per row so that rows
-// can sit row_stride bytes apart (a stride that is 64 mod 128 keeps the
+// can sit kRowStride bytes apart (a stride that is 64 mod 128 keeps the
 // 16-byte fragment reads of eight different rows in different banks). A
 // stage holds one 16-row tile x up to 2048 bytes of each row. Warps 0-15
 // consume: all of them work on the same stage, each on its own 64-byte
@@ -213,16 +222,13 @@ __global__ void __launch_bounds__(kThreads, 1)
     gemv_imma_kernel(const float* __restrict__ x, const uint8_t* __restrict__ q, const float* __restrict__ scale,
                      const float* __restrict__ zero, const float* __restrict__ bias, float* __restrict__ y, uint32_t k,
                      uint32_t n, uint32_t vecs, uint32_t groups, uint32_t gshift, uint32_t gblocks, uint32_t nblocks,
-                     uint32_t nstages, uint32_t row_stride, uint32_t stage_bytes, uint32_t* status, Prologue pro, bool early) {
+                     uint32_t nstages, uint32_t* status, Prologue pro, bool early) {
     // Launched so that it may start before the kernel ahead of it has finished: nothing below touches global memory
     // before a griddepcontrol.wait, except the producer's weight copies when `early` says that kernel did not write them.
     constexpr int R = IS4 ? 8 : 4;
     extern __shared__ __align__(128) uint8_t smem_raw[];
-    // nstages stages of stage_bytes (rows row_stride apart: 2112 bytes and 16 rows for long rows and many of them; a
-    // short row or a CTA with few rows takes less, so that the kernel launched behind this one can be resident beside it and
-    // fetch its weights while this one computes), then one tile's worth of slack for the reads of rows a short stage lacks
-    uint8_t* stages = smem_raw;
-    uint32_t* xb = reinterpret_cast<uint32_t*>(stages + (size_t)nstages * stage_bytes + 16 * row_stride);  // nblocks * 32 * R words
+    uint8_t* stages = smem_raw;                                                  // nstages * kStageBytes
+    uint32_t* xb = reinterpret_cast<uint32_t*>(stages + (size_t)nstages * kStageBytes);  // nblocks * 32 * R words
     float* xinv = reinterpret_cast<float*>(xb + (size_t)nblocks * 32 * R);      // MR * nblocks
     float* xsum = xinv + MR * nblocks;                                           // MR * nblocks (int4)
     float* partial = xsum + (IS4 ? MR * nblocks : 0);                            // kWarps * kPanel * MR
@@ -261,7 +267,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                 if (lane == 0) mbar_arrive_expect_tx(full + s, nrows * bytes);
                 __syncwarp();
                 if (lane < nrows)
-                    bulk_load(stages + (size_t)s * stage_bytes + lane * row_stride,
+                    bulk_load(stages + (size_t)s * kStageBytes + lane * kRowStride,
                               q + (size_t)(row0 + lane) * rowbytes + (size_t)part * kPartBytes, bytes, full + s);
                 if (++s == nstages) s = 0, ++round;
             }
@@ -329,14 +335,14 @@ __global__ void __launch_bounds__(kThreads, 1)
             __syncwarp();
             ok = ok && mbar_wait(full + s, round & 1, failed, status, kStatusFullWaitTimedOut);
             if (ok) {
-                const uint8_t* st = stages + (size_t)s * stage_bytes;
+                const uint8_t* st = stages + (size_t)s * kStageBytes;
 #pragma unroll
                 for (int bi = 0; bi < kBlocksPerWarp; ++bi) {
                     const uint32_t b = warp + kWarps * bi;             // block within the part
                     const uint32_t blk = part * (kPartBytes / 64) + b;  // block within the row
                     if (blk >= nblocks) break;
-                    const uint4 u4 = *reinterpret_cast<const uint4*>(st + g * row_stride + 64 * b + 16 * t);        // row g
-                    const uint4 l4 = *reinterpret_cast<const uint4*>(st + (g + 8) * row_stride + 64 * b + 16 * t);  // row g + 8
+                    const uint4 u4 = *reinterpret_cast<const uint4*>(st + g * kRowStride + 64 * b + 16 * t);        // row g
+                    const uint4 l4 = *reinterpret_cast<const uint4*>(st + (g + 8) * kRowStride + 64 * b + 16 * t);  // row g + 8
                     uint32_t bf[R];  // B fragments: this lane's column is g (digit g % 4 of x row g / 4)
                     if (g < 4 * MR) {
                         const uint4* src = reinterpret_cast<const uint4*>(xb + ((size_t)(blk * 4 + t) * 8 + g) * R);
@@ -424,26 +430,18 @@ bool run(cudaStream_t s, int sm_count, uint32_t* status, const float* x, uint64_
     const size_t fixed = ((size_t)nblocks * 32 * R + (size_t)MR * nblocks * (IS4 ? 2 : 1) + (size_t)kWarps * kPanel * MR + 1) * 4 +
                          2 * kMaxStages * 8 + 32 + (IS4 ? (size_t)kMaxStages * kWarps * kBlocksPerWarp * 16 * 2 * 4 : 0);
     const size_t budget = 226 * 1024;
-    const uint32_t grid = (uint32_t)(n < (uint64_t)sm_count ? n : (uint64_t)sm_count);
-    // Rows lie row_stride apart, 64 mod 128 bytes (the fragment reads of eight rows then fall in different banks), a stage
-    // holds up to 16 of them. A short row, or a CTA that gets fewer than 16 rows, takes correspondingly less, and a small
-    // layer only the stages a CTA fills: the kernel launched behind this one can then be resident beside it.
-    const uint64_t rows_per_cta = (n + grid - 1) / grid, rowbytes64 = (uint64_t)vecs * 16;
-    const uint32_t part_max = (uint32_t)(rowbytes64 < kPartBytes ? rowbytes64 : kPartBytes);
-    const uint32_t row_stride = (part_max + 127) / 128 * 128 + 64;
-    const uint32_t stage_rows = (uint32_t)(rows_per_cta < 16 ? rows_per_cta : 16);
-    const uint32_t stage_bytes = (stage_rows * row_stride + 127) / 128 * 128;
-    const size_t slack = 16 * (size_t)row_stride;
-    if (fixed + slack + 2 * (size_t)stage_bytes > budget) return false;
-    uint32_t nstages = (uint32_t)((budget - fixed - slack) / stage_bytes);
+    if (fixed + 2 * (size_t)kStageBytes > budget) return false;
+    uint32_t nstages = (uint32_t)((budget - fixed) / kStageBytes);
     if (nstages > kMaxStages) nstages = kMaxStages;
-    const uint64_t tiles_per_cta = (rows_per_cta + 15) / 16, parts = (rowbytes64 + kPartBytes - 1) / kPartBytes;
-    const uint64_t used = tiles_per_cta * parts;
+    const uint32_t grid = (uint32_t)(n < (uint64_t)sm_count ? n : (uint64_t)sm_count);
+    // A small layer asks only for the stages a CTA fills (a kernel launched behind it can then be resident beside it).
+    const uint64_t rows_per_cta = (n + grid - 1) / grid, rowbytes64 = (uint64_t)vecs * 16;
+    const uint64_t used = ((rows_per_cta + 15) / 16 + 1) * ((rowbytes64 + kPartBytes - 1) / kPartBytes);
     if (used < nstages) nstages = (uint32_t)(used < 2 ? 2 : used);
-    const size_t smem = fixed + slack + (size_t)nstages * stage_bytes;
+    const size_t smem = fixed + (size_t)nstages * kStageBytes;
     const bool xvec = aligned16(x) && k % 4 == 0;
     using Kernel = void (*)(const float*, const uint8_t*, const float*, const float*, const float*, float*, uint32_t, uint32_t, uint32_t,
-                            uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t*, Prologue, bool);
+                            uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t*, Prologue, bool);
     Kernel kernel = xvec ? gemv_imma_kernel<IS4, MR, true, 0> : gemv_imma_kernel<IS4, MR, false, 0>;
     if (kind != 0) {
         if (IS4 || MR != 1 || !xvec) return false;  // prologues: int8 weights, one aligned row of x
@@ -452,7 +450,7 @@ bool run(cudaStream_t s, int sm_count, uint32_t* status, const float* x, uint64_
     }
     GQ_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     launch_after(kernel, dim3(grid), dim3(kThreads), smem, s, x, reinterpret_cast<const uint8_t*>(q), scale, zero, bias, y, (uint32_t)k,
-                 (uint32_t)n, vecs, groups, gshift, gblocks, nblocks, nstages, row_stride, stage_bytes, status, pro, early);
+                 (uint32_t)n, vecs, groups, gshift, gblocks, nblocks, nstages, status, pro, early);
     return true;
 }
 

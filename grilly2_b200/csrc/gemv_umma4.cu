@@ -57,6 +57,12 @@
 // warps do share with the four nibble warps is the shared-memory pipe: a 16-byte load costs four wavefronts however
 // many lanes read the same address, so the (s, s', z - 8 s, z' - 8 s') of a column pair costs every warp four
 // wavefronts per block of eight columns — ~1000 wavefronts per stage for the drain, ~500 for the nibbles.
+// Under all of that lies the way the weight arrives: a box of the TMA takes 128 bytes from each of the tile's rows,
+// which lie K / 2 bytes apart — one short burst per DRAM page — and a box asked for comes back ~4.7 us later with
+// four in flight, i.e. ~2.3 TB/s over the GPU whatever the warps do (one row of x, a quarter of the drain's work,
+// runs at that rate). Asking each row's whole K slice into L2 ahead of the boxes (cp.async.bulk.prefetch.L2, 512
+// bytes per row) made it slower (the boxes overtake the prefetches and the bytes are fetched twice). The ring
+// kernel's 4 KB contiguous copies do not have this problem; a layout of the weight in tile order would remove it.
 //
 // Replaces, for these shapes, the decode branch of Int4Weight::linear
 // (crates/grilly-infer/src/quant4.rs:371-442, g2-linear-q4.glsl:43-111), which
@@ -82,7 +88,7 @@ constexpr int kMinStages = 2;
 constexpr uint32_t kTmemCols = 512;  // two accumulators of 256 columns
 constexpr uint32_t kSmemBudget = 227 * 1024;
 constexpr uint32_t kMaxTileStages = 16;  // stages of a tile (pairs of groups of a K slice)
-constexpr uint32_t kBarrierBytes = (2 * kMaxStages + 2 + 4 + kMaxTileStages) * 8 + 16;
+constexpr uint32_t kBarrierBytes = (2 * kMaxStages + 4 + 4 + kMaxTileStages) * 8 + 16;
 
 struct Plan {
     uint32_t slices, gps, tile_rows, tiles, lanes, grid;
@@ -236,14 +242,14 @@ __global__ void __launch_bounds__(kThreads, 1)
     const uint32_t stage_bytes = tile_rows * 128u, dstride = plan.rows_pad * 128u, slot_bytes = tile_rows * 16u;
     uint8_t* ring = smem;                                    // nstages x (tile_rows x 128 raw bytes, as the TMA leaves them)
     uint8_t* digits = ring + (size_t)nstages * stage_bytes;  // gps tiles of dstride bytes (the instruction reads 8 KB from each: the tail is whatever follows)
-    uint8_t* hibuf = digits + (size_t)gps * dstride;         // the high nibbles of a stage: four K slices of tile_rows x 32 bytes
-    uint8_t* szring = hibuf + stage_bytes;                   // kSzSlots x [2 groups][tile_rows / 2] float4 (s, s', z - 8 s, z' - 8 s') of two features
+    uint8_t* hibuf = digits + (size_t)gps * dstride;         // two buffers of a stage's high nibbles: four K slices of tile_rows x 32 bytes each
+    uint8_t* szring = hibuf + 2 * stage_bytes;                   // kSzSlots x [2 groups][tile_rows / 2] float4 (s, s', z - 8 s, z' - 8 s') of two features
     float2* xsinv = reinterpret_cast<float2*>(szring + kSzSlots * slot_bytes);  // [gps][16]: (sum of x, 2^(e-26)) per group and row
     uint64_t* full = reinterpret_cast<uint64_t*>(xsinv + (size_t)gps * 16);
     uint64_t* empty = full + kMaxStages;
-    uint64_t* hfull = empty + kMaxStages;  // the stage's high nibbles and scales are in shared memory
-    uint64_t* hempty = hfull + 1;          // ... and the nibbles have been multiplied
-    uint64_t* dfull = hempty + 1;          // [2] an accumulator (two groups) is complete
+    uint64_t* hfull = empty + kMaxStages;  // [2] a stage's high nibbles and scales are in shared memory
+    uint64_t* hempty = hfull + 2;          // [2] ... and the nibbles have been multiplied
+    uint64_t* dfull = hempty + 2;          // [2] an accumulator (two groups) is complete
     uint64_t* dempty = dfull + 2;          // [2] ... and has been read out
     uint64_t* dgfull = dempty + 2;         // [kMaxTileStages] the digit tiles of the slice's stage i are in shared memory
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dgfull + kMaxTileStages);
@@ -265,8 +271,10 @@ __global__ void __launch_bounds__(kThreads, 1)
             mbar_init(full + s, 1);
             mbar_init(empty + s, 1 + kNibbleWarps);  // the raw multiplications (one commit) and the warps that read the stage
         }
-        mbar_init(hfull, kNibbleWarps);
-        mbar_init(hempty, 1);
+        for (uint32_t h = 0; h < 2; ++h) {
+            mbar_init(hfull + h, kNibbleWarps);
+            mbar_init(hempty + h, 1);
+        }
         for (uint32_t d = 0; d < 2; ++d) {
             mbar_init(dfull + d, 1);
             mbar_init(dempty + d, kDrainWarps);
@@ -358,7 +366,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                         ++raw_next, progressed = true;
                     }
                 }
-                if (hi_next < raw_next && ready(hfull, hi_next & 1)) {
+                if (hi_next < raw_next && ready(hfull + (hi_next & 1u), (hi_next >> 1) & 1)) {
                     const uint32_t it = hi_next, buf = it & 1u, i = it % nstage_tile;
                     tc_fence_after_sync();
 #pragma unroll
@@ -366,9 +374,9 @@ __global__ void __launch_bounds__(kThreads, 1)
                         const uint32_t gi = j >> 1, h = j & 1u;
                         const uint32_t x_addr = smem_u32(digits + (size_t)(2 * i + gi) * dstride);
                         umma_i8_ss(tmem_addr(tmem, 16 * gi, buf * kTileMax), umma_desc_k128(x_addr + 64 + 32 * h),
-                                   umma_desc_plain(hi_addr + j * tile_rows * 32u, 128, 256), idesc, true);
+                                   umma_desc_plain(hi_addr + buf * stage_bytes + j * tile_rows * 32u, 128, 256), idesc, true);
                     }
-                    umma_commit(hempty);
+                    umma_commit(hempty + buf);
                     umma_commit(dfull + buf);
                     ++hi_next, progressed = true;
                 }
@@ -429,7 +437,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                 };
                 auto write_row = [&](uint32_t rw, uint32_t rr) {
                     if (rw >= tile_rows) return;
-                    uint8_t* dst = hibuf + (rw >> 3) * 256u + (rw & 7u) * 16u;
+                    uint8_t* dst = hibuf + (it & 1u) * stage_bytes + (rw >> 3) * 256u + (rw & 7u) * 16u;
 #pragma unroll
                     for (uint32_t c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(dst + (c >> 1) * tile_rows * 32u + (c & 1u) * 128u) = w[c];
                     float* slot = reinterpret_cast<float*>(szring + (it % kSzSlots) * slot_bytes) + (rw >> 1) * 4 + (rw & 1u);
@@ -437,8 +445,8 @@ __global__ void __launch_bounds__(kThreads, 1)
                     slot[tile_rows * 2] = sv[rr][1], slot[tile_rows * 2 + 2] = __fmaf_rn(-8.0f, sv[rr][1], zv[rr][1]);
                 };
                 read_row(row);
-                if (it >= 1) {
-                    if (lane == 0) ok = mbar_wait(hempty, (it - 1) & 1, failed, status, kStatusMmaWaitTimedOut);
+                if (it >= 2) {  // the buffer the stage before last used
+                    if (lane == 0) ok = mbar_wait(hempty + (it & 1u), ((it >> 1) - 1) & 1, failed, status, kStatusMmaWaitTimedOut);
                     ok = __shfl_sync(0xffffffffu, ok, 0);
                     if (!ok) break;
                 }
@@ -449,7 +457,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                 write_row(row + 128, 1);
                 fence_proxy_async_smem();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(hfull);
+                if (lane == 0) mbar_arrive(hfull + (it & 1u));
                 if (++s == nstages) s = 0, ++round;
             }
         }
@@ -460,7 +468,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         const uint32_t dw = warp - kFirstDrainWarp, sub = warp & 3u, cq = dw >> 2, q = lane & 3u, dp = (lane >> 2) & 1u;
         const uint32_t r = 4 * sub + (lane >> 3);
         const float dscale = dp ? 65536.0f : 1.0f;  // 256^(2 p)
-        const bool live = 64 * cq < tile_rows;       // a narrow tile leaves the last quarters without columns
+        const bool live = 64 * cq < tile_rows && 4 * sub < m;  // a narrow tile leaves the last quarters without columns, few rows of x the last quarters of tensor memory without rows
         bool ok = my_tiles != 0;
         if (ok) {  // the (sum of x, 2^(e-26)) pairs arrive with the first stage's digits
             if (lane == 0) ok = mbar_wait(dgfull, 0, failed, status, kStatusFullWaitTimedOut);
@@ -580,7 +588,7 @@ double mma_ns(uint32_t ncols) {
 }
 
 size_t smem_bytes(uint32_t gps, uint32_t tile_rows, uint32_t rows_pad, uint32_t nstages) {
-    return 1024 + (size_t)(nstages + 1) * tile_rows * 128 + (size_t)gps * rows_pad * 128 + (size_t)kSzSlots * tile_rows * 16 + (size_t)gps * 128 + kBarrierBytes + 64 +
+    return 1024 + (size_t)(nstages + 2) * tile_rows * 128 + (size_t)gps * rows_pad * 128 + (size_t)kSzSlots * tile_rows * 16 + (size_t)gps * 128 + kBarrierBytes + 64 +
            8192;  // the instruction reads 8 KB from the last group's digits whatever rows_pad is: keep that inside the allocation
 }
 
