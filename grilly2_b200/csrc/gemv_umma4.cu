@@ -56,13 +56,16 @@
 // ~0.1 us; replacing the integer-to-float conversions by exact magic-number arithmetic made it slower. What the 16
 // warps do share with the four nibble warps is the shared-memory pipe: a 16-byte load costs four wavefronts however
 // many lanes read the same address, so the (s, s', z - 8 s, z' - 8 s') of a column pair costs every warp four
-// wavefronts per block of eight columns — ~1000 wavefronts per stage for the drain, ~500 for the nibbles.
-// Under all of that lies the way the weight arrives: a box of the TMA takes 128 bytes from each of the tile's rows,
-// which lie K / 2 bytes apart — one short burst per DRAM page — and a box asked for comes back ~4.7 us later with
-// four in flight, i.e. ~2.3 TB/s over the GPU whatever the warps do (one row of x, a quarter of the drain's work,
-// runs at that rate). Asking each row's whole K slice into L2 ahead of the boxes (cp.async.bulk.prefetch.L2, 512
-// bytes per row) made it slower (the boxes overtake the prefetches and the bytes are fetched twice). The ring
-// kernel's 4 KB contiguous copies do not have this problem; a layout of the weight in tile order would remove it.
+// wavefronts per block of eight columns — ~1000 wavefronts per stage for the drain, ~500 for the nibbles,
+// ~550 more for the tensor core's operand reads and ~200 for the TMA's writes: ~2300 cycles = 1.2 us of the pipe per
+// stage. While the nibble warps work on the stages ahead, a stage takes ~2.0 us at 16 rows; once they have finished
+// the CTA's last tile, the same drain takes ~1.2 us. With one row of x only the four drain warps of the first lane
+// quarter have rows, all four on one scheduler, and a stage still takes ~1.4 us: the read-out is then a chain of
+// waits in those warps, not a pipe that is full.
+// Not the way the weight arrives: with the TMA boxes (128 bytes from each of the tile's rows, K / 2 bytes apart)
+// replaced by contiguous copies of the same size (wrong bytes, timing only) a call took 6 % less, and asking each
+// row's K slice into L2 ahead of the boxes (cp.async.bulk.prefetch.L2) made it slower. Nor a branch between the
+// drain's column blocks: without it (and 28 bytes of spills) a call took 5 % more.
 //
 // Replaces, for these shapes, the decode branch of Int4Weight::linear
 // (crates/grilly-infer/src/quant4.rs:371-442, g2-linear-q4.glsl:43-111), which
