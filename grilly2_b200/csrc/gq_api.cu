@@ -588,7 +588,7 @@ int32_t gq_int8_linear(gq_ctx* ctx, gq_buf x, uint64_t x_off, uint64_t m, uint64
     return guarded([&] {
         Locked l(ctx);
         check_dims("gq_int8_linear", m, k, n);
-        if (kernel < GQ_KERNEL_AUTO || kernel > GQ_KERNEL_UMMA) fail("gq_int8_linear: unknown kernel selector %d", kernel);
+        if (kernel < GQ_KERNEL_AUTO || (kernel > GQ_KERNEL_UMMA && kernel != GQ_KERNEL_TENSOR_I8)) fail("gq_int8_linear: unknown kernel selector %d", kernel);
         auto xp = (const float*)view(ctx, x, x_off, m * k, 4, "gq_int8_linear input");
         auto qp = (const uint32_t*)view(ctx, q, 0, n * words8(k), 4, "gq_int8_linear q");
         auto sp = (const float*)view(ctx, scale, 0, n, 4, "gq_int8_linear scale");
@@ -598,7 +598,16 @@ int32_t gq_int8_linear(gq_ctx* ctx, gq_buf x, uint64_t x_off, uint64_t m, uint64
         if (m == 0 || n == 0) return;  // quant.rs:267-269
         bool done = false;
         const char* name = "gemv_q8";
-        if (kernel == GQ_KERNEL_TENSOR || (kernel == GQ_KERNEL_AUTO && m >= kTensorMinRows)) {
+        if (kernel == GQ_KERNEL_TENSOR_I8 || (kernel == GQ_KERNEL_AUTO && m >= kTensorMinRows)) {
+            // (a scratch that would have to grow inside a capture leaves AUTO to the tf32 kernel, which needs none)
+            const uint64_t need = gemm_q8_i8_scratch_bytes(m, k);
+            if (kernel == GQ_KERNEL_TENSOR_I8 || !(ctx->capturing && ctx->scratch_bytes < need))
+                done = launch_gemm_q8_i8(ctx->stream, ctx->prop.multiProcessorCount, ctx->status_dev, xp, m, k, qp, sp, bp, n, yp, context_scratch(ctx, need));
+            if (done) name = "gemm_i8_q8", ctx->stats.launches += 1;  // the digit planes of x ahead of it
+            if (!done && kernel == GQ_KERNEL_TENSOR_I8)
+                fail("gq_int8_linear: the integer tensor-core GEMM takes in_features up to 131072 (k = %llu)", (unsigned long long)k);
+        }
+        if (!done && (kernel == GQ_KERNEL_TENSOR || (kernel == GQ_KERNEL_AUTO && m >= kTensorMinRows))) {
             done = launch_gemm_q8_tc(ctx->stream, ctx->prop.multiProcessorCount, ctx->status_dev, xp, m, k, qp, sp, bp, n, yp);
             if (done) name = "gemm_tf32_q8";
             if (!done && kernel == GQ_KERNEL_TENSOR)

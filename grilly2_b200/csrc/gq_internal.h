@@ -225,6 +225,11 @@ bool launch_gemv_q8_tc(cudaStream_t s, int sm_count, uint32_t* status, const flo
 
 bool launch_gemm_q8_tc(cudaStream_t s, int sm_count, uint32_t* status, const float* x, uint64_t m, uint64_t k, const uint32_t* q,
                        const float* scale, const float* bias, uint64_t n, float* y);
+// The same product in exact integer arithmetic (kind::i8 against three digit planes of x); `scratch` holds
+// gemm_q8_i8_scratch_bytes(m, k) bytes.
+uint64_t gemm_q8_i8_scratch_bytes(uint64_t m, uint64_t k);
+bool launch_gemm_q8_i8(cudaStream_t s, int sm_count, uint32_t* status, const float* x, uint64_t m, uint64_t k, const uint32_t* q,
+                       const float* scale, const float* bias, uint64_t n, float* y, void* scratch);
 // Rows of x from which AUTO takes the tensor-core GEMM instead of a GEMV.
 constexpr uint64_t kTensorMinRows = 64;
 

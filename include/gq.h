@@ -79,6 +79,12 @@ typedef uint64_t gq_buf; /* 0 is never a valid handle */
                               warps (digits of x in registers, weights through a deep ring of bulk copies): in_features 4096
                               or 8192, up to four rows of x per launch and up to 16 in passes: what AUTO picks there */
 
+#define GQ_KERNEL_TENSOR_I8 7 /* int8 only: the prefill GEMM in exact integer arithmetic on tcgen05 (kind::i8): x as three
+                                 signed base-256 digit planes of a per-row fixed-point integer (error 2^-23 of the row's
+                                 largest |x| per element), the packed weight fed to the tensor core as it lies in HBM, digits
+                                 joined as a 64-bit integer in the epilogue. What AUTO picks from 64 rows of x on (it falls
+                                 back to GQ_KERNEL_TENSOR only when the context's scratch would have to grow inside a capture) */
+
 typedef struct gq_caps { /* replaces gc_caps, gc_shim.h:43-50 */
     char device_name[256];
     uint32_t cc_major, cc_minor;
