@@ -35,18 +35,22 @@ namespace gq {
 
 namespace {
 
-constexpr uint32_t kFT = 256;                    // features per tile: two M = 128 operands
-constexpr uint32_t kXR = 80;                     // rows of x per tile
 constexpr uint32_t kND = 3;                      // digit planes
-constexpr uint32_t kN = kXR * kND;               // 240: N of the instruction
 constexpr uint32_t kChunk = 128;                 // bytes of K per stage
-constexpr uint32_t kABytes = 128 * kChunk;       // 16 KB per A operand
-constexpr uint32_t kPlaneBytes = kXR * kChunk;   // 10 KB per plane: ten whole swizzle atoms
-constexpr uint32_t kStageBytes = 2 * kABytes + kND * kPlaneBytes;  // 62 KB
-constexpr int kStages = 3;
+constexpr uint32_t kABytes = 128 * kChunk;       // 16 KB per A operand (128 features)
 constexpr uint32_t kTmemCols = 512;              // accumulators at columns 0 and 256
-constexpr int kEpilogueWarps = 8;
-constexpr int kThreads = (2 + kEpilogueWarps) * 32;  // warp 0 TMA, warp 1 MMA, warps 2-9 epilogue
+
+// A tile is NA x 128 features by XR rows of x (XR a multiple of 16): N = 3 XR columns per accumulator. Prefill runs
+// <2, 80>; fewer rows of x run one A operand and a narrower B, so that a decode batch costs the bytes of its rows only.
+template <int NA, int XR>
+struct Tile {
+    static constexpr uint32_t kFT = 128 * NA, kN = XR * kND, kPlaneBytes = XR * kChunk;  // whole 1 KB swizzle atoms
+    static constexpr uint32_t kStageBytes = NA * kABytes + kND * kPlaneBytes;
+    static constexpr int kStages = (224 * 1024) / kStageBytes < 8 ? (224 * 1024) / kStageBytes : 8;
+    static constexpr int kEpilogueWarps = 4 * NA;
+    static constexpr int kThreads = (2 + kEpilogueWarps) * 32;  // warp 0 TMA, warp 1 MMA, then the epilogue
+    static constexpr size_t kSmem = (size_t)kStages * kStageBytes + 256 + 1024;
+};
 
 // Row r of x -> planes[d][r][0 .. kp) and xinv[r] = 2^(e-22); rows m .. mpad - 1 are zeros.
 __global__ void __launch_bounds__(256) x_planes_kernel(const float* __restrict__ x, uint32_t m, uint32_t k, uint32_t kp, uint32_t mpad,
@@ -125,16 +129,20 @@ __global__ void __launch_bounds__(256) x_planes_kernel(const float* __restrict__
     }
 }
 
-__global__ void __launch_bounds__(kThreads, 1)
+template <int NA, int XR>
+__global__ void __launch_bounds__((Tile<NA, XR>::kThreads), 1)
     gemm_i8_q8_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap, const float* __restrict__ xinv,
                       const float* __restrict__ scale, const float* __restrict__ bias, float* __restrict__ y, uint32_t m, uint32_t mpad,
                       uint32_t k, uint32_t n, uint32_t band, uint32_t* status) {
+    using T = Tile<NA, XR>;
+    constexpr uint32_t kFT = T::kFT, kXR = XR, kN = T::kN, kPlaneBytes = T::kPlaneBytes, kStageBytes = T::kStageBytes;
+    constexpr int kStages = T::kStages, kEpilogueWarps = T::kEpilogueWarps;
     extern __shared__ uint8_t smem_unaligned[];
     uint8_t* smem = smem_unaligned + ((1024u - (smem_u32(smem_unaligned) & 1023u)) & 1023u);
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + (size_t)kStages * kStageBytes);  // [kStages] the TMA's bytes landed
     uint64_t* empty = full + kStages;                                                     // [kStages] the MMAs read the stage
     uint64_t* dfull = empty + kStages;                                                    // the accumulators are complete
-    uint64_t* dempty = dfull + 1;                                                         // ... and read out (8 warps)
+    uint64_t* dempty = dfull + 1;                                                         // ... and read out (every epilogue warp)
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dempty + 1);
     volatile uint32_t* failed = tmem_slot + 1;
 
@@ -179,11 +187,12 @@ __global__ void __launch_bounds__(kThreads, 1)
                     if (round && !mbar_wait(empty + s, (round - 1) & 1, failed, status, kStatusEmptyWaitTimedOut)) return;
                     uint8_t* st = smem + (size_t)s * kStageBytes;
                     mbar_arrive_expect_tx(full + s, kStageBytes);
-                    tma_load_2d(st, &wmap, (int32_t)(c * kChunk), (int32_t)f0, full + s);
-                    tma_load_2d(st + kABytes, &wmap, (int32_t)(c * kChunk), (int32_t)(f0 + 128), full + s);
+#pragma unroll
+                    for (uint32_t a = 0; a < (uint32_t)NA; ++a)
+                        tma_load_2d(st + a * kABytes, &wmap, (int32_t)(c * kChunk), (int32_t)(f0 + 128 * a), full + s);
 #pragma unroll
                     for (uint32_t d = 0; d < kND; ++d)
-                        tma_load_2d(st + 2 * kABytes + d * kPlaneBytes, &xmap, (int32_t)(c * kChunk), (int32_t)(d * mpad + m0), full + s);
+                        tma_load_2d(st + NA * kABytes + d * kPlaneBytes, &xmap, (int32_t)(c * kChunk), (int32_t)(d * mpad + m0), full + s);
                     if (++s == kStages) s = 0, ++round;
                 }
             }
@@ -200,12 +209,13 @@ __global__ void __launch_bounds__(kThreads, 1)
                     ok = mbar_wait(full + s, round & 1, failed, status, kStatusFullWaitTimedOut);
                     if (!ok) break;
                     tc_fence_after_sync();
-                    const uint32_t a_addr = smem_u32(smem + (size_t)s * kStageBytes), b_addr = a_addr + 2 * kABytes;
+                    const uint32_t a_addr = smem_u32(smem + (size_t)s * kStageBytes), b_addr = a_addr + NA * kABytes;
 #pragma unroll
                     for (uint32_t j = 0; j < 4; ++j) {
                         const uint64_t bd = umma_desc_k128(b_addr + 32 * j);
-                        umma_i8_ss(tmem, umma_desc_k128(a_addr + 32 * j), bd, idesc, (c | j) != 0);
-                        umma_i8_ss(tmem + 256, umma_desc_k128(a_addr + kABytes + 32 * j), bd, idesc, (c | j) != 0);
+#pragma unroll
+                        for (uint32_t a = 0; a < (uint32_t)NA; ++a)
+                            umma_i8_ss(tmem + 256 * a, umma_desc_k128(a_addr + a * kABytes + 32 * j), bd, idesc, (c | j) != 0);
                     }
                     umma_commit(empty + s);
                     if (++s == kStages) s = 0, ++round;
@@ -260,8 +270,30 @@ __global__ void __launch_bounds__(kThreads, 1)
     if (warp == 1) tmem_dealloc(tmem, kTmemCols);
 }
 
-inline uint64_t padded_rows(uint64_t m) { return (m + kXR - 1) / kXR * kXR; }
+// rows of x per tile by the number of rows of the call
+inline uint32_t tile_rows_for(uint64_t m) { return m <= 16 ? 16u : m <= 32 ? 32u : m <= 64 ? 64u : 80u; }
+inline uint64_t padded_rows(uint64_t m) {
+    const uint64_t xr = tile_rows_for(m);
+    return (m + xr - 1) / xr * xr;
+}
 inline uint64_t planes_bytes(uint64_t m, uint64_t k) { return (kND * padded_rows(m) * ((k + 15) / 16 * 16) + 255) / 256 * 256; }
+
+template <int NA, int XR>
+void launch_tiles(cudaStream_t s, int sm_count, uint32_t* status, const uint8_t* planes, const float* xinv, uint64_t m, uint64_t mpad, uint64_t k,
+                  const uint32_t* q, const float* scale, const float* bias, uint64_t n, float* y) {
+    using T = Tile<NA, XR>;
+    const uint64_t rowbytes = (k + 15) / 16 * 16;
+    const CUtensorMap xmap = make_tensor_map_2d(planes, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, rowbytes, kND * mpad, rowbytes, kChunk, XR, Swizzle::B128);
+    const CUtensorMap wmap = make_tensor_map_2d(q, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, rowbytes, n, rowbytes, kChunk, 128, Swizzle::B128);
+    const uint64_t tiles = ((n + T::kFT - 1) / T::kFT) * (mpad / XR);
+    const uint32_t grid = (uint32_t)(tiles < (uint64_t)sm_count ? tiles : (uint64_t)sm_count);
+    // a band's digit planes: at most ~32 MB, so that they and the weight fit the 126 MB L2 together
+    uint64_t band = (32ull << 20) / (kND * XR * rowbytes);
+    band = band < 1 ? 1 : band > mpad / XR ? mpad / XR : band;
+    GQ_CUDA(cudaFuncSetAttribute(gemm_i8_q8_kernel<NA, XR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)T::kSmem));
+    launch_after(gemm_i8_q8_kernel<NA, XR>, dim3(grid), dim3(T::kThreads), T::kSmem, s, xmap, wmap, xinv, scale, bias, y, (uint32_t)m, (uint32_t)mpad,
+                 (uint32_t)k, (uint32_t)n, (uint32_t)band, status);
+}
 
 }  // namespace
 
@@ -277,18 +309,13 @@ bool launch_gemm_q8_i8(cudaStream_t s, int sm_count, uint32_t* status, const flo
     if (kND * mpad > 0x7fffffffull || m * n > (1ull << 40)) return false;
     uint8_t* planes = reinterpret_cast<uint8_t*>(scratch);
     float* xinv = reinterpret_cast<float*>(planes + planes_bytes(m, k));
-    const CUtensorMap xmap = make_tensor_map_2d(planes, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, rowbytes, kND * mpad, rowbytes, kChunk, kXR, Swizzle::B128);
-    const CUtensorMap wmap = make_tensor_map_2d(q, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, rowbytes, n, rowbytes, kChunk, 128, Swizzle::B128);
     launch_after(x_planes_kernel, dim3((uint32_t)mpad), dim3(256), 0, s, x, (uint32_t)m, (uint32_t)k, (uint32_t)rowbytes, (uint32_t)mpad, planes, xinv);
-    const uint64_t tiles = ((n + kFT - 1) / kFT) * (mpad / kXR);
-    const uint32_t grid = (uint32_t)(tiles < (uint64_t)sm_count ? tiles : (uint64_t)sm_count);
-    // a band's digit planes: at most ~32 MB, so that they and the weight fit the 126 MB L2 together
-    uint64_t band = (32ull << 20) / (kND * kXR * rowbytes);
-    band = band < 1 ? 1 : band > mpad / kXR ? mpad / kXR : band;
-    const size_t smem = (size_t)kStages * kStageBytes + 256 + 1024;
-    GQ_CUDA(cudaFuncSetAttribute(gemm_i8_q8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    launch_after(gemm_i8_q8_kernel, dim3(grid), dim3(kThreads), smem, s, xmap, wmap, (const float*)xinv, scale, bias, y, (uint32_t)m, (uint32_t)mpad,
-                 (uint32_t)k, (uint32_t)n, (uint32_t)band, status);
+    switch (tile_rows_for(m)) {
+        case 16: launch_tiles<1, 16>(s, sm_count, status, planes, xinv, m, mpad, k, q, scale, bias, n, y); break;
+        case 32: launch_tiles<1, 32>(s, sm_count, status, planes, xinv, m, mpad, k, q, scale, bias, n, y); break;
+        case 64: launch_tiles<1, 64>(s, sm_count, status, planes, xinv, m, mpad, k, q, scale, bias, n, y); break;
+        default: launch_tiles<2, 80>(s, sm_count, status, planes, xinv, m, mpad, k, q, scale, bias, n, y); break;
+    }
     return true;
 }
 

@@ -598,7 +598,10 @@ int32_t gq_int8_linear(gq_ctx* ctx, gq_buf x, uint64_t x_off, uint64_t m, uint64
         if (m == 0 || n == 0) return;  // quant.rs:267-269
         bool done = false;
         const char* name = "gemv_q8";
-        if (kernel == GQ_KERNEL_TENSOR_I8 || (kernel == GQ_KERNEL_AUTO && m >= kTensorMinRows)) {
+        // AUTO: the integer tensor-core kernel from three rows of x on (at three rows only where the weight is 8 MB and more:
+        // measured, dp4a still wins on the small projections there); one or two rows stay with the streaming IMMA kernel
+        const bool auto_i8 = kernel == GQ_KERNEL_AUTO && (m >= 4 || (m == 3 && n * k >= (8ull << 20)));
+        if (kernel == GQ_KERNEL_TENSOR_I8 || auto_i8) {
             // (a scratch that would have to grow inside a capture leaves AUTO to the tf32 kernel, which needs none)
             const uint64_t need = gemm_q8_i8_scratch_bytes(m, k);
             if (kernel == GQ_KERNEL_TENSOR_I8 || !(ctx->capturing && ctx->scratch_bytes < need))

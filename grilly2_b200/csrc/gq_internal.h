@@ -230,7 +230,8 @@ bool launch_gemm_q8_tc(cudaStream_t s, int sm_count, uint32_t* status, const flo
 uint64_t gemm_q8_i8_scratch_bytes(uint64_t m, uint64_t k);
 bool launch_gemm_q8_i8(cudaStream_t s, int sm_count, uint32_t* status, const float* x, uint64_t m, uint64_t k, const uint32_t* q,
                        const float* scale, const float* bias, uint64_t n, float* y, void* scratch);
-// Rows of x from which AUTO takes the tensor-core GEMM instead of a GEMV.
+// Rows of x from which AUTO takes the tf32 tensor-core GEMM when the integer one cannot run (its scratch would have to
+// grow inside a capture).
 constexpr uint64_t kTensorMinRows = 64;
 
 // multi-GPU (sharded.cu)

@@ -82,8 +82,10 @@ typedef uint64_t gq_buf; /* 0 is never a valid handle */
 #define GQ_KERNEL_TENSOR_I8 7 /* int8 only: the prefill GEMM in exact integer arithmetic on tcgen05 (kind::i8): x as three
                                  signed base-256 digit planes of a per-row fixed-point integer (error 2^-23 of the row's
                                  largest |x| per element), the packed weight fed to the tensor core as it lies in HBM, digits
-                                 joined as a 64-bit integer in the epilogue. What AUTO picks from 64 rows of x on (it falls
-                                 back to GQ_KERNEL_TENSOR only when the context's scratch would have to grow inside a capture) */
+                                 joined as a 64-bit integer in the epilogue. Tiles of 256 features x 80 rows of x for prefill,
+                                 128 features x 16 / 32 / 64 rows for decode batches, so a few rows cost one pass over the
+                                 weight. What AUTO picks from three rows of x on (inside a capture in which the context's
+                                 scratch would have to grow it falls back to dp4a, from 64 rows to GQ_KERNEL_TENSOR) */
 
 typedef struct gq_caps { /* replaces gc_caps, gc_shim.h:43-50 */
     char device_name[256];

@@ -52,7 +52,7 @@ def test_int8_linear(g, m, n, k, with_bias):
     y = t._q.linear(xt, bt, _lib.KERNEL_GEMV).numpy()
     np.testing.assert_array_equal(y, ref)  # same summation order as the reference's decode shader
     assert (np.abs(y - want) <= bound).all()
-    kernels = [_lib.KERNEL_DP4A, _lib.KERNEL_AUTO] + ([_lib.KERNEL_IMMA, _lib.KERNEL_UMMA] if m <= 2 else [])
+    kernels = [_lib.KERNEL_DP4A, _lib.KERNEL_AUTO, _lib.KERNEL_TENSOR_I8] + ([_lib.KERNEL_IMMA, _lib.KERNEL_UMMA] if m <= 2 else [])
     for kernel in kernels:
         y = t._q.linear(xt, bt, kernel).numpy()
         assert rel(y, ref) <= TOL
