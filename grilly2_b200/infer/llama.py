@@ -187,7 +187,7 @@ class LlamaDecoder:
 
     def prefill(self, tokens: "_C.Tensor"):
         """tokens: int32 [T], continuing the cache from its cursor. Every layer runs on all T rows at once — the linears
-        take the kernel their row count selects (decode kernels up to 16 rows, the tensor-core GEMM from 64) — with causal
+        take the kernel their row count selects (the streaming decode kernels for one or two rows, the integer tensor-core GEMM from three) — with causal
         attention over the cache (python/grilly/infer/models/llama.py:340-366 with logits_to_keep=1). Returns the LAST
         position's logits [1, vocab] and advances the cursor by T."""
         c, lib, ctx = self.cfg, _lib.load(), _C.context()
