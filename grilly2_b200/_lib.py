@@ -17,6 +17,7 @@ GQ_OK, GQ_ERR = 0, 1
 MEM_DEVICE, MEM_PERSISTENT = 0, 3
 KERNEL_AUTO, KERNEL_GEMV, KERNEL_TENSOR, KERNEL_DP4A, KERNEL_IMMA, KERNEL_UMMA, KERNEL_RING = 0, 1, 2, 3, 4, 5, 6
 KERNEL_TENSOR_I8 = 7
+KERNEL_UMMA_LANES = 8
 
 u64, i32, u32, vp = ctypes.c_uint64, ctypes.c_int32, ctypes.c_uint32, ctypes.c_void_p
 P = ctypes.POINTER

@@ -583,6 +583,280 @@ __global__ void __launch_bounds__(256) slice_sum_kernel(const float* __restrict_
     else y[idx] = out[0];
 }
 
+// ───────────────────────── the same product with the FEATURES on the lanes ─────────────────────────
+// The kernel above keeps the rows of x on the lanes of tensor memory, so a thread of the drain meets a new pair of
+// features in every block of eight columns and has to fetch their (scale, zero - 8 scale) from shared memory each time:
+// those loads, not the arithmetic, are what its drain costs. Here the operands change places: the packed weight is the
+// A operand (M = 128 features: raw bytes as the TMA left them, high nibbles from the four nibble warps), the digit tiles
+// of x are the B operand (N = 16 / 32 / 64 digit rows), and an accumulator is [feature][digit row of x]. A kind::i8
+// instruction takes 65 cycles for any N up to 128 (128 at N = 256), so eight instructions of N <= 64 per 128 features
+// and two groups cost what four of N = 256 cost per 256 features: nothing is lost. A drain thread now owns ONE feature:
+// its scale and zero point are two registers per group (read from global memory while it waits for the accumulator),
+// the 64 digit sums of the 16 rows of x arrive with four loads from tensor memory, and the accumulator is released
+// before the arithmetic starts. Each group has an accumulator of its own (eight slots of 64 columns), so the
+// multiplications run up to eight groups ahead of the drain. A CTA owns tiles of 128 features over ALL of K: the digit
+// tiles of x stream through the ring beside the weight (two groups = one stage), nothing is split, no partial sums,
+// no second kernel.
+constexpr int kLThreads = 448;            // warp 0 producer, 1 MMA issuer, 2-5 nibbles, 6-13 drain (two sets of four)
+constexpr uint32_t kLTile = 128;          // features per tile = M of the instruction
+constexpr uint32_t kLRaw = kLTile * 128;  // a stage's packed weight: 128 features x two groups
+constexpr uint32_t kLSlots = 8;           // accumulators in flight, 64 columns each
+constexpr uint32_t kLSets = 2;            // drain sets: set j reads out the tile's groups j, j + 2, ...
+constexpr int kLMaxStages = 6;
+constexpr uint32_t kLMaxGroups = 128;     // the (sum of x, 2^(e-26)) pairs of every group stay in shared memory: 128 bytes a group
+
+__global__ void __launch_bounds__(kLThreads, 1)
+    gemv_q4_lanes_kernel(const __grid_constant__ CUtensorMap wmap, const uint8_t* __restrict__ xdigits, const float* __restrict__ scale,
+                         const float* __restrict__ zero, const float* __restrict__ bias, float* __restrict__ y, uint32_t m, uint32_t n,
+                         uint32_t groups, uint32_t rows_pad, uint32_t nstages, uint32_t* status) {
+    extern __shared__ uint8_t smem_unaligned[];
+    uint8_t* smem = smem_unaligned + ((1024u - (smem_u32(smem_unaligned) & 1023u)) & 1023u);
+    const uint32_t dstride = rows_pad * 128u, stage_bytes = kLRaw + 2u * dstride;
+    uint8_t* ring = smem;                                                   // nstages x (raw 16 KB | two digit tiles)
+    uint8_t* hibuf = ring + (size_t)nstages * stage_bytes;                  // two buffers of a stage's high nibbles
+    float2* xsinv = reinterpret_cast<float2*>(hibuf + 2 * kLRaw);           // [groups][16] (sum of x, 2^(e-26))
+    float* exchange = reinterpret_cast<float*>(xsinv + (size_t)groups * 16);  // [16 rows][128 features]: set 1's sums on their way to set 0
+    uint64_t* full = reinterpret_cast<uint64_t*>(exchange + 16 * kLTile);
+    uint64_t* empty = full + kLMaxStages;
+    uint64_t* hfull = empty + kLMaxStages;
+    uint64_t* hempty = hfull + 2;
+    uint64_t* dfull = hempty + 2;
+    uint64_t* dempty = dfull + kLSlots;
+    uint64_t* xsfull = dempty + kLSlots;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(xsfull + 1);
+    volatile uint32_t* failed = tmem_slot + 1;
+
+    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t tiles = (n + kLTile - 1) / kLTile, chunks = (groups + 1) >> 1;
+    const uint32_t my_tiles = blockIdx.x < tiles ? (tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0u;
+
+    // As above: the kernel ahead in the stream is this call's x_digits_kernel; the weights are settled, the digit tiles
+    // are not. The first weight stages are requested before the dependency wait, the digit copies after it.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (tid == 0) {
+        for (uint32_t s = 0; s < nstages; ++s) {
+            mbar_init(full + s, 1);
+            mbar_init(empty + s, 1 + kNibbleWarps);  // the multiplications (one commit) and the warps that read the raw bytes
+        }
+        for (uint32_t h = 0; h < 2; ++h) {
+            mbar_init(hfull + h, kNibbleWarps);
+            mbar_init(hempty + h, 1);
+        }
+        for (uint32_t d = 0; d < kLSlots; ++d) {
+            mbar_init(dfull + d, 1);
+            mbar_init(dempty + d, 4);  // the four warps of the set that reads the slot out
+        }
+        mbar_init(xsfull, 1);
+        *failed = 0;
+        mbar_fence_init();
+        tma_prefetch_map(&wmap);
+    }
+    if (warp == 1) tmem_alloc(tmem_slot, kTmemCols);
+    __syncthreads();
+
+    uint32_t ps = 0, pround = 0, pt = 0, pc = 0;  // producer position (warp 0, lane 0)
+    auto stage_groups = [&](uint32_t c) { return min(2u, groups - 2u * c); };
+    auto request_weights = [&]() -> bool {  // the next stage's barrier and raw bytes; false when nothing is left or a wait gave up
+        if (pt >= my_tiles) return false;
+        if (pround && !mbar_wait(empty + ps, (pround - 1) & 1, failed, status, kStatusEmptyWaitTimedOut)) return false;
+        mbar_arrive_expect_tx(full + ps, kLRaw + stage_groups(pc) * dstride);
+        tma_load_2d(ring + (size_t)ps * stage_bytes, &wmap, (int32_t)(pc * 128u), (int32_t)((blockIdx.x + pt * gridDim.x) * kLTile), full + ps);
+        return true;
+    };
+    auto request_digits = [&]() {  // ... and its digit tiles; then on to the next stage
+        bulk_load(ring + (size_t)ps * stage_bytes + kLRaw, xdigits + (size_t)2 * pc * dstride, stage_groups(pc) * dstride, full + ps);
+        if (++pc == chunks) pc = 0, ++pt;
+        if (++ps == nstages) ps = 0, ++pround;
+    };
+    if (warp == 0 && lane == 0 && my_tiles) {
+        // raw bytes of the first stages, then (the digit kernel has finished) their digits and the pairs of every group
+        uint32_t ahead = 0;
+        {
+            uint32_t s0 = ps, r0 = pround, t0 = pt, c0 = pc;
+            while (ahead < nstages && request_weights()) {
+                ++ahead;
+                if (++pc == chunks) pc = 0, ++pt;
+                if (++ps == nstages) ps = 0, ++pround;
+            }
+            ps = s0, pround = r0, pt = t0, pc = c0;
+        }
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        mbar_arrive_expect_tx(xsfull, groups * 128u);
+        bulk_load(xsinv, xdigits + (size_t)groups * dstride, groups * 128u, xsfull);
+        for (uint32_t i = 0; i < ahead; ++i) request_digits();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0)
+            while (request_weights()) request_digits();
+    } else if (warp == 1) {
+        if (lane == 0 && my_tiles) {
+            // One thread issues everything, and a lone thread runs an instruction every few cycles at best: the loop is kept
+            // to ~100 instructions a stage (counters instead of divisions, descriptors as a 32-bit base plus a constant).
+            const uint32_t idesc = umma_idesc(2, 0, 1, kLTile, rows_pad);  // s32 accumulate, u8 weights x s8 digits
+            // descriptor = (high word: stride between 8-row groups, version, layout) | (low word: address >> 4 | leading offset)
+            constexpr uint32_t k128_hi = (1024u >> 4) | (1u << 14) | (2u << 29), plain_hi = (256u >> 4) | (1u << 14);
+            constexpr uint32_t k128_lo = 1u << 16, plain_lo = (128u >> 4) << 16;
+            auto desc = [](uint32_t hi, uint32_t lo) { return ((uint64_t)hi << 32) | lo; };
+            const uint32_t ring_lo = ((smem_u32(ring) & 0x3FFFFu) >> 4) | k128_lo, hi_lo = ((smem_u32(hibuf) & 0x3FFFFu) >> 4) | plain_lo;
+            const uint32_t stage_step = stage_bytes >> 4, dstep = dstride >> 4;
+            const uint32_t bar_empty = smem_u32(empty), bar_hempty = smem_u32(hempty), bar_dfull = smem_u32(dfull);
+            auto commit_at = [](uint32_t bar_addr) {
+                asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_addr) : "memory");
+            };
+            uint32_t s = 0, sparity = 0, stage_lo = ring_lo, it = 0, gc = 0;
+            bool ok = true;
+            for (uint32_t t = 0; t < my_tiles && ok; ++t) {
+                for (uint32_t c = 0; c < chunks && ok; ++c, ++it) {
+                    const uint32_t hb = it & 1u, ng = 2u * c + 2u <= groups ? 2u : 1u;
+                    const uint32_t slot0 = gc & (kLSlots - 1), slot1 = (gc + 1) & (kLSlots - 1);
+                    if (gc >= kLSlots) {  // the groups' accumulators have been read out
+                        ok = mbar_wait(dempty + slot0, ((gc >> 3) - 1) & 1, failed, status, kStatusMmaWaitTimedOut);
+                        if (ng == 2) ok = ok && mbar_wait(dempty + slot1, (((gc + 1) >> 3) - 1) & 1, failed, status, kStatusMmaWaitTimedOut);
+                    }
+                    ok = ok && mbar_wait(full + s, sparity, failed, status, kStatusFullWaitTimedOut) &&
+                         mbar_wait(hfull + hb, (it >> 1) & 1, failed, status, kStatusMmaWaitTimedOut);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    const uint32_t dig_lo = stage_lo + (kLRaw >> 4), hib_lo = hi_lo + hb * (kLRaw >> 4);
+                    {
+                        const uint32_t acc = tmem + slot0 * 64u;
+                        umma_i8_ss(acc, desc(k128_hi, stage_lo), desc(k128_hi, dig_lo), idesc, false);           // raw bytes x digits of U
+                        umma_i8_ss(acc, desc(k128_hi, stage_lo + 2), desc(k128_hi, dig_lo + 2), idesc, true);
+                        umma_i8_ss(acc, desc(plain_hi, hib_lo), desc(k128_hi, dig_lo + 4), idesc, true);          // high nibbles x digits of V
+                        umma_i8_ss(acc, desc(plain_hi, hib_lo + (kLTile * 32u >> 4)), desc(k128_hi, dig_lo + 6), idesc, true);
+                        commit_at(bar_dfull + 8 * slot0);
+                    }
+                    if (ng == 2) {
+                        const uint32_t acc = tmem + slot1 * 64u, x_lo = dig_lo + dstep;
+                        umma_i8_ss(acc, desc(k128_hi, stage_lo + 4), desc(k128_hi, x_lo), idesc, false);
+                        umma_i8_ss(acc, desc(k128_hi, stage_lo + 6), desc(k128_hi, x_lo + 2), idesc, true);
+                        umma_i8_ss(acc, desc(plain_hi, hib_lo + 2 * (kLTile * 32u >> 4)), desc(k128_hi, x_lo + 4), idesc, true);
+                        umma_i8_ss(acc, desc(plain_hi, hib_lo + 3 * (kLTile * 32u >> 4)), desc(k128_hi, x_lo + 6), idesc, true);
+                        commit_at(bar_dfull + 8 * slot1);
+                    }
+                    commit_at(bar_empty + 8 * s);
+                    commit_at(bar_hempty + 8 * hb);
+                    gc += ng;
+                    stage_lo += stage_step;
+                    if (++s == nstages) s = 0, sparity ^= 1u, stage_lo = ring_lo;
+                }
+            }
+        }
+    } else if (warp >= kFirstNibbleWarp && warp < kFirstDrainWarp) {
+        // per stage: the high nibbles of the thread's feature row
+        const uint32_t row = tid - kFirstNibbleWarp * 32;  // 0 .. 127
+        uint32_t it = 0;
+        bool ok = true;
+        for (uint32_t t = 0; t < my_tiles && ok; ++t) {
+            for (uint32_t c = 0; c < chunks && ok; ++c, ++it) {
+                const uint32_t s = it % nstages, hb = it & 1u;
+                if (lane == 0) ok = mbar_wait(full + s, (it / nstages) & 1, failed, status, kStatusFullWaitTimedOut);
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) break;
+                uint4 w[8];
+                const uint8_t* src = ring + (size_t)s * stage_bytes + row * 128u;
+#pragma unroll
+                for (uint32_t q = 0; q < 8; ++q) {
+                    w[q] = *reinterpret_cast<const uint4*>(src + ((q ^ (row & 7u)) << 4));
+                    w[q].x = (w[q].x >> 4) & 0x0f0f0f0fu, w[q].y = (w[q].y >> 4) & 0x0f0f0f0fu;
+                    w[q].z = (w[q].z >> 4) & 0x0f0f0f0fu, w[q].w = (w[q].w >> 4) & 0x0f0f0f0fu;
+                }
+                if (it >= 2) {  // the buffer's previous stage has been multiplied
+                    if (lane == 0) ok = mbar_wait(hempty + hb, ((it >> 1) - 1) & 1, failed, status, kStatusMmaWaitTimedOut);
+                    ok = __shfl_sync(0xffffffffu, ok, 0);
+                    if (!ok) break;
+                }
+                uint8_t* dst = hibuf + hb * kLRaw + (row >> 3) * 256u + (row & 7u) * 16u;
+#pragma unroll
+                for (uint32_t q = 0; q < 8; ++q) *reinterpret_cast<uint4*>(dst + (q >> 1) * kLTile * 32u + (q & 1u) * 128u) = w[q];
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(empty + s);
+                    mbar_arrive(hfull + hb);
+                }
+            }
+        }
+    } else if (warp >= kFirstDrainWarp) {
+        // drain: thread = one feature (a lane of tensor memory); set j takes the tile's groups j, j + 2, ...
+        const uint32_t set = (warp - kFirstDrainWarp) >> 2, quarter = warp & 3u, fl = 32 * quarter + lane;
+        bool ok = my_tiles != 0;
+        if (ok) {
+            if (lane == 0) ok = mbar_wait(xsfull, 0, failed, status, kStatusFullWaitTimedOut);
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+        }
+        for (uint32_t t = 0; t < my_tiles; ++t) {
+            const uint32_t feature = (blockIdx.x + t * gridDim.x) * kLTile + fl;
+            const bool have = feature < n;
+            const float* srow = scale + (size_t)(have ? feature : 0) * groups;
+            const float* zrow = zero + (size_t)(have ? feature : 0) * groups;
+            float acc[16];
+#pragma unroll
+            for (uint32_t r = 0; r < 16; ++r) acc[r] = 0.0f;
+            for (uint32_t g = set; g < groups && ok; g += kLSets) {
+                const uint32_t gc = t * groups + g, slot = gc & (kLSlots - 1);
+                const float sv = have ? __ldg(srow + g) : 0.0f, zv = have ? __ldg(zrow + g) : 0.0f;  // their latency runs under the wait
+                if (lane == 0) ok = mbar_wait(dfull + slot, (gc >> 3) & 1, failed, status, kStatusMmaWaitTimedOut);
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) break;
+                tc_fence_after_sync();
+                uint32_t d[4][16];
+#pragma unroll
+                for (uint32_t q = 0; q < 4; ++q)
+                    if (16 * q < rows_pad) tmem_ld16(tmem_addr(tmem, 32 * quarter, slot * 64 + 16 * q), d[q]);
+                tmem_wait_ld();
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(dempty + slot);  // the sums are in registers: the slot may be multiplied into again
+                const float zm = __fmaf_rn(-8.0f, sv, zv);
+                const float2* xs = xsinv + (size_t)g * 16;
+#pragma unroll
+                for (uint32_t q = 0; q < 4; ++q) {
+                    if (4 * q >= m) continue;  // uniform
+#pragma unroll
+                    for (uint32_t i = 0; i < 4; ++i) {
+                        // digits 0 .. 3 of row 4 q + i sit in columns 2 i, 2 i + 8, 2 i + 1, 2 i + 9 of the block (digit_row);
+                        // |digit sum| < 2^22: D + 256 D' is exact in int32, the two halves meet in one rounded fma
+                        const int lo = (int)d[q][2 * i] + 256 * (int)d[q][2 * i + 8], hi = (int)d[q][2 * i + 1] + 256 * (int)d[q][2 * i + 9];
+                        const float tsum = __fmaf_rn(__int2float_rn(hi), 65536.0f, __int2float_rn(lo));
+                        const float2 p = xs[4 * q + i];  // (sum of x, 2^(e-26)) of the group and row: 0 for rows the call does not have
+                        acc[4 * q + i] = __fmaf_rn(zm, p.x, __fmaf_rn(sv, __fmul_rn(tsum, p.y), acc[4 * q + i]));
+                    }
+                }
+            }
+            // set 1 hands its sums to set 0, which adds them (set 0 + set 1, a fixed order) and writes y
+            if (set == 1) {
+#pragma unroll
+                for (uint32_t r = 0; r < 16; ++r) exchange[r * kLTile + fl] = acc[r];
+            }
+            named_barrier_sync(1, 8 * 32);
+            if (set == 0 && ok && have) {
+                const float bs = bias ? bias[feature] : 0.0f;
+#pragma unroll
+                for (uint32_t r = 0; r < 16; ++r) {
+                    if (r >= m) continue;
+                    const float v = __fadd_rn(acc[r], exchange[r * kLTile + fl]);
+                    y[(size_t)r * n + feature] = bias ? __fadd_rn(v, bs) : v;
+                }
+            }
+            named_barrier_sync(2, 8 * 32);  // the exchange buffer is free for the next tile
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem, kTmemCols);
+}
+
+size_t lanes_smem_bytes(uint32_t groups, uint32_t rows_pad, uint32_t nstages) {
+    return 1024 + (size_t)nstages * (kLRaw + 2u * rows_pad * 128u) + 2 * kLRaw + (size_t)groups * 128 + 16 * kLTile * 4 +
+           (2 * kLMaxStages + 4 + 2 * kLSlots + 1) * 8 + 64;
+}
+
 // nanoseconds of one instruction at N columns (M = 64, K = 32 bytes)
 double mma_ns(uint32_t ncols) {
     if (ncols <= 64) return 83.0;
@@ -671,6 +945,32 @@ bool launch_gemv_q4_umma(cudaStream_t s, int sm_count, uint32_t* status, const f
             launch_after(slice_sum_kernel<1>, dim3((uint32_t)((m * n + 255) / 256)), dim3(256), 0, s, (const float*)partials, p.slices, (uint32_t)(m * n),
                          (uint32_t)n, bias, y);
     }
+    return true;
+}
+
+// The features-on-the-lanes kernel: group_size 128, in_features a multiple of 128 up to 16384, 1 to 16 rows of x, 16-byte
+// aligned x and weights. `scratch` holds gemv_q4_umma_scratch_bytes bytes (it uses the digit region only). Two launches:
+// x -> digit tiles (tiny), the linear.
+bool launch_gemv_q4_lanes(cudaStream_t s, int sm_count, uint32_t* status, const float* x, uint64_t m, uint64_t k, const uint32_t* q,
+                          const float* scale, const float* zero, const float* bias, uint64_t n, uint64_t group, float* y, void* scratch) {
+    if (m < 1 || m > 16 || group != 128 || k == 0 || k % 128 || k / 128 > kLMaxGroups || n == 0 || m * n > 0x7fffffffull) return false;
+    if (((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(x)) & 15) != 0) return false;
+    const uint64_t groups = k / 128, row_bytes = k / 2;
+    const Plan p = make_plan(m, n, groups, sm_count);  // (for rows_pad: the scratch layout is the other kernel's)
+    if (p.grid == 0) return false;
+    const uint32_t rows_pad = p.rows_pad;
+    uint32_t nstages = kLMaxStages;
+    while (nstages > 2 && lanes_smem_bytes((uint32_t)groups, rows_pad, nstages) > kSmemBudget) --nstages;
+    if (lanes_smem_bytes((uint32_t)groups, rows_pad, nstages) > kSmemBudget) return false;
+    uint8_t* xdigits = reinterpret_cast<uint8_t*>(scratch);
+    const CUtensorMap wmap = make_tensor_map_2d(q, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, row_bytes, n, row_bytes, 128, kLTile, Swizzle::B128);
+    const size_t smem = lanes_smem_bytes((uint32_t)groups, rows_pad, nstages);
+    const uint64_t tiles = (n + kLTile - 1) / kLTile;
+    launch_after(x_digits_kernel, dim3((uint32_t)((groups * (rows_pad / 4) + 7) / 8)), dim3(128), 0, s, x, (uint32_t)m, (uint32_t)k, (uint32_t)groups, rows_pad,
+                 xdigits);
+    GQ_CUDA(cudaFuncSetAttribute(gemv_q4_lanes_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    launch_after(gemv_q4_lanes_kernel, dim3((uint32_t)(tiles < (uint64_t)sm_count ? tiles : (uint64_t)sm_count)), dim3(kLThreads), smem, s, wmap,
+                 (const uint8_t*)xdigits, scale, zero, bias, y, (uint32_t)m, (uint32_t)n, (uint32_t)groups, rows_pad, nstages, status);
     return true;
 }
 

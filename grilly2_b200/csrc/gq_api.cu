@@ -696,7 +696,7 @@ int32_t gq_int4_linear(gq_ctx* ctx, gq_buf x, uint64_t x_off, uint64_t m, uint64
         Locked l(ctx);
         check_dims("gq_int4_linear", m, k, n);
         check_group(group);
-        if (kernel < GQ_KERNEL_AUTO || kernel > GQ_KERNEL_RING) fail("gq_int4_linear: unknown kernel selector %d", kernel);
+        if (kernel < GQ_KERNEL_AUTO || (kernel > GQ_KERNEL_RING && kernel != GQ_KERNEL_UMMA_LANES)) fail("gq_int4_linear: unknown kernel selector %d", kernel);
         uint64_t groups = (k + group - 1) / group;
         auto xp = (const float*)view(ctx, x, x_off, m * k, 4, "gq_int4_linear input");
         auto qp = (const uint32_t*)view(ctx, q, 0, n * words4(k), 4, "gq_int4_linear q");
@@ -715,6 +715,17 @@ int32_t gq_int4_linear(gq_ctx* ctx, gq_buf x, uint64_t x_off, uint64_t m, uint64
                 ctx->stats.launches += 2;  // the digit conversion ahead of it and the sum over the K slices behind it
                 return;
             }
+        }
+        if (kernel == GQ_KERNEL_UMMA_LANES) {
+            const uint64_t need = gemv_q4_umma_scratch_bytes(m, k, n, ctx->prop.multiProcessorCount);
+            if (!need || !launch_gemv_q4_lanes(ctx->stream, ctx->prop.multiProcessorCount, ctx->status_dev, xp, m, k, qp, sp, zp, bp, n, group, yp,
+                                               context_scratch(ctx, need)))
+                fail("gq_int4_linear: the features-on-the-lanes tcgen05 kernel takes group_size 128, in_features a multiple of 128 up to 16384, 1 to 16 "
+                     "rows of x and 16-byte aligned x (m = %llu, k = %llu, group_size = %llu, x_off = %llu)",
+                     (unsigned long long)m, (unsigned long long)k, (unsigned long long)group, (unsigned long long)x_off);
+            after_launch(ctx, "gemv_q4_lanes", {x, q, scale, zero, bias, y}, {y});
+            ctx->stats.launches += 1;  // the digit conversion ahead of it
+            return;
         }
         if (kernel == GQ_KERNEL_UMMA) {
             const uint64_t need = gemv_q4_umma_scratch_bytes(m, k, n, ctx->prop.multiProcessorCount);

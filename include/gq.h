@@ -87,6 +87,11 @@ typedef uint64_t gq_buf; /* 0 is never a valid handle */
                                  weight. What AUTO picks from three rows of x on (inside a capture in which the context's
                                  scratch would have to grow it falls back to dp4a, from 64 rows to GQ_KERNEL_TENSOR) */
 
+#define GQ_KERNEL_UMMA_LANES 8 /* int4 only (group_size 128, in_features a multiple of 128 up to 16384, 1 to 16 rows of x): the
+                                  tcgen05 decode kernel with the operands exchanged, the output features on the lanes of
+                                  tensor memory, so that a read-out thread owns one feature and its scale; tiles of 128
+                                  features over all of K, no partial sums */
+
 typedef struct gq_caps { /* replaces gc_caps, gc_shim.h:43-50 */
     char device_name[256];
     uint32_t cc_major, cc_minor;
