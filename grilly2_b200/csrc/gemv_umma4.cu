@@ -598,17 +598,18 @@ __global__ void __launch_bounds__(256) slice_sum_kernel(const float* __restrict_
 // tiles of x stream through the ring beside the weight (two groups = one stage), nothing is split, no partial sums,
 // no second kernel.
 constexpr int kLThreads = 448;            // warp 0 producer, 1 MMA issuer, 2-5 nibbles, 6-13 drain (two sets of four)
+constexpr uint32_t kLFirstDrainWarp = 6;
 constexpr uint32_t kLTile = 128;          // features per tile = M of the instruction
 constexpr uint32_t kLRaw = kLTile * 128;  // a stage's packed weight: 128 features x two groups
 constexpr uint32_t kLSlots = 8;           // accumulators in flight, 64 columns each
 constexpr uint32_t kLSets = 2;            // drain sets: set j reads out the tile's groups j, j + 2, ...
-constexpr int kLMaxStages = 6;
+constexpr int kLMaxStages = 8;
 constexpr uint32_t kLMaxGroups = 128;     // the (sum of x, 2^(e-26)) pairs of every group stay in shared memory: 128 bytes a group
 
 __global__ void __launch_bounds__(kLThreads, 1)
     gemv_q4_lanes_kernel(const __grid_constant__ CUtensorMap wmap, const uint8_t* __restrict__ xdigits, const float* __restrict__ scale,
                          const float* __restrict__ zero, const float* __restrict__ bias, float* __restrict__ y, uint32_t m, uint32_t n,
-                         uint32_t groups, uint32_t rows_pad, uint32_t nstages, uint32_t* status) {
+                         uint32_t groups, uint32_t rows_pad, uint32_t nstages, uint32_t tile_rows, uint32_t* status) {
     extern __shared__ uint8_t smem_unaligned[];
     uint8_t* smem = smem_unaligned + ((1024u - (smem_u32(smem_unaligned) & 1023u)) & 1023u);
     const uint32_t dstride = rows_pad * 128u, stage_bytes = kLRaw + 2u * dstride;
@@ -627,7 +628,9 @@ __global__ void __launch_bounds__(kLThreads, 1)
     volatile uint32_t* failed = tmem_slot + 1;
 
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const uint32_t tiles = (n + kLTile - 1) / kLTile, chunks = (groups + 1) >> 1;
+    // A tile is tile_rows <= 128 features (the host sizes it so that the tiles fill whole waves of CTAs); the instruction
+    // still multiplies 128 rows, the rest being whatever the stage held before: those lanes are never read out.
+    const uint32_t tiles = (n + tile_rows - 1) / tile_rows, chunks = (groups + 1) >> 1;
     const uint32_t my_tiles = blockIdx.x < tiles ? (tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0u;
 
     // As above: the kernel ahead in the stream is this call's x_digits_kernel; the weights are settled, the digit tiles
@@ -659,8 +662,8 @@ __global__ void __launch_bounds__(kLThreads, 1)
     auto request_weights = [&]() -> bool {  // the next stage's barrier and raw bytes; false when nothing is left or a wait gave up
         if (pt >= my_tiles) return false;
         if (pround && !mbar_wait(empty + ps, (pround - 1) & 1, failed, status, kStatusEmptyWaitTimedOut)) return false;
-        mbar_arrive_expect_tx(full + ps, kLRaw + stage_groups(pc) * dstride);
-        tma_load_2d(ring + (size_t)ps * stage_bytes, &wmap, (int32_t)(pc * 128u), (int32_t)((blockIdx.x + pt * gridDim.x) * kLTile), full + ps);
+        mbar_arrive_expect_tx(full + ps, tile_rows * 128u + stage_groups(pc) * dstride);
+        tma_load_2d(ring + (size_t)ps * stage_bytes, &wmap, (int32_t)(pc * 128u), (int32_t)((blockIdx.x + pt * gridDim.x) * tile_rows), full + ps);
         return true;
     };
     auto request_digits = [&]() {  // ... and its digit tiles; then on to the next stage
@@ -747,52 +750,61 @@ __global__ void __launch_bounds__(kLThreads, 1)
                 }
             }
         }
-    } else if (warp >= kFirstNibbleWarp && warp < kFirstDrainWarp) {
-        // per stage: the high nibbles of the thread's feature row
+    } else if (warp >= kFirstNibbleWarp && warp < kLFirstDrainWarp) {
+        // per stage: the high nibbles of the thread's feature row (a second set of four warps taking every other stage changed
+        // nothing: the stages do not wait for these warps). Every lane waits on the barriers itself (no broadcast
+        // of the outcome), positions are counters: the loop around the sixteen loads and stores is what a stage costs here.
         const uint32_t row = tid - kFirstNibbleWarp * 32;  // 0 .. 127
-        uint32_t it = 0;
+        const uint8_t* src_row = ring + row * 128u;
+        uint8_t* dst_row = hibuf + (row >> 3) * 256u + (row & 7u) * 16u;
+        const uint32_t sw = row & 7u;
+        uint32_t s = 0, sparity = 0;
         bool ok = true;
-        for (uint32_t t = 0; t < my_tiles && ok; ++t) {
-            for (uint32_t c = 0; c < chunks && ok; ++c, ++it) {
-                const uint32_t s = it % nstages, hb = it & 1u;
-                if (lane == 0) ok = mbar_wait(full + s, (it / nstages) & 1, failed, status, kStatusFullWaitTimedOut);
-                ok = __shfl_sync(0xffffffffu, ok, 0);
+        {
+            for (uint32_t it = 0, total = my_tiles * chunks; it < total && ok; ++it) {
+                const uint32_t hb = it & 1u;
+                ok = mbar_wait(full + s, sparity, failed, status, kStatusFullWaitTimedOut);
                 if (!ok) break;
                 uint4 w[8];
-                const uint8_t* src = ring + (size_t)s * stage_bytes + row * 128u;
+                const uint8_t* src = src_row + (size_t)s * stage_bytes;
+                if (row < tile_rows) {
+#pragma unroll
+                    for (uint32_t q = 0; q < 8; ++q) w[q] = *reinterpret_cast<const uint4*>(src + ((q ^ sw) << 4));
+                }
 #pragma unroll
                 for (uint32_t q = 0; q < 8; ++q) {
-                    w[q] = *reinterpret_cast<const uint4*>(src + ((q ^ (row & 7u)) << 4));
                     w[q].x = (w[q].x >> 4) & 0x0f0f0f0fu, w[q].y = (w[q].y >> 4) & 0x0f0f0f0fu;
                     w[q].z = (w[q].z >> 4) & 0x0f0f0f0fu, w[q].w = (w[q].w >> 4) & 0x0f0f0f0fu;
                 }
                 if (it >= 2) {  // the buffer's previous stage has been multiplied
-                    if (lane == 0) ok = mbar_wait(hempty + hb, ((it >> 1) - 1) & 1, failed, status, kStatusMmaWaitTimedOut);
-                    ok = __shfl_sync(0xffffffffu, ok, 0);
+                    ok = mbar_wait(hempty + hb, ((it >> 1) - 1) & 1, failed, status, kStatusMmaWaitTimedOut);
                     if (!ok) break;
                 }
-                uint8_t* dst = hibuf + hb * kLRaw + (row >> 3) * 256u + (row & 7u) * 16u;
+                uint8_t* dst = dst_row + hb * kLRaw;
+                if (row < tile_rows) {
 #pragma unroll
-                for (uint32_t q = 0; q < 8; ++q) *reinterpret_cast<uint4*>(dst + (q >> 1) * kLTile * 32u + (q & 1u) * 128u) = w[q];
+                    for (uint32_t q = 0; q < 8; ++q) *reinterpret_cast<uint4*>(dst + (q >> 1) * kLTile * 32u + (q & 1u) * 128u) = w[q];
+                }
                 fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0) {
                     mbar_arrive(empty + s);
                     mbar_arrive(hfull + hb);
                 }
+                if (++s == nstages) s = 0, sparity ^= 1u;
             }
         }
-    } else if (warp >= kFirstDrainWarp) {
+    } else if (warp >= kLFirstDrainWarp) {
         // drain: thread = one feature (a lane of tensor memory); set j takes the tile's groups j, j + 2, ...
-        const uint32_t set = (warp - kFirstDrainWarp) >> 2, quarter = warp & 3u, fl = 32 * quarter + lane;
+        const uint32_t set = (warp - kLFirstDrainWarp) >> 2, quarter = warp & 3u, fl = 32 * quarter + lane;
         bool ok = my_tiles != 0;
         if (ok) {
             if (lane == 0) ok = mbar_wait(xsfull, 0, failed, status, kStatusFullWaitTimedOut);
             ok = __shfl_sync(0xffffffffu, ok, 0);
         }
         for (uint32_t t = 0; t < my_tiles; ++t) {
-            const uint32_t feature = (blockIdx.x + t * gridDim.x) * kLTile + fl;
-            const bool have = feature < n;
+            const uint32_t feature = (blockIdx.x + t * gridDim.x) * tile_rows + fl;
+            const bool have = fl < tile_rows && feature < n;
             const float* srow = scale + (size_t)(have ? feature : 0) * groups;
             const float* zrow = zero + (size_t)(have ? feature : 0) * groups;
             float acc[16];
@@ -801,10 +813,11 @@ __global__ void __launch_bounds__(kLThreads, 1)
             for (uint32_t g = set; g < groups && ok; g += kLSets) {
                 const uint32_t gc = t * groups + g, slot = gc & (kLSlots - 1);
                 const float sv = have ? __ldg(srow + g) : 0.0f, zv = have ? __ldg(zrow + g) : 0.0f;  // their latency runs under the wait
-                if (lane == 0) ok = mbar_wait(dfull + slot, (gc >> 3) & 1, failed, status, kStatusMmaWaitTimedOut);
-                ok = __shfl_sync(0xffffffffu, ok, 0);
+                ok = mbar_wait(dfull + slot, (gc >> 3) & 1, failed, status, kStatusMmaWaitTimedOut);
                 if (!ok) break;
                 tc_fence_after_sync();
+                const float zm = __fmaf_rn(-8.0f, sv, zv);
+                const float2* xs = xsinv + (size_t)g * 16;
                 uint32_t d[4][16];
 #pragma unroll
                 for (uint32_t q = 0; q < 4; ++q)
@@ -813,8 +826,6 @@ __global__ void __launch_bounds__(kLThreads, 1)
                 tc_fence_before_sync();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(dempty + slot);  // the sums are in registers: the slot may be multiplied into again
-                const float zm = __fmaf_rn(-8.0f, sv, zv);
-                const float2* xs = xsinv + (size_t)g * 16;
 #pragma unroll
                 for (uint32_t q = 0; q < 4; ++q) {
                     if (4 * q >= m) continue;  // uniform
@@ -963,14 +974,20 @@ bool launch_gemv_q4_lanes(cudaStream_t s, int sm_count, uint32_t* status, const 
     while (nstages > 2 && lanes_smem_bytes((uint32_t)groups, rows_pad, nstages) > kSmemBudget) --nstages;
     if (lanes_smem_bytes((uint32_t)groups, rows_pad, nstages) > kSmemBudget) return false;
     uint8_t* xdigits = reinterpret_cast<uint8_t*>(scratch);
-    const CUtensorMap wmap = make_tensor_map_2d(q, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, row_bytes, n, row_bytes, 128, kLTile, Swizzle::B128);
+    // With more than one wave of CTAs the tiles are made equal (28672 features on 148 SMs: 296 tiles of 97, two per CTA,
+    // instead of 224 of 128, two for some and one for others). A stage costs about the same whatever its width, so a
+    // single wave keeps 128-feature tiles (more, narrower tiles measured slower: 14336 features 16.0 -> 17.0 us).
+    const uint64_t waves = ((n + kLTile - 1) / kLTile + sm_count - 1) / sm_count;
+    uint64_t tile_rows = waves > 1 ? (n + waves * sm_count - 1) / (waves * sm_count) : kLTile;
+    tile_rows = tile_rows < 8 ? 8 : tile_rows > kLTile ? kLTile : tile_rows;
+    const CUtensorMap wmap = make_tensor_map_2d(q, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, row_bytes, n, row_bytes, 128, (uint32_t)tile_rows, Swizzle::B128);
     const size_t smem = lanes_smem_bytes((uint32_t)groups, rows_pad, nstages);
-    const uint64_t tiles = (n + kLTile - 1) / kLTile;
+    const uint64_t tiles = (n + tile_rows - 1) / tile_rows;
     launch_after(x_digits_kernel, dim3((uint32_t)((groups * (rows_pad / 4) + 7) / 8)), dim3(128), 0, s, x, (uint32_t)m, (uint32_t)k, (uint32_t)groups, rows_pad,
                  xdigits);
     GQ_CUDA(cudaFuncSetAttribute(gemv_q4_lanes_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     launch_after(gemv_q4_lanes_kernel, dim3((uint32_t)(tiles < (uint64_t)sm_count ? tiles : (uint64_t)sm_count)), dim3(kLThreads), smem, s, wmap,
-                 (const uint8_t*)xdigits, scale, zero, bias, y, (uint32_t)m, (uint32_t)n, (uint32_t)groups, rows_pad, nstages, status);
+                 (const uint8_t*)xdigits, scale, zero, bias, y, (uint32_t)m, (uint32_t)n, (uint32_t)groups, rows_pad, nstages, (uint32_t)tile_rows, status);
     return true;
 }
 

@@ -671,24 +671,31 @@ int32_t gq_int4_dequantize(gq_ctx* ctx, gq_buf q, gq_buf scale, gq_buf zero, uin
     });
 }
 
-// Whether GQ_KERNEL_AUTO sends an int4 group-128 linear of m rows to the tcgen05 decode kernel. That kernel reads the weight
-// once whatever m is, at about 2.2 bytes per ns after ~9 us of launches and start-up; the warp-level ring kernel (K = 4096
-// or 8192) takes a pass at ~4.5 bytes per ns (one row) per four rows of x, a pass with three or four rows running ~1.7 times
-// as long as a one-row pass (its IMMA issue rate); the dp4a kernel elsewhere grows with every row. Measured on B200
-// (14336 x 4096, 28672 x 8192, 3584 x 8192); weights under 4 MB stay with the single-launch kernels.
-static bool int4_prefers_umma(uint64_t m, uint64_t n, uint64_t k, uint64_t group) {
-    if (m < 3 || m > 16 || group != 128 || k % 128) return false;
+// Which kernel GQ_KERNEL_AUTO gives an int4 group-128 linear of m rows: 0 = the single-launch kernels (ring passes, dp4a),
+// 1 = the tcgen05 decode kernel with K cut in slices (gemv_q4_umma), 2 = the one with the features on the lanes
+// (gemv_q4_lanes). Both tcgen05 kernels read the weight once whatever m is. The sliced one runs at about 2.2 bytes per ns
+// after ~9 us of launches and start-up. The lanes one takes ~0.78 us per stage of two groups, whatever the stage's width,
+// and a CTA owns whole tiles of up to 128 features: waves x groups / 2 stages after ~4.5 us, so it wins where the features
+// fill the SMs (14336 x 4096: 16-18 us against 24-25; 28672 x 8192: 52-57 against 61-70) and loses on a narrow shard with
+// a long K (3584 x 8192: 27 against 17). The warp-level ring kernel (K = 4096 or 8192) takes a pass at ~4.5 bytes per ns
+// (one row) per four rows of x, a pass with three or four rows running ~1.7 times as long as a one-row pass (its IMMA issue
+// rate); the dp4a kernel elsewhere grows with every row. Measured on B200; weights under 4 MB stay with the single-launch
+// kernels.
+static int int4_tensor_route(uint64_t m, uint64_t n, uint64_t k, uint64_t group, int sm_count) {
+    if (m < 3 || m > 16 || group != 128 || k % 128) return 0;
     const double mb = (double)n * (double)k / 2e6;
-    if (mb < 4.0) return false;
+    if (mb < 4.0) return 0;
     const double umma_us = 9.0 + mb / 2.2;
+    const uint64_t groups = k / 128, waves = ((n + 127) / 128 + sm_count - 1) / sm_count;
+    const double lanes_us = groups <= 128 ? 4.5 + 0.78 * (double)(waves * ((groups + 1) / 2)) : 1e30;
     double other_us = mb * (0.26 * (double)m + 0.27);
     if (k == 4096 || k == 8192) {
         other_us = 0.0;
         for (uint64_t r = 0; r < m; r += 4) other_us += (2.5 + mb / 4.5) * (m - r >= 3 ? 1.7 : m - r == 2 ? 1.1 : 1.0);
     }
-    return umma_us < other_us;
+    if (lanes_us <= umma_us) return lanes_us < other_us ? 2 : 0;
+    return umma_us < other_us ? 1 : 0;
 }
-
 int32_t gq_int4_linear(gq_ctx* ctx, gq_buf x, uint64_t x_off, uint64_t m, uint64_t k, gq_buf q, gq_buf scale,
                        gq_buf zero, gq_buf bias, uint64_t b_off, uint64_t n, uint64_t group, gq_buf y,
                        int32_t kernel) {
@@ -706,7 +713,17 @@ int32_t gq_int4_linear(gq_ctx* ctx, gq_buf x, uint64_t x_off, uint64_t m, uint64
         auto yp = (float*)view(ctx, y, 0, m * n, 4, "gq_int4_linear output");
         if (ranges_overlap(yp, m * n * 4, xp, m * k * 4)) fail("gq_int4_linear: the output must not overlap the input (CTAs read x while others write y)");
         if (m == 0 || n == 0) return;
-        if (kernel == GQ_KERNEL_AUTO && int4_prefers_umma(m, n, k, group)) {
+        const int route = kernel == GQ_KERNEL_AUTO ? int4_tensor_route(m, n, k, group, ctx->prop.multiProcessorCount) : 0;
+        if (route == 2) {
+            const uint64_t need = gemv_q4_umma_scratch_bytes(m, k, n, ctx->prop.multiProcessorCount);
+            if (need && !(ctx->capturing && ctx->scratch_bytes < need) &&
+                launch_gemv_q4_lanes(ctx->stream, ctx->prop.multiProcessorCount, ctx->status_dev, xp, m, k, qp, sp, zp, bp, n, group, yp, context_scratch(ctx, need))) {
+                after_launch(ctx, "gemv_q4_lanes", {x, q, scale, zero, bias, y}, {y});
+                ctx->stats.launches += 1;  // the digit conversion ahead of it
+                return;
+            }
+        }
+        if (route != 0) {
             const uint64_t need = gemv_q4_umma_scratch_bytes(m, k, n, ctx->prop.multiProcessorCount);
             // (a scratch that would have to grow inside a capture leaves the choice to the kernels that need none)
             if (need && !(ctx->capturing && ctx->scratch_bytes < need) &&
@@ -1051,14 +1068,17 @@ int32_t gq_int4_linear_gather(gq_ctx* ctx, gq_buf x, uint64_t x_off, uint64_t m,
         if (y_full == x) fail("gq_int4_linear_gather: y_full must not be the input buffer");
         // Many rows on a large shard: the tcgen05 decode kernel (one pass over the weight), and the gather adds up its K
         // slices' partial sums as it sends them.
-        if (int4_prefers_umma(m, n_shard, k, group)) {
+        const int route = int4_tensor_route(m, n_shard, k, group, ctx->prop.multiProcessorCount);
+        if (route != 0) {
             const int sms = ctx->prop.multiProcessorCount;
             const uint64_t need = gemv_q4_umma_scratch_bytes(m, k, n_shard, sms);
             if (need && !(ctx->capturing && ctx->scratch_bytes < need)) {
                 void* scratch = context_scratch(ctx, need);
                 const float* part = gemv_q4_umma_partials(scratch, m, k, n_shard, sms);  // the slices' sums, or (K not split) the shard's y
                 uint32_t slices = 0;
-                if (launch_gemv_q4_umma(ctx->stream, sms, ctx->status_dev, xp, m, k, qp, sp, zp, bp, n_shard, group, const_cast<float*>(part), scratch, &slices)) {
+                // (the kernel with the features on the lanes writes the shard's y, bias included, where the other leaves its sums)
+                if ((route == 2 && launch_gemv_q4_lanes(ctx->stream, sms, ctx->status_dev, xp, m, k, qp, sp, zp, bp, n_shard, group, const_cast<float*>(part), scratch)) ||
+                    launch_gemv_q4_umma(ctx->stream, sms, ctx->status_dev, xp, m, k, qp, sp, zp, bp, n_shard, group, const_cast<float*>(part), scratch, &slices)) {
                     peer.row0 = 0;
                     launch_peer_gather(ctx->stream, sms, peer, part, m, n_shard, ctx->status_dev, slices, slices ? bp : nullptr);
                     after_launch(ctx, "gemv_q4_umma_gather", {x, q, scale, zero, bias, peer_recv[rank], state, y_full}, {peer_recv[rank], state, y_full});

@@ -87,6 +87,7 @@ def test_int4_linear(g, m, n, k, group, with_bias):
     kernels = [_lib.KERNEL_DP4A, _lib.KERNEL_AUTO] + ([_lib.KERNEL_IMMA] if m <= 2 and group % 128 == 0 else [])
     kernels += [_lib.KERNEL_RING] if group == 128 and m <= 16 and k in (4096, 8192) else []
     kernels += [_lib.KERNEL_UMMA] if group == 128 and m <= 16 and k % 128 == 0 else []  # tcgen05: one pass for up to 16 rows
+    kernels += [_lib.KERNEL_UMMA_LANES] if group == 128 and m <= 16 and k % 128 == 0 and k <= 16384 else []  # the same with the features on the lanes
     for kernel in kernels:
         y = t._q.linear(xt, bt, kernel).numpy()
         assert rel(y, ref) <= TOL
@@ -221,8 +222,10 @@ def test_dp4a_digit_planes_on_hard_inputs(g):
             assert rel(w8.linear(xt, None, kernel).numpy(), oracle.linear_q8_f64(xr, q, scale, None, k)[0]) <= TOL
             assert rel(w4.linear(xt, None, kernel).numpy(), oracle.linear_q4_f64(xr, q4, s4, z4, None, k, 128)[0]) <= TOL
         assert rel(w4.linear(xt, None, _lib.KERNEL_RING).numpy(), oracle.linear_q4_f64(xr, q4, s4, z4, None, k, 128)[0]) <= TOL
-        assert rel(w4.linear(xt, None, _lib.KERNEL_UMMA).numpy(), oracle.linear_q4_f64(xr, q4, s4, z4, None, k, 128)[0]) <= TOL
-    assert rel(w4.linear(_C.Tensor.from_numpy(x), None, _lib.KERNEL_UMMA).numpy(), oracle.linear_q4_f64(x, q4, s4, z4, None, k, 128)[0]) <= TOL
+        for kernel in (_lib.KERNEL_UMMA, _lib.KERNEL_UMMA_LANES):
+            assert rel(w4.linear(xt, None, kernel).numpy(), oracle.linear_q4_f64(xr, q4, s4, z4, None, k, 128)[0]) <= TOL
+    for kernel in (_lib.KERNEL_UMMA, _lib.KERNEL_UMMA_LANES):
+        assert rel(w4.linear(_C.Tensor.from_numpy(x), None, kernel).numpy(), oracle.linear_q4_f64(x, q4, s4, z4, None, k, 128)[0]) <= TOL
     xbad = x[:1].copy()
     xbad[0, 5] = np.inf
     for kernel in (_lib.KERNEL_DP4A, _lib.KERNEL_IMMA):
@@ -234,6 +237,7 @@ def test_dp4a_digit_planes_on_hard_inputs(g):
         xbad[0, 5] = bad
         assert np.isnan(w4.linear(_C.Tensor.from_numpy(xbad), None, _lib.KERNEL_RING).numpy()).all()
         assert np.isnan(w4.linear(_C.Tensor.from_numpy(xbad), None, _lib.KERNEL_UMMA).numpy()).all()
+        assert np.isnan(w4.linear(_C.Tensor.from_numpy(xbad), None, _lib.KERNEL_UMMA_LANES).numpy()).all()
 
 
 def test_outputs_that_overlap_inputs_are_refused(g):
