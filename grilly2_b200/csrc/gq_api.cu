@@ -733,6 +733,25 @@ int32_t gq_int4_linear(gq_ctx* ctx, gq_buf x, uint64_t x_off, uint64_t m, uint64
                 return;
             }
         }
+        // More than sixteen rows (a prompt through an int4 layer): passes of sixteen through the same kernel, each reading the
+        // weight once (the reference's tiled path does not exist for int4 either; dp4a would read it once per row).
+        if (kernel == GQ_KERNEL_AUTO && m > 16 && group == 128 && k % 128 == 0 && n * k >= (8ull << 20)) {
+            const uint64_t need = gemv_q4_umma_scratch_bytes(16, k, n, ctx->prop.multiProcessorCount);
+            if (need && !(ctx->capturing && ctx->scratch_bytes < need)) {
+                void* scratch = context_scratch(ctx, need);
+                bool all = true;
+                uint64_t passes = 0;
+                for (uint64_t r = 0; r < m && all; r += 16, ++passes)
+                    all = launch_gemv_q4_lanes(ctx->stream, ctx->prop.multiProcessorCount, ctx->status_dev, xp + r * k, m - r < 16 ? m - r : 16, k, qp, sp, zp, bp, n, group,
+                                               yp + r * n, scratch);
+                if (all) {
+                    after_launch(ctx, "gemv_q4_lanes", {x, q, scale, zero, bias, y}, {y});
+                    ctx->stats.launches += 2 * passes - 1;
+                    return;
+                }
+                if (passes > 1) fail("gq_int4_linear: a pass of the tcgen05 kernel was refused after an earlier one had been launched");
+            }
+        }
         if (kernel == GQ_KERNEL_UMMA_LANES) {
             const uint64_t need = gemv_q4_umma_scratch_bytes(m, k, n, ctx->prop.multiProcessorCount);
             if (!need || !launch_gemv_q4_lanes(ctx->stream, ctx->prop.multiProcessorCount, ctx->status_dev, xp, m, k, qp, sp, zp, bp, n, group, yp,

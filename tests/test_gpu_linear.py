@@ -94,6 +94,24 @@ def test_int4_linear(g, m, n, k, group, with_bias):
         assert (np.abs(y - want) <= bound).all()
 
 
+def test_int4_many_rows_go_in_passes_of_sixteen(g):
+    """More than 16 rows of x through a large int4 group-128 layer: AUTO runs the tcgen05 kernel in passes of 16 rows,
+    so the result equals that kernel's on each block of rows bit for bit, and the oracle within the decode tolerance."""
+    from grilly2_b200 import _C, _lib
+    m, n, k = 40, 2100, 4096
+    rng = np.random.default_rng(40)
+    w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    b = rng.standard_normal(n).astype(np.float32)
+    w4 = _C.Int4Weight.quantize(_C.Tensor.from_numpy(w), 128)
+    q4, s4, z4 = oracle.quantize_q4(w, 128)
+    y = w4.linear(_C.Tensor.from_numpy(x), _C.Tensor.from_numpy(b)).numpy()
+    assert rel(y, oracle.linear_q4_f64(x, q4, s4, z4, b, k, 128)[0]) <= TOL
+    for r in range(0, m, 16):
+        part = w4.linear(_C.Tensor.from_numpy(x[r:r + 16]), _C.Tensor.from_numpy(b), _lib.KERNEL_UMMA_LANES).numpy()
+        np.testing.assert_array_equal(y[r:r + 16], part)
+
+
 @pytest.mark.parametrize("x_off", [1, 2, 4])
 def test_x_and_bias_at_element_offsets(g, x_off):
     """x may start at any element (crates/grilly-core/src/kernel.rs:26-36);
