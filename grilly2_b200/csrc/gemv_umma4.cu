@@ -608,8 +608,9 @@ constexpr uint32_t kLMaxGroups = 128;     // the (sum of x, 2^(e-26)) pairs of e
 
 __global__ void __launch_bounds__(kLThreads, 1)
     gemv_q4_lanes_kernel(const __grid_constant__ CUtensorMap wmap, const uint8_t* __restrict__ xdigits, const float* __restrict__ scale,
-                         const float* __restrict__ zero, const float* __restrict__ bias, float* __restrict__ y, uint32_t m, uint32_t n,
-                         uint32_t groups, uint32_t rows_pad, uint32_t nstages, uint32_t tile_rows, uint32_t* status) {
+                         const float* __restrict__ zero, const float* __restrict__ bias, float* __restrict__ y, float* __restrict__ partials, uint32_t m,
+                         uint32_t n, uint32_t groups, uint32_t rows_pad, uint32_t nstages, uint32_t tile_rows, uint32_t kslices, uint32_t gps,
+                         uint32_t* status) {
     extern __shared__ uint8_t smem_unaligned[];
     uint8_t* smem = smem_unaligned + ((1024u - (smem_u32(smem_unaligned) & 1023u)) & 1023u);
     const uint32_t dstride = rows_pad * 128u, stage_bytes = kLRaw + 2u * dstride;
@@ -630,8 +631,13 @@ __global__ void __launch_bounds__(kLThreads, 1)
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     // A tile is tile_rows <= 128 features (the host sizes it so that the tiles fill whole waves of CTAs); the instruction
     // still multiplies 128 rows, the rest being whatever the stage held before: those lanes are never read out.
-    const uint32_t tiles = (n + tile_rows - 1) / tile_rows, chunks = (groups + 1) >> 1;
-    const uint32_t my_tiles = blockIdx.x < tiles ? (tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0u;
+    // Where the features alone do not fill the SMs (a narrow shard with a long K), K is cut in `kslices` slices of `gps`
+    // groups: CTA c works on slice c % kslices of the tiles c / kslices, + lanes, ...; the slices' sums go to `partials`
+    // and are added in slice order afterwards (slice_sum_kernel, or the gather that sends them).
+    const uint32_t slice = blockIdx.x % kslices, lane_idx = blockIdx.x / kslices, lanes_n = gridDim.x / kslices;
+    const uint32_t gbeg = slice * gps, ng_slice = gbeg < groups ? min(gps, groups - gbeg) : 0u;
+    const uint32_t tiles = (n + tile_rows - 1) / tile_rows, chunks = (ng_slice + 1) >> 1;
+    const uint32_t my_tiles = (lane_idx < tiles && ng_slice) ? (tiles - lane_idx + lanes_n - 1) / lanes_n : 0u;
 
     // As above: the kernel ahead in the stream is this call's x_digits_kernel; the weights are settled, the digit tiles
     // are not. The first weight stages are requested before the dependency wait, the digit copies after it.
@@ -658,16 +664,16 @@ __global__ void __launch_bounds__(kLThreads, 1)
     __syncthreads();
 
     uint32_t ps = 0, pround = 0, pt = 0, pc = 0;  // producer position (warp 0, lane 0)
-    auto stage_groups = [&](uint32_t c) { return min(2u, groups - 2u * c); };
+    auto stage_groups = [&](uint32_t c) { return min(2u, ng_slice - 2u * c); };
     auto request_weights = [&]() -> bool {  // the next stage's barrier and raw bytes; false when nothing is left or a wait gave up
         if (pt >= my_tiles) return false;
         if (pround && !mbar_wait(empty + ps, (pround - 1) & 1, failed, status, kStatusEmptyWaitTimedOut)) return false;
         mbar_arrive_expect_tx(full + ps, tile_rows * 128u + stage_groups(pc) * dstride);
-        tma_load_2d(ring + (size_t)ps * stage_bytes, &wmap, (int32_t)(pc * 128u), (int32_t)((blockIdx.x + pt * gridDim.x) * tile_rows), full + ps);
+        tma_load_2d(ring + (size_t)ps * stage_bytes, &wmap, (int32_t)(gbeg * 64u + pc * 128u), (int32_t)((lane_idx + pt * lanes_n) * tile_rows), full + ps);
         return true;
     };
     auto request_digits = [&]() {  // ... and its digit tiles; then on to the next stage
-        bulk_load(ring + (size_t)ps * stage_bytes + kLRaw, xdigits + (size_t)2 * pc * dstride, stage_groups(pc) * dstride, full + ps);
+        bulk_load(ring + (size_t)ps * stage_bytes + kLRaw, xdigits + (size_t)(gbeg + 2 * pc) * dstride, stage_groups(pc) * dstride, full + ps);
         if (++pc == chunks) pc = 0, ++pt;
         if (++ps == nstages) ps = 0, ++pround;
     };
@@ -715,7 +721,7 @@ __global__ void __launch_bounds__(kLThreads, 1)
             bool ok = true;
             for (uint32_t t = 0; t < my_tiles && ok; ++t) {
                 for (uint32_t c = 0; c < chunks && ok; ++c, ++it) {
-                    const uint32_t hb = it & 1u, ng = 2u * c + 2u <= groups ? 2u : 1u;
+                    const uint32_t hb = it & 1u, ng = 2u * c + 2u <= ng_slice ? 2u : 1u;
                     const uint32_t slot0 = gc & (kLSlots - 1), slot1 = (gc + 1) & (kLSlots - 1);
                     if (gc >= kLSlots) {  // the groups' accumulators have been read out
                         ok = mbar_wait(dempty + slot0, ((gc >> 3) - 1) & 1, failed, status, kStatusMmaWaitTimedOut);
@@ -803,7 +809,7 @@ __global__ void __launch_bounds__(kLThreads, 1)
             ok = __shfl_sync(0xffffffffu, ok, 0);
         }
         for (uint32_t t = 0; t < my_tiles; ++t) {
-            const uint32_t feature = (blockIdx.x + t * gridDim.x) * tile_rows + fl;
+            const uint32_t feature = (lane_idx + t * lanes_n) * tile_rows + fl;
             const bool have = fl < tile_rows && feature < n;
             const float* srow = scale + (size_t)(have ? feature : 0) * groups;
             const float* zrow = zero + (size_t)(have ? feature : 0) * groups;
@@ -812,11 +818,11 @@ __global__ void __launch_bounds__(kLThreads, 1)
             for (uint32_t r = 0; r < 16; ++r) acc[r] = 0.0f;
             // the scale and zero point of the set's next group are requested a group ahead: a read-out that has fallen behind
             // finds its accumulator ready at once and would otherwise wait out the load's latency every time
-            float sv_next = have && set < groups ? __ldg(srow + set) : 0.0f, zv_next = have && set < groups ? __ldg(zrow + set) : 0.0f;
-            for (uint32_t g = set; g < groups && ok; g += kLSets) {
-                const uint32_t gc = t * groups + g, slot = gc & (kLSlots - 1);
+            float sv_next = have && set < ng_slice ? __ldg(srow + gbeg + set) : 0.0f, zv_next = have && set < ng_slice ? __ldg(zrow + gbeg + set) : 0.0f;
+            for (uint32_t gl = set; gl < ng_slice && ok; gl += kLSets) {
+                const uint32_t g = gbeg + gl, gc = t * ng_slice + gl, slot = gc & (kLSlots - 1);
                 const float sv = sv_next, zv = zv_next;
-                if (have && g + kLSets < groups) sv_next = __ldg(srow + g + kLSets), zv_next = __ldg(zrow + g + kLSets);
+                if (have && gl + kLSets < ng_slice) sv_next = __ldg(srow + g + kLSets), zv_next = __ldg(zrow + g + kLSets);
                 ok = mbar_wait(dfull + slot, (gc >> 3) & 1, failed, status, kStatusMmaWaitTimedOut);
                 if (!ok) break;
                 tc_fence_after_sync();
@@ -856,7 +862,8 @@ __global__ void __launch_bounds__(kLThreads, 1)
                 for (uint32_t r = 0; r < 16; ++r) {
                     if (r >= m) continue;
                     const float v = __fadd_rn(acc[r], exchange[r * kLTile + fl]);
-                    y[(size_t)r * n + feature] = bias ? __fadd_rn(v, bs) : v;
+                    if (kslices == 1) y[(size_t)r * n + feature] = bias ? __fadd_rn(v, bs) : v;
+                    else partials[((size_t)slice * m + r) * n + feature] = v;  // K is split: added up (with the bias) afterwards
                 }
             }
             named_barrier_sync(2, 8 * 32);  // the exchange buffer is free for the next tile
@@ -918,12 +925,36 @@ Plan make_plan(uint64_t m, uint64_t n, uint64_t groups, int sm_count) {
 
 static uint64_t digits_region_bytes(uint64_t groups, uint32_t rows_pad) { return (groups * (rows_pad * 128ull + 128ull) + 1023) / 1024 * 1024; }
 
+// How many K slices the features-on-the-lanes kernel cuts a call in (1: none) and the groups per slice: as many slices as
+// fit the SMs beside the feature tiles, each of whole stages.
+static void lanes_slices(uint64_t n, uint64_t groups, int sm_count, uint32_t* kslices, uint32_t* gps) {
+    const uint64_t tiles = (n + kLTile - 1) / kLTile;
+    uint64_t ks = tiles * 4 >= (uint64_t)sm_count * 3 ? 1 : (uint64_t)sm_count / tiles;  // three quarters of the SMs busy: leave it
+    ks = ks > 8 ? 8 : ks < 1 ? 1 : ks;
+    uint64_t per = (groups + ks - 1) / ks;
+    per += per & 1;
+    if (per < 4) per = groups < 4 ? groups + (groups & 1) : 4;  // two stages a slice at least
+    *gps = (uint32_t)per;
+    *kslices = (uint32_t)((groups + per - 1) / per);
+}
+
+// What AUTO's cost model needs of it: the K slices and the stages (of two groups) the busiest CTA works through.
+void gemv_q4_lanes_shape(uint64_t n, uint64_t k, int sm_count, uint32_t* kslices, uint32_t* stages_per_cta) {
+    uint32_t ks, gps;
+    lanes_slices(n, k / 128, sm_count, &ks, &gps);
+    const uint64_t waves = ((n + kLTile - 1) / kLTile * ks + sm_count - 1) / sm_count;
+    *kslices = ks, *stages_per_cta = (uint32_t)(waves * ((gps + 1) / 2));
+}
+
 // The scratch holds the digit tiles of x and, when K is split, the slices' partial sums.
 uint64_t gemv_q4_umma_scratch_bytes(uint64_t m, uint64_t k, uint64_t n, int sm_count) {
     if (m < 1 || m > 16 || k == 0 || k % 128 || n == 0) return 0;
     const Plan p = make_plan(m, n, k / 128, sm_count);
     if (p.grid == 0) return 0;
-    return digits_region_bytes(k / 128, p.rows_pad) + (p.slices > 1 ? (uint64_t)p.slices : 1ull) * m * n * 4;  // (K not split: room for a copy of y)
+    uint32_t ls = 1, lg = 0;
+    if (k / 128 <= kLMaxGroups) lanes_slices(n, k / 128, sm_count, &ls, &lg);  // (the other kernel's slices, if more)
+    const uint64_t slices = p.slices > ls ? p.slices : ls;
+    return digits_region_bytes(k / 128, p.rows_pad) + slices * m * n * 4;  // (K not split: room for a copy of y)
 }
 
 const float* gemv_q4_umma_partials(const void* scratch, uint64_t m, uint64_t k, uint64_t n, int sm_count) {
@@ -964,10 +995,12 @@ bool launch_gemv_q4_umma(cudaStream_t s, int sm_count, uint32_t* status, const f
 }
 
 // The features-on-the-lanes kernel: group_size 128, in_features a multiple of 128 up to 16384, 1 to 16 rows of x, 16-byte
-// aligned x and weights. `scratch` holds gemv_q4_umma_scratch_bytes bytes (it uses the digit region only). Two launches:
-// x -> digit tiles (tiny), the linear.
+// aligned x and weights. `scratch` holds gemv_q4_umma_scratch_bytes bytes. Two launches — x -> digit tiles (tiny), the
+// linear — and, where K is cut in slices, the sum over them (left to the caller when `deferred` is given: it receives the
+// slice count, 0 for none, and the sums lie where gemv_q4_umma_partials says).
 bool launch_gemv_q4_lanes(cudaStream_t s, int sm_count, uint32_t* status, const float* x, uint64_t m, uint64_t k, const uint32_t* q,
-                          const float* scale, const float* zero, const float* bias, uint64_t n, uint64_t group, float* y, void* scratch) {
+                          const float* scale, const float* zero, const float* bias, uint64_t n, uint64_t group, float* y, void* scratch,
+                          uint32_t* deferred) {
     if (m < 1 || m > 16 || group != 128 || k == 0 || k % 128 || k / 128 > kLMaxGroups || n == 0 || m * n > 0x7fffffffull) return false;
     if (((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(x)) & 15) != 0) return false;
     const uint64_t groups = k / 128, row_bytes = k / 2;
@@ -978,6 +1011,9 @@ bool launch_gemv_q4_lanes(cudaStream_t s, int sm_count, uint32_t* status, const 
     while (nstages > 2 && lanes_smem_bytes((uint32_t)groups, rows_pad, nstages) > kSmemBudget) --nstages;
     if (lanes_smem_bytes((uint32_t)groups, rows_pad, nstages) > kSmemBudget) return false;
     uint8_t* xdigits = reinterpret_cast<uint8_t*>(scratch);
+    float* partials = reinterpret_cast<float*>(xdigits + digits_region_bytes(groups, rows_pad));
+    uint32_t kslices, gps;
+    lanes_slices(n, groups, sm_count, &kslices, &gps);
     // With more than one wave of CTAs the tiles are made equal (28672 features on 148 SMs: 296 tiles of 97, two per CTA,
     // instead of 224 of 128, two for some and one for others). A stage costs about the same whatever its width, so a
     // single wave keeps 128-feature tiles (more, narrower tiles measured slower: 14336 features 16.0 -> 17.0 us).
@@ -987,11 +1023,21 @@ bool launch_gemv_q4_lanes(cudaStream_t s, int sm_count, uint32_t* status, const 
     const CUtensorMap wmap = make_tensor_map_2d(q, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, row_bytes, n, row_bytes, 128, (uint32_t)tile_rows, Swizzle::B128);
     const size_t smem = lanes_smem_bytes((uint32_t)groups, rows_pad, nstages);
     const uint64_t tiles = (n + tile_rows - 1) / tile_rows;
+    const uint64_t lanes = tiles * kslices <= (uint64_t)sm_count ? tiles : (uint64_t)sm_count / kslices;
     launch_after(x_digits_kernel, dim3((uint32_t)((groups * (rows_pad / 4) + 7) / 8)), dim3(128), 0, s, x, (uint32_t)m, (uint32_t)k, (uint32_t)groups, rows_pad,
                  xdigits);
     GQ_CUDA(cudaFuncSetAttribute(gemv_q4_lanes_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    launch_after(gemv_q4_lanes_kernel, dim3((uint32_t)(tiles < (uint64_t)sm_count ? tiles : (uint64_t)sm_count)), dim3(kLThreads), smem, s, wmap,
-                 (const uint8_t*)xdigits, scale, zero, bias, y, (uint32_t)m, (uint32_t)n, (uint32_t)groups, rows_pad, nstages, (uint32_t)tile_rows, status);
+    launch_after(gemv_q4_lanes_kernel, dim3((uint32_t)(lanes * kslices)), dim3(kLThreads), smem, s, wmap, (const uint8_t*)xdigits, scale, zero,
+                 kslices > 1 ? nullptr : bias, y, partials, (uint32_t)m, (uint32_t)n, (uint32_t)groups, rows_pad, nstages, (uint32_t)tile_rows, kslices, gps, status);
+    if (deferred) *deferred = kslices > 1 ? kslices : 0u;
+    if (kslices > 1 && !deferred) {
+        if (n % 4 == 0 && (reinterpret_cast<uintptr_t>(y) & 15) == 0)
+            launch_after(slice_sum_kernel<4>, dim3((uint32_t)((m * n / 4 + 255) / 256)), dim3(256), 0, s, (const float*)partials, kslices, (uint32_t)(m * n),
+                         (uint32_t)n, bias, y);
+        else
+            launch_after(slice_sum_kernel<1>, dim3((uint32_t)((m * n + 255) / 256)), dim3(256), 0, s, (const float*)partials, kslices, (uint32_t)(m * n),
+                         (uint32_t)n, bias, y);
+    }
     return true;
 }
 

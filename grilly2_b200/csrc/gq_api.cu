@@ -675,9 +675,8 @@ int32_t gq_int4_dequantize(gq_ctx* ctx, gq_buf q, gq_buf scale, gq_buf zero, uin
 // 1 = the tcgen05 decode kernel with K cut in slices (gemv_q4_umma), 2 = the one with the features on the lanes
 // (gemv_q4_lanes). Both tcgen05 kernels read the weight once whatever m is. The sliced one runs at about 2.2 bytes per ns
 // after ~9 us of launches and start-up. The lanes one takes ~0.78 us per stage of two groups, whatever the stage's width,
-// and a CTA owns whole tiles of up to 128 features: waves x groups / 2 stages after ~4.5 us, so it wins where the features
-// fill the SMs (14336 x 4096: 16-18 us against 24-25; 28672 x 8192: 52-57 against 61-70) and loses on a narrow shard with
-// a long K (3584 x 8192: 27 against 17). The warp-level ring kernel (K = 4096 or 8192) takes a pass at ~4.5 bytes per ns
+// after ~4.5 us; a CTA owns tiles of up to 128 features over all of K (14336 x 4096: 16-18 us against 24-25; 28672 x 8192:
+// 52-57 against 61-70) or, where the features alone do not fill the SMs, over a slice of K (+ ~3 us for the sum). The warp-level ring kernel (K = 4096 or 8192) takes a pass at ~4.5 bytes per ns
 // (one row) per four rows of x, a pass with three or four rows running ~1.7 times as long as a one-row pass (its IMMA issue
 // rate); the dp4a kernel elsewhere grows with every row. Measured on B200; weights under 4 MB stay with the single-launch
 // kernels.
@@ -686,8 +685,12 @@ static int int4_tensor_route(uint64_t m, uint64_t n, uint64_t k, uint64_t group,
     const double mb = (double)n * (double)k / 2e6;
     if (mb < 4.0) return 0;
     const double umma_us = 9.0 + mb / 2.2;
-    const uint64_t groups = k / 128, waves = ((n + 127) / 128 + sm_count - 1) / sm_count;
-    const double lanes_us = groups <= 128 ? 4.5 + 0.78 * (double)(waves * ((groups + 1) / 2)) : 1e30;
+    double lanes_us = 1e30;
+    if (k / 128 <= 128) {
+        uint32_t kslices, stages;
+        gemv_q4_lanes_shape(n, k, sm_count, &kslices, &stages);
+        lanes_us = 4.5 + 0.78 * (double)stages + (kslices > 1 ? 3.0 : 0.0);  // (the sum over its K slices, where it cuts K)
+    }
     double other_us = mb * (0.26 * (double)m + 0.27);
     if (k == 4096 || k == 8192) {
         other_us = 0.0;
@@ -1096,7 +1099,7 @@ int32_t gq_int4_linear_gather(gq_ctx* ctx, gq_buf x, uint64_t x_off, uint64_t m,
                 const float* part = gemv_q4_umma_partials(scratch, m, k, n_shard, sms);  // the slices' sums, or (K not split) the shard's y
                 uint32_t slices = 0;
                 // (the kernel with the features on the lanes writes the shard's y, bias included, where the other leaves its sums)
-                if ((route == 2 && launch_gemv_q4_lanes(ctx->stream, sms, ctx->status_dev, xp, m, k, qp, sp, zp, bp, n_shard, group, const_cast<float*>(part), scratch)) ||
+                if ((route == 2 && launch_gemv_q4_lanes(ctx->stream, sms, ctx->status_dev, xp, m, k, qp, sp, zp, bp, n_shard, group, const_cast<float*>(part), scratch, &slices)) ||
                     launch_gemv_q4_umma(ctx->stream, sms, ctx->status_dev, xp, m, k, qp, sp, zp, bp, n_shard, group, const_cast<float*>(part), scratch, &slices)) {
                     peer.row0 = 0;
                     launch_peer_gather(ctx->stream, sms, peer, part, m, n_shard, ctx->status_dev, slices, slices ? bp : nullptr);

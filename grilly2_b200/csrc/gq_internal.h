@@ -214,7 +214,9 @@ uint64_t gemv_q4_umma_scratch_bytes(uint64_t m, uint64_t k, uint64_t n, int sm_c
 // `deferred`, when given: the sum over the K slices is left to the caller — *deferred receives the number of slices (their
 // partial sums lie at gemv_q4_umma_partials(scratch, ...), bias NOT added), or 0 when K was not split and y (with bias) is complete.
 bool launch_gemv_q4_lanes(cudaStream_t s, int sm_count, uint32_t* status, const float* x, uint64_t m, uint64_t k, const uint32_t* q,
-                          const float* scale, const float* zero, const float* bias, uint64_t n, uint64_t group, float* y, void* scratch);
+                          const float* scale, const float* zero, const float* bias, uint64_t n, uint64_t group, float* y, void* scratch,
+                          uint32_t* deferred = nullptr);
+void gemv_q4_lanes_shape(uint64_t n, uint64_t k, int sm_count, uint32_t* kslices, uint32_t* stages_per_cta);
 bool launch_gemv_q4_umma(cudaStream_t s, int sm_count, uint32_t* status, const float* x, uint64_t m, uint64_t k, const uint32_t* q,
                          const float* scale, const float* zero, const float* bias, uint64_t n, uint64_t group, float* y, void* scratch,
                          uint32_t* deferred = nullptr);
