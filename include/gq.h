@@ -89,8 +89,10 @@ typedef uint64_t gq_buf; /* 0 is never a valid handle */
 
 #define GQ_KERNEL_UMMA_LANES 8 /* int4 only (group_size 128, in_features a multiple of 128 up to 16384, 1 to 16 rows of x): the
                                   tcgen05 decode kernel with the operands exchanged, the output features on the lanes of
-                                  tensor memory, so that a read-out thread owns one feature and its scale; tiles of 128
-                                  features over all of K, no partial sums */
+                                  tensor memory, so that a read-out thread owns one feature and its scale; tiles of up
+                                  to 128 features over all of K (over a slice of K where the features alone do not fill
+                                  the SMs). What AUTO runs for 5 to 16 rows of x on weights of 4 MB and more, and in
+                                  passes of 16 rows beyond that */
 
 typedef struct gq_caps { /* replaces gc_caps, gc_shim.h:43-50 */
     char device_name[256];
