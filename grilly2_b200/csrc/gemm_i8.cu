@@ -271,12 +271,21 @@ __global__ void __launch_bounds__((Tile<NA, XR>::kThreads), 1)
 }
 
 // rows of x per tile by the number of rows of the call
-inline uint32_t tile_rows_for(uint64_t m) { return m <= 16 ? 16u : m <= 32 ? 32u : m <= 64 ? 64u : 80u; }
-inline uint64_t padded_rows(uint64_t m) {
-    const uint64_t xr = tile_rows_for(m);
-    return (m + xr - 1) / xr * xr;
+inline uint64_t pad_to(uint64_t m, uint64_t xr) { return (m + xr - 1) / xr * xr; }
+// Up to 64 rows: one A operand and the narrowest B that holds the rows. Beyond: two A operands and 80 rows of x a tile, or
+// 64 where that makes the busiest CTA's share smaller (256 rows x 14336 features: 224 tiles either way, in two waves).
+inline uint32_t tile_rows_for(uint64_t m, uint64_t n, int sm_count) {
+    if (m <= 64) return m <= 16 ? 16u : m <= 32 ? 32u : 64u;
+    const uint64_t ft = (n + 255) / 256;
+    const uint64_t c80 = (ft * ((m + 79) / 80) + sm_count - 1) / sm_count * 80, c64 = (ft * ((m + 63) / 64) + sm_count - 1) / sm_count * 64;
+    return c64 < c80 ? 64u : 80u;
 }
-inline uint64_t planes_bytes(uint64_t m, uint64_t k) { return (kND * padded_rows(m) * ((k + 15) / 16 * 16) + 255) / 256 * 256; }
+// the scratch is sized without knowing the features: room for either padding
+inline uint64_t padded_rows_most(uint64_t m) {
+    if (m <= 64) return pad_to(m, tile_rows_for(m, 1, 1));
+    return pad_to(m, 80) > pad_to(m, 64) ? pad_to(m, 80) : pad_to(m, 64);
+}
+inline uint64_t planes_bytes(uint64_t m, uint64_t k) { return (kND * padded_rows_most(m) * ((k + 15) / 16 * 16) + 255) / 256 * 256; }
 
 template <int NA, int XR>
 void launch_tiles(cudaStream_t s, int sm_count, uint32_t* status, const uint8_t* planes, const float* xinv, uint64_t m, uint64_t mpad, uint64_t k,
@@ -298,23 +307,28 @@ void launch_tiles(cudaStream_t s, int sm_count, uint32_t* status, const uint8_t*
 }  // namespace
 
 // Bytes of scratch a call needs: the three digit planes of x and a float per row.
-uint64_t gemm_q8_i8_scratch_bytes(uint64_t m, uint64_t k) { return planes_bytes(m, k) + padded_rows(m) * 4; }
+uint64_t gemm_q8_i8_scratch_bytes(uint64_t m, uint64_t k) { return planes_bytes(m, k) + padded_rows_most(m) * 4; }
 
 // Returns false when the shape is outside this kernel: K beyond 2^17 (the int32 sums) or a weight that is not 16-byte
 // aligned. `scratch` holds gemm_q8_i8_scratch_bytes(m, k) bytes. Two launches: x -> digit planes, the product.
 bool launch_gemm_q8_i8(cudaStream_t s, int sm_count, uint32_t* status, const float* x, uint64_t m, uint64_t k, const uint32_t* q,
                        const float* scale, const float* bias, uint64_t n, float* y, void* scratch) {
     if (m == 0 || n == 0 || k == 0 || k > (1u << 17) || (reinterpret_cast<uintptr_t>(q) & 15) != 0) return false;
-    const uint64_t rowbytes = (k + 15) / 16 * 16, mpad = padded_rows(m);
+    const uint32_t xr = tile_rows_for(m, n, sm_count);
+    const uint64_t rowbytes = (k + 15) / 16 * 16, mpad = pad_to(m, xr);
     if (kND * mpad > 0x7fffffffull || m * n > (1ull << 40)) return false;
     uint8_t* planes = reinterpret_cast<uint8_t*>(scratch);
     float* xinv = reinterpret_cast<float*>(planes + planes_bytes(m, k));
     launch_after(x_planes_kernel, dim3((uint32_t)mpad), dim3(256), 0, s, x, (uint32_t)m, (uint32_t)k, (uint32_t)rowbytes, (uint32_t)mpad, planes, xinv);
-    switch (tile_rows_for(m)) {
-        case 16: launch_tiles<1, 16>(s, sm_count, status, planes, xinv, m, mpad, k, q, scale, bias, n, y); break;
-        case 32: launch_tiles<1, 32>(s, sm_count, status, planes, xinv, m, mpad, k, q, scale, bias, n, y); break;
-        case 64: launch_tiles<1, 64>(s, sm_count, status, planes, xinv, m, mpad, k, q, scale, bias, n, y); break;
-        default: launch_tiles<2, 80>(s, sm_count, status, planes, xinv, m, mpad, k, q, scale, bias, n, y); break;
+    if (m > 64) {
+        if (xr == 64) launch_tiles<2, 64>(s, sm_count, status, planes, xinv, m, mpad, k, q, scale, bias, n, y);
+        else launch_tiles<2, 80>(s, sm_count, status, planes, xinv, m, mpad, k, q, scale, bias, n, y);
+    } else if (xr == 16) {
+        launch_tiles<1, 16>(s, sm_count, status, planes, xinv, m, mpad, k, q, scale, bias, n, y);
+    } else if (xr == 32) {
+        launch_tiles<1, 32>(s, sm_count, status, planes, xinv, m, mpad, k, q, scale, bias, n, y);
+    } else {
+        launch_tiles<1, 64>(s, sm_count, status, planes, xinv, m, mpad, k, q, scale, bias, n, y);
     }
     return true;
 }
