@@ -185,9 +185,11 @@ int32_t gq_int8_quantize_rows(gq_ctx* ctx, gq_buf w, uint64_t w_off, uint64_t ro
 /* LINEAR / LINEAR_TILED{x,q,scale,bias,y; m,k,n,vecs,x_off,b_off,has_bias,x_vec4}
  * — quant.rs:25-39,233-304, g2-linear-q8.glsl:33-95, g2-linear-q8-tiled.glsl:41-100.
  * y[m][n] = (sum_k x[m][k] * q[n][k]) * scale[n] (+ bias[n]); bias == 0 means none.
- * AUTO: IMMA for one or two rows, the dp4a GEMV for a few more; the
- * tensor-core GEMM for many, when the shape meets its alignment rules
- * (k % 4 == 0, x_off % 4 == 0). y must not overlap x (refused). */
+ * AUTO: the streaming IMMA kernel for one or two rows of x; from three rows on (at three rows on weights of 8 MB and
+ * more) the integer tensor-core GEMM GQ_KERNEL_TENSOR_I8, with tiles sized to the row count (it holds three digit planes
+ * of x in the context's scratch: inside a capture in which the scratch would have to grow, dp4a, or from 64 rows the tf32
+ * GEMM when the shape meets its alignment rules, k % 4 == 0 and x_off % 4 == 0); dp4a elsewhere. y must not overlap x
+ * (refused). */
 int32_t gq_int8_linear(gq_ctx* ctx, gq_buf x, uint64_t x_off, uint64_t m, uint64_t k, gq_buf q, gq_buf scale,
                        gq_buf bias, uint64_t b_off, uint64_t n, gq_buf y, int32_t kernel);
 
@@ -216,9 +218,10 @@ int32_t gq_int4_quantize_rows(gq_ctx* ctx, gq_buf w, uint64_t w_off, uint64_t ro
 /* LINEAR{x,q,scale,zero,bias,y; m,k,n,vecs,group,groups,x_off,b_off,has_bias,x_vec4}
  * — quant4.rs:33-39,371-442, g2-linear-q4.glsl:43-111.
  * AUTO (group_size 128): one to four rows of x on the warp-level ring kernel where it applies (in_features 4096 or
- * 8192), more rows — and three or more rows of other in_features that are multiples of 128 — on the tcgen05 kernel,
- * which reads the weight once for up to 16 rows, when the weight is large enough to pay for its start-up; the IMMA
- * and dp4a kernels elsewhere. y must not overlap x (refused). */
+ * 8192), more rows — and three or more rows of other in_features that are multiples of 128 — on a tcgen05 kernel
+ * (GQ_KERNEL_UMMA_LANES up to in_features 16384, GQ_KERNEL_UMMA beyond), which reads the weight once for up to 16 rows,
+ * when the weight is large enough to pay for its start-up (4 MB); more than 16 rows in passes of 16 through the same
+ * kernel; the IMMA and dp4a kernels elsewhere. y must not overlap x (refused). */
 int32_t gq_int4_linear(gq_ctx* ctx, gq_buf x, uint64_t x_off, uint64_t m, uint64_t k, gq_buf q, gq_buf scale,
                        gq_buf zero, gq_buf bias, uint64_t b_off, uint64_t n, uint64_t group, gq_buf y,
                        int32_t kernel);
