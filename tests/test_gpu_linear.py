@@ -132,6 +132,7 @@ def test_x_and_bias_at_element_offsets(g, x_off):
     np.testing.assert_array_equal(w8.linear(xs, bs, _lib.KERNEL_GEMV).numpy(), ref8)
     assert rel(w8.linear(xs, bs, _lib.KERNEL_DP4A).numpy(), ref8) <= TOL
     assert rel(w8.linear(_C.Tensor(xs.storage, (1, k), "float32", x_off), bs, _lib.KERNEL_IMMA).numpy(), ref8[:1]) <= TOL
+    assert rel(w8.linear(xs, bs, _lib.KERNEL_TENSOR_I8).numpy(), ref8) <= TOL  # its digit-plane kernel reads x element by element there
     w4 = _C.Int4Weight.quantize(_C.Tensor.from_numpy(w), 64)
     q4, s4, z4 = oracle.quantize_q4(w, 64)
     ref = oracle.linear_q4(x, q4, s4, z4, b, k, 64, x_vec4=(x_off % 4 == 0))
@@ -141,6 +142,14 @@ def test_x_and_bias_at_element_offsets(g, x_off):
     q4, s4, z4 = oracle.quantize_q4(w, 128)
     ref = oracle.linear_q4(x[:1], q4, s4, z4, b, k, 128, x_vec4=(x_off % 4 == 0))
     assert rel(w4g.linear(_C.Tensor(xs.storage, (1, k), "float32", x_off), bs, _lib.KERNEL_RING).numpy(), ref) <= TOL
+    ref3 = oracle.linear_q4_f64(x, q4, s4, z4, b, k, 128)[0]
+    for kernel in (_lib.KERNEL_UMMA_LANES, _lib.KERNEL_UMMA):  # the tcgen05 kernels fetch x sixteen bytes at a time
+        if x_off % 4 == 0:
+            assert rel(w4g.linear(xs, bs, kernel).numpy(), ref3) <= TOL
+        else:
+            with pytest.raises(RuntimeError, match="16-byte aligned x"):
+                w4g.linear(xs, bs, kernel)
+    assert rel(w4g.linear(xs, bs).numpy(), ref3) <= TOL  # AUTO answers either way
 
 
 def test_leading_dims_empty_and_refusals(g):
