@@ -2,6 +2,12 @@
 // fifth-generation tensor cores (tcgen05.mma kind::i8, accumulators in tensor
 // memory), ONE pass over the weight whatever the number of rows.
 //
+// Two kernels share the arithmetic, the digit tiles of x and the nibble warps. The first (gemv_q4_umma_kernel,
+// described here) keeps the rows of x on the lanes of tensor memory and the weight as the wide B operand; the
+// second (gemv_q4_lanes_kernel, further down, with its own account) exchanges the operands so that a read-out thread
+// owns one output feature. The second is the faster on every shape measured and is what GQ_KERNEL_AUTO runs up to
+// in_features 16384.
+//
 // Why it is shaped like this (measured on B200 with loops of back-to-back
 // instructions): a kind::i8 tcgen05.mma takes ~83 ns for any N up to 64, ~92 ns
 // at N = 128 and ~133 ns at N = 256 (M = 64; K = 32 bytes). Time goes with the
