@@ -37,6 +37,16 @@ def test_ctypes_prototypes_cover_the_header():
     assert set(declared_functions()) == bound
 
 
+def test_kernel_selectors_match_the_header():
+    """The host mirror's KERNEL_* constants are the header's GQ_KERNEL_* macros, every one of them."""
+    from grilly2_b200 import _lib
+    text = open(os.path.join(ROOT, "include", "gq.h")).read()
+    macros = {name: int(value) for name, value in re.findall(r"#define\s+GQ_(KERNEL_[A-Z0-9_]+)\s+(\d+)", text)}
+    assert len(macros) >= 9 and len(set(macros.values())) == len(macros)
+    for name, value in macros.items():
+        assert getattr(_lib, name) == value, name
+
+
 def test_no_gpu_is_an_error_not_a_fallback():
     import torch
     if torch.cuda.is_available():
